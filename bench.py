@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""KV handoff benchmark: GB/s of prefill->decode KV movement, device-timed, max over ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one handoff of the whole batch.  N = 1 moves the batch between a prefill pool and
+a decode pool on the same GPU (HBM-bound); N = 2, 4, 8 is one process per GPU, ranks
+[0, N/2) prefill and ranks [N/2, N) decode, every pair moving its own batch with peer stores
+over NVLink (weak scaling: work per pair is fixed).  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+METRIC = "kv_handoff_GBps"
+UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch divided by the algorithmic bytes of
+# the same launch, from the ncu captures summarised under profiles/ (None until captured).
+NCU_TRAFFIC_RATIO = {"handoff_copy_vec": None, "handoff_f16_e4m3_warp": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.marks = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.t = threading.Thread(target=self._read, daemon=True)
+        self.t.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), line.strip()))
+
+    def mark(self):
+        self.marks.append(time.perf_counter())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        lo = self.marks[0] if self.marks else 0.0
+        hi = self.marks[-1] if len(self.marks) > 1 else float("inf")
+        sm, mx, reasons, n = [], [], set(), 0
+        for t, line in self.rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clk, cmax = float(parts[1]), float(parts[2])
+            except ValueError:
+                continue
+            inside = lo - 0.05 <= t <= hi + 0.05
+            if inside:
+                sm.append(clk)
+                n += 1
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            mx.append(cmax)
+        if not sm:   # region shorter than the sampling period: use everything seen
+            sm = [float(r[1].split(",")[1]) for r in self.rows if len(r[1].split(",")) >= 9] or [0.0]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": n}
+
+
+# ----------------------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------------------
+def pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None):
+    from tempura_b200 import workloads as W
+    if name == "cfg1":
+        return W.tinyllama_cpu()
+    if name in ("cfg2", "cfg3", "cfg4"):
+        if pool_blocks is None:
+            pool_blocks = 32768 if n_gpus == 1 else 65536      # two pools share one GPU at N = 1
+        fn = {"cfg2": W.llama8b_f16, "cfg3": W.llama8b_fp8, "cfg4": W.llama8b_prefix}[name]
+        return fn(pool_blocks=pool_blocks)
+    if name == "cfg5":
+        pairs = max(1, n_gpus // 2)
+        return W.llama70b_f16(n_kv_heads=heads or 8 // pairs)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def fill_source(pool, w, seed: int):
+    """Seeded N(0, sigma) F16 values in every block a table names; the 0xA5 pattern stays
+    elsewhere.  Outlier channels (config 3) are scaled by the workload's gain."""
+    import torch
+    g = torch.Generator(device=f"cuda:{pool.device}")
+    g.manual_seed(seed)
+    bs = w.block_size
+    used = np.unique(np.concatenate([w.src_tables[q, : (int(w.seq_lens[q]) + bs - 1) // bs] for q in range(len(w.seq_lens))]))
+    idx = torch.from_numpy(used.astype(np.int64)).to(f"cuda:{pool.device}")
+    for l in range(pool.n_layers):
+        for is_v in (False, True):
+            vals = torch.randn((len(used), bs, pool.n_kv_heads, pool.head_dim), generator=g,
+                               device=idx.device, dtype=torch.float32) * w.sigma
+            for c in w.outlier_channels:
+                vals[..., c] *= w.outlier_gain
+            pool.blocks(l, is_v).index_copy_(0, idx, vals.to(torch.float16))
+    torch.cuda.synchronize()
+
+
+def spot_check(src, dst, w, layer: int):
+    """Not timed: destination blocks of one layer equal the source blocks they came from."""
+    import torch
+    bs = w.block_size
+    for q in (0, len(w.seq_lens) - 1):
+        pre = int(w.prefix_lens[q]) // bs if w.prefix_lens is not None else 0
+        nfull = int(w.seq_lens[q]) // bs
+        if nfull <= pre:
+            continue
+        s = torch.from_numpy(w.src_tables[q, pre:nfull].astype(np.int64)).cuda(src.device)
+        d = torch.from_numpy(w.dst_tables[q, pre:nfull].astype(np.int64)).cuda(dst.device)
+        if src.dtype == dst.dtype:
+            a = src.blocks(layer).index_select(0, s)
+            b = dst.blocks(layer).index_select(0, d).to(a.device)
+            if not torch.equal(a.view(torch.int16), b.view(torch.int16)):
+                raise SystemExit("spot check failed: destination blocks differ from source blocks")
+        else:
+            sc = dst.k_scales[layer].index_select(0, d)
+            if not bool((sc > 0).all()):
+                raise SystemExit("spot check failed: scales not written")
+
+
+# ----------------------------------------------------------------------------------------
+# CPU baseline (oracle) on a bounded sample
+# ----------------------------------------------------------------------------------------
+def cpu_sample_workload(w, layers: int, pool_blocks: int):
+    from tempura_b200 import workloads as W
+    s = W.Workload(w.name + "-cpu-sample", layers, w.n_kv_heads, w.head_dim, w.block_size, pool_blocks, pool_blocks,
+                   w.seq_lens.copy(), src_dtype=w.src_dtype, dst_dtype=w.dst_dtype, prefix_lens=w.prefix_lens,
+                   outlier_channels=w.outlier_channels, outlier_gain=w.outlier_gain, seed=w.seed)
+    return s.build_tables()
+
+
+def time_cpu(w, threads: int, layers: int, reps: int):
+    """Times the oracle's handoff (the reference's CPU path restated) on `layers` layers of
+    the workload with all its sequences; pool shrunk so two pools fit host RAM."""
+    import oracle
+    need = int(((w.seq_lens.astype(np.int64) + w.block_size - 1) // w.block_size).sum()) + 256
+    pool_blocks = 1 << int(np.ceil(np.log2(need)))
+    s = cpu_sample_workload(w, layers, pool_blocks)
+    npdt = {"f16": np.uint16, "e4m3": np.uint8, "f32": np.float32}
+    src = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.src_dtype], 0xA5)
+    dst = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.dst_dtype], 0x5A,
+                                 with_scales=(s.dst_dtype == "e4m3"))
+    for l in range(layers if s.dst_dtype == "e4m3" else 0):   # values only matter to the FP8 path
+        for kv, arrs in enumerate((src.k, src.v)):
+            arrs[l][:] = oracle.gen_normal_f16(arrs[l].size, s.seed, 2 * l + kv, s.sigma, s.head_dim,
+                                               s.outlier_channels, s.outlier_gain)
+    batch = oracle.make_batch(s.seq_lens, s.src_tables, s.dst_tables, s.table_stride, s.prefix_lens)
+    mode = "copy" if s.src_dtype == s.dst_dtype else "f16_e4m3"
+    best = float("inf")
+    for _ in range(reps + 1):        # first pass is the warm-up
+        t0 = time.perf_counter()
+        oracle.handoff(src, dst, batch, None, mode, n_threads=threads)
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+    payload = s.payload_bytes
+    return payload / best / 1e9, f"{layers} of {w.n_layers} layers, all {len(w.seq_lens)} sequences ({payload / 1e6:.0f} MB payload), pools shrunk to {pool_blocks} blocks; best of {reps}"
+
+
+def run_reference(args):
+    """The reference's CPU handoff (its Rust cannot be built here: the oracle port stands in),
+    on all host cores, on a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = pick_workload(args.workload or "cfg2", args.gpus, 4096)
+    cores = os.cpu_count() or 1
+    layers = 2 if w.dst_dtype == "e4m3" else 4
+    vals = []
+    t0 = time.perf_counter()
+    for _ in range(max(1, min(args.steps, 5))):
+        v, sample = time_cpu(w, cores, layers, 2)
+        vals.append(v)
+        if time.perf_counter() - t0 > 120:
+            break
+    v = max(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u16" if w.dst_dtype != "e4m3" else "f16->e4m3", "data": "synthetic",
+        "config": {"workload": w.name, "note": "reference CPU handoff restated in C (oracle port), OpenMP over (sequence, layer, K|V)"},
+        "cpu_baseline": {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(v, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from tempura_b200 import handoff as H
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch N > 1 with torch.distributed.run, one rank per GPU")
+        args.gpus = world
+    torch.cuda.set_device(local)
+    multi = world > 1
+    if multi:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pairs = max(1, world // 2)
+    is_prefill = rank < pairs
+    partner = rank + pairs if is_prefill else rank - pairs
+
+    wname = args.workload or "cfg2"
+    w = pick_workload(wname, world, args.pool_blocks)
+    dst_dtype = w.dst_dtype
+    scales = dst_dtype == "e4m3"
+    flags = 0
+    if args.variant == "vector":
+        flags |= H.N.PLAN_FORCE_VECTOR
+    elif args.variant == "bulk":
+        flags |= H.N.PLAN_FORCE_BULK
+
+    sampler = ClockSampler(local)
+    src = dst = None
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    if not multi:
+        src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
+        dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
+                              scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
+        fill_source(src, w, 1234)
+    else:
+        if world % 2:
+            raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
+        info = None
+        if not is_prefill:
+            dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
+                                  scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
+            hs, off = H.ipc_export(dst.storage.data_ptr())
+            hf, foff = H.ipc_export(flag.data_ptr())
+            info = {"pool": (hs, off), "flag": (hf, foff), "base": dst.storage.data_ptr(),
+                    "k": [int(p) for p in dst.k_ptrs], "v": [int(p) for p in dst.v_ptrs], "device": local}
+            if scales:
+                info["ks"] = H.ipc_export(dst.k_scales.data_ptr())
+                info["vs"] = H.ipc_export(dst.v_scales.data_ptr())
+            if dst.refcounts is not None:
+                info["rc"] = H.ipc_export(dst.refcounts.data_ptr())
+        infos = [None] * world
+        dist.all_gather_object(infos, info)
+        if is_prefill:
+            src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
+            fill_source(src, w, 1234 + rank)
+            pi = infos[partner]
+            base = H.ipc_import(*pi["pool"])
+            remote_flag = H.ipc_import(*pi["flag"])
+            rel = lambda p: base + (p - pi["base"])
+            dst = H.Pool.from_pointers(pi["device"], dst_dtype, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks,
+                                       [rel(p) for p in pi["k"]], [rel(p) for p in pi["v"]],
+                                       H.ipc_import(*pi["ks"]) if scales else 0, H.ipc_import(*pi["vs"]) if scales else 0,
+                                       H.ipc_import(*pi["rc"]) if "rc" in pi else 0)
+
+    batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens)
+    plan = None
+    if is_prefill:
+        plan = H.Plan(src, dst, batch, None, flags)
+    stream = torch.cuda.current_stream()
+    done_flag = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
+
+    def barrier():
+        if multi:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler.start()
+    # ---- warm-up -------------------------------------------------------------------------
+    gen = 0
+    for _ in range(args.warmup):
+        gen += 1
+        if is_prefill:
+            plan.enqueue(stream, done_flag, gen)
+        else:
+            H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
+    barrier()
+    sampler.mark()
+
+    # ---- timed: K handoffs, inputs resident in HBM -------------------------------------------
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    if is_prefill:
+        ev0.record(stream)
+        for _ in range(args.steps):
+            gen += 1
+            plan.enqueue(stream, done_flag, gen)
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+    else:
+        gen += args.steps
+        H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+        ms = (time.perf_counter() - t_wall0) * 1e3
+    barrier()
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if multi:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+
+    # ---- end to end: host tables -> plan update (H2D work list) -> kernel -> D2H flag ----------
+    e2e_steps = args.steps
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        gen += 1
+        if is_prefill:
+            plan.update(batch)
+            plan.enqueue(stream, done_flag, gen)
+            if not multi:
+                H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
+        else:
+            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if multi:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    sampler.mark()
+    clocks = sampler.stop()
+
+    if not multi:
+        spot_check(src, dst, w, w.n_layers - 1)
+
+    if rank == 0:
+        st = plan.stats()
+        payload_all = st.payload_bytes * pairs                      # every pair moves its own batch
+        per_launch_ms = ms_total / args.steps
+        value = payload_all / (per_launch_ms * 1e-3) / 1e9
+        peak, peak_kind = measured_peaks()
+        algo = st.bytes_read + st.bytes_written                     # one launch, one GPU
+        if multi:
+            bound, peak_used, algo_used, peak_note = "nvlink", 770.0, st.bytes_written, "measured peer copy, per direction"
+        else:
+            bound, peak_used, algo_used, peak_note = "hbm", peak, algo, f"{peak_kind} copy peak"
+        achieved = algo_used / (per_launch_ms * 1e-3) / 1e9
+        kname = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e4m3_warp", 4: "handoff_f16_e4m3_generic",
+                 5: "handoff_f32_cast_generic"}.get(st.kernel_variant, "?")
+        ratio = NCU_TRAFFIC_RATIO.get(kname)
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u16" if dst_dtype == "f16" else "f16->e4m3", "data": "synthetic",
+            "config": {"workload": w.name, "layers": w.n_layers, "kv_heads": w.n_kv_heads, "head_dim": w.head_dim,
+                       "block_size": w.block_size, "n_seqs": len(w.seq_lens), "tokens_moved": w.tokens_moved,
+                       "payload_bytes_per_pair": int(st.payload_bytes), "pool_blocks": [w.src_blocks, w.dst_blocks],
+                       "pairs": pairs, "placement": "intra-device" if not multi else "prefill rank i -> decode rank i+N/2, peer stores",
+                       "l2": "inputs larger than L2 (no flush needed)", "kernel": kname, "grid": [st.grid, st.block]},
+            "roofline": {"bound": bound, "achieved": round(achieved, 1), "peak": peak_used, "unit": "GB/s",
+                         "frac": round(achieved / peak_used, 4), "traffic": (int(ratio * algo) if ratio else None),
+                         "algorithmic_bytes": int(algo_used), "peak_source": peak_note,
+                         "frac_of_nominal_8000": round(achieved / 8000.0, 4) if not multi else None},
+            "e2e": {"value": round(payload_all * e2e_steps / e2e_s / 1e9, 2), "unit": UNIT,
+                    "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4,
+                    "what": "host block tables -> tkv_plan_update (validate, build, upload work list) -> tkv_handoff_enqueue -> flag read back; KV pools stay on the devices that own them"},
+            "gpu_launches": args.warmup + args.steps + e2e_steps,
+            "clocks": clocks,
+        }
+        if not multi and not args.no_cpu:
+            layers = 2 if dst_dtype == "e4m3" else 4
+            v1, sample = time_cpu(w, 1, layers, 3)
+            vall, _ = time_cpu(w, os.cpu_count() or 1, layers, 3)
+            line["cpu_baseline"] = {"value": round(v1, 3), "unit": UNIT, "cores": 1, "kind": "port", "sample": sample,
+                                    "all_cores": {"value": round(vall, 3), "cores": os.cpu_count() or 1}}
+        print(json.dumps(line), flush=True)
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--pool-blocks", type=int, default=None)
+    ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

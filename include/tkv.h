@@ -1,0 +1,267 @@
+/*
+ * tkv.h -- C ABI of the B200 (sm_100a) prefill->decode KV-cache handoff.
+ *
+ * This is the boundary a tempura build links through `build.rs`: plain pointers
+ * and sizes, POD structs, int32_t status codes.  Device memory is addressed as
+ * raw uint64_t CUdeviceptr values and streams as raw CUstream/cudaStream_t
+ * handles (void*), the conventions of the reference's own launchers
+ * (kernels/src/kv_scatter_write.rs:822-861, engine/src/cutile_kv_cache.rs:92-126).
+ * The library never allocates or frees pool memory; the caller keeps pools,
+ * tables and streams alive until the stream work completes.  One host thread
+ * per device, as in the reference (engine/src/cutile_kv_cache.rs:217-220).
+ *
+ * Citations are paths inside the tempura repository.
+ */
+#ifndef TKV_H
+#define TKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  1 and 2 map onto kernel-api/src/lib.rs:5-13 (KernelError::
+ * DimensionMismatch / InvalidConfig); 3 carries a CUDA error the way
+ * kernels/src/kv_scatter_write.rs:855-859 folds `rc` into InvalidConfig;
+ * 5 is the recoverable PoolExhausted of engine/src/cutile_kv_cache.rs:27-44. */
+enum {
+    TKV_OK = 0,
+    TKV_ERR_DIMENSION_MISMATCH = 1,
+    TKV_ERR_INVALID_CONFIG = 2,
+    TKV_ERR_CUDA = 3,
+    TKV_ERR_TIMEOUT = 4,
+    TKV_ERR_POOL_EXHAUSTED = 5
+};
+
+/* engine/src/cutile_kv_cache.rs:57-62 (KvDtype) */
+enum { TKV_DTYPE_F32 = 0, TKV_DTYPE_F16 = 1, TKV_DTYPE_E4M3 = 2 };
+
+/* A paged KV pool on one device.  Layout per layer, separately for K and V:
+ * [block][token_in_block][kv_head][head_dim], i.e. the byte offset of a block
+ * is block * block_size * n_kv_heads * head_dim * elem
+ * (engine/src/cutile_kv_cache.rs:1584-1602, engine/src/kv_cache.rs:925-936;
+ * row formula kernels/src/attention.rs:472-484).                             */
+typedef struct TkvPool {
+    int32_t device;               /* CUDA ordinal that owns the memory            */
+    int32_t dtype;                /* TKV_DTYPE_*                                   */
+    uint32_t n_layers;            /* layers held by this pool                      */
+    uint32_t n_kv_heads;          /* kv heads held by this pool                    */
+    uint32_t head_dim;
+    uint32_t block_size;          /* tokens per block (reference constant: 16)     */
+    uint32_t total_blocks;
+    uint32_t reserved;
+    const uint64_t* k_layer_ptrs; /* HOST array [n_layers] of device addresses     */
+    const uint64_t* v_layer_ptrs;
+    uint64_t k_scales;            /* E4M3 pools: device float[n_layers][total_blocks][n_kv_heads] */
+    uint64_t v_scales;            /*   (0 for other dtypes, or for unscaled E4M3)  */
+    uint64_t refcounts;           /* device uint32_t[total_blocks], or 0           */
+} TkvPool;
+
+/* One batch of finished prompts.  Tables hold physical block ids, logical
+ * block i of sequence q at tables[q*table_stride + i]
+ * (BlockTable, engine/src/kv_cache.rs:836-893).  Tokens
+ * [prefix_lens[q], seq_lens[q]) move; tokens below prefix_lens[q] are shared
+ * prefix blocks already resident on the destination (prefix_lens must be a
+ * multiple of block_size).                                                    */
+typedef struct TkvBatch {
+    uint32_t n_seqs;
+    uint32_t table_stride;
+    uint32_t table_layer_stride;  /* 0: one table per sequence for all layers (GPU pool,
+                                     engine/src/cutile_kv_cache.rs:1054-1072); else layer l's
+                                     tables start l*table_layer_stride entries further
+                                     (per-layer tables, engine/src/kv_cache.rs:925-936) */
+    uint32_t reserved;
+    const uint32_t* seq_lens;     /* HOST arrays */
+    const uint32_t* prefix_lens;  /* may be NULL (all zero) */
+    const uint32_t* src_tables;
+    const uint32_t* dst_tables;
+} TkvBatch;
+
+/* Which heads and layers one prefill->decode pair moves. */
+typedef struct TkvShard {
+    uint32_t src_head_begin, dst_head_begin, n_heads;
+    uint32_t src_layer_begin, dst_layer_begin, n_layers;
+} TkvShard;
+
+typedef struct TkvPairing {
+    int32_t prefill_device;
+    int32_t decode_device;
+    TkvShard shard;               /* head/layer ranges in GLOBAL (unsharded) numbering:
+                                     src_* == dst_* */
+} TkvPairing;
+
+typedef struct TkvStats {
+    uint64_t payload_bytes;       /* source bytes of the moved tokens                    */
+    uint64_t bytes_read;          /* algorithmic bytes read per enqueue                  */
+    uint64_t bytes_written;       /* algorithmic bytes written per enqueue (incl. scales) */
+    uint64_t n_blocks;            /* (src block, dst block) pairs in the work list        */
+    uint64_t n_chunks;            /* blocks * layers * 2 (K and V)                        */
+    uint64_t n_tokens;
+    uint64_t n_prefix_refs;       /* shared prefix block references in the batch          */
+    uint64_t worklist_bytes;      /* host->device bytes uploaded by plan create/update    */
+    uint32_t grid, block;         /* launch shape of the handoff kernel                   */
+    uint32_t kernel_variant;      /* TKV_VARIANT_* actually selected                      */
+    uint32_t peer;                /* 1 when destination is another device                 */
+} TkvStats;
+
+typedef struct tkv_plan tkv_plan;
+
+/* Plan flags */
+enum {
+    TKV_PLAN_DEFAULT = 0,
+    TKV_PLAN_ALLOW_SHARED_DST = 1,  /* skip the "destination block ids are unique" check   */
+    TKV_PLAN_FORCE_VECTOR = 2,      /* use the register/vector copy kernel (no bulk copies) */
+    TKV_PLAN_FORCE_BULK = 4,        /* use the shared-memory bulk-copy pipeline             */
+    TKV_PLAN_INT_QUANTIZER = 8      /* FP8: integer bit-math encoder instead of cvt + flush */
+};
+enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
+       TKV_VARIANT_CAST_GENERIC = 5 };
+
+/* ---- library -------------------------------------------------------------- */
+/* Copies the calling thread's last error text (NUL-terminated) into buf. */
+void tkv_last_error(char* buf, size_t len);
+int32_t tkv_last_cuda_error(void);
+const char* tkv_version(void);
+
+/* Enables peer access between every ordered pair of `devices` that supports it.
+ * Replaces nothing in the reference (it has no multi-device path:
+ * kernels/src/allreduce.rs:38-43); needed once per process before a plan whose
+ * pools live on two devices.                                                  */
+int32_t tkv_init(const int32_t* devices, int32_t n_devices);
+int32_t tkv_shutdown(void);
+
+/* ---- the handoff ---------------------------------------------------------- */
+/* Validates shapes, tables and refcount rules, builds the (src block, dst
+ * block, valid tokens) work list and uploads it to the source device.
+ * Replaces the gather half KvCache::to_transfer / PagedKvCache::k_contiguous
+ * (engine/src/kv_cache.rs:402-417,1032-1060) and the scatter half
+ * KvCache::from_transfer / PagedKvCache::append_kv / Fp8PagedKvCache::append_kv
+ * (engine/src/kv_cache.rs:419-431,986-1004,1204-1225) as one planned move.
+ * dtype pairs: same dtype (byte copy), F16->E4M3 (per-block scales when the
+ * destination has scale arrays, else unscaled as kernels/src/kv_scatter_write.rs:
+ * 176-273), F32->F16 and F32->E4M3 (append_kv's casts, engine/src/kv_cache.rs:
+ * 209-221; kernels/src/cutile_elementwise.rs:82-178).                         */
+int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch,
+                        const TkvShard* shard /* NULL = everything */, uint32_t flags,
+                        tkv_plan** out);
+/* Re-validates and re-uploads a new batch into an existing plan (same pools,
+ * shard and flags; no allocation unless the work list outgrew its capacity). */
+int32_t tkv_plan_update(tkv_plan* plan, const TkvBatch* batch);
+int32_t tkv_plan_destroy(tkv_plan* plan);
+int32_t tkv_plan_stats(const tkv_plan* plan, TkvStats* out);
+
+/* Asynchronous on `stream` (a stream of the SOURCE device): gathers through the
+ * source tables, converts if asked, and stores straight into the destination
+ * pool (local or peer).  If done_flag != 0 the last CTA to finish stores
+ * flag_value there (system-scope release) after all payload stores.
+ * Launch convention follows kernels/src/kv_scatter_write.rs:822-861.          */
+int32_t tkv_handoff_enqueue(tkv_plan* plan, void* stream, uint64_t done_flag, uint32_t flag_value);
+
+/* Bounded waits on a completion flag (uint32_t in device memory of the
+ * waiting side).  Host form polls with small device->host copies; device form
+ * enqueues a one-thread kernel that spins at most max_spins times and records
+ * TKV_OK or TKV_ERR_TIMEOUT in *status (device uint32_t).  Neither can hang.   */
+int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uint64_t timeout_us);
+int32_t tkv_flag_wait_enqueue(void* stream, uint64_t flag, uint32_t expected, uint64_t max_spins,
+                              uint64_t status);
+
+/* refcounts[block] += 1 (delta > 0) or saturating -= 1 (delta < 0) for every
+ * shared prefix block reference of the plan's batch, on the destination pool's
+ * refcount array.  PrefixCacheTable::probe / release
+ * (engine/src/kv_cache.rs:622-647,688-693), RadixTree::lookup / release
+ * (engine/src/prefix_cache.rs:58-97), at block granularity.                    */
+int32_t tkv_refcount_apply(tkv_plan* plan, int32_t delta, void* stream);
+
+/* Prefill GPU i <-> decode GPU i + P, P = max(1, n_gpus / 2); KV heads split
+ * evenly over the P pairs, layers when there are fewer heads than pairs.  With
+ * n_gpus == 1 the single device plays both roles.  `out` holds P entries.
+ * (No reference counterpart: engine/src/disaggregated.rs:21-62 pairs two local
+ * workers in one process.)                                                     */
+int32_t tkv_pairing_make(int32_t n_gpus, uint32_t n_layers, uint32_t n_kv_heads, TkvPairing* out,
+                         int32_t out_cap, int32_t* n_pairs);
+
+/* ---- element casts (kernels/src/cutile_elementwise.rs:82-212) -------------- */
+int32_t tkv_cast(uint64_t src, int32_t src_dtype, uint64_t dst, int32_t dst_dtype, uint64_t n,
+                 void* stream);
+/* Device self-check of the FP8 encoder used on the fast path against the
+ * integer bit-math port of kernels/src/e4m3.rs:50-94 over every f32 whose low
+ * `skip_bits` bits are zero (0 = all 2^32).  Writes the mismatch count.        */
+int32_t tkv_selfcheck_e4m3(uint32_t skip_bits, uint64_t* mismatches);
+
+/* ---- bits checksum (engine/src/cutile_kv_cache.rs:1274-1368) --------------- */
+/* Wrapping sum of the f32 bit patterns of n elements (narrow dtypes widened). */
+int32_t tkv_bits_checksum(uint64_t data, int32_t dtype, uint64_t n, void* stream, uint64_t* out);
+
+/* ---- cross-process mapping of a destination pool --------------------------- */
+/* One process per GPU: the decode process exports its pool allocation, the
+ * prefill process imports it and uses the mapped address in TkvPool.          */
+int32_t tkv_ipc_export(uint64_t devptr, uint8_t handle[64], uint64_t* offset_in_allocation);
+int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset_in_allocation, uint64_t* devptr);
+int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset_in_allocation);
+
+/* ---- host-side block bookkeeping ------------------------------------------- */
+/* PageAllocator (engine/src/kv_cache.rs:762-793) */
+typedef struct tkv_page_allocator tkv_page_allocator;
+tkv_page_allocator* tkv_page_allocator_new(size_t total_pages);
+void tkv_page_allocator_delete(tkv_page_allocator*);
+int32_t tkv_page_allocator_allocate(tkv_page_allocator*, size_t* page); /* TKV_ERR_POOL_EXHAUSTED when empty */
+void tkv_page_allocator_free(tkv_page_allocator*, size_t page);
+size_t tkv_page_allocator_available(const tkv_page_allocator*);
+size_t tkv_page_allocator_in_use(const tkv_page_allocator*);
+size_t tkv_page_allocator_total(const tkv_page_allocator*);
+
+/* BlockTable (engine/src/kv_cache.rs:836-893) */
+typedef struct tkv_block_table tkv_block_table;
+tkv_block_table* tkv_block_table_new(size_t max_blocks);
+void tkv_block_table_delete(tkv_block_table*);
+int32_t tkv_block_table_set_block(tkv_block_table*, size_t logical, size_t page);
+int32_t tkv_block_table_get_block(const tkv_block_table*, size_t logical, size_t* page); /* 1 = Some */
+size_t tkv_block_table_num_blocks(const tkv_block_table*);
+size_t tkv_block_table_max_blocks(const tkv_block_table*);
+const uint32_t* tkv_block_table_as_slice(const tkv_block_table*);
+size_t tkv_block_table_clear(tkv_block_table*, size_t* freed, size_t cap);
+
+/* PageRunAllocator (engine/src/gpu_page_pool.rs:34-218) */
+typedef struct tkv_run_allocator tkv_run_allocator;
+tkv_run_allocator* tkv_run_allocator_new(size_t total_pages);
+void tkv_run_allocator_delete(tkv_run_allocator*);
+int32_t tkv_run_allocator_alloc(tkv_run_allocator*, size_t pages, size_t* start); /* 1 = Some */
+int32_t tkv_run_allocator_free(tkv_run_allocator*, size_t start, size_t pages);
+int32_t tkv_run_allocator_try_extend(tkv_run_allocator*, size_t start, size_t pages, size_t target);
+size_t tkv_run_allocator_free_pages(const tkv_run_allocator*);
+size_t tkv_run_allocator_allocated_pages(const tkv_run_allocator*);
+size_t tkv_run_allocator_free_runs(const tkv_run_allocator*, size_t* starts, size_t* pages, size_t cap);
+
+/* RadixTree (engine/src/prefix_cache.rs:17-149) */
+typedef struct tkv_radix_tree tkv_radix_tree;
+tkv_radix_tree* tkv_radix_tree_new(void);
+void tkv_radix_tree_delete(tkv_radix_tree*);
+void tkv_radix_tree_insert(tkv_radix_tree*, const uint32_t* tokens, size_t n, const size_t* pages, size_t n_pages);
+size_t tkv_radix_tree_lookup(tkv_radix_tree*, const uint32_t* tokens, size_t n, size_t* pages_out,
+                             size_t cap, size_t* n_pages);
+void tkv_radix_tree_release(tkv_radix_tree*, const uint32_t* tokens, size_t n);
+size_t tkv_radix_tree_evict_lru(tkv_radix_tree*, size_t* freed, size_t cap);
+uint64_t tkv_radix_tree_hit_count(const tkv_radix_tree*);
+uint64_t tkv_radix_tree_tokens_saved(const tkv_radix_tree*);
+size_t tkv_radix_tree_node_count(const tkv_radix_tree*);
+
+/* PrefixCacheTable (engine/src/kv_cache.rs:581-730); entries name destination
+ * block ids instead of holding cloned K/V vectors.                            */
+typedef struct tkv_prefix_table tkv_prefix_table;
+tkv_prefix_table* tkv_prefix_table_new(size_t max_entries);
+void tkv_prefix_table_delete(tkv_prefix_table*);
+void tkv_prefix_table_store(tkv_prefix_table*, const uint32_t* tokens, size_t n, const char* salt,
+                            const uint32_t* blocks, size_t n_blocks, size_t seq_len);
+size_t tkv_prefix_table_probe(tkv_prefix_table*, const uint32_t* tokens, size_t n, const char* salt,
+                              uint32_t* blocks_out, size_t cap, size_t* n_blocks);
+void tkv_prefix_table_release(tkv_prefix_table*, const uint32_t* tokens, size_t n, const char* salt);
+size_t tkv_prefix_table_len(const tkv_prefix_table*);
+uint64_t tkv_prefix_table_hit_count(const tkv_prefix_table*);
+uint64_t tkv_prefix_table_tokens_saved(const tkv_prefix_table*);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TKV_H */

@@ -1,0 +1,152 @@
+"""ctypes view of ``libtkv.so``.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import _build
+
+_lib = None
+
+
+class TkvError(RuntimeError):
+    """Mirror of the reference's ``KernelError`` (kernel-api/src/lib.rs:5-13) plus the
+    CUDA, timeout and pool-exhaustion codes of the C ABI."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{STATUS_NAMES.get(code, code)}] {message}")
+        self.code = code
+        self.message = message
+
+
+OK, ERR_DIMENSION_MISMATCH, ERR_INVALID_CONFIG, ERR_CUDA, ERR_TIMEOUT, ERR_POOL_EXHAUSTED = range(6)
+STATUS_NAMES = {0: "Ok", 1: "DimensionMismatch", 2: "InvalidConfig", 3: "CudaError", 4: "Timeout", 5: "PoolExhausted"}
+DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
+PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER = 1, 2, 4, 8
+
+
+class TkvPool(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32), ("dtype", C.c_int32),
+        ("n_layers", C.c_uint32), ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32),
+        ("block_size", C.c_uint32), ("total_blocks", C.c_uint32), ("reserved", C.c_uint32),
+        ("k_layer_ptrs", C.POINTER(C.c_uint64)), ("v_layer_ptrs", C.POINTER(C.c_uint64)),
+        ("k_scales", C.c_uint64), ("v_scales", C.c_uint64), ("refcounts", C.c_uint64),
+    ]
+
+
+class TkvBatch(C.Structure):
+    _fields_ = [
+        ("n_seqs", C.c_uint32), ("table_stride", C.c_uint32), ("table_layer_stride", C.c_uint32),
+        ("reserved", C.c_uint32),
+        ("seq_lens", C.POINTER(C.c_uint32)), ("prefix_lens", C.POINTER(C.c_uint32)),
+        ("src_tables", C.POINTER(C.c_uint32)), ("dst_tables", C.POINTER(C.c_uint32)),
+    ]
+
+
+class TkvShard(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in (
+        "src_head_begin", "dst_head_begin", "n_heads", "src_layer_begin", "dst_layer_begin", "n_layers")]
+
+
+class TkvPairing(C.Structure):
+    _fields_ = [("prefill_device", C.c_int32), ("decode_device", C.c_int32), ("shard", TkvShard)]
+
+
+class TkvStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "payload_bytes", "bytes_read", "bytes_written", "n_blocks", "n_chunks", "n_tokens",
+        "n_prefix_refs", "worklist_bytes")] + [(n, C.c_uint32) for n in ("grid", "block", "kernel_variant", "peer")]
+
+
+# every symbol include/tkv.h declares: name -> (restype, argtypes)
+_u8p, _u32p, _u64p, _szp = C.POINTER(C.c_uint8), C.POINTER(C.c_uint32), C.POINTER(C.c_uint64), C.POINTER(C.c_size_t)
+_vp, _i32, _u32, _u64, _sz = C.c_void_p, C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t
+SIGNATURES = {
+    "tkv_last_error": (None, [C.c_char_p, _sz]),
+    "tkv_last_cuda_error": (_i32, []),
+    "tkv_version": (C.c_char_p, []),
+    "tkv_init": (_i32, [C.POINTER(_i32), _i32]),
+    "tkv_shutdown": (_i32, []),
+    "tkv_plan_create": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _u32, C.POINTER(_vp)]),
+    "tkv_plan_update": (_i32, [_vp, C.POINTER(TkvBatch)]),
+    "tkv_plan_destroy": (_i32, [_vp]),
+    "tkv_plan_stats": (_i32, [_vp, C.POINTER(TkvStats)]),
+    "tkv_handoff_enqueue": (_i32, [_vp, _vp, _u64, _u32]),
+    "tkv_flag_wait_host": (_i32, [_i32, _u64, _u32, _u64]),
+    "tkv_flag_wait_enqueue": (_i32, [_vp, _u64, _u32, _u64, _u64]),
+    "tkv_refcount_apply": (_i32, [_vp, _i32, _vp]),
+    "tkv_pairing_make": (_i32, [_i32, _u32, _u32, C.POINTER(TkvPairing), _i32, C.POINTER(_i32)]),
+    "tkv_cast": (_i32, [_u64, _i32, _u64, _i32, _u64, _vp]),
+    "tkv_selfcheck_e4m3": (_i32, [_u32, _u64p]),
+    "tkv_bits_checksum": (_i32, [_u64, _i32, _u64, _vp, _u64p]),
+    "tkv_ipc_export": (_i32, [_u64, _u8p, _u64p]),
+    "tkv_ipc_import": (_i32, [_u8p, _u64, _u64p]),
+    "tkv_ipc_close": (_i32, [_u64, _u64]),
+    "tkv_page_allocator_new": (_vp, [_sz]),
+    "tkv_page_allocator_delete": (None, [_vp]),
+    "tkv_page_allocator_allocate": (_i32, [_vp, _szp]),
+    "tkv_page_allocator_free": (None, [_vp, _sz]),
+    "tkv_page_allocator_available": (_sz, [_vp]),
+    "tkv_page_allocator_in_use": (_sz, [_vp]),
+    "tkv_page_allocator_total": (_sz, [_vp]),
+    "tkv_block_table_new": (_vp, [_sz]),
+    "tkv_block_table_delete": (None, [_vp]),
+    "tkv_block_table_set_block": (_i32, [_vp, _sz, _sz]),
+    "tkv_block_table_get_block": (_i32, [_vp, _sz, _szp]),
+    "tkv_block_table_num_blocks": (_sz, [_vp]),
+    "tkv_block_table_max_blocks": (_sz, [_vp]),
+    "tkv_block_table_as_slice": (_u32p, [_vp]),
+    "tkv_block_table_clear": (_sz, [_vp, _szp, _sz]),
+    "tkv_run_allocator_new": (_vp, [_sz]),
+    "tkv_run_allocator_delete": (None, [_vp]),
+    "tkv_run_allocator_alloc": (_i32, [_vp, _sz, _szp]),
+    "tkv_run_allocator_free": (_i32, [_vp, _sz, _sz]),
+    "tkv_run_allocator_try_extend": (_i32, [_vp, _sz, _sz, _sz]),
+    "tkv_run_allocator_free_pages": (_sz, [_vp]),
+    "tkv_run_allocator_allocated_pages": (_sz, [_vp]),
+    "tkv_run_allocator_free_runs": (_sz, [_vp, _szp, _szp, _sz]),
+    "tkv_radix_tree_new": (_vp, []),
+    "tkv_radix_tree_delete": (None, [_vp]),
+    "tkv_radix_tree_insert": (None, [_vp, _u32p, _sz, _szp, _sz]),
+    "tkv_radix_tree_lookup": (_sz, [_vp, _u32p, _sz, _szp, _sz, _szp]),
+    "tkv_radix_tree_release": (None, [_vp, _u32p, _sz]),
+    "tkv_radix_tree_evict_lru": (_sz, [_vp, _szp, _sz]),
+    "tkv_radix_tree_hit_count": (_u64, [_vp]),
+    "tkv_radix_tree_tokens_saved": (_u64, [_vp]),
+    "tkv_radix_tree_node_count": (_sz, [_vp]),
+    "tkv_prefix_table_new": (_vp, [_sz]),
+    "tkv_prefix_table_delete": (None, [_vp]),
+    "tkv_prefix_table_store": (None, [_vp, _u32p, _sz, C.c_char_p, _u32p, _sz, _sz]),
+    "tkv_prefix_table_probe": (_sz, [_vp, _u32p, _sz, C.c_char_p, _u32p, _sz, _szp]),
+    "tkv_prefix_table_release": (None, [_vp, _u32p, _sz, C.c_char_p]),
+    "tkv_prefix_table_len": (_sz, [_vp]),
+    "tkv_prefix_table_hit_count": (_u64, [_vp]),
+    "tkv_prefix_table_tokens_saved": (_u64, [_vp]),
+}
+
+
+def lib() -> C.CDLL:
+    """Loads the in-tree ``libtkv.so``; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(there is no CPU fallback for the KV handoff)")
+    L = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)          # AttributeError here == header/library drift
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        buf = C.create_string_buffer(512)
+        lib().tkv_last_error(buf, 512)
+        raise TkvError(rc, buf.value.decode(errors="replace"))

@@ -1,0 +1,431 @@
+// Device code of the KV handoff for sm_100a.
+//
+// Unit of work ("chunk"): one (block pair, layer, K|V).  At source and at
+// destination a chunk is `n_valid` token rows of `row_bytes`, `row_stride`
+// apart; when a pair moves every kv head of both pools the rows abut and the
+// chunk is one contiguous run (32 KiB for 16 tokens x 8 heads x 128 dims of F16).
+// The work list holds one uint4 {src_block, dst_block, n_valid, 0} per block
+// pair; chunk index w decodes as kv = w & 1, layer = (w >> 1) % L,
+// pair = (w >> 1) / L, so neighbouring CTAs stream K and V of one block.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tkv {
+
+struct HandoffArgs {
+    const uint4* work;
+    const uint64_t* src_k;  // [n_layers] device addresses, shard-relative
+    const uint64_t* src_v;
+    const uint64_t* dst_k;
+    const uint64_t* dst_v;
+    float* dst_k_scales;    // [pool layers][total_blocks][pool heads] or null
+    float* dst_v_scales;
+    uint32_t* done_counter; // in plan memory on the launching device
+    uint32_t* done_flag;    // anywhere reachable (peer ok) or null
+    uint64_t src_block_stride;  // bytes
+    uint64_t dst_block_stride;
+    uint32_t n_pairs;           // block pairs per layer
+    uint32_t work_layer_stride; // 0 = one list for all layers
+    uint32_t n_layers;
+    uint32_t n_heads;
+    uint32_t head_dim;
+    uint32_t block_size;
+    uint32_t src_row_bytes, dst_row_bytes;   // bytes moved per token row
+    uint32_t src_row_stride, dst_row_stride; // bytes between token rows
+    uint32_t src_head_off, dst_head_off;     // byte offset of the first moved head in a row
+    uint32_t dst_total_blocks, dst_pool_heads, dst_head_begin, dst_layer_begin;
+    uint32_t flag_value;
+    uint32_t contiguous;        // rows abut on both sides
+};
+
+struct Chunk {
+    const char* src;
+    char* dst;
+    uint32_t n_valid, layer, is_v, dst_block;
+};
+
+__device__ __forceinline__ Chunk decode_chunk(const HandoffArgs& a, uint32_t w) {
+    Chunk c;
+    c.is_v = w & 1u;
+    uint32_t q = w >> 1;
+    c.layer = q % a.n_layers;
+    uint32_t pair = q / a.n_layers;
+    uint4 t = __ldg(a.work + (size_t)c.layer * a.work_layer_stride + pair);
+    uint64_t sb = c.is_v ? a.src_v[c.layer] : a.src_k[c.layer];
+    uint64_t db = c.is_v ? a.dst_v[c.layer] : a.dst_k[c.layer];
+    c.src = reinterpret_cast<const char*>(sb + (uint64_t)t.x * a.src_block_stride + a.src_head_off);
+    c.dst = reinterpret_cast<char*>(db + (uint64_t)t.y * a.dst_block_stride + a.dst_head_off);
+    c.n_valid = t.z;
+    c.dst_block = t.y;
+    return c;
+}
+
+// Last CTA to finish publishes the completion flag.  Every CTA fences its
+// payload stores to system scope before counting itself, so a reader that
+// acquires the flag (host, peer GPU) sees all of them.
+__device__ __forceinline__ void signal_done(const HandoffArgs& a) {
+    if (a.done_flag == nullptr) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        uint32_t prev = atomicAdd(a.done_counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *a.done_counter = 0;  // ready for the next enqueue (stream order)
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.done_flag), "r"(a.flag_value) : "memory");
+        }
+    }
+}
+
+// ---- streaming loads / stores of a given width ---------------------------------
+template <int BYTES> struct VecT;
+template <> struct VecT<16> { using type = uint4; };
+template <> struct VecT<8> { using type = uint2; };
+template <> struct VecT<4> { using type = uint32_t; };
+template <> struct VecT<2> { using type = uint16_t; };
+template <> struct VecT<1> { using type = uint8_t; };
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+template <typename T> __device__ __forceinline__ T ld_stream(const T* p) { return __ldg(p); }
+
+// ---------------------------------------------------------------------------------
+// Same-dtype handoff, register path: 16-byte (or narrower) loads, UNROLL in
+// flight per thread, then the stores.  Also the peer-store path: the stores go
+// wherever the destination pointers point.
+// ---------------------------------------------------------------------------------
+template <int VEC, int UNROLL>
+__global__ void __launch_bounds__(256) handoff_copy_vec(const HandoffArgs a) {
+    using V = typename VecT<VEC>::type;
+    const uint32_t total = a.n_pairs * a.n_layers * 2u;
+    const uint32_t vec_per_row = a.src_row_bytes / VEC;
+    for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
+        const Chunk c = decode_chunk(a, w);
+        const uint32_t nvec = c.n_valid * vec_per_row;
+        if (a.contiguous) {
+            const V* s = reinterpret_cast<const V*>(c.src);
+            V* d = reinterpret_cast<V*>(c.dst);
+            for (uint32_t base = 0; base < nvec; base += 256u * UNROLL) {
+                V v[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) v[u] = ld_stream(s + i);
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) d[i] = v[u];
+                }
+            }
+        } else {
+            for (uint32_t base = 0; base < nvec; base += 256u * UNROLL) {
+                V v[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) {
+                        uint32_t r = i / vec_per_row, col = i - r * vec_per_row;
+                        v[u] = ld_stream(reinterpret_cast<const V*>(c.src + (size_t)r * a.src_row_stride) + col);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) {
+                        uint32_t r = i / vec_per_row, col = i - r * vec_per_row;
+                        reinterpret_cast<V*>(c.dst + (size_t)r * a.dst_row_stride)[col] = v[u];
+                    }
+                }
+            }
+        }
+    }
+    signal_done(a);
+}
+
+// ---------------------------------------------------------------------------------
+// FP8 E4M3 encoders.
+// ---------------------------------------------------------------------------------
+
+// Integer bit-math statement of the element rule: NaN -> 0x7F, clamp to +-448,
+// f32 exponent below 121 -> signed zero, round to nearest even on the 20 dropped
+// mantissa bits with carry into the exponent.
+__device__ __forceinline__ uint32_t e4m3_encode_int(float x) {
+    uint32_t bits = __float_as_uint(x);
+    uint32_t sign = (bits >> 24) & 0x80u;
+    uint32_t abs = bits & 0x7FFFFFFFu;
+    if (abs > 0x7F800000u) return 0x7Fu;
+    abs = min(abs, 0x43E00000u);  // 448.0f; also catches Inf
+    uint32_t exp = abs >> 23;
+    if (exp < 121u) return sign;
+    uint32_t man = abs & 0x7FFFFFu;
+    uint32_t mag = ((exp - 120u) << 3) | (man >> 20);  // exponent and kept bits, carry-ready
+    uint32_t dropped = man & 0xFFFFFu;
+    uint32_t up = (dropped > 0x80000u) || (dropped == 0x80000u && (mag & 1u));
+    return sign | (mag + up);
+}
+
+// Hardware conversion (round to nearest even, saturate to +-448) with the
+// reference's flush applied first: inputs below 2^-6 in magnitude become a
+// signed zero instead of an e4m3 subnormal.  NaN of either sign -> 0x7F.
+// Returns {byte(hi) << 8 | byte(lo)}.
+__device__ __forceinline__ uint32_t e4m3_encode_pair_hw(float lo, float hi) {
+    uint32_t bl = __float_as_uint(lo), bh = __float_as_uint(hi);
+    if ((bl & 0x7FFFFFFFu) < 0x3C800000u) bl &= 0x80000000u;
+    if ((bh & 0x7FFFFFFFu) < 0x3C800000u) bh &= 0x80000000u;
+    if ((bl & 0x7FFFFFFFu) > 0x7F800000u) bl = 0x7FC00000u;
+    if ((bh & 0x7FFFFFFFu) > 0x7F800000u) bh = 0x7FC00000u;
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(__uint_as_float(bh)), "f"(__uint_as_float(bl)));
+    return r;
+}
+
+template <bool HW> __device__ __forceinline__ uint32_t e4m3_encode_pair(float lo, float hi) {
+    if (HW) return e4m3_encode_pair_hw(lo, hi);
+    return e4m3_encode_int(lo) | (e4m3_encode_int(hi) << 8);
+}
+
+// Scale rule: amax taken as the integer maximum of (bits & 0x7FFF); a zero or
+// non-finite amax leaves the block unscaled; otherwise the stored scale is
+// amax / 448 and elements are multiplied by 448 / amax, each one IEEE
+// round-to-nearest operation.
+__device__ __forceinline__ float block_scale(uint32_t amax_bits, float& inv) {
+    if (amax_bits == 0u || amax_bits >= 0x7C00u) {
+        inv = 1.0f;
+        return 1.0f;
+    }
+    float amax = __half2float(__ushort_as_half((unsigned short)amax_bits));
+    inv = __fdiv_rn(448.0f, amax);
+    return __fdiv_rn(amax, 448.0f);
+}
+
+// two F16 in a u32 -> two e4m3 bytes in the low 16 bits
+template <bool HW> __device__ __forceinline__ uint32_t quant_h2(uint32_t h2, float inv) {
+    float lo = __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
+    float hi = __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
+    return e4m3_encode_pair<HW>(__fmul_rn(lo, inv), __fmul_rn(hi, inv));
+}
+
+// ---------------------------------------------------------------------------------
+// F16 -> E4M3 handoff, one warp per (chunk, kv head).  The warp keeps its
+// BS x D halves in registers between the absmax pass and the encode pass, so the
+// source is read once.  Each lane owns 32 contiguous source bytes of a token row
+// (two 16-byte loads) and writes the 16 encoded bytes with one 16-byte store.
+// ---------------------------------------------------------------------------------
+template <int D, int BS, bool HW, bool SCALED>
+__global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a) {
+    constexpr int LPR = D / 16;        // lanes per token row
+    constexpr int RPP = 32 / LPR;      // token rows per pass
+    constexpr int NP = (BS + RPP - 1) / RPP;
+    static_assert(D % 16 == 0 && LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "head_dim");
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t r0 = lane / LPR, col = lane % LPR;
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint64_t total = (uint64_t)chunks * a.n_heads;
+    for (uint64_t wi = (uint64_t)blockIdx.x * 8u + warp; wi < total; wi += (uint64_t)gridDim.x * 8u) {
+        const uint32_t h = (uint32_t)(wi % a.n_heads);
+        const Chunk c = decode_chunk(a, (uint32_t)(wi / a.n_heads));
+        const char* s = c.src + (size_t)h * D * 2 + col * 32;
+        char* d = c.dst + (size_t)h * D + col * 16;
+        uint4 v[NP][2];
+        uint32_t m = 0;
+#pragma unroll
+        for (int p = 0; p < NP; p++) {
+            uint32_t row = p * RPP + r0;
+            if (row < c.n_valid) {
+                const uint4* sp = reinterpret_cast<const uint4*>(s + (size_t)row * a.src_row_stride);
+                v[p][0] = ld_stream(sp);
+                v[p][1] = ld_stream(sp + 1);
+            } else {
+                v[p][0] = make_uint4(0, 0, 0, 0);
+                v[p][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float inv = 1.0f;
+        if (SCALED) {
+#pragma unroll
+            for (int p = 0; p < NP; p++) {
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    m = __vmaxu2(m, v[p][k].x & 0x7FFF7FFFu);
+                    m = __vmaxu2(m, v[p][k].y & 0x7FFF7FFFu);
+                    m = __vmaxu2(m, v[p][k].z & 0x7FFF7FFFu);
+                    m = __vmaxu2(m, v[p][k].w & 0x7FFF7FFFu);
+                }
+            }
+            uint32_t amax = max(m & 0xFFFFu, m >> 16);
+            amax = __reduce_max_sync(0xFFFFFFFFu, amax);
+            float scale = block_scale(amax, inv);
+            if (lane == 0) {
+                float* sc = c.is_v ? a.dst_v_scales : a.dst_k_scales;
+                sc[((size_t)(a.dst_layer_begin + c.layer) * a.dst_total_blocks + c.dst_block) * a.dst_pool_heads +
+                   a.dst_head_begin + h] = scale;
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < NP; p++) {
+            uint32_t row = p * RPP + r0;
+            if (row < c.n_valid) {
+                uint4 o;
+                o.x = quant_h2<HW>(v[p][0].x, inv) | (quant_h2<HW>(v[p][0].y, inv) << 16);
+                o.y = quant_h2<HW>(v[p][0].z, inv) | (quant_h2<HW>(v[p][0].w, inv) << 16);
+                o.z = quant_h2<HW>(v[p][1].x, inv) | (quant_h2<HW>(v[p][1].y, inv) << 16);
+                o.w = quant_h2<HW>(v[p][1].z, inv) | (quant_h2<HW>(v[p][1].w, inv) << 16);
+                *reinterpret_cast<uint4*>(d + (size_t)row * a.dst_row_stride) = o;
+            }
+        }
+    }
+    signal_done(a);
+}
+
+// Any head_dim / block_size: one warp per (chunk, kv head), two passes over the
+// source (the second one hits L2), element-wide accesses.
+template <bool HW, bool SCALED>
+__global__ void __launch_bounds__(256) handoff_f16_e4m3_generic(const HandoffArgs a) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint64_t total = (uint64_t)chunks * a.n_heads;
+    const uint32_t D = a.head_dim;
+    for (uint64_t wi = (uint64_t)blockIdx.x * 8u + warp; wi < total; wi += (uint64_t)gridDim.x * 8u) {
+        const uint32_t h = (uint32_t)(wi % a.n_heads);
+        const Chunk c = decode_chunk(a, (uint32_t)(wi / a.n_heads));
+        const uint32_t n = c.n_valid * D;
+        float inv = 1.0f;
+        if (SCALED) {
+            uint32_t amax = 0;
+            for (uint32_t i = lane; i < n; i += 32u) {
+                uint32_t r = i / D, e = i - r * D;
+                uint16_t b = *reinterpret_cast<const uint16_t*>(c.src + (size_t)r * a.src_row_stride + ((size_t)h * D + e) * 2);
+                amax = max(amax, (uint32_t)(b & 0x7FFFu));
+            }
+            amax = __reduce_max_sync(0xFFFFFFFFu, amax);
+            float scale = block_scale(amax, inv);
+            if (lane == 0) {
+                float* sc = c.is_v ? a.dst_v_scales : a.dst_k_scales;
+                sc[((size_t)(a.dst_layer_begin + c.layer) * a.dst_total_blocks + c.dst_block) * a.dst_pool_heads +
+                   a.dst_head_begin + h] = scale;
+            }
+        }
+        for (uint32_t i = lane; i < n; i += 32u) {
+            uint32_t r = i / D, e = i - r * D;
+            uint16_t b = *reinterpret_cast<const uint16_t*>(c.src + (size_t)r * a.src_row_stride + ((size_t)h * D + e) * 2);
+            float y = __fmul_rn(__half2float(__ushort_as_half(b)), inv);
+            uint32_t q = HW ? (e4m3_encode_pair_hw(y, 0.0f) & 0xFFu) : e4m3_encode_int(y);
+            *reinterpret_cast<uint8_t*>(c.dst + (size_t)r * a.dst_row_stride + (size_t)h * D + e) = (uint8_t)q;
+        }
+    }
+    signal_done(a);
+}
+
+// F32 source with a narrower destination (append_kv's casts): element-wide.
+// MODE 0: F32 -> F16 (round to nearest even; NaN -> 0x7FFF as cvt.rn.f16.f32 does)
+// MODE 1: F32 -> E4M3, unscaled
+template <int MODE>
+__global__ void __launch_bounds__(256) handoff_f32_cast_generic(const HandoffArgs a) {
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t row_elems = a.n_heads * a.head_dim;
+    for (uint32_t w = blockIdx.x; w < chunks; w += gridDim.x) {
+        const Chunk c = decode_chunk(a, w);
+        const uint32_t n = c.n_valid * row_elems;
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            uint32_t r = i / row_elems, e = i - r * row_elems;
+            float x = *reinterpret_cast<const float*>(c.src + (size_t)r * a.src_row_stride + (size_t)e * 4);
+            if (MODE == 0) {
+                *reinterpret_cast<__half*>(c.dst + (size_t)r * a.dst_row_stride + (size_t)e * 2) = __float2half_rn(x);
+            } else {
+                *reinterpret_cast<uint8_t*>(c.dst + (size_t)r * a.dst_row_stride + e) = (uint8_t)e4m3_encode_int(x);
+            }
+        }
+    }
+    signal_done(a);
+}
+
+// ---------------------------------------------------------------------------------
+// small kernels
+// ---------------------------------------------------------------------------------
+__global__ void refcount_apply_kernel(uint32_t* refcounts, const uint32_t* ids, uint32_t n, int delta) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        uint32_t* p = refcounts + ids[i];
+        if (delta > 0) {
+            atomicAdd(p, 1u);
+        } else {
+            uint32_t old = *p;
+            while (old != 0u) {  // saturating decrement; ends when the CAS lands or the count is 0
+                uint32_t seen = atomicCAS(p, old, old - 1u);
+                if (seen == old) break;
+                old = seen;
+            }
+        }
+    }
+}
+
+// Bounded wait: gives up after max_spins polls and records a status instead of
+// spinning forever.
+__global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, unsigned long long max_spins,
+                                 uint32_t* status) {
+    uint32_t v = 0;
+    for (unsigned long long i = 0; i < max_spins; i++) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == expected) {
+            if (status) *status = 0u;  // TKV_OK
+            return;
+        }
+        __nanosleep(256);
+    }
+    if (status) *status = 4u;  // TKV_ERR_TIMEOUT
+}
+
+__device__ __forceinline__ float e4m3_decode(uint32_t b) {
+    uint32_t sign = (b & 0x80u) << 24, exp = (b >> 3) & 0xFu, man = b & 7u;
+    return __uint_as_float(exp == 0u ? sign : (sign | ((exp + 120u) << 23) | (man << 20)));
+}
+
+// dtype codes: 0 = F32, 1 = F16, 2 = E4M3
+template <int SRC, int DST>
+__global__ void cast_kernel(const void* __restrict__ src, void* __restrict__ dst, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float x;
+        if (SRC == 0) x = reinterpret_cast<const float*>(src)[i];
+        else if (SRC == 1) x = __half2float(reinterpret_cast<const __half*>(src)[i]);
+        else x = e4m3_decode(reinterpret_cast<const uint8_t*>(src)[i]);
+        if (DST == 0) reinterpret_cast<float*>(dst)[i] = x;
+        else if (DST == 1) reinterpret_cast<__half*>(dst)[i] = __float2half_rn(x);
+        else reinterpret_cast<uint8_t*>(dst)[i] = (uint8_t)e4m3_encode_int(x);
+    }
+}
+
+__global__ void selfcheck_e4m3_kernel(uint32_t skip_bits, unsigned long long* mismatches) {
+    const uint64_t n = 1ull << (32 - skip_bits);
+    unsigned long long bad = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float x = __uint_as_float((uint32_t)(i << skip_bits));
+        uint32_t want = e4m3_encode_int(x);
+        uint32_t p = e4m3_encode_pair_hw(x, -x);
+        if ((p & 0xFFu) != want) bad++;
+        uint32_t want_neg = e4m3_encode_int(-x);
+        if ((p >> 8) != want_neg) bad++;
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+template <int DT>
+__global__ void bits_checksum_kernel(const void* __restrict__ data, uint64_t n, unsigned long long* out) {
+    unsigned long long s = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float x;
+        if (DT == 0) x = reinterpret_cast<const float*>(data)[i];
+        else if (DT == 1) x = __half2float(reinterpret_cast<const __half*>(data)[i]);
+        else x = e4m3_decode(reinterpret_cast<const uint8_t*>(data)[i]);
+        s += __float_as_uint(x);
+    }
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xFFFFFFFFu, s, o);
+    if ((threadIdx.x & 31) == 0 && s) atomicAdd(out, s);
+}
+
+}  // namespace tkv

@@ -1,0 +1,699 @@
+// Host side of the C ABI declared in include/tkv.h: argument validation, work-list
+// construction, launches.  No CPU fallback exists: every entry point that moves KV
+// bytes launches a kernel on the source device or returns an error.
+#include "tkv_kernels.cuh"
+
+#include <algorithm>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/tkv.h"
+
+namespace {
+
+thread_local std::string g_err;
+thread_local int32_t g_cuda_err = 0;
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+    g_cuda_err = (int32_t)e;
+    return fail(TKV_ERR_CUDA, "%s: %s (cuda error %d)", what, cudaGetErrorString(e), (int)e);
+}
+
+#define CU(call)                                             \
+    do {                                                     \
+        cudaError_t e_ = (call);                             \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call);  \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && (prev == dev || cudaSetDevice(dev) == cudaSuccess)) ok = true;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+uint32_t elem_size(int32_t dt) { return dt == TKV_DTYPE_F32 ? 4u : dt == TKV_DTYPE_F16 ? 2u : dt == TKV_DTYPE_E4M3 ? 1u : 0u; }
+
+enum Mode { MODE_COPY, MODE_F16_E4M3, MODE_F32_F16, MODE_F32_E4M3 };
+
+struct DevInfo {
+    int sm_count = 0;
+};
+std::mutex g_mu;
+DevInfo g_dev[64];
+cudaStream_t g_copy_stream[64] = {};
+
+int32_t dev_info(int dev, DevInfo* out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (dev < 0 || dev >= 64) return fail(TKV_ERR_INVALID_CONFIG, "device ordinal %d out of range", dev);
+    if (g_dev[dev].sm_count == 0) {
+        int n = 0;
+        CU(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+        g_dev[dev].sm_count = n;
+    }
+    *out = g_dev[dev];
+    return TKV_OK;
+}
+
+// a non-blocking stream per device for the library's own small copies
+int32_t copy_stream(int dev, cudaStream_t* out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (dev < 0 || dev >= 64) return fail(TKV_ERR_INVALID_CONFIG, "device ordinal %d out of range", dev);
+    if (!g_copy_stream[dev]) CU(cudaStreamCreateWithFlags(&g_copy_stream[dev], cudaStreamNonBlocking));
+    *out = g_copy_stream[dev];
+    return TKV_OK;
+}
+
+}  // namespace
+
+struct tkv_plan {
+    TkvPool src{}, dst{};
+    std::vector<uint64_t> src_k, src_v, dst_k, dst_v;  // owned copies of the layer pointers
+    TkvShard shard{};
+    uint32_t flags = 0;
+    Mode mode = MODE_COPY;
+    uint32_t variant = 0;
+    int vec = 16;
+    // device block on src.device: [4*L u64 layer ptrs][u32 done counter .. pad 16][work list][prefix ids]
+    char* d_buf = nullptr;
+    size_t d_cap = 0;
+    char* h_buf = nullptr;  // pinned mirror
+    size_t h_cap = 0;
+    size_t off_work = 0, off_prefix = 0, used = 0;
+    uint32_t n_pairs = 0, n_prefix = 0;
+    tkv::HandoffArgs args{};
+    TkvStats stats{};
+    uint32_t grid = 0;
+    std::vector<uint8_t> seen;  // scratch bitmap over destination blocks
+    std::vector<char> image;    // host image of the device block, built before any CUDA call
+};
+
+namespace {
+
+int32_t validate_pools(const TkvPool* s, const TkvPool* d, const TkvShard& sh, Mode* mode) {
+    if (!s->k_layer_ptrs || !s->v_layer_ptrs || !d->k_layer_ptrs || !d->v_layer_ptrs)
+        return fail(TKV_ERR_INVALID_CONFIG, "pool layer pointer arrays must not be NULL");
+    if (elem_size(s->dtype) == 0 || elem_size(d->dtype) == 0)
+        return fail(TKV_ERR_INVALID_CONFIG, "unknown pool dtype (src %d, dst %d)", s->dtype, d->dtype);
+    if (s->head_dim != d->head_dim) {
+        return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (head_dim)", s->head_dim, d->head_dim);
+    }
+    if (s->block_size != d->block_size)
+        return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (block_size)", s->block_size, d->block_size);
+    if (s->head_dim == 0 || s->block_size == 0 || s->n_kv_heads == 0 || d->n_kv_heads == 0 || s->n_layers == 0 || d->n_layers == 0)
+        return fail(TKV_ERR_INVALID_CONFIG, "zero-sized pool geometry");
+    if (sh.n_heads == 0 || sh.n_layers == 0) return fail(TKV_ERR_INVALID_CONFIG, "empty shard");
+    if ((uint64_t)sh.src_head_begin + sh.n_heads > s->n_kv_heads || (uint64_t)sh.dst_head_begin + sh.n_heads > d->n_kv_heads)
+        return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (shard heads exceed pool heads)",
+                    std::min(s->n_kv_heads, d->n_kv_heads), sh.n_heads);
+    if ((uint64_t)sh.src_layer_begin + sh.n_layers > s->n_layers || (uint64_t)sh.dst_layer_begin + sh.n_layers > d->n_layers)
+        return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (shard layers exceed pool layers)",
+                    std::min(s->n_layers, d->n_layers), sh.n_layers);
+    if (s->dtype == d->dtype) *mode = MODE_COPY;
+    else if (s->dtype == TKV_DTYPE_F16 && d->dtype == TKV_DTYPE_E4M3) *mode = MODE_F16_E4M3;
+    else if (s->dtype == TKV_DTYPE_F32 && d->dtype == TKV_DTYPE_F16) *mode = MODE_F32_F16;
+    else if (s->dtype == TKV_DTYPE_F32 && d->dtype == TKV_DTYPE_E4M3) *mode = MODE_F32_E4M3;
+    else return fail(TKV_ERR_INVALID_CONFIG, "unsupported dtype pair %d -> %d", s->dtype, d->dtype);
+    if ((d->k_scales == 0) != (d->v_scales == 0))
+        return fail(TKV_ERR_INVALID_CONFIG, "k_scales and v_scales must both be set or both be 0");
+    if (*mode == MODE_COPY && s->dtype == TKV_DTYPE_E4M3 && (d->k_scales || s->k_scales))
+        return fail(TKV_ERR_INVALID_CONFIG, "E4M3 -> E4M3 with scale arrays is not supported");
+    return TKV_OK;
+}
+
+// Builds the host image of the plan's device block from a batch.
+int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
+    const TkvPool &s = p->src, &d = p->dst;
+    const TkvShard& sh = p->shard;
+    const uint32_t bs = s.block_size;
+    if (b->n_seqs && (!b->seq_lens || !b->src_tables || !b->dst_tables))
+        return fail(TKV_ERR_INVALID_CONFIG, "batch arrays must not be NULL");
+    const uint32_t n_tab = b->table_layer_stride ? sh.n_layers : 1u;
+
+    uint64_t pairs = 0, prefix_refs = 0, tokens = 0;
+    for (uint32_t q = 0; q < b->n_seqs; q++) {
+        uint32_t len = b->seq_lens[q], pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
+        if (pre > len) return fail(TKV_ERR_INVALID_CONFIG, "sequence %u: prefix_len %u exceeds seq_len %u", q, pre, len);
+        if (pre % bs) return fail(TKV_ERR_INVALID_CONFIG, "sequence %u: prefix_len %u is not a multiple of block_size %u", q, pre, bs);
+        uint32_t nb = (len + bs - 1) / bs;
+        if (nb > b->table_stride)
+            return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (sequence %u needs more blocks than table_stride)",
+                        b->table_stride, nb, q);
+        pairs += nb - pre / bs;
+        prefix_refs += pre / bs;
+        tokens += len - pre;
+    }
+    if (pairs * n_tab > 0x7FFFFFFFull / (2ull * sh.n_layers))
+        return fail(TKV_ERR_INVALID_CONFIG, "batch too large: %llu block pairs", (unsigned long long)pairs);
+
+    const size_t L = sh.n_layers;
+    const size_t off_counter = 4 * L * sizeof(uint64_t);
+    const size_t off_work = (off_counter + 16 + 15) & ~(size_t)15;
+    const size_t off_prefix = off_work + (size_t)pairs * n_tab * sizeof(uint4);
+    const size_t need = off_prefix + (size_t)prefix_refs * sizeof(uint32_t) + 16;
+
+    p->image.assign(need, 0);
+    char* h = p->image.data();
+    uint64_t* ptrs = reinterpret_cast<uint64_t*>(h);
+    for (size_t l = 0; l < L; l++) {
+        ptrs[0 * L + l] = p->src_k[sh.src_layer_begin + l];
+        ptrs[1 * L + l] = p->src_v[sh.src_layer_begin + l];
+        ptrs[2 * L + l] = p->dst_k[sh.dst_layer_begin + l];
+        ptrs[3 * L + l] = p->dst_v[sh.dst_layer_begin + l];
+    }
+    memset(h + off_counter, 0, off_work - off_counter);
+
+    // destination blocks written by this call must be unique and must not be
+    // one of the call's own shared prefix blocks
+    const bool check_unique = !(p->flags & TKV_PLAN_ALLOW_SHARED_DST);
+    p->seen.assign(d.total_blocks, 0);
+    uint32_t* pre_ids = reinterpret_cast<uint32_t*>(h + off_prefix);
+    size_t np = 0;
+    for (uint32_t q = 0; q < b->n_seqs; q++) {
+        uint32_t pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
+        for (uint32_t i = 0; i < pre / bs; i++) {
+            uint32_t id = b->dst_tables[(size_t)q * b->table_stride + i];
+            if (id >= d.total_blocks)
+                return fail(TKV_ERR_INVALID_CONFIG, "sequence %u: prefix block id %u outside destination pool (%u blocks)", q, id, d.total_blocks);
+            p->seen[id] = 2;
+            pre_ids[np++] = id;
+        }
+    }
+    uint4* work = reinterpret_cast<uint4*>(h + off_work);
+    for (uint32_t t = 0; t < n_tab; t++) {
+        const size_t so = (size_t)(sh.src_layer_begin + t) * b->table_layer_stride;
+        const size_t dof = (size_t)(sh.dst_layer_begin + t) * b->table_layer_stride;
+        if (t > 0 && check_unique)
+            for (auto& x : p->seen) x &= 2;
+        size_t k = 0;
+        for (uint32_t q = 0; q < b->n_seqs; q++) {
+            uint32_t len = b->seq_lens[q], pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
+            uint32_t nb = (len + bs - 1) / bs;
+            for (uint32_t i = pre / bs; i < nb; i++) {
+                uint32_t sid = b->src_tables[so + (size_t)q * b->table_stride + i];
+                uint32_t did = b->dst_tables[dof + (size_t)q * b->table_stride + i];
+                if (sid >= s.total_blocks)
+                    return fail(TKV_ERR_INVALID_CONFIG, "sequence %u block %u: source id %u outside pool (%u blocks)", q, i, sid, s.total_blocks);
+                if (did >= d.total_blocks)
+                    return fail(TKV_ERR_INVALID_CONFIG, "sequence %u block %u: destination id %u outside pool (%u blocks)", q, i, did, d.total_blocks);
+                if (p->seen[did] == 2)
+                    return fail(TKV_ERR_INVALID_CONFIG, "sequence %u block %u: destination id %u is a shared prefix block of this batch", q, i, did);
+                if (check_unique) {
+                    if (p->seen[did])
+                        return fail(TKV_ERR_INVALID_CONFIG, "sequence %u block %u: destination id %u written twice in one batch", q, i, did);
+                    p->seen[did] = 1;
+                }
+                uint32_t valid = std::min(bs, len - i * bs);
+                work[(size_t)t * pairs + k++] = make_uint4(sid, did, valid, q);
+            }
+        }
+    }
+
+    p->off_work = off_work;
+    p->off_prefix = off_prefix;
+    p->used = need;
+    p->n_pairs = (uint32_t)pairs;
+    p->n_prefix = (uint32_t)prefix_refs;
+
+    // ---- everything above is pure host logic; CUDA starts here ----
+    if (s.device != d.device) {
+        int can = 0;
+        CU(cudaDeviceCanAccessPeer(&can, s.device, d.device));
+        if (!can) return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot store into device %d", s.device, d.device);
+    }
+    {
+        DeviceGuard g(s.device);
+        if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", s.device);
+        if (need > p->h_cap) {
+            size_t cap = std::max(need, p->h_cap * 2);
+            if (p->h_buf) cudaFreeHost(p->h_buf);
+            if (p->d_buf) cudaFree(p->d_buf);
+            p->h_buf = nullptr;
+            p->d_buf = nullptr;
+            p->h_cap = p->d_cap = 0;
+            CU(cudaMallocHost((void**)&p->h_buf, cap));
+            CU(cudaMalloc((void**)&p->d_buf, cap));
+            p->h_cap = p->d_cap = cap;
+        }
+        // one pinned copy, waited for, so the plan is ready when we return
+        memcpy(p->h_buf, p->image.data(), need);
+        cudaStream_t cs;
+        int32_t rc = copy_stream(s.device, &cs);
+        if (rc) return rc;
+        CU(cudaMemcpyAsync(p->d_buf, p->h_buf, need, cudaMemcpyHostToDevice, cs));
+        CU(cudaStreamSynchronize(cs));
+    }
+
+    // kernel arguments
+    tkv::HandoffArgs& a = p->args;
+    const uint32_t se = elem_size(s.dtype), de = elem_size(d.dtype);
+    const uint64_t* dp = reinterpret_cast<const uint64_t*>(p->d_buf);
+    a.work = reinterpret_cast<const uint4*>(p->d_buf + off_work);
+    a.src_k = dp + 0 * L;
+    a.src_v = dp + 1 * L;
+    a.dst_k = dp + 2 * L;
+    a.dst_v = dp + 3 * L;
+    a.dst_k_scales = reinterpret_cast<float*>(d.k_scales);
+    a.dst_v_scales = reinterpret_cast<float*>(d.v_scales);
+    a.done_counter = reinterpret_cast<uint32_t*>(p->d_buf + off_counter);
+    a.done_flag = nullptr;
+    a.src_block_stride = (uint64_t)bs * s.n_kv_heads * s.head_dim * se;
+    a.dst_block_stride = (uint64_t)bs * d.n_kv_heads * d.head_dim * de;
+    a.n_pairs = (uint32_t)pairs;
+    a.work_layer_stride = b->table_layer_stride ? (uint32_t)pairs : 0u;
+    a.n_layers = sh.n_layers;
+    a.n_heads = sh.n_heads;
+    a.head_dim = s.head_dim;
+    a.block_size = bs;
+    a.src_row_bytes = sh.n_heads * s.head_dim * se;
+    a.dst_row_bytes = sh.n_heads * s.head_dim * de;
+    a.src_row_stride = s.n_kv_heads * s.head_dim * se;
+    a.dst_row_stride = d.n_kv_heads * d.head_dim * de;
+    a.src_head_off = sh.src_head_begin * s.head_dim * se;
+    a.dst_head_off = sh.dst_head_begin * d.head_dim * de;
+    a.dst_total_blocks = d.total_blocks;
+    a.dst_pool_heads = d.n_kv_heads;
+    a.dst_head_begin = sh.dst_head_begin;
+    a.dst_layer_begin = sh.dst_layer_begin;
+    a.flag_value = 0;
+    a.contiguous = (a.src_row_bytes == a.src_row_stride && a.dst_row_bytes == a.dst_row_stride) ? 1u : 0u;
+
+    // widest vector that divides every offset and address involved
+    int vec = 16;
+    auto fits = [&](int v) {
+        if (a.src_row_bytes % v || a.src_row_stride % v || a.dst_row_stride % v || a.src_head_off % v || a.dst_head_off % v) return false;
+        if (a.src_block_stride % v || a.dst_block_stride % v) return false;
+        for (size_t l = 0; l < 4 * L; l++)
+            if (ptrs[l] % v) return false;
+        return true;
+    };
+    while (vec > 1 && !fits(vec)) vec >>= 1;
+    p->vec = vec;
+
+    TkvStats& st = p->stats;
+    st = TkvStats{};
+    st.n_blocks = pairs;
+    st.n_chunks = pairs * L * 2;
+    st.n_tokens = tokens;
+    st.n_prefix_refs = prefix_refs;
+    st.payload_bytes = tokens * L * 2ull * a.src_row_bytes;
+    st.bytes_read = st.payload_bytes;
+    st.bytes_written = tokens * L * 2ull * a.dst_row_bytes;
+    if (p->mode == MODE_F16_E4M3 && d.k_scales) st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
+    st.worklist_bytes = need;
+    st.peer = s.device != d.device;
+    return TKV_OK;
+}
+
+template <typename K> int32_t occupancy_grid(K kernel, int dev, uint64_t work_ctas, uint32_t* grid) {
+    DevInfo di;
+    int32_t rc = dev_info(dev, &di);
+    if (rc) return rc;
+    int per_sm = 0;
+    CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
+    if (per_sm < 1) per_sm = 1;
+    uint64_t g = (uint64_t)di.sm_count * per_sm;
+    *grid = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(g, work_ctas));
+    return TKV_OK;
+}
+
+template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, cudaStream_t st) {
+    uint32_t grid = 0;
+    int32_t rc = occupancy_grid(kernel, p->src.device, work_ctas, &grid);
+    if (rc) return rc;
+    p->grid = grid;
+    kernel<<<grid, 256, 0, st>>>(p->args);
+    CU(cudaGetLastError());
+    return TKV_OK;
+}
+
+template <bool HW, bool SCALED> int32_t launch_fp8(tkv_plan* p, cudaStream_t st) {
+    const tkv::HandoffArgs& a = p->args;
+    const uint64_t warps = (uint64_t)a.n_pairs * a.n_layers * 2 * a.n_heads;
+    const uint64_t ctas = (warps + 7) / 8;
+    const bool fast = p->vec == 16 && a.block_size == 16;
+    if (fast && a.head_dim == 128) {
+        p->variant = TKV_VARIANT_FP8_WARP;
+        return launch(tkv::handoff_f16_e4m3_warp<128, 16, HW, SCALED>, p, ctas, st);
+    }
+    if (fast && a.head_dim == 64) {
+        p->variant = TKV_VARIANT_FP8_WARP;
+        return launch(tkv::handoff_f16_e4m3_warp<64, 16, HW, SCALED>, p, ctas, st);
+    }
+    if (fast && a.head_dim == 256) {
+        p->variant = TKV_VARIANT_FP8_WARP;
+        return launch(tkv::handoff_f16_e4m3_warp<256, 16, HW, SCALED>, p, ctas, st);
+    }
+    p->variant = TKV_VARIANT_FP8_GENERIC;
+    return launch(tkv::handoff_f16_e4m3_generic<HW, SCALED>, p, ctas, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+void tkv_last_error(char* buf, size_t len) {
+    if (!buf || !len) return;
+    snprintf(buf, len, "%s", g_err.c_str());
+}
+int32_t tkv_last_cuda_error(void) { return g_cuda_err; }
+const char* tkv_version(void) { return "tkv 0.1 (sm_100a)"; }
+
+int32_t tkv_init(const int32_t* devices, int32_t n) {
+    if (n < 0 || (n > 0 && !devices)) return fail(TKV_ERR_INVALID_CONFIG, "bad device list");
+    int count = 0;
+    CU(cudaGetDeviceCount(&count));
+    for (int i = 0; i < n; i++)
+        if (devices[i] < 0 || devices[i] >= count)
+            return fail(TKV_ERR_INVALID_CONFIG, "device %d not present (%d devices)", devices[i], count);
+    int prev = 0;
+    CU(cudaGetDevice(&prev));
+    for (int i = 0; i < n; i++) {
+        for (int j = 0; j < n; j++) {
+            if (i == j || devices[i] == devices[j]) continue;
+            int can = 0;
+            CU(cudaDeviceCanAccessPeer(&can, devices[i], devices[j]));
+            if (!can) {
+                cudaSetDevice(prev);
+                return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot access device %d as a peer", devices[i], devices[j]);
+            }
+            CU(cudaSetDevice(devices[i]));
+            cudaError_t e = cudaDeviceEnablePeerAccess(devices[j], 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) {
+                cudaGetLastError();
+            } else if (e != cudaSuccess) {
+                cudaSetDevice(prev);
+                return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+            }
+        }
+    }
+    CU(cudaSetDevice(prev));
+    return TKV_OK;
+}
+
+int32_t tkv_shutdown(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int prev = 0;
+    cudaGetDevice(&prev);
+    for (int d = 0; d < 64; d++)
+        if (g_copy_stream[d]) {
+            cudaSetDevice(d);
+            cudaStreamDestroy(g_copy_stream[d]);
+            g_copy_stream[d] = nullptr;
+        }
+    cudaSetDevice(prev);
+    return TKV_OK;
+}
+
+int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch, const TkvShard* shard,
+                        uint32_t flags, tkv_plan** out) {
+    if (!src || !dst || !batch || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    *out = nullptr;
+    TkvShard sh;
+    if (shard) {
+        sh = *shard;
+    } else {
+        sh.src_head_begin = sh.dst_head_begin = 0;
+        sh.n_heads = std::min(src->n_kv_heads, dst->n_kv_heads);
+        sh.src_layer_begin = sh.dst_layer_begin = 0;
+        sh.n_layers = std::min(src->n_layers, dst->n_layers);
+    }
+    Mode mode;
+    int32_t rc = validate_pools(src, dst, sh, &mode);
+    if (rc) return rc;
+    if ((flags & TKV_PLAN_FORCE_VECTOR) && (flags & TKV_PLAN_FORCE_BULK))
+        return fail(TKV_ERR_INVALID_CONFIG, "FORCE_VECTOR and FORCE_BULK are exclusive");
+    tkv_plan* p = new tkv_plan();
+    p->src = *src;
+    p->dst = *dst;
+    p->src_k.assign(src->k_layer_ptrs, src->k_layer_ptrs + src->n_layers);
+    p->src_v.assign(src->v_layer_ptrs, src->v_layer_ptrs + src->n_layers);
+    p->dst_k.assign(dst->k_layer_ptrs, dst->k_layer_ptrs + dst->n_layers);
+    p->dst_v.assign(dst->v_layer_ptrs, dst->v_layer_ptrs + dst->n_layers);
+    p->src.k_layer_ptrs = p->src_k.data();
+    p->src.v_layer_ptrs = p->src_v.data();
+    p->dst.k_layer_ptrs = p->dst_k.data();
+    p->dst.v_layer_ptrs = p->dst_v.data();
+    p->shard = sh;
+    p->flags = flags;
+    p->mode = mode;
+    rc = build_worklist(p, batch);
+    if (rc) {
+        tkv_plan_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return TKV_OK;
+}
+
+int32_t tkv_plan_update(tkv_plan* p, const TkvBatch* batch) {
+    if (!p || !batch) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    return build_worklist(p, batch);
+}
+
+int32_t tkv_plan_destroy(tkv_plan* p) {
+    if (!p) return TKV_OK;
+    {
+        DeviceGuard g(p->src.device);
+        if (p->h_buf) cudaFreeHost(p->h_buf);
+        if (p->d_buf) cudaFree(p->d_buf);
+    }
+    delete p;
+    return TKV_OK;
+}
+
+int32_t tkv_plan_stats(const tkv_plan* p, TkvStats* out) {
+    if (!p || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    *out = p->stats;
+    out->grid = p->grid;
+    out->block = 256;
+    out->kernel_variant = p->variant;
+    return TKV_OK;
+}
+
+int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint32_t flag_value) {
+    if (!p) return fail(TKV_ERR_INVALID_CONFIG, "NULL plan");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceGuard g(p->src.device);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    tkv::HandoffArgs& a = p->args;
+    a.done_flag = reinterpret_cast<uint32_t*>(done_flag);
+    a.flag_value = flag_value;
+    const uint64_t chunks = (uint64_t)a.n_pairs * a.n_layers * 2;
+    if (chunks == 0) {
+        // nothing moves; still publish the flag, in stream order
+        if (done_flag) CU(cudaMemcpyAsync(reinterpret_cast<void*>(done_flag), &a.flag_value, 4, cudaMemcpyHostToDevice, st));
+        p->grid = 0;
+        return TKV_OK;
+    }
+    switch (p->mode) {
+        case MODE_COPY:
+            p->variant = TKV_VARIANT_VECTOR;
+            switch (p->vec) {
+                case 16: return launch(tkv::handoff_copy_vec<16, 8>, p, chunks, st);
+                case 8: return launch(tkv::handoff_copy_vec<8, 8>, p, chunks, st);
+                case 4: return launch(tkv::handoff_copy_vec<4, 8>, p, chunks, st);
+                case 2: return launch(tkv::handoff_copy_vec<2, 8>, p, chunks, st);
+                default: return launch(tkv::handoff_copy_vec<1, 8>, p, chunks, st);
+            }
+        case MODE_F16_E4M3: {
+            const bool hw = !(p->flags & TKV_PLAN_INT_QUANTIZER);
+            const bool scaled = p->dst.k_scales != 0;
+            if (hw) return scaled ? launch_fp8<true, true>(p, st) : launch_fp8<true, false>(p, st);
+            return scaled ? launch_fp8<false, true>(p, st) : launch_fp8<false, false>(p, st);
+        }
+        case MODE_F32_F16:
+            p->variant = TKV_VARIANT_CAST_GENERIC;
+            return launch(tkv::handoff_f32_cast_generic<0>, p, chunks, st);
+        case MODE_F32_E4M3:
+            p->variant = TKV_VARIANT_CAST_GENERIC;
+            return launch(tkv::handoff_f32_cast_generic<1>, p, chunks, st);
+    }
+    return fail(TKV_ERR_INVALID_CONFIG, "unreachable mode");
+}
+
+int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uint64_t timeout_us) {
+    if (!flag) return fail(TKV_ERR_INVALID_CONFIG, "NULL flag");
+    DeviceGuard g(device);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", device);
+    cudaStream_t cs;
+    int32_t rc = copy_stream(device, &cs);
+    if (rc) return rc;
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        uint32_t v = 0;
+        CU(cudaMemcpyAsync(&v, reinterpret_cast<const void*>(flag), 4, cudaMemcpyDeviceToHost, cs));
+        CU(cudaStreamSynchronize(cs));
+        if (v == expected) return TKV_OK;
+        auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        if ((uint64_t)us >= timeout_us)
+            return fail(TKV_ERR_TIMEOUT, "flag still %u after %llu us (expected %u)", v, (unsigned long long)timeout_us, expected);
+        std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+}
+
+int32_t tkv_flag_wait_enqueue(void* stream, uint64_t flag, uint32_t expected, uint64_t max_spins, uint64_t status) {
+    if (!flag) return fail(TKV_ERR_INVALID_CONFIG, "NULL flag");
+    if (max_spins == 0 || max_spins > (1ull << 26))
+        return fail(TKV_ERR_INVALID_CONFIG, "max_spins must be in [1, 2^26] so the wait stays bounded");
+    tkv::flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint32_t*>(flag), expected,
+                                                                          (unsigned long long)max_spins,
+                                                                          reinterpret_cast<uint32_t*>(status));
+    CU(cudaGetLastError());
+    return TKV_OK;
+}
+
+int32_t tkv_refcount_apply(tkv_plan* p, int32_t delta, void* stream) {
+    if (!p) return fail(TKV_ERR_INVALID_CONFIG, "NULL plan");
+    if (delta == 0 || p->n_prefix == 0) return TKV_OK;
+    if (!p->dst.refcounts) return fail(TKV_ERR_INVALID_CONFIG, "destination pool has no refcount array");
+    DeviceGuard g(p->src.device);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    uint32_t blocks = std::min<uint32_t>((p->n_prefix + 255) / 256, 1024);
+    tkv::refcount_apply_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<uint32_t*>(p->dst.refcounts), reinterpret_cast<const uint32_t*>(p->d_buf + p->off_prefix),
+        p->n_prefix, delta);
+    CU(cudaGetLastError());
+    return TKV_OK;
+}
+
+int32_t tkv_pairing_make(int32_t n_gpus, uint32_t n_layers, uint32_t n_kv_heads, TkvPairing* out, int32_t cap,
+                         int32_t* n_pairs) {
+    if (!out || !n_pairs) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (n_gpus < 1 || (n_gpus > 1 && (n_gpus & 1))) return fail(TKV_ERR_INVALID_CONFIG, "n_gpus must be 1 or even, got %d", n_gpus);
+    if (n_layers == 0 || n_kv_heads == 0) return fail(TKV_ERR_INVALID_CONFIG, "zero-sized model");
+    const uint32_t P = n_gpus == 1 ? 1u : (uint32_t)n_gpus / 2u;
+    if ((int32_t)P > cap) return fail(TKV_ERR_INVALID_CONFIG, "output holds %d pairings, need %u", cap, P);
+    const bool by_head = n_kv_heads >= P;
+    if (by_head && n_kv_heads % P) return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (kv heads not divisible by pairs)", P, n_kv_heads);
+    if (!by_head && n_layers < P) return fail(TKV_ERR_INVALID_CONFIG, "neither %u heads nor %u layers cover %u pairs", n_kv_heads, n_layers, P);
+    for (uint32_t i = 0; i < P; i++) {
+        TkvPairing& pr = out[i];
+        pr.prefill_device = (int32_t)i;
+        pr.decode_device = n_gpus == 1 ? 0 : (int32_t)(i + P);
+        if (by_head) {
+            uint32_t per = n_kv_heads / P;
+            pr.shard = TkvShard{i * per, i * per, per, 0, 0, n_layers};
+        } else {
+            uint32_t lo = (uint32_t)((uint64_t)n_layers * i / P), hi = (uint32_t)((uint64_t)n_layers * (i + 1) / P);
+            pr.shard = TkvShard{0, 0, n_kv_heads, lo, lo, hi - lo};
+        }
+    }
+    *n_pairs = (int32_t)P;
+    return TKV_OK;
+}
+
+int32_t tkv_cast(uint64_t src, int32_t sdt, uint64_t dst, int32_t ddt, uint64_t n, void* stream) {
+    if (n == 0) return TKV_OK;
+    if (!src || !dst) return fail(TKV_ERR_INVALID_CONFIG, "NULL buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const void* s = reinterpret_cast<const void*>(src);
+    void* d = reinterpret_cast<void*>(dst);
+    uint32_t grid = (uint32_t)std::min<uint64_t>((n + 255) / 256, 148ull * 16);
+#define TKV_CAST(S, D)                                            \
+    if (sdt == S && ddt == D) {                                   \
+        tkv::cast_kernel<S, D><<<grid, 256, 0, st>>>(s, d, n);    \
+        CU(cudaGetLastError());                                   \
+        return TKV_OK;                                            \
+    }
+    TKV_CAST(0, 1) TKV_CAST(1, 0) TKV_CAST(0, 2) TKV_CAST(2, 0) TKV_CAST(1, 2) TKV_CAST(2, 1)
+#undef TKV_CAST
+    return fail(TKV_ERR_INVALID_CONFIG, "unsupported cast %d -> %d", sdt, ddt);
+}
+
+int32_t tkv_selfcheck_e4m3(uint32_t skip_bits, uint64_t* mismatches) {
+    if (!mismatches || skip_bits > 24) return fail(TKV_ERR_INVALID_CONFIG, "bad argument");
+    unsigned long long* d = nullptr;
+    CU(cudaMalloc((void**)&d, 8));
+    CU(cudaMemset(d, 0, 8));
+    tkv::selfcheck_e4m3_kernel<<<148 * 8, 256>>>(skip_bits, d);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpy(mismatches, d, 8, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) return cuda_fail(e, "selfcheck");
+    return TKV_OK;
+}
+
+int32_t tkv_bits_checksum(uint64_t data, int32_t dtype, uint64_t n, void* stream, uint64_t* out) {
+    if (!out || (!data && n)) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned long long* d = nullptr;
+    CU(cudaMalloc((void**)&d, 8));
+    cudaError_t e = cudaMemsetAsync(d, 0, 8, st);
+    if (e == cudaSuccess && n) {
+        uint32_t grid = (uint32_t)std::min<uint64_t>((n + 255) / 256, 148ull * 16);
+        const void* p = reinterpret_cast<const void*>(data);
+        if (dtype == TKV_DTYPE_F32) tkv::bits_checksum_kernel<0><<<grid, 256, 0, st>>>(p, n, d);
+        else if (dtype == TKV_DTYPE_F16) tkv::bits_checksum_kernel<1><<<grid, 256, 0, st>>>(p, n, d);
+        else if (dtype == TKV_DTYPE_E4M3) tkv::bits_checksum_kernel<2><<<grid, 256, 0, st>>>(p, n, d);
+        else {
+            cudaFree(d);
+            return fail(TKV_ERR_INVALID_CONFIG, "unknown dtype %d", dtype);
+        }
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, d, 8, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d);
+    if (e != cudaSuccess) return cuda_fail(e, "bits checksum");
+    return TKV_OK;
+}
+
+int32_t tkv_ipc_export(uint64_t devptr, uint8_t handle[64], uint64_t* offset) {
+    if (!devptr || !handle || !offset) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "ipc handle size");
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(devptr)));
+    memcpy(handle, &h, 64);
+    // The handle names the whole allocation; report where devptr sits inside it.
+    // cuMemGetAddressRange has no runtime-API twin, so fetch it from the driver.
+    typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    CU(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr));
+    if (!fn) return fail(TKV_ERR_CUDA, "cuMemGetAddressRange not found");
+    unsigned long long base = 0;
+    size_t size = 0;
+    int r = reinterpret_cast<range_fn>(fn)(&base, &size, (unsigned long long)devptr);
+    if (r != 0) return fail(TKV_ERR_CUDA, "cuMemGetAddressRange failed (%d)", r);
+    *offset = devptr - (uint64_t)base;
+    return TKV_OK;
+}
+
+int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset, uint64_t* devptr) {
+    if (!handle || !devptr) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void* base = nullptr;
+    CU(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    *devptr = reinterpret_cast<uint64_t>(base) + offset;
+    return TKV_OK;
+}
+
+int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset) {
+    if (!devptr) return TKV_OK;
+    CU(cudaIpcCloseMemHandle(reinterpret_cast<void*>(devptr - offset)));
+    return TKV_OK;
+}
+
+}  // extern "C"

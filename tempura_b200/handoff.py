@@ -1,0 +1,246 @@
+"""Python face of the KV handoff C ABI.
+
+Thin by design: torch supplies device memory and streams, everything that moves KV
+bytes goes through ``libtkv.so``.  Names follow the reference's domain: pools of
+paged blocks, block tables, shards, prefill and decode sides
+(engine/src/kv_cache.rs, engine/src/cutile_kv_cache.rs, engine/src/disaggregated.rs
+in the tempura repository).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _native as N
+from ._native import TkvError, check, lib
+
+_ELEM = {N.DTYPE_F32: 4, N.DTYPE_F16: 2, N.DTYPE_E4M3: 1}
+_TORCH_VIEW = {N.DTYPE_F32: torch.float32, N.DTYPE_F16: torch.float16, N.DTYPE_E4M3: torch.uint8}
+KvDtype = {"f32": N.DTYPE_F32, "f16": N.DTYPE_F16, "e4m3": N.DTYPE_E4M3}
+
+
+def _u32(x) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(x, dtype=np.uint32))
+
+
+def init(devices: Sequence[int]) -> None:
+    """Enable peer access between the listed devices (once per process)."""
+    arr = (C.c_int32 * len(devices))(*devices)
+    check(lib().tkv_init(arr, len(devices)))
+
+
+@dataclass
+class Pool:
+    """A paged KV pool on one device: per layer one K and one V tensor laid out
+    ``[block][token_in_block][kv_head][head_dim]`` (GpuKvPagePool,
+    engine/src/cutile_kv_cache.rs:1584-1602)."""
+    device: int
+    dtype: int
+    n_layers: int
+    n_kv_heads: int
+    head_dim: int
+    block_size: int
+    total_blocks: int
+    k_ptrs: np.ndarray
+    v_ptrs: np.ndarray
+    k_scales_ptr: int = 0
+    v_scales_ptr: int = 0
+    refcounts_ptr: int = 0
+    # tensors that own the memory (None when built from foreign pointers)
+    storage: Optional[torch.Tensor] = None
+    k: List[torch.Tensor] = field(default_factory=list)
+    v: List[torch.Tensor] = field(default_factory=list)
+    k_scales: Optional[torch.Tensor] = None
+    v_scales: Optional[torch.Tensor] = None
+    refcounts: Optional[torch.Tensor] = None
+
+    @property
+    def elem_size(self) -> int:
+        return _ELEM[self.dtype]
+
+    @property
+    def layer_bytes(self) -> int:
+        return self.total_blocks * self.block_size * self.n_kv_heads * self.head_dim * self.elem_size
+
+    @staticmethod
+    def allocate(device: int, n_layers: int, n_kv_heads: int, head_dim: int, block_size: int,
+                 total_blocks: int, dtype: str = "f16", scales: bool = False, refcounts: bool = False,
+                 fill_byte: Optional[int] = 0xA5) -> "Pool":
+        """One flat allocation carved into 2*n_layers layer tensors (so a decode
+        process can export the whole pool with a single IPC handle)."""
+        dt = KvDtype[dtype]
+        dev = torch.device("cuda", device)
+        layer_bytes = total_blocks * block_size * n_kv_heads * head_dim * _ELEM[dt]
+        pad = (-layer_bytes) % 256
+        stride = layer_bytes + pad
+        storage = torch.empty(2 * n_layers * stride, dtype=torch.uint8, device=dev)
+        if fill_byte is not None:
+            storage.fill_(fill_byte)
+        k, v = [], []
+        for l in range(n_layers):
+            k.append(storage[(2 * l) * stride:(2 * l) * stride + layer_bytes].view(_TORCH_VIEW[dt]))
+            v.append(storage[(2 * l + 1) * stride:(2 * l + 1) * stride + layer_bytes].view(_TORCH_VIEW[dt]))
+        pool = Pool(device, dt, n_layers, n_kv_heads, head_dim, block_size, total_blocks,
+                    np.array([t.data_ptr() for t in k], dtype=np.uint64),
+                    np.array([t.data_ptr() for t in v], dtype=np.uint64),
+                    storage=storage, k=k, v=v)
+        if scales:
+            pool.k_scales = torch.full((n_layers, total_blocks, n_kv_heads), -123.0, dtype=torch.float32, device=dev)
+            pool.v_scales = torch.full((n_layers, total_blocks, n_kv_heads), -123.0, dtype=torch.float32, device=dev)
+            pool.k_scales_ptr, pool.v_scales_ptr = pool.k_scales.data_ptr(), pool.v_scales.data_ptr()
+        if refcounts:
+            pool.refcounts = torch.zeros(total_blocks, dtype=torch.int32, device=dev)
+            pool.refcounts_ptr = pool.refcounts.data_ptr()
+        return pool
+
+    @staticmethod
+    def from_pointers(device: int, dtype: str, n_kv_heads: int, head_dim: int, block_size: int,
+                      total_blocks: int, k_ptrs: Sequence[int], v_ptrs: Sequence[int],
+                      k_scales_ptr: int = 0, v_scales_ptr: int = 0, refcounts_ptr: int = 0) -> "Pool":
+        """Describe memory owned elsewhere (another process's pool mapped through IPC,
+        or an engine's own tensors)."""
+        return Pool(device, KvDtype[dtype], len(k_ptrs), n_kv_heads, head_dim, block_size, total_blocks,
+                    np.array(list(k_ptrs), dtype=np.uint64), np.array(list(v_ptrs), dtype=np.uint64),
+                    k_scales_ptr, v_scales_ptr, refcounts_ptr)
+
+    def blocks(self, layer: int, is_v: bool = False) -> torch.Tensor:
+        """[total_blocks, block_size, n_kv_heads, head_dim] view of one layer."""
+        t = (self.v if is_v else self.k)[layer]
+        return t.view(self.total_blocks, self.block_size, self.n_kv_heads, self.head_dim)
+
+    def c_struct(self) -> N.TkvPool:
+        s = N.TkvPool(self.device, self.dtype, self.n_layers, self.n_kv_heads, self.head_dim,
+                      self.block_size, self.total_blocks, 0,
+                      self.k_ptrs.ctypes.data_as(C.POINTER(C.c_uint64)),
+                      self.v_ptrs.ctypes.data_as(C.POINTER(C.c_uint64)),
+                      self.k_scales_ptr, self.v_scales_ptr, self.refcounts_ptr)
+        s._keep = (self.k_ptrs, self.v_ptrs)
+        return s
+
+
+@dataclass
+class Batch:
+    """Block tables and lengths of the prompts that finished prefill."""
+    seq_lens: np.ndarray
+    src_tables: np.ndarray
+    dst_tables: np.ndarray
+    table_stride: int
+    prefix_lens: Optional[np.ndarray] = None
+    table_layer_stride: int = 0
+
+    def __post_init__(self):
+        self.seq_lens = _u32(self.seq_lens)
+        self.src_tables = _u32(self.src_tables).reshape(-1)
+        self.dst_tables = _u32(self.dst_tables).reshape(-1)
+        if self.prefix_lens is not None:
+            self.prefix_lens = _u32(self.prefix_lens)
+
+    def c_struct(self) -> N.TkvBatch:
+        p = C.POINTER(C.c_uint32)
+        s = N.TkvBatch(len(self.seq_lens), self.table_stride, self.table_layer_stride, 0,
+                       self.seq_lens.ctypes.data_as(p),
+                       self.prefix_lens.ctypes.data_as(p) if self.prefix_lens is not None else None,
+                       self.src_tables.ctypes.data_as(p), self.dst_tables.ctypes.data_as(p))
+        s._keep = self
+        return s
+
+
+def Shard(src_head_begin=0, dst_head_begin=0, n_heads=0, src_layer_begin=0, dst_layer_begin=0, n_layers=0) -> N.TkvShard:
+    return N.TkvShard(src_head_begin, dst_head_begin, n_heads, src_layer_begin, dst_layer_begin, n_layers)
+
+
+class Plan:
+    """A validated, uploaded work list binding one batch to a source and a destination
+    pool.  ``enqueue`` is asynchronous on a stream of the source device."""
+
+    def __init__(self, src: Pool, dst: Pool, batch: Batch, shard: Optional[N.TkvShard] = None, flags: int = 0):
+        self.src, self.dst = src, dst
+        self._s, self._d = src.c_struct(), dst.c_struct()
+        self._h = C.c_void_p()
+        b = batch.c_struct()
+        check(lib().tkv_plan_create(C.byref(self._s), C.byref(self._d), C.byref(b),
+                                    C.byref(shard) if shard is not None else None, flags, C.byref(self._h)))
+
+    def update(self, batch: Batch) -> None:
+        b = batch.c_struct()
+        check(lib().tkv_plan_update(self._h, C.byref(b)))
+
+    def enqueue(self, stream: Optional[torch.cuda.Stream] = None, done_flag: int = 0, flag_value: int = 0) -> None:
+        if stream is None:
+            stream = torch.cuda.current_stream(self.src.device)
+        check(lib().tkv_handoff_enqueue(self._h, C.c_void_p(stream.cuda_stream), done_flag, flag_value))
+
+    def refcount_apply(self, delta: int, stream: Optional[torch.cuda.Stream] = None) -> None:
+        if stream is None:
+            stream = torch.cuda.current_stream(self.src.device)
+        check(lib().tkv_refcount_apply(self._h, delta, C.c_void_p(stream.cuda_stream)))
+
+    def stats(self) -> N.TkvStats:
+        st = N.TkvStats()
+        check(lib().tkv_plan_stats(self._h, C.byref(st)))
+        return st
+
+    def destroy(self) -> None:
+        if self._h:
+            lib().tkv_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def pairing_make(n_gpus: int, n_layers: int, n_kv_heads: int) -> List[N.TkvPairing]:
+    out = (N.TkvPairing * 8)()
+    n = C.c_int32(0)
+    check(lib().tkv_pairing_make(n_gpus, n_layers, n_kv_heads, out, 8, C.byref(n)))
+    return [out[i] for i in range(n.value)]
+
+
+def flag_wait_host(device: int, flag_ptr: int, expected: int, timeout_us: int) -> None:
+    check(lib().tkv_flag_wait_host(device, flag_ptr, expected, timeout_us))
+
+
+def flag_wait_enqueue(stream: torch.cuda.Stream, flag_ptr: int, expected: int, max_spins: int, status_ptr: int) -> None:
+    check(lib().tkv_flag_wait_enqueue(C.c_void_p(stream.cuda_stream), flag_ptr, expected, max_spins, status_ptr))
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor, src_dtype: str, dst_dtype: str) -> None:
+    n = src.numel()
+    assert dst.numel() == n and src.is_cuda and dst.is_cuda
+    st = torch.cuda.current_stream(src.device)
+    check(lib().tkv_cast(src.data_ptr(), KvDtype[src_dtype], dst.data_ptr(), KvDtype[dst_dtype], n,
+                         C.c_void_p(st.cuda_stream)))
+
+
+def bits_checksum(t: torch.Tensor, dtype: str) -> int:
+    out = C.c_uint64(0)
+    st = torch.cuda.current_stream(t.device)
+    check(lib().tkv_bits_checksum(t.data_ptr(), KvDtype[dtype], t.numel(), C.c_void_p(st.cuda_stream), C.byref(out)))
+    return out.value
+
+
+def selfcheck_e4m3(skip_bits: int = 0) -> int:
+    out = C.c_uint64(0)
+    check(lib().tkv_selfcheck_e4m3(skip_bits, C.byref(out)))
+    return out.value
+
+
+def ipc_export(ptr: int):
+    h = (C.c_uint8 * 64)()
+    off = C.c_uint64(0)
+    check(lib().tkv_ipc_export(ptr, h, C.byref(off)))
+    return bytes(h), off.value
+
+
+def ipc_import(handle: bytes, offset: int) -> int:
+    h = (C.c_uint8 * 64)(*handle)
+    out = C.c_uint64(0)
+    check(lib().tkv_ipc_import(h, offset, C.byref(out)))
+    return out.value

@@ -1,0 +1,98 @@
+"""Argument validation of tkv_plan_create runs before any CUDA call, so it is
+checked here without a GPU.  Error classes follow the reference's KernelError
+(kernel-api/src/lib.rs:5-13)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tempura_b200 import _build, _native as N
+from tempura_b200 import handoff as H
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    _build.build()
+
+
+def fake_pool(layers=2, heads=4, dim=16, bs=4, blocks=32, dtype="f16", scales=False):
+    # addresses are never dereferenced: validation fails first
+    base = 0x10000000
+    k = [base + 0x100000 * (2 * l) for l in range(layers)]
+    v = [base + 0x100000 * (2 * l + 1) for l in range(layers)]
+    return H.Pool.from_pointers(0, dtype, heads, dim, bs, blocks, k, v,
+                                k_scales_ptr=0x7000000 if scales else 0, v_scales_ptr=0x7100000 if scales else 0)
+
+
+def batch(seq_lens, src, dst, stride, prefix=None):
+    return H.Batch(np.array(seq_lens), np.array(src), np.array(dst), stride, None if prefix is None else np.array(prefix))
+
+
+def expect(code, fn):
+    with pytest.raises(N.TkvError) as e:
+        fn()
+    assert e.value.code == code, e.value
+    return e.value.message
+
+
+def test_dimension_mismatch_head_dim_and_block_size():
+    b = batch([4], [[0]], [[0]], 1)
+    msg = expect(N.ERR_DIMENSION_MISMATCH, lambda: H.Plan(fake_pool(dim=16), fake_pool(dim=32), b))
+    assert "expected 16, got 32" in msg
+    expect(N.ERR_DIMENSION_MISMATCH, lambda: H.Plan(fake_pool(bs=4), fake_pool(bs=8), b))
+
+
+def test_unsupported_dtype_pair_and_half_set_scales():
+    b = batch([4], [[0]], [[0]], 1)
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(dtype="e4m3"), fake_pool(dtype="f16"), b))
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(dtype="f16"), fake_pool(dtype="f32"), b))
+    p = fake_pool(dtype="e4m3", scales=True)
+    p.v_scales_ptr = 0
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), p, b))
+
+
+def test_shard_out_of_range():
+    b = batch([4], [[0]], [[0]], 1)
+    expect(N.ERR_DIMENSION_MISMATCH, lambda: H.Plan(fake_pool(), fake_pool(), b, H.Shard(2, 0, 3, 0, 0, 2)))
+    expect(N.ERR_DIMENSION_MISMATCH, lambda: H.Plan(fake_pool(), fake_pool(), b, H.Shard(0, 0, 4, 1, 0, 2)))
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), b, H.Shard(0, 0, 0, 0, 0, 2)))
+
+
+def test_table_too_short_and_ids_out_of_pool():
+    expect(N.ERR_DIMENSION_MISMATCH, lambda: H.Plan(fake_pool(), fake_pool(), batch([9], [[0, 1]], [[0, 1]], 2)))
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), batch([8], [[0, 32]], [[0, 1]], 2)))
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), batch([8], [[0, 1]], [[0, 0xFFFFFFFF]], 2)))
+
+
+def test_prefix_rules():
+    # prefix longer than the sequence, and not block-aligned
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), batch([4], [[0, 1]], [[0, 1]], 2, [8])))
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), batch([8], [[0, 1]], [[0, 1]], 2, [3])))
+    # a moved block may not land on one of the batch's shared prefix blocks
+    msg = expect(N.ERR_INVALID_CONFIG,
+                 lambda: H.Plan(fake_pool(), fake_pool(), batch([8, 8], [[0, 1], [2, 3]], [[5, 6], [5, 5]], 2, [4, 4])))
+    assert "shared prefix block" in msg
+
+
+def test_duplicate_destination_rejected_unless_allowed():
+    b = batch([4, 4], [[0], [1]], [[7], [7]], 1)
+    msg = expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), b))
+    assert "written twice" in msg
+    # with the flag the duplicate passes validation; the next failure is CUDA (no device here)
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = False
+    if not has_gpu:
+        expect(N.ERR_CUDA, lambda: H.Plan(fake_pool(), fake_pool(), b, flags=N.PLAN_ALLOW_SHARED_DST))
+
+
+def test_null_arguments():
+    L = N.lib()
+    out = C.c_void_p()
+    assert L.tkv_plan_create(None, None, None, None, 0, C.byref(out)) == N.ERR_INVALID_CONFIG
+    assert L.tkv_plan_destroy(None) == 0
+    assert L.tkv_handoff_enqueue(None, None, 0, 0) == N.ERR_INVALID_CONFIG
+    assert L.tkv_flag_wait_enqueue(None, 0, 0, 10, 0) == N.ERR_INVALID_CONFIG
+    assert L.tkv_flag_wait_enqueue(None, 0x1000, 0, 0, 0) == N.ERR_INVALID_CONFIG   # unbounded wait refused
