@@ -382,10 +382,15 @@ static void handoff_unit(const orc_pool* s, const orc_pool* d, const orc_batch* 
                         uint16_t a = hsrc[(size_t)(t - pre) * row + (size_t)h * D + i] & 0x7FFFu;
                         if (a > amax) amax = a;
                     }
-                float inv;
-                float scale = orc_block_scale(amax, &inv);
-                scales[((size_t)dl * d->total_blocks + dt[blk]) * d->n_kv_heads +
-                       sh->dst_head_begin + h] = scale;
+                /* A pool without scale arrays stores raw e4m3 bytes, as the reference's own
+                 * pools do (engine/src/cutile_kv_cache.rs:1593-1595; element rule as the
+                 * e4m3 row writer, kernels/src/kv_scatter_write.rs:172-273).               */
+                float inv = 1.0f;
+                if (scales) {
+                    float scale = orc_block_scale(amax, &inv);
+                    scales[((size_t)dl * d->total_blocks + dt[blk]) * d->n_kv_heads +
+                           sh->dst_head_begin + h] = scale;
+                }
                 for (uint32_t t = t0; t < t1; t++) {
                     size_t off = orc_paged_row_offset(dt, bs, d_stride, t, sh->dst_head_begin + h, D);
                     uint8_t* o = (uint8_t*)dp + off;
@@ -403,7 +408,7 @@ static int handoff_run(const orc_pool* s, const orc_pool* d, const orc_batch* b,
     int rc = check_args(s, d, b, sh);
     if (rc) return rc;
     if (mode == MODE_COPY && s->elem_size != d->elem_size) return -8;
-    if (mode == MODE_F16_E4M3 && (s->elem_size != 2 || d->elem_size != 1 || !d->k_scales || !d->v_scales))
+    if (mode == MODE_F16_E4M3 && (s->elem_size != 2 || d->elem_size != 1 || (!d->k_scales != !d->v_scales)))
         return -8;
     if (mode == MODE_F32_F16 && (s->elem_size != 4 || d->elem_size != 2)) return -8;
     const long units = (long)b->n_seqs * sh->n_layers * 2;

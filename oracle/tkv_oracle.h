@@ -125,7 +125,8 @@ typedef struct {
  * negative code for an invalid argument.                                    */
 int orc_handoff_copy(const orc_pool* src, const orc_pool* dst, const orc_batch* batch,
                      const orc_shard* shard, int n_threads);
-/* F16 source, E4M3 destination with per-(layer, kv-head, block) scales.      */
+/* F16 source, E4M3 destination with per-(layer, kv-head, block) scales; a
+ * destination without scale arrays receives unscaled e4m3 bytes.             */
 int orc_handoff_f16_to_e4m3(const orc_pool* src, const orc_pool* dst, const orc_batch* batch,
                             const orc_shard* shard, int n_threads);
 /* F32 source, F16 destination (from_transfer into a use_f16 cache).          */

@@ -104,7 +104,8 @@ def test_config3_fp8_special_blocks(H):
         plan.enqueue()
         torch.cuda.synchronize()
         assert_pool_equals_host(dd, hd, f"special flags={flags}")
-    assert hd.k_scales[0, t[0], 0] == 1.0 and hd.k_scales[0, t[1], 2] == 1.0 and hd.k_scales[0, t[2], 1] == 1.0
+    d = w.dst_tables[0]
+    assert hd.k_scales[0, d[0], 0] == 1.0 and hd.k_scales[0, d[1], 2] == 1.0 and hd.k_scales[0, d[2], 1] == 1.0
 
 
 def test_fp8_unscaled_destination(H):
