@@ -159,6 +159,32 @@ int32_t tkv_plan_stats(const tkv_plan* plan, TkvStats* out);
  * Launch convention follows kernels/src/kv_scatter_write.rs:822-861.          */
 int32_t tkv_handoff_enqueue(tkv_plan* plan, void* stream, uint64_t done_flag, uint32_t flag_value);
 
+/* No counterpart in the reference.  A same-dtype handoff (gather through the source
+ * tables, store into the destination pool) for callers that must not allocate device
+ * memory at handoff time: an engine whose KV pools already own nearly all of HBM, so a
+ * late cudaMalloc can fail; a serving loop that cannot afford the device-wide stall a
+ * cudaMalloc/cudaFree causes while other streams are decoding; a host that hands this
+ * library a fixed memory budget.  Instead of a plan's device buffer, the layer
+ * pointers and the work list live in ONE fixed array compiled into the library
+ * (TKV_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads it, held until
+ * the process exits).  The call validates exactly like tkv_plan_create, copies the
+ * work list into that array on `stream` and launches the copy kernel behind it; it
+ * calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Limits: at most TKV_NOALLOC_MAX_BLOCK_PAIRS (source block, destination block)
+ *     pairs and TKV_NOALLOC_MAX_LAYERS layers per call; more is refused with
+ *     TKV_ERR_INVALID_CONFIG and nothing is launched.
+ *   - The first call on a device looks up the array's device address; make that call
+ *     before any stream capture begins on that device.
+ *   - Every call on a device shares the array and overwrites the previous call's
+ *     contents: calls whose GPU work may overlap (different streams, or different
+ *     threads) race on it.  Order them on one stream or with events.
+ *   - `stream` belongs to the SOURCE pool's device.                              */
+#define TKV_NOALLOC_MAX_BLOCK_PAIRS 16384u
+#define TKV_NOALLOC_MAX_LAYERS 128u
+#define TKV_NOALLOC_SCRATCH_BYTES (4u * TKV_NOALLOC_MAX_LAYERS * 8u + 256u + TKV_NOALLOC_MAX_BLOCK_PAIRS * 16u)
+int32_t tkv_handoff_noalloc(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch,
+                            const TkvShard* shard /* NULL = everything */, void* stream);
+
 /* Bounded waits on a completion flag (uint32_t in device memory of the
  * waiting side).  Host form polls with small device->host copies; device form
  * enqueues a one-thread kernel that spins at most max_spins times and records

@@ -73,6 +73,7 @@ SIGNATURES = {
     "tkv_plan_destroy": (_i32, [_vp]),
     "tkv_plan_stats": (_i32, [_vp, C.POINTER(TkvStats)]),
     "tkv_handoff_enqueue": (_i32, [_vp, _vp, _u64, _u32]),
+    "tkv_handoff_noalloc": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _vp]),
     "tkv_flag_wait_host": (_i32, [_i32, _u64, _u32, _u64]),
     "tkv_flag_wait_enqueue": (_i32, [_vp, _u64, _u32, _u64, _u64]),
     "tkv_refcount_apply": (_i32, [_vp, _i32, _vp]),

@@ -346,6 +346,9 @@ __global__ void __launch_bounds__(256) handoff_f32_cast_generic(const HandoffArg
     signal_done(a);
 }
 
+// Non-template kernels have one definition per program: a second translation unit that
+// only needs the templates above defines TKV_KERNELS_TEMPLATES_ONLY before including.
+#ifndef TKV_KERNELS_TEMPLATES_ONLY
 // ---------------------------------------------------------------------------------
 // small kernels
 // ---------------------------------------------------------------------------------
@@ -427,5 +430,7 @@ __global__ void bits_checksum_kernel(const void* __restrict__ data, uint64_t n, 
     for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xFFFFFFFFu, s, o);
     if ((threadIdx.x & 31) == 0 && s) atomicAdd(out, s);
 }
+
+#endif  // TKV_KERNELS_TEMPLATES_ONLY
 
 }  // namespace tkv

@@ -86,6 +86,15 @@ int32_t copy_stream(int dev, cudaStream_t* out) {
 
 }  // namespace
 
+// Lets other translation units of this library report through tkv_last_error().
+namespace tkv_internal {
+int32_t set_error(int32_t code, int32_t cuda_code, const char* text) {
+    g_err = text ? text : "";
+    if (cuda_code) g_cuda_err = cuda_code;
+    return code;
+}
+}  // namespace tkv_internal
+
 struct tkv_plan {
     TkvPool src{}, dst{};
     std::vector<uint64_t> src_k, src_v, dst_k, dst_v;  // owned copies of the layer pointers

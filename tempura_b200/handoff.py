@@ -196,6 +196,21 @@ class Plan:
             pass
 
 
+def handoff_noalloc(src: Pool, dst: Pool, batch: Batch, shard: Optional[N.TkvShard] = None,
+                    stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Same-dtype handoff that allocates no device memory: the work list goes into a fixed
+    array inside the library instead of a plan's buffer.  For callers that cannot call
+    cudaMalloc when a handoff happens (HBM already owned by the KV pools, or a serving loop
+    that must not stall the device).  Calls on one device share that array, so their GPU
+    work must not overlap; at most 16384 block pairs and 128 layers per call."""
+    if stream is None:
+        stream = torch.cuda.current_stream(src.device)
+    s, d, b = src.c_struct(), dst.c_struct(), batch.c_struct()
+    check(lib().tkv_handoff_noalloc(C.byref(s), C.byref(d), C.byref(b),
+                                    C.byref(shard) if shard is not None else None,
+                                    C.c_void_p(stream.cuda_stream)))
+
+
 def pairing_make(n_gpus: int, n_layers: int, n_kv_heads: int) -> List[N.TkvPairing]:
     out = (N.TkvPairing * 8)()
     n = C.c_int32(0)
