@@ -108,7 +108,15 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------
 # workloads
 # ----------------------------------------------------------------------------------------
-def pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None):
+def pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None, layers: int | None = None):
+    w = _pick_workload(name, n_gpus, pool_blocks, heads)
+    if layers:                      # profiling aid: same batch and tables, fewer layers
+        w.n_layers = layers
+        w.name += f"-{layers}layers"
+    return w
+
+
+def _pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None):
     from tempura_b200 import workloads as W
     if name == "cfg1":
         return W.tinyllama_cpu()
@@ -255,7 +263,7 @@ def run_ours(args):
     partner = rank + pairs if is_prefill else rank - pairs
 
     wname = args.workload or "cfg2"
-    w = pick_workload(wname, world, args.pool_blocks)
+    w = pick_workload(wname, world, args.pool_blocks, layers=args.layers)
     dst_dtype = w.dst_dtype
     scales = dst_dtype == "e4m3"
     flags = 0
@@ -306,6 +314,10 @@ def run_ours(args):
     plan = None
     if is_prefill:
         plan = H.Plan(src, dst, batch, None, flags)
+        if args.bulk_tune:
+            plan.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
+        if args.grid_tune:
+            plan.tune_grid(args.grid_tune)
     stream = torch.cuda.current_stream()
     done_flag = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
 
@@ -427,7 +439,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--pool-blocks", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep the batch, use fewer layers")
     ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
+    ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
+    ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -185,6 +185,16 @@ int32_t tkv_handoff_enqueue(tkv_plan* plan, void* stream, uint64_t done_flag, ui
 int32_t tkv_handoff_noalloc(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch,
                             const TkvShard* shard /* NULL = everything */, void* stream);
 
+/* Tuning of the bulk-copy variant (ring depth per CTA, CTAs per SM, bytes per ring
+ * stage); ctas_per_sm 0 derives it from the stage size.  No reference counterpart.
+ * Takes effect at the next enqueue.                                             */
+int32_t tkv_plan_tune_bulk(tkv_plan* plan, uint32_t stages, uint32_t ctas_per_sm, uint32_t stage_bytes);
+/* Caps the resident CTAs per SM of the register (non-bulk) kernels; 0 = as many as fit. */
+int32_t tkv_plan_tune_grid(tkv_plan* plan, uint32_t ctas_per_sm);
+/* Reads the plan's device-side error word (synchronous): 0, or 1 when a kernel of
+ * this plan gave up on one of its own bounded waits.                            */
+int32_t tkv_plan_error(const tkv_plan* plan, uint32_t* device_error);
+
 /* Bounded waits on a completion flag (uint32_t in device memory of the
  * waiting side).  Host form polls with small device->host copies; device form
  * enqueues a one-thread kernel that spins at most max_spins times and records
@@ -215,6 +225,10 @@ int32_t tkv_cast(uint64_t src, int32_t src_dtype, uint64_t dst, int32_t dst_dtyp
  * integer bit-math port of kernels/src/e4m3.rs:50-94 over every f32 whose low
  * `skip_bits` bits are zero (0 = all 2^32).  Writes the mismatch count.        */
 int32_t tkv_selfcheck_e4m3(uint32_t skip_bits, uint64_t* mismatches);
+/* Device self-check of the scaled fast path (flush threshold on the F16 magnitude +
+ * hardware conversion) against the integer port applied to the same FP32 product, for
+ * every finite non-zero block amax and every F16 value of magnitude <= amax.       */
+int32_t tkv_selfcheck_scaled_quant(uint64_t* mismatches);
 
 /* ---- bits checksum (engine/src/cutile_kv_cache.rs:1274-1368) --------------- */
 /* Wrapping sum of the f32 bit patterns of n elements (narrow dtypes widened). */

@@ -74,12 +74,16 @@ SIGNATURES = {
     "tkv_plan_stats": (_i32, [_vp, C.POINTER(TkvStats)]),
     "tkv_handoff_enqueue": (_i32, [_vp, _vp, _u64, _u32]),
     "tkv_handoff_noalloc": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _vp]),
+    "tkv_plan_tune_bulk": (_i32, [_vp, _u32, _u32, _u32]),
+    "tkv_plan_tune_grid": (_i32, [_vp, _u32]),
+    "tkv_plan_error": (_i32, [_vp, _u32p]),
     "tkv_flag_wait_host": (_i32, [_i32, _u64, _u32, _u64]),
     "tkv_flag_wait_enqueue": (_i32, [_vp, _u64, _u32, _u64, _u64]),
     "tkv_refcount_apply": (_i32, [_vp, _i32, _vp]),
     "tkv_pairing_make": (_i32, [_i32, _u32, _u32, C.POINTER(TkvPairing), _i32, C.POINTER(_i32)]),
     "tkv_cast": (_i32, [_u64, _i32, _u64, _i32, _u64, _vp]),
     "tkv_selfcheck_e4m3": (_i32, [_u32, _u64p]),
+    "tkv_selfcheck_scaled_quant": (_i32, [_u64p]),
     "tkv_bits_checksum": (_i32, [_u64, _i32, _u64, _vp, _u64p]),
     "tkv_ipc_export": (_i32, [_u64, _u8p, _u64p]),
     "tkv_ipc_import": (_i32, [_u8p, _u64, _u64p]),

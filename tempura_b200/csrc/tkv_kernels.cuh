@@ -150,6 +150,139 @@ __global__ void __launch_bounds__(256) handoff_copy_vec(const HandoffArgs a) {
 }
 
 // ---------------------------------------------------------------------------------
+// Same-dtype handoff, bulk-copy path (same device, contiguous chunks): one warp per
+// CTA; lane 0 drives a ring of shared-memory stages with the bulk async-copy engine
+// (cp.async.bulk global->shared completing on an mbarrier, then shared->global as a
+// bulk group).  No thread touches the payload.  All lanes decode work items 32 at a
+// time into a small shared table so lane 0 never waits on a dependent global load.
+// Every wait is bounded: on a timeout the CTA records an error, drains its copies and
+// leaves.
+// ---------------------------------------------------------------------------------
+struct BulkItem {
+    uint64_t src, dst;
+    uint32_t bytes, pad;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); it++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+#ifndef TKV_KERNELS_TEMPLATES_ONLY
+__global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uint32_t stage_bytes, uint32_t n_stages,
+                                                        uint32_t pieces, uint32_t* error_flag) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                    // up to 8 barriers
+    BulkItem* items = reinterpret_cast<BulkItem*>(smem + 64);              // 64 decoded items
+    unsigned char* data = smem + 64 + 64 * sizeof(BulkItem);               // 1600: 16-byte aligned
+    const uint32_t lane = threadIdx.x;
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint64_t total = (uint64_t)chunks * pieces;
+    const uint32_t n_mine = blockIdx.x < total ? (uint32_t)((total - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < n_stages; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bars + s)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    // decode items [32*b, 32*b + 32) of this CTA into the half of the table that batch b owns
+    auto decode_batch = [&](uint32_t b) {
+        uint32_t k = b * 32u + lane;
+        if (k < n_mine) {
+            uint64_t it = (uint64_t)blockIdx.x + (uint64_t)k * gridDim.x;
+            uint32_t piece = (uint32_t)(it % pieces);
+            Chunk c = decode_chunk(a, (uint32_t)(it / pieces));
+            uint32_t cb = c.n_valid * a.src_row_bytes;                     // valid bytes of this chunk
+            uint32_t off = piece * stage_bytes;
+            BulkItem bi;
+            bi.bytes = off < cb ? min(stage_bytes, cb - off) : 0u;
+            bi.src = reinterpret_cast<uint64_t>(c.src) + off;
+            bi.dst = reinterpret_cast<uint64_t>(c.dst) + off;
+            bi.pad = 0;
+            items[(b & 1u) * 32u + lane] = bi;
+        }
+        __syncwarp();
+    };
+
+    auto issue_load = [&](uint32_t k) {                                    // lane 0 only
+        const BulkItem bi = items[k & 63u];
+        const uint32_t s = k % n_stages;
+        const uint32_t bar = smem_u32(bars + s);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bi.bytes) : "memory");
+        if (bi.bytes)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(data + (size_t)s * stage_bytes)), "l"(bi.src), "r"(bi.bytes), "r"(bar) : "memory");
+    };
+
+    uint32_t decoded = 0;                                                  // batches decoded so far
+    if (n_mine) {
+        decode_batch(0);
+        decoded = 1;
+    }
+    const uint32_t pre = min(n_stages, n_mine);
+    if (pre > 32u) {                                                        // cannot happen: n_stages <= 8
+        decode_batch(1);
+        decoded = 2;
+    }
+    if (lane == 0)
+        for (uint32_t k = 0; k < pre; k++) issue_load(k);
+
+    uint32_t failed = 0;
+    for (uint32_t k = 0; k < n_mine; k++) {
+        const uint32_t refill = k + n_stages - 1u;                         // item that reuses stage (k-1) % S
+        if (k >= 1u && refill < n_mine && refill / 32u >= decoded) {
+            decode_batch(refill / 32u);
+            decoded = refill / 32u + 1u;
+        }
+        if (lane == 0) {
+            const uint32_t s = k % n_stages;
+            if (!mbar_wait_bounded(smem_u32(bars + s), (k / n_stages) & 1u)) {
+                failed = 1;
+            } else {
+                const BulkItem bi = items[k & 63u];
+                if (bi.bytes)
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(bi.dst), "r"(smem_u32(data + (size_t)s * stage_bytes)), "r"(bi.bytes) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                if (k >= 1u && refill < n_mine) {
+                    // the store issued one iteration ago has read its stage: refill it
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    issue_load(refill);
+                }
+            }
+        }
+        failed = __shfl_sync(0xFFFFFFFFu, failed, 0);
+        if (failed) {
+            // give the loads still in flight a bounded chance to land before leaving
+            if (lane == 0)
+                for (uint32_t j = k + 1u; j < n_mine && j < k + n_stages; j++)
+                    mbar_wait_bounded(smem_u32(bars + j % n_stages), (j / n_stages) & 1u);
+            break;
+        }
+    }
+    if (lane == 0) {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (failed && error_flag) atomicExch(error_flag, 1u);
+    }
+    __syncwarp();
+    signal_done(a);
+}
+#endif  // TKV_KERNELS_TEMPLATES_ONLY
+
+// ---------------------------------------------------------------------------------
 // FP8 E4M3 encoders.
 // ---------------------------------------------------------------------------------
 
@@ -212,6 +345,45 @@ template <bool HW> __device__ __forceinline__ uint32_t quant_h2(uint32_t h2, flo
     return e4m3_encode_pair<HW>(__fmul_rn(lo, inv), __fmul_rn(hi, inv));
 }
 
+// ---- fast path of the scaled encoder ---------------------------------------------
+// For a block whose amax is finite and non-zero no element is NaN or Inf, and the
+// only place the hardware conversion departs from the element rule is the flush of
+// products below 2^-6.  RN(x * inv) is monotone in |x|, so the flush is a single
+// threshold on the F16 magnitude: the smallest half h with RN(float(h) * inv) >= 2^-6.
+// The guess T / inv is off by far less than the F16 spacing; start one below its
+// floor and step up while the exact test fails.
+__device__ __forceinline__ uint32_t flush_threshold_bits(float inv) {
+    const float T = 0.015625f;
+    uint32_t c = (uint32_t)__half_as_ushort(__float2half_rd(__fdiv_rn(T, inv)));
+    c = c > 0u ? c - 1u : 0u;
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        float y = __fmul_rn(__half2float(__ushort_as_half((unsigned short)c)), inv);
+        if (y < T) c++;
+    }
+    return c;
+}
+
+// two F16 in a u32 -> two e4m3 bytes in the low 16 bits; thr2 holds the flush
+// threshold in both halves.  Magnitudes below it become signed zeros before widening.
+__device__ __forceinline__ uint32_t quant_h2_fast(uint32_t w, float inv, __half2 thr2) {
+    __half2 x = *reinterpret_cast<__half2*>(&w);
+    uint32_t keep = __hge2_mask(__habs2(x), thr2) | 0x80008000u;
+    w &= keep;
+    x = *reinterpret_cast<__half2*>(&w);
+    float lo = __fmul_rn(__low2float(x), inv), hi = __fmul_rn(__high2float(x), inv);
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// max over |a|, |b| lanes; a NaN lane stays NaN (bits 0x7FFF), so an integer compare
+// of the result against 0x7C00 still detects Inf and NaN.
+__device__ __forceinline__ uint32_t amax_h2(uint32_t m, uint32_t w) {
+    __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m), __habs2(*reinterpret_cast<__half2*>(&w)));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
 // ---------------------------------------------------------------------------------
 // F16 -> E4M3 handoff, one warp per (chunk, kv head).  The warp keeps its
 // BS x D halves in registers between the absmax pass and the encode pass, so the
@@ -234,7 +406,7 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
         const char* s = c.src + (size_t)h * D * 2 + col * 32;
         char* d = c.dst + (size_t)h * D + col * 16;
         uint4 v[NP][2];
-        uint32_t m = 0;
+        uint32_t m = 0, amax = 0x7C00u;  // amax stays 'non-finite' when no scale pass runs
 #pragma unroll
         for (int p = 0; p < NP; p++) {
             uint32_t row = p * RPP + r0;
@@ -253,13 +425,13 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
             for (int p = 0; p < NP; p++) {
 #pragma unroll
                 for (int k = 0; k < 2; k++) {
-                    m = __vmaxu2(m, v[p][k].x & 0x7FFF7FFFu);
-                    m = __vmaxu2(m, v[p][k].y & 0x7FFF7FFFu);
-                    m = __vmaxu2(m, v[p][k].z & 0x7FFF7FFFu);
-                    m = __vmaxu2(m, v[p][k].w & 0x7FFF7FFFu);
+                    m = amax_h2(m, v[p][k].x);
+                    m = amax_h2(m, v[p][k].y);
+                    m = amax_h2(m, v[p][k].z);
+                    m = amax_h2(m, v[p][k].w);
                 }
             }
-            uint32_t amax = max(m & 0xFFFFu, m >> 16);
+            amax = max(m & 0xFFFFu, m >> 16);
             amax = __reduce_max_sync(0xFFFFFFFFu, amax);
             float scale = block_scale(amax, inv);
             if (lane == 0) {
@@ -268,6 +440,26 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
                    a.dst_head_begin + h] = scale;
             }
         }
+        if (SCALED && HW && amax < 0x7C00u) {
+            // finite block: threshold flush on the F16 bits, hardware conversion
+            const uint32_t t = flush_threshold_bits(inv);
+            const uint32_t t2u = t | (t << 16);
+            const __half2 thr2 = *reinterpret_cast<const __half2*>(&t2u);
+#pragma unroll
+            for (int p = 0; p < NP; p++) {
+                uint32_t row = p * RPP + r0;
+                if (row < c.n_valid) {
+                    uint4 o;
+                    o.x = __byte_perm(quant_h2_fast(v[p][0].x, inv, thr2), quant_h2_fast(v[p][0].y, inv, thr2), 0x5410);
+                    o.y = __byte_perm(quant_h2_fast(v[p][0].z, inv, thr2), quant_h2_fast(v[p][0].w, inv, thr2), 0x5410);
+                    o.z = __byte_perm(quant_h2_fast(v[p][1].x, inv, thr2), quant_h2_fast(v[p][1].y, inv, thr2), 0x5410);
+                    o.w = __byte_perm(quant_h2_fast(v[p][1].z, inv, thr2), quant_h2_fast(v[p][1].w, inv, thr2), 0x5410);
+                    *reinterpret_cast<uint4*>(d + (size_t)row * a.dst_row_stride) = o;
+                }
+            }
+            continue;
+        }
+        // unscaled destination, integer encoder, or a block holding Inf / NaN
 #pragma unroll
         for (int p = 0; p < NP; p++) {
             uint32_t row = p * RPP + r0;
@@ -413,6 +605,27 @@ __global__ void selfcheck_e4m3_kernel(uint32_t skip_bits, unsigned long long* mi
         if ((p & 0xFFu) != want) bad++;
         uint32_t want_neg = e4m3_encode_int(-x);
         if ((p >> 8) != want_neg) bad++;
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+// Every finite non-zero amax, every |h| <= amax of both signs: the fast scaled path
+// (threshold flush + hardware conversion) against the integer encoder applied to the
+// same FP32 product.  One CTA per amax value.
+__global__ void selfcheck_scaled_quant_kernel(unsigned long long* mismatches) {
+    unsigned long long bad = 0;
+    for (uint32_t amax = 1u + blockIdx.x; amax < 0x7C00u; amax += gridDim.x) {
+        float inv;
+        block_scale(amax, inv);
+        const uint32_t t = flush_threshold_bits(inv);
+        const uint32_t t2u = t | (t << 16);
+        const __half2 thr2 = *reinterpret_cast<const __half2*>(&t2u);
+        for (uint32_t h = threadIdx.x; h <= amax; h += blockDim.x) {
+            uint32_t got = quant_h2_fast(h | ((h | 0x8000u) << 16), inv, thr2);
+            float x = __half2float(__ushort_as_half((unsigned short)h));
+            uint32_t want = e4m3_encode_int(__fmul_rn(x, inv)) | (e4m3_encode_int(__fmul_rn(-x, inv)) << 8);
+            if (got != want) bad++;
+        }
     }
     if (bad) atomicAdd(mismatches, bad);
 }

@@ -179,6 +179,17 @@ class Plan:
             stream = torch.cuda.current_stream(self.src.device)
         check(lib().tkv_refcount_apply(self._h, delta, C.c_void_p(stream.cuda_stream)))
 
+    def tune_bulk(self, stages: int, ctas_per_sm: int, stage_bytes: int = 32768) -> None:
+        check(lib().tkv_plan_tune_bulk(self._h, stages, ctas_per_sm, stage_bytes))
+
+    def tune_grid(self, ctas_per_sm: int) -> None:
+        check(lib().tkv_plan_tune_grid(self._h, ctas_per_sm))
+
+    def device_error(self) -> int:
+        out = C.c_uint32(0)
+        check(lib().tkv_plan_error(self._h, C.byref(out)))
+        return out.value
+
     def stats(self) -> N.TkvStats:
         st = N.TkvStats()
         check(lib().tkv_plan_stats(self._h, C.byref(st)))
@@ -244,6 +255,12 @@ def bits_checksum(t: torch.Tensor, dtype: str) -> int:
 def selfcheck_e4m3(skip_bits: int = 0) -> int:
     out = C.c_uint64(0)
     check(lib().tkv_selfcheck_e4m3(skip_bits, C.byref(out)))
+    return out.value
+
+
+def selfcheck_scaled_quant() -> int:
+    out = C.c_uint64(0)
+    check(lib().tkv_selfcheck_scaled_quant(C.byref(out)))
     return out.value
 
 

@@ -59,8 +59,10 @@ def test_config1_tinyllama_full_size(H):
 
 # ---- config 2 shape: F16 -> F16, ragged lengths ---------------------------------------
 @pytest.mark.parametrize("seed", [0, 1])
-def test_config2_shape_f16_copy(H, seed):
-    run_case(H, reduced_8b(seed=seed))
+@pytest.mark.parametrize("flags,variant", [(0, 2), (N.PLAN_FORCE_VECTOR, 1)])
+def test_config2_shape_f16_copy(H, seed, flags, variant):
+    plan, *_ = run_case(H, reduced_8b(seed=seed), flags=flags)
+    assert plan.stats().kernel_variant == variant     # 2 = bulk-copy ring, 1 = register copy
 
 
 def test_config2_lengths_exact_multiple_and_single_token(H):
@@ -258,6 +260,36 @@ def test_plan_update_reuses_plan(H):
     assert_pool_equals_host(dd, hd, "second batch through the same plan")
 
 
+# ---- bulk-copy variant of the same-dtype handoff ---------------------------------------------
+@pytest.mark.parametrize("tune", [(3, 2, 32768), (2, 1, 32768), (8, 1, 8192), (4, 4, 4096)])
+def test_bulk_variant_parity(H, tune):
+    import torch
+    cases = [W.tinyllama_cpu(),                                              # 8 KiB chunks
+             reduced_8b(seed=40),                                            # 32 KiB chunks, ragged tails
+             W.Workload("bs32", 2, 8, 128, 32, 64, 64, np.array([100, 31, 64], dtype=np.uint32), seed=41).build_tables()]  # 64 KiB chunks
+    for w in cases:
+        hs, hd = host_pools(w)
+        ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "f16")
+        oracle.handoff(hs, hd, oracle_batch(w))
+        plan = H.Plan(ds, dd, device_batch(w), None, N.PLAN_FORCE_BULK)
+        plan.tune_bulk(*tune)
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        plan.enqueue(done_flag=flag.data_ptr(), flag_value=5)
+        H.flag_wait_host(0, flag.data_ptr(), 5, 5_000_000)
+        assert plan.stats().kernel_variant == 2 and plan.device_error() == 0
+        assert_pool_equals_host(dd, hd, f"bulk {w.name} {tune}")
+
+
+def test_bulk_variant_refuses_strided_rows(H):
+    w = W.Workload("bulk-shard", 2, 8, 128, 16, 64, 64, np.array([40], dtype=np.uint32), seed=42).build_tables()
+    hs, hd = host_pools(w, dst_heads=2)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "f16")
+    plan = H.Plan(ds, dd, device_batch(w), H.Shard(4, 0, 2, 0, 0, 2), N.PLAN_FORCE_BULK)
+    with pytest.raises(N.TkvError) as e:
+        plan.enqueue()
+    assert e.value.code == N.ERR_INVALID_CONFIG
+
+
 # ---- completion flag and bounded waits ------------------------------------------------------
 def test_done_flag_and_bounded_waits(H):
     import torch
@@ -289,6 +321,10 @@ def test_done_flag_and_bounded_waits(H):
 # ---- element casts and checksum -----------------------------------------------------------------
 def test_fast_fp8_encoder_equals_integer_port_on_every_f32(H):
     assert H.selfcheck_e4m3(0) == 0
+
+
+def test_scaled_fast_path_equals_integer_port_for_every_amax_and_value(H):
+    assert H.selfcheck_scaled_quant() == 0
 
 
 def test_cast_kernels_against_oracle(H):
