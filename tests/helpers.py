@@ -70,6 +70,7 @@ def to_device_pool(hp: oracle.HostPool, dtype: str, device: int = 0, refcounts=N
     for l in range(hp.n_layers):
         p.k[l].view(torch.uint8).copy_(torch.from_numpy(hp.k[l].view(np.uint8)))
         p.v[l].view(torch.uint8).copy_(torch.from_numpy(hp.v[l].view(np.uint8)))
+    torch.cuda.synchronize(device)
     if hp.k_scales is not None:
         p.k_scales.copy_(torch.from_numpy(hp.k_scales))
         p.v_scales.copy_(torch.from_numpy(hp.v_scales))

@@ -1,0 +1,69 @@
+"""Two-GPU parity: the prefill GPU's kernel stores straight into the decode GPU's pool
+over NVLink (one process, peer access).  Skipped on a single-GPU box."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import assert_pool_equals_host, device_batch, host_pools, oracle_batch, to_device_pool
+from tempura_b200 import _native as N
+from tempura_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def H():
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from tempura_b200 import handoff
+    handoff.init([0, 1])
+    return handoff
+
+
+def _run(H, w, mode, shard=None, oshard=None, dst_heads=None, flags=0):
+    import torch
+    hs, hd = host_pools(w, dst_heads=dst_heads)
+    src = to_device_pool(hs, w.src_dtype, device=0)
+    dst = to_device_pool(hd, w.dst_dtype, device=1)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda:1")
+    oracle.handoff(hs, hd, oracle_batch(w), oshard, mode)
+    plan = H.Plan(src, dst, device_batch(w), shard, flags)
+    with torch.cuda.device(0):
+        plan.enqueue(torch.cuda.current_stream(0), done_flag=flag.data_ptr(), flag_value=9)
+    H.flag_wait_host(1, flag.data_ptr(), 9, 10_000_000)      # decode side sees the flag ...
+    with torch.cuda.device(1):
+        assert_pool_equals_host(dst, hd, f"peer {w.name}")    # ... and every byte behind it
+    st = plan.stats()
+    assert st.peer == 1
+    return plan
+
+
+def test_peer_f16_copy_uses_register_stores(H):
+    w = W.Workload("peer-f16", 3, 8, 128, 16, 256, 256, W.lengths(6, 40, 300, 50, 7), seed=50).build_tables()
+    plan = _run(H, w, "copy")
+    assert plan.stats().kernel_variant == 1          # peer destinations never take the bulk-copy path
+
+
+def test_peer_bulk_refused(H):
+    import torch
+    w = W.Workload("peer-bulk", 1, 8, 128, 16, 32, 32, np.array([20], dtype=np.uint32), seed=51).build_tables()
+    hs, hd = host_pools(w)
+    src, dst = to_device_pool(hs, "f16", device=0), to_device_pool(hd, "f16", device=1)
+    plan = H.Plan(src, dst, device_batch(w), None, N.PLAN_FORCE_BULK)
+    with pytest.raises(N.TkvError):
+        plan.enqueue(torch.cuda.current_stream(0))
+
+
+def test_peer_fp8_scaled_cast_before_the_wire(H):
+    w = W.Workload("peer-fp8", 2, 8, 128, 16, 256, 256, W.lengths(5, 30, 200, 52, 7), dst_dtype="e4m3",
+                   outlier_channels=(9,), outlier_gain=20.0, seed=52).build_tables()
+    plan = _run(H, w, "f16_e4m3")
+    st = plan.stats()
+    assert st.bytes_written < st.bytes_read          # half the payload (+ scales) crosses NVLink
+
+
+def test_peer_head_shard_pair(H):
+    """One pair of the 4 -> 4 layout: source holds 8 heads, this pair's decode pool its 2."""
+    w = W.Workload("peer-shard", 4, 8, 128, 16, 128, 128, np.full(5, 70, dtype=np.uint32), seed=53).build_tables()
+    _run(H, w, "copy", shard=H.Shard(2, 0, 2, 0, 0, 4), oshard=oracle.OrcShard(2, 0, 2, 0, 0, 4), dst_heads=2)
