@@ -29,7 +29,7 @@ METRIC = "kv_handoff_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch divided by the algorithmic bytes of
 # the same launch, from the ncu captures summarised under profiles/ (None until captured).
-NCU_TRAFFIC_RATIO = {"handoff_copy_vec": None, "handoff_f16_e4m3_warp": None}
+NCU_TRAFFIC_RATIO = {"handoff_copy_bulk": 0.961, "handoff_copy_vec": 0.954, "handoff_f16_e4m3_warp": 0.942}
 
 
 def measured_peaks():
@@ -240,6 +240,57 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------
+# comparison baseline for N > 1: staged copy through NCCL
+# ----------------------------------------------------------------------------------------
+def nccl_baseline(H, w, batch, src, dst, is_prefill, partner, local, scales, steps, barrier):
+    """The conventional route the peer-store kernel replaces: gather the prompts' blocks into a
+    contiguous staging buffer (cast before the wire for an E4M3 pool), ncclSend it, ncclRecv
+    it on the decode GPU, scatter it into the decode pool.  Device-timed per rank, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    n_blocks = H.batch_blocks(batch, w.block_size)
+    wire = "e4m3" if scales else "f16"
+    x = H.Transfer.allocate(w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, n_blocks, wire, device=local, scales=scales)
+    if is_prefill:
+        plan = H.Plan.to_transfer(src, x, batch)
+    else:
+        own = H.Batch(batch.seq_lens, batch.dst_tables, batch.dst_tables, batch.table_stride, batch.prefix_lens)
+        plan = H.Plan.from_transfer(x, dst, own)
+    used = x.data                                   # whole planes travel, padding rows included
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def step():
+        if is_prefill:
+            plan.enqueue()
+            dist.send(used, partner)
+            if scales:
+                dist.send(x.scales, partner)
+        else:
+            dist.recv(used, partner)
+            if scales:
+                dist.recv(x.scales, partner)
+            plan.enqueue()
+
+    for _ in range(2):
+        step()
+    barrier()
+    ev0.record()
+    for _ in range(steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    barrier()
+    ms = float(t.item()) / steps
+    pairs = dist.get_world_size() // 2
+    payload = w.payload_bytes * pairs
+    return {"value": round(payload / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms, 5), "steps": steps,
+            "wire_bytes_per_pair": int(used.numel()) + (int(x.scales.numel()) * 4 if scales else 0),
+            "what": "tkv to_transfer kernel -> ncclSend/ncclRecv (torch.distributed) -> tkv from_transfer kernel"}
+
+
+# ----------------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------------
 def run_ours(args):
@@ -359,7 +410,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
 
-    # ---- end to end: host tables -> plan update (H2D work list) -> kernel -> D2H flag ----------
+    # ---- end to end, device-resident pools: host tables -> plan update (H2D work list) -> kernel -> D2H flag
     e2e_steps = args.steps
     barrier()
     t0 = time.perf_counter()
@@ -373,17 +424,63 @@ def run_ours(args):
         else:
             H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    res_s = time.perf_counter() - t0
     barrier()
-    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    t = torch.tensor([res_s], dtype=torch.float64, device="cuda")
     if multi:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
-    sampler.mark()
-    clocks = sampler.stop()
+    res_s = float(t.item())
 
     if not multi:
         spot_check(src, dst, w, w.n_layers - 1)
+
+    # ---- end to end, HOST buffers: the prompts' K/V sit in page-locked host memory in the contiguous
+    # transfer layout (the reference's KvCacheTransfer); every step uploads the tables, runs the
+    # from_transfer kernel, which pulls the payload over PCIe and stores it into the decode pool
+    # (casting on the way for an E4M3 pool), and reads the completion flag back.
+    host_steps = max(1, min(args.steps, args.host_steps))
+    xfer = plan_h = None
+    # bounded by host memory: at most ~8 GB of page-locked buffer; larger batches move their first layers only
+    per_layer = w.payload_bytes // w.n_layers
+    host_layers = int(max(1, min(w.n_layers, 8_000_000_000 // max(per_layer, 1))))
+    if is_prefill:
+        n_blocks = H.batch_blocks(batch, w.block_size)
+        xfer = H.Transfer.allocate(host_layers, w.n_kv_heads, w.head_dim, w.block_size, n_blocks, "f16", device=local, host=True)
+        hv = xfer.data.view(torch.int16)
+        tile = torch.randint(-15000, 15000, (1 << 24,), dtype=torch.int16)          # finite F16 bit patterns
+        for o in range(0, hv.numel(), tile.numel()):
+            n = min(tile.numel(), hv.numel() - o)
+            hv[o:o + n].copy_(tile[:n])
+        plan_h = H.Plan.from_transfer(xfer, dst, batch, H.Shard(0, 0, w.n_kv_heads, 0, 0, host_layers), 0)
+    barrier()
+    for it in range(1 + host_steps):             # first pass is the warm-up
+        if it == 1:
+            barrier()
+            t0 = time.perf_counter()
+        gen += 1
+        if is_prefill:
+            plan_h.update(batch)
+            plan_h.enqueue(stream, done_flag, gen)
+            if not multi:
+                H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+        else:
+            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+    torch.cuda.synchronize()
+    host_s = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([host_s], dtype=torch.float64, device="cuda")
+    if multi:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    host_s = float(t.item())
+    host_h2d = (plan_h.stats().payload_bytes + plan_h.stats().worklist_bytes) if is_prefill else 0
+    del plan_h, xfer
+
+    # ---- comparison baseline (N > 1): pack kernel -> NCCL send/recv -> scatter kernel ------------------
+    nccl = None
+    if multi and not args.no_nccl:
+        nccl = nccl_baseline(H, w, batch, src, dst, is_prefill, partner, local, scales, max(3, min(args.steps, 10)), barrier)
+    sampler.mark()
+    clocks = sampler.stop()
 
     if rank == 0:
         st = plan.stats()
@@ -413,12 +510,21 @@ def run_ours(args):
                          "frac": round(achieved / peak_used, 4), "traffic": (int(ratio * algo) if ratio else None),
                          "algorithmic_bytes": int(algo_used), "peak_source": peak_note,
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4) if not multi else None},
-            "e2e": {"value": round(payload_all * e2e_steps / e2e_s / 1e9, 2), "unit": UNIT,
-                    "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4,
-                    "what": "host block tables -> tkv_plan_update (validate, build, upload work list) -> tkv_handoff_enqueue -> flag read back; KV pools stay on the devices that own them"},
-            "gpu_launches": args.warmup + args.steps + e2e_steps,
+            "e2e": {"value": round(payload_all * host_layers / w.n_layers * host_steps / host_s / 1e9, 2), "unit": UNIT,
+                    "h2d_bytes_per_step": int(host_h2d), "d2h_bytes_per_step": 4, "steps": host_steps,
+                    "layers": host_layers,
+                    "what": "K/V of the batch in page-locked HOST memory (contiguous transfer layout) + host block tables -> "
+                            "tkv_plan_update -> tkv_handoff_enqueue of a from_transfer plan (the kernel reads the host buffer "
+                            "over PCIe and stores into the decode pool) -> flag read back"},
+            "e2e_resident": {"value": round(payload_all * e2e_steps / res_s / 1e9, 2), "unit": UNIT,
+                             "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4,
+                             "what": "same call sequence with the K/V already in the prefill GPU's paged pool (where prefill "
+                                     "wrote it): host block tables -> tkv_plan_update -> tkv_handoff_enqueue -> flag read back"},
+            "gpu_launches": args.warmup + args.steps + e2e_steps + 1 + host_steps,
             "clocks": clocks,
         }
+        if nccl is not None:
+            line["nccl_baseline"] = nccl
         if not multi and not args.no_cpu:
             layers = 2 if dst_dtype == "e4m3" else 4
             v1, sample = time_cpu(w, 1, layers, 3)
@@ -444,6 +550,8 @@ def main():
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")
+    ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

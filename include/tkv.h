@@ -106,6 +106,28 @@ typedef struct TkvStats {
     uint32_t peer;                /* 1 when destination is another device                 */
 } TkvStats;
 
+/* A contiguous transfer buffer: the batch form of KvCacheTransfer{k_data, v_data}
+ * (engine/src/kv_cache.rs:514-522).  For each moved layer, K then V, it holds the moved
+ * blocks of sequence 0, 1, ... in work-list order, each block `block_size` rows of
+ * [kv_head][head_dim] restricted to the shard's heads; one sequence's rows are therefore
+ * contiguous [token][kv_head][head_dim], which is what k_data[layer] is.  With n moved
+ * blocks, layer l's K plane starts at data + (2l) * n * block_bytes and its V plane one
+ * plane later.  An E4M3 buffer may carry scales: float[K|V][layer][block][kv_head].
+ * `device` is the GPU whose kernel touches the buffer.  host_memory == 0: the buffer is
+ * device memory of that GPU.  host_memory == 1: it is page-locked host memory that GPU can
+ * address (cudaHostAlloc / cudaHostRegister); the kernel then reads or writes it over PCIe
+ * directly, which is the DRAM swap tier of engine/src/cutile_kv_cache.rs:1127-1368 without
+ * a staging copy.                                                                    */
+typedef struct TkvTransfer {
+    int32_t device;
+    int32_t dtype;                /* TKV_DTYPE_* of the buffer                          */
+    uint32_t host_memory;
+    uint32_t reserved;
+    uint64_t data;
+    uint64_t bytes;               /* capacity; at least tkv_transfer_bytes(...)          */
+    uint64_t scales;              /* 0, or the scale array described above               */
+} TkvTransfer;
+
 typedef struct tkv_plan tkv_plan;
 
 /* Plan flags */
@@ -146,6 +168,31 @@ int32_t tkv_shutdown(void);
 int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch,
                         const TkvShard* shard /* NULL = everything */, uint32_t flags,
                         tkv_plan** out);
+/* The two halves on their own, against a contiguous transfer buffer.
+ * to_transfer: gather through the source tables into the buffer (KvCache::to_transfer,
+ * PagedKvCache::k_contiguous / v_contiguous, engine/src/kv_cache.rs:402-417,1032-1060;
+ * swap_out, engine/src/cutile_kv_cache.rs:1127-1230); batch->dst_tables is not read.
+ * A buffer dtype narrower than the pool's casts on the way (F16 pool -> E4M3 buffer with
+ * scales is the "cast before the wire" form).
+ * from_transfer: scatter the buffer into the destination pool through the destination
+ * tables (KvCache::from_transfer, append_kv, engine/src/kv_cache.rs:419-431,986-1004;
+ * swap_in, engine/src/cutile_kv_cache.rs:1232-1368); batch->src_tables is not read, and an
+ * E4M3 buffer with scales lands in an E4M3 pool with scales.  The shard's head and layer
+ * ranges apply to the pool; the buffer holds exactly the shard.  to_transfer runs with
+ * tkv_handoff_enqueue on a stream of the source pool's device, from_transfer on a stream
+ * of the buffer's device (xfer->device), which stores into the pool locally or as a peer. */
+int32_t tkv_plan_create_to_transfer(const TkvPool* src, const TkvTransfer* xfer, const TkvBatch* batch,
+                                    const TkvShard* shard /* NULL = everything */, uint32_t flags,
+                                    tkv_plan** out);
+int32_t tkv_plan_create_from_transfer(const TkvTransfer* xfer, const TkvPool* dst, const TkvBatch* batch,
+                                      const TkvShard* shard /* NULL = everything */, uint32_t flags,
+                                      tkv_plan** out);
+/* Bytes a transfer buffer needs for n_blocks moved blocks, and the number of blocks a
+ * batch moves (sum over sequences of ceil(seq_len / block_size) - prefix_len / block_size). */
+uint64_t tkv_transfer_bytes(uint32_t n_layers, uint32_t n_heads, uint32_t head_dim, uint32_t block_size,
+                            int32_t dtype, uint64_t n_blocks);
+uint64_t tkv_batch_blocks(const TkvBatch* batch, uint32_t block_size);
+
 /* Re-validates and re-uploads a new batch into an existing plan (same pools,
  * shard and flags; no allocation unless the work list outgrew its capacity). */
 int32_t tkv_plan_update(tkv_plan* plan, const TkvBatch* batch);

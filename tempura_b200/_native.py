@@ -23,6 +23,7 @@ OK, ERR_DIMENSION_MISMATCH, ERR_INVALID_CONFIG, ERR_CUDA, ERR_TIMEOUT, ERR_POOL_
 STATUS_NAMES = {0: "Ok", 1: "DimensionMismatch", 2: "InvalidConfig", 3: "CudaError", 4: "Timeout", 5: "PoolExhausted"}
 DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
 PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER = 1, 2, 4, 8
+VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC = 1, 2, 3, 4, 5
 
 
 class TkvPool(C.Structure):
@@ -42,6 +43,11 @@ class TkvBatch(C.Structure):
         ("seq_lens", C.POINTER(C.c_uint32)), ("prefix_lens", C.POINTER(C.c_uint32)),
         ("src_tables", C.POINTER(C.c_uint32)), ("dst_tables", C.POINTER(C.c_uint32)),
     ]
+
+
+class TkvTransfer(C.Structure):
+    _fields_ = [("device", C.c_int32), ("dtype", C.c_int32), ("host_memory", C.c_uint32), ("reserved", C.c_uint32),
+                ("data", C.c_uint64), ("bytes", C.c_uint64), ("scales", C.c_uint64)]
 
 
 class TkvShard(C.Structure):
@@ -69,6 +75,10 @@ SIGNATURES = {
     "tkv_init": (_i32, [C.POINTER(_i32), _i32]),
     "tkv_shutdown": (_i32, []),
     "tkv_plan_create": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _u32, C.POINTER(_vp)]),
+    "tkv_plan_create_to_transfer": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvTransfer), C.POINTER(TkvBatch), C.POINTER(TkvShard), _u32, C.POINTER(_vp)]),
+    "tkv_plan_create_from_transfer": (_i32, [C.POINTER(TkvTransfer), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _u32, C.POINTER(_vp)]),
+    "tkv_transfer_bytes": (_u64, [_u32, _u32, _u32, _u32, _i32, _u64]),
+    "tkv_batch_blocks": (_u64, [C.POINTER(TkvBatch), _u32]),
     "tkv_plan_update": (_i32, [_vp, C.POINTER(TkvBatch)]),
     "tkv_plan_destroy": (_i32, [_vp]),
     "tkv_plan_stats": (_i32, [_vp, C.POINTER(TkvStats)]),

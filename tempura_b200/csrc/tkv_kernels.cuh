@@ -22,6 +22,8 @@ struct HandoffArgs {
     const uint64_t* dst_v;
     float* dst_k_scales;    // [pool layers][total_blocks][pool heads] or null
     float* dst_v_scales;
+    const float* src_k_scales;  // same layout on the source side; set only when a same-dtype
+    const float* src_v_scales;  // E4M3 move carries its per-block scales along
     uint32_t* done_counter; // in plan memory on the launching device
     uint32_t* done_flag;    // anywhere reachable (peer ok) or null
     uint64_t src_block_stride;  // bytes
@@ -36,6 +38,7 @@ struct HandoffArgs {
     uint32_t src_row_stride, dst_row_stride; // bytes between token rows
     uint32_t src_head_off, dst_head_off;     // byte offset of the first moved head in a row
     uint32_t dst_total_blocks, dst_pool_heads, dst_head_begin, dst_layer_begin;
+    uint32_t src_total_blocks, src_pool_heads, src_head_begin, src_layer_begin;
     uint32_t flag_value;
     uint32_t contiguous;        // rows abut on both sides
 };
@@ -43,7 +46,7 @@ struct HandoffArgs {
 struct Chunk {
     const char* src;
     char* dst;
-    uint32_t n_valid, layer, is_v, dst_block;
+    uint32_t n_valid, layer, is_v, dst_block, src_block;
 };
 
 __device__ __forceinline__ Chunk decode_chunk(const HandoffArgs& a, uint32_t w) {
@@ -59,6 +62,7 @@ __device__ __forceinline__ Chunk decode_chunk(const HandoffArgs& a, uint32_t w) 
     c.dst = reinterpret_cast<char*>(db + (uint64_t)t.y * a.dst_block_stride + a.dst_head_off);
     c.n_valid = t.z;
     c.dst_block = t.y;
+    c.src_block = t.x;
     return c;
 }
 
@@ -144,6 +148,16 @@ __global__ void __launch_bounds__(256) handoff_copy_vec(const HandoffArgs a) {
                     }
                 }
             }
+        }
+        if (a.src_k_scales != nullptr) {
+            // E4M3 blocks travel with their per-(layer, block, kv-head) scales
+            const float* ss = c.is_v ? a.src_v_scales : a.src_k_scales;
+            float* ds = c.is_v ? a.dst_v_scales : a.dst_k_scales;
+            for (uint32_t h = threadIdx.x; h < a.n_heads; h += 256u)
+                ds[((size_t)(a.dst_layer_begin + c.layer) * a.dst_total_blocks + c.dst_block) * a.dst_pool_heads +
+                   a.dst_head_begin + h] =
+                    ss[((size_t)(a.src_layer_begin + c.layer) * a.src_total_blocks + c.src_block) * a.src_pool_heads +
+                       a.src_head_begin + h];
         }
     }
     signal_done(a);
@@ -387,15 +401,16 @@ __device__ __forceinline__ uint32_t amax_h2(uint32_t m, uint32_t w) {
 // ---------------------------------------------------------------------------------
 // F16 -> E4M3 handoff, one warp per (chunk, kv head).  The warp keeps its
 // BS x D halves in registers between the absmax pass and the encode pass, so the
-// source is read once.  Each lane owns 32 contiguous source bytes of a token row
-// (two 16-byte loads) and writes the 16 encoded bytes with one 16-byte store.
+// source is read once.  Each lane owns 16 contiguous source bytes of a token row per
+// pass, so one load instruction of the warp covers whole, adjacent 32-byte sectors
+// (two rows of a 128-wide head); the 8 encoded bytes go out as one 8-byte store.
 // ---------------------------------------------------------------------------------
 template <int D, int BS, bool HW, bool SCALED>
 __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a) {
-    constexpr int LPR = D / 16;        // lanes per token row
+    constexpr int LPR = D / 8;         // lanes per token row
     constexpr int RPP = 32 / LPR;      // token rows per pass
     constexpr int NP = (BS + RPP - 1) / RPP;
-    static_assert(D % 16 == 0 && LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "head_dim");
+    static_assert(D % 8 == 0 && LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "head_dim");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t r0 = lane / LPR, col = lane % LPR;
     const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
@@ -403,33 +418,24 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
     for (uint64_t wi = (uint64_t)blockIdx.x * 8u + warp; wi < total; wi += (uint64_t)gridDim.x * 8u) {
         const uint32_t h = (uint32_t)(wi % a.n_heads);
         const Chunk c = decode_chunk(a, (uint32_t)(wi / a.n_heads));
-        const char* s = c.src + (size_t)h * D * 2 + col * 32;
-        char* d = c.dst + (size_t)h * D + col * 16;
-        uint4 v[NP][2];
+        const char* s = c.src + (size_t)h * D * 2 + col * 16;
+        char* d = c.dst + (size_t)h * D + col * 8;
+        uint4 v[NP];
         uint32_t m = 0, amax = 0x7C00u;  // amax stays 'non-finite' when no scale pass runs
 #pragma unroll
         for (int p = 0; p < NP; p++) {
             uint32_t row = p * RPP + r0;
-            if (row < c.n_valid) {
-                const uint4* sp = reinterpret_cast<const uint4*>(s + (size_t)row * a.src_row_stride);
-                v[p][0] = ld_stream(sp);
-                v[p][1] = ld_stream(sp + 1);
-            } else {
-                v[p][0] = make_uint4(0, 0, 0, 0);
-                v[p][1] = make_uint4(0, 0, 0, 0);
-            }
+            if (row < c.n_valid) v[p] = ld_stream(reinterpret_cast<const uint4*>(s + (size_t)row * a.src_row_stride));
+            else v[p] = make_uint4(0, 0, 0, 0);
         }
         float inv = 1.0f;
         if (SCALED) {
 #pragma unroll
             for (int p = 0; p < NP; p++) {
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    m = amax_h2(m, v[p][k].x);
-                    m = amax_h2(m, v[p][k].y);
-                    m = amax_h2(m, v[p][k].z);
-                    m = amax_h2(m, v[p][k].w);
-                }
+                m = amax_h2(m, v[p].x);
+                m = amax_h2(m, v[p].y);
+                m = amax_h2(m, v[p].z);
+                m = amax_h2(m, v[p].w);
             }
             amax = max(m & 0xFFFFu, m >> 16);
             amax = __reduce_max_sync(0xFFFFFFFFu, amax);
@@ -449,12 +455,10 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
             for (int p = 0; p < NP; p++) {
                 uint32_t row = p * RPP + r0;
                 if (row < c.n_valid) {
-                    uint4 o;
-                    o.x = __byte_perm(quant_h2_fast(v[p][0].x, inv, thr2), quant_h2_fast(v[p][0].y, inv, thr2), 0x5410);
-                    o.y = __byte_perm(quant_h2_fast(v[p][0].z, inv, thr2), quant_h2_fast(v[p][0].w, inv, thr2), 0x5410);
-                    o.z = __byte_perm(quant_h2_fast(v[p][1].x, inv, thr2), quant_h2_fast(v[p][1].y, inv, thr2), 0x5410);
-                    o.w = __byte_perm(quant_h2_fast(v[p][1].z, inv, thr2), quant_h2_fast(v[p][1].w, inv, thr2), 0x5410);
-                    *reinterpret_cast<uint4*>(d + (size_t)row * a.dst_row_stride) = o;
+                    uint2 o;
+                    o.x = __byte_perm(quant_h2_fast(v[p].x, inv, thr2), quant_h2_fast(v[p].y, inv, thr2), 0x5410);
+                    o.y = __byte_perm(quant_h2_fast(v[p].z, inv, thr2), quant_h2_fast(v[p].w, inv, thr2), 0x5410);
+                    *reinterpret_cast<uint2*>(d + (size_t)row * a.dst_row_stride) = o;
                 }
             }
             continue;
@@ -464,12 +468,10 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
         for (int p = 0; p < NP; p++) {
             uint32_t row = p * RPP + r0;
             if (row < c.n_valid) {
-                uint4 o;
-                o.x = quant_h2<HW>(v[p][0].x, inv) | (quant_h2<HW>(v[p][0].y, inv) << 16);
-                o.y = quant_h2<HW>(v[p][0].z, inv) | (quant_h2<HW>(v[p][0].w, inv) << 16);
-                o.z = quant_h2<HW>(v[p][1].x, inv) | (quant_h2<HW>(v[p][1].y, inv) << 16);
-                o.w = quant_h2<HW>(v[p][1].z, inv) | (quant_h2<HW>(v[p][1].w, inv) << 16);
-                *reinterpret_cast<uint4*>(d + (size_t)row * a.dst_row_stride) = o;
+                uint2 o;
+                o.x = quant_h2<HW>(v[p].x, inv) | (quant_h2<HW>(v[p].y, inv) << 16);
+                o.y = quant_h2<HW>(v[p].z, inv) | (quant_h2<HW>(v[p].w, inv) << 16);
+                *reinterpret_cast<uint2*>(d + (size_t)row * a.dst_row_stride) = o;
             }
         }
     }

@@ -117,6 +117,11 @@ struct tkv_plan {
     uint32_t grid_ctas_per_sm = 0;   // cap for the register kernels (0 = occupancy limit)   // ring depth and residency of the bulk-copy kernel
     std::vector<uint8_t> seen;  // scratch bitmap over destination blocks
     std::vector<char> image;    // host image of the device block, built before any CUDA call
+    // Transfer plans: one side is a contiguous transfer buffer, described as a pool whose
+    // block ids are 0, 1, 2, ... in work-list order (virt 1 = source side, 2 = destination).
+    int virt = 0;
+    TkvTransfer xfer{};
+    bool host_side = false;     // the transfer buffer is page-locked host memory
 };
 
 namespace {
@@ -147,8 +152,10 @@ int32_t validate_pools(const TkvPool* s, const TkvPool* d, const TkvShard& sh, M
     else return fail(TKV_ERR_INVALID_CONFIG, "unsupported dtype pair %d -> %d", s->dtype, d->dtype);
     if ((d->k_scales == 0) != (d->v_scales == 0))
         return fail(TKV_ERR_INVALID_CONFIG, "k_scales and v_scales must both be set or both be 0");
-    if (*mode == MODE_COPY && s->dtype == TKV_DTYPE_E4M3 && (d->k_scales || s->k_scales))
-        return fail(TKV_ERR_INVALID_CONFIG, "E4M3 -> E4M3 with scale arrays is not supported");
+    if ((s->k_scales == 0) != (s->v_scales == 0))
+        return fail(TKV_ERR_INVALID_CONFIG, "k_scales and v_scales must both be set or both be 0");
+    if (*mode == MODE_COPY && s->dtype == TKV_DTYPE_E4M3 && ((d->k_scales == 0) != (s->k_scales == 0)))
+        return fail(TKV_ERR_INVALID_CONFIG, "E4M3 -> E4M3: both pools carry per-block scales or neither does");
     return TKV_OK;
 }
 
@@ -157,7 +164,7 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     const TkvPool &s = p->src, &d = p->dst;
     const TkvShard& sh = p->shard;
     const uint32_t bs = s.block_size;
-    if (b->n_seqs && (!b->seq_lens || !b->src_tables || !b->dst_tables))
+    if (b->n_seqs && (!b->seq_lens || (!b->src_tables && p->virt != 1) || (!b->dst_tables && p->virt != 2)))
         return fail(TKV_ERR_INVALID_CONFIG, "batch arrays must not be NULL");
     const uint32_t n_tab = b->table_layer_stride ? sh.n_layers : 1u;
 
@@ -171,13 +178,37 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
             return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (sequence %u needs more blocks than table_stride)",
                         b->table_stride, nb, q);
         pairs += nb - pre / bs;
-        prefix_refs += pre / bs;
+        if (p->virt != 2) prefix_refs += pre / bs;   // a transfer buffer holds no shared prefix blocks
         tokens += len - pre;
     }
     if (pairs * n_tab > 0x7FFFFFFFull / (2ull * sh.n_layers))
         return fail(TKV_ERR_INVALID_CONFIG, "batch too large: %llu block pairs", (unsigned long long)pairs);
 
     const size_t L = sh.n_layers;
+    if (p->virt) {
+        // the transfer buffer as a pool: `pairs` blocks, layer l's K at 2l, V at 2l + 1
+        TkvPool& vp = p->virt == 1 ? p->src : p->dst;
+        std::vector<uint64_t>& vk = p->virt == 1 ? p->src_k : p->dst_k;
+        std::vector<uint64_t>& vv = p->virt == 1 ? p->src_v : p->dst_v;
+        const uint64_t plane = pairs * (uint64_t)bs * vp.n_kv_heads * vp.head_dim * elem_size(vp.dtype);
+        if (2 * L * plane > p->xfer.bytes)
+            return fail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %llu, got %llu (transfer buffer bytes)",
+                        (unsigned long long)(2 * L * plane), (unsigned long long)p->xfer.bytes);
+        if (pairs > 0xFFFFFFFFull) return fail(TKV_ERR_INVALID_CONFIG, "batch too large");
+        vp.total_blocks = (uint32_t)pairs;
+        vk.resize(L);
+        vv.resize(L);
+        for (size_t l = 0; l < L; l++) {
+            vk[l] = p->xfer.data + (2 * l) * plane;
+            vv[l] = p->xfer.data + (2 * l + 1) * plane;
+        }
+        vp.k_layer_ptrs = vk.data();
+        vp.v_layer_ptrs = vv.data();
+        if (p->xfer.scales) {
+            vp.k_scales = p->xfer.scales;
+            vp.v_scales = p->xfer.scales + L * pairs * vp.n_kv_heads * sizeof(float);
+        }
+    }
     const size_t off_counter = 4 * L * sizeof(uint64_t);
     const size_t off_work = (off_counter + 16 + 15) & ~(size_t)15;
     const size_t off_prefix = off_work + (size_t)pairs * n_tab * sizeof(uint4);
@@ -202,7 +233,7 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     size_t np = 0;
     for (uint32_t q = 0; q < b->n_seqs; q++) {
         uint32_t pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
-        for (uint32_t i = 0; i < pre / bs; i++) {
+        for (uint32_t i = 0; i < pre / bs && p->virt != 2; i++) {
             uint32_t id = b->dst_tables[(size_t)q * b->table_stride + i];
             if (id >= d.total_blocks)
                 return fail(TKV_ERR_INVALID_CONFIG, "sequence %u: prefix block id %u outside destination pool (%u blocks)", q, id, d.total_blocks);
@@ -221,8 +252,8 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
             uint32_t len = b->seq_lens[q], pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
             uint32_t nb = (len + bs - 1) / bs;
             for (uint32_t i = pre / bs; i < nb; i++) {
-                uint32_t sid = b->src_tables[so + (size_t)q * b->table_stride + i];
-                uint32_t did = b->dst_tables[dof + (size_t)q * b->table_stride + i];
+                uint32_t sid = p->virt == 1 ? (uint32_t)k : b->src_tables[so + (size_t)q * b->table_stride + i];
+                uint32_t did = p->virt == 2 ? (uint32_t)k : b->dst_tables[dof + (size_t)q * b->table_stride + i];
                 if (sid >= s.total_blocks)
                     return fail(TKV_ERR_INVALID_CONFIG, "sequence %u block %u: source id %u outside pool (%u blocks)", q, i, sid, s.total_blocks);
                 if (did >= d.total_blocks)
@@ -286,6 +317,13 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     a.dst_v = dp + 3 * L;
     a.dst_k_scales = reinterpret_cast<float*>(d.k_scales);
     a.dst_v_scales = reinterpret_cast<float*>(d.v_scales);
+    const bool carry_scales = p->mode == MODE_COPY && s.dtype == TKV_DTYPE_E4M3 && s.k_scales && d.k_scales;
+    a.src_k_scales = carry_scales ? reinterpret_cast<const float*>(s.k_scales) : nullptr;
+    a.src_v_scales = carry_scales ? reinterpret_cast<const float*>(s.v_scales) : nullptr;
+    a.src_total_blocks = s.total_blocks;
+    a.src_pool_heads = s.n_kv_heads;
+    a.src_head_begin = sh.src_head_begin;
+    a.src_layer_begin = sh.src_layer_begin;
     a.done_counter = reinterpret_cast<uint32_t*>(p->d_buf + off_counter);
     a.done_flag = nullptr;
     a.src_block_stride = (uint64_t)bs * s.n_kv_heads * s.head_dim * se;
@@ -331,6 +369,10 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     st.bytes_read = st.payload_bytes;
     st.bytes_written = tokens * L * 2ull * a.dst_row_bytes;
     if (p->mode == MODE_F16_E4M3 && d.k_scales) st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
+    if (carry_scales) {
+        st.bytes_read += pairs * L * 2ull * sh.n_heads * sizeof(float);
+        st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
+    }
     st.worklist_bytes = need;
     st.peer = s.device != d.device;
     return TKV_OK;
@@ -369,7 +411,8 @@ template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, 
 
 // Bulk-copy variant: only for same-device, contiguous, 16-byte aligned chunks.
 bool bulk_eligible(const tkv_plan* p) {
-    return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && p->src.device == p->dst.device;
+    return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && p->src.device == p->dst.device &&
+           !p->host_side && p->args.src_k_scales == nullptr;
 }
 
 int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
@@ -475,9 +518,8 @@ int32_t tkv_shutdown(void) {
     return TKV_OK;
 }
 
-int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch, const TkvShard* shard,
-                        uint32_t flags, tkv_plan** out) {
-    if (!src || !dst || !batch || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+static int32_t create_plan(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch, const TkvShard* shard,
+                           uint32_t flags, int virt, const TkvTransfer* xfer, tkv_plan** out) {
     *out = nullptr;
     TkvShard sh;
     if (shard) {
@@ -496,10 +538,14 @@ int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* 
     tkv_plan* p = new tkv_plan();
     p->src = *src;
     p->dst = *dst;
-    p->src_k.assign(src->k_layer_ptrs, src->k_layer_ptrs + src->n_layers);
-    p->src_v.assign(src->v_layer_ptrs, src->v_layer_ptrs + src->n_layers);
-    p->dst_k.assign(dst->k_layer_ptrs, dst->k_layer_ptrs + dst->n_layers);
-    p->dst_v.assign(dst->v_layer_ptrs, dst->v_layer_ptrs + dst->n_layers);
+    if (virt != 1) {
+        p->src_k.assign(src->k_layer_ptrs, src->k_layer_ptrs + src->n_layers);
+        p->src_v.assign(src->v_layer_ptrs, src->v_layer_ptrs + src->n_layers);
+    }
+    if (virt != 2) {
+        p->dst_k.assign(dst->k_layer_ptrs, dst->k_layer_ptrs + dst->n_layers);
+        p->dst_v.assign(dst->v_layer_ptrs, dst->v_layer_ptrs + dst->n_layers);
+    }
     p->src.k_layer_ptrs = p->src_k.data();
     p->src.v_layer_ptrs = p->src_v.data();
     p->dst.k_layer_ptrs = p->dst_k.data();
@@ -507,6 +553,11 @@ int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* 
     p->shard = sh;
     p->flags = flags;
     p->mode = mode;
+    p->virt = virt;
+    if (xfer) {
+        p->xfer = *xfer;
+        p->host_side = xfer->host_memory != 0;
+    }
     rc = build_worklist(p, batch);
     if (rc) {
         tkv_plan_destroy(p);
@@ -514,6 +565,86 @@ int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* 
     }
     *out = p;
     return TKV_OK;
+}
+
+int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch, const TkvShard* shard,
+                        uint32_t flags, tkv_plan** out) {
+    if (!src || !dst || !batch || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    return create_plan(src, dst, batch, shard, flags, 0, nullptr, out);
+}
+
+// The transfer buffer described as a pool that holds exactly the shard: same geometry as
+// `like`, the shard's heads and layers only, block ids assigned later in work-list order.
+static int32_t transfer_as_pool(const TkvTransfer* x, const TkvPool* like, const TkvShard* shard, int side,
+                                TkvPool* vp, TkvShard* sh) {
+    if (!x->data) return fail(TKV_ERR_INVALID_CONFIG, "transfer buffer address is 0");
+    if (x->device < 0) return fail(TKV_ERR_INVALID_CONFIG, "transfer buffer names no device");
+    if (side == 2 && x->host_memory && x->device != like->device)
+        return fail(TKV_ERR_INVALID_CONFIG, "a host transfer buffer is written by the source pool's device %d, not %d", like->device, x->device);
+    if (elem_size(x->dtype) == 0) return fail(TKV_ERR_INVALID_CONFIG, "unknown transfer dtype %d", x->dtype);
+    if (x->scales && x->dtype != TKV_DTYPE_E4M3) return fail(TKV_ERR_INVALID_CONFIG, "only an E4M3 transfer buffer carries scales");
+    if (shard) {
+        *sh = *shard;
+    } else {
+        *sh = TkvShard{0, 0, like->n_kv_heads, 0, 0, like->n_layers};
+    }
+    // the buffer's own numbering starts at 0 whatever slice of the pool it holds
+    if (side == 1) {
+        sh->src_head_begin = 0;
+        sh->src_layer_begin = 0;
+    } else {
+        sh->dst_head_begin = 0;
+        sh->dst_layer_begin = 0;
+    }
+    *vp = TkvPool{};
+    vp->device = x->device;
+    vp->dtype = x->dtype;
+    vp->n_layers = sh->n_layers;
+    vp->n_kv_heads = sh->n_heads;
+    vp->head_dim = like->head_dim;
+    vp->block_size = like->block_size;
+    vp->total_blocks = 0;
+    static const uint64_t none = 0;
+    vp->k_layer_ptrs = &none;   // placeholders; the real addresses depend on the batch
+    vp->v_layer_ptrs = &none;
+    vp->k_scales = x->scales;   // split into K and V halves once the block count is known
+    vp->v_scales = x->scales;
+    return TKV_OK;
+}
+
+int32_t tkv_plan_create_to_transfer(const TkvPool* src, const TkvTransfer* xfer, const TkvBatch* batch,
+                                    const TkvShard* shard, uint32_t flags, tkv_plan** out) {
+    if (!src || !xfer || !batch || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    TkvPool vp;
+    TkvShard sh;
+    int32_t rc = transfer_as_pool(xfer, src, shard, 2, &vp, &sh);
+    if (rc) return rc;
+    return create_plan(src, &vp, batch, &sh, flags | TKV_PLAN_ALLOW_SHARED_DST, 2, xfer, out);
+}
+
+int32_t tkv_plan_create_from_transfer(const TkvTransfer* xfer, const TkvPool* dst, const TkvBatch* batch,
+                                      const TkvShard* shard, uint32_t flags, tkv_plan** out) {
+    if (!dst || !xfer || !batch || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    TkvPool vp;
+    TkvShard sh;
+    int32_t rc = transfer_as_pool(xfer, dst, shard, 1, &vp, &sh);
+    if (rc) return rc;
+    return create_plan(&vp, dst, batch, &sh, flags, 1, xfer, out);
+}
+
+uint64_t tkv_transfer_bytes(uint32_t n_layers, uint32_t n_heads, uint32_t head_dim, uint32_t block_size, int32_t dtype,
+                            uint64_t n_blocks) {
+    return 2ull * n_layers * n_blocks * block_size * n_heads * head_dim * elem_size(dtype);
+}
+
+uint64_t tkv_batch_blocks(const TkvBatch* b, uint32_t block_size) {
+    if (!b || !block_size || (b->n_seqs && !b->seq_lens)) return 0;
+    uint64_t n = 0;
+    for (uint32_t q = 0; q < b->n_seqs; q++) {
+        const uint32_t len = b->seq_lens[q], pre = b->prefix_lens ? b->prefix_lens[q] : 0u;
+        if (pre <= len) n += (len + block_size - 1) / block_size - pre / block_size;
+    }
+    return n;
 }
 
 int32_t tkv_plan_update(tkv_plan* p, const TkvBatch* batch) {
@@ -536,7 +667,7 @@ int32_t tkv_plan_stats(const tkv_plan* p, TkvStats* out) {
     if (!p || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
     *out = p->stats;
     out->grid = p->grid;
-    out->block = 256;
+    out->block = p->variant == TKV_VARIANT_BULK ? 32u : 256u;
     out->kernel_variant = p->variant;
     return TKV_OK;
 }

@@ -149,6 +149,51 @@ class Batch:
         return s
 
 
+@dataclass
+class Transfer:
+    """A contiguous transfer buffer (the batch form of KvCacheTransfer,
+    engine/src/kv_cache.rs:514-522): per moved layer a K plane then a V plane of the moved
+    blocks in work-list order.  ``data`` is a tensor on ``device``, or (``host``) a pinned
+    host tensor that ``device``'s kernel reads or writes over PCIe."""
+    data: torch.Tensor
+    dtype: int
+    device: int
+    scales: Optional[torch.Tensor] = None
+    host: bool = False
+
+    @staticmethod
+    def allocate(n_layers: int, n_heads: int, head_dim: int, block_size: int, n_blocks: int, dtype: str = "f16",
+                 device: int = 0, scales: bool = False, fill_byte: Optional[int] = None, host: bool = False) -> "Transfer":
+        dt = KvDtype[dtype]
+        nbytes = int(lib().tkv_transfer_bytes(n_layers, n_heads, head_dim, block_size, dt, n_blocks))
+        if host:
+            data = torch.empty(max(nbytes, 16), dtype=torch.uint8, pin_memory=True)
+        else:
+            data = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=torch.device("cuda", device))
+        if fill_byte is not None:
+            data.fill_(fill_byte)
+        sc = None
+        if scales:
+            shape = (2, n_layers, max(n_blocks, 1), n_heads)
+            sc = (torch.full(shape, -123.0, dtype=torch.float32, pin_memory=True) if host else
+                  torch.full(shape, -123.0, dtype=torch.float32, device=data.device))
+        return Transfer(data, dt, device, sc, host)
+
+    def planes(self, n_layers: int, n_blocks: int) -> torch.Tensor:
+        """[layer][K|V][block][bytes of one block] view of the used part of the buffer."""
+        used = self.data[: (self.data.numel() // max(2 * n_layers * n_blocks, 1)) * 2 * n_layers * n_blocks]
+        return used.view(n_layers, 2, n_blocks, -1)
+
+    def c_struct(self) -> N.TkvTransfer:
+        return N.TkvTransfer(self.device, self.dtype, 1 if self.host else 0, 0, self.data.data_ptr(), self.data.numel(),
+                             self.scales.data_ptr() if self.scales is not None else 0)
+
+
+def batch_blocks(batch: "Batch", block_size: int) -> int:
+    b = batch.c_struct()
+    return int(lib().tkv_batch_blocks(C.byref(b), block_size))
+
+
 def Shard(src_head_begin=0, dst_head_begin=0, n_heads=0, src_layer_begin=0, dst_layer_begin=0, n_layers=0) -> N.TkvShard:
     return N.TkvShard(src_head_begin, dst_head_begin, n_heads, src_layer_begin, dst_layer_begin, n_layers)
 
@@ -157,13 +202,38 @@ class Plan:
     """A validated, uploaded work list binding one batch to a source and a destination
     pool.  ``enqueue`` is asynchronous on a stream of the source device."""
 
-    def __init__(self, src: Pool, dst: Pool, batch: Batch, shard: Optional[N.TkvShard] = None, flags: int = 0):
-        self.src, self.dst = src, dst
-        self._s, self._d = src.c_struct(), dst.c_struct()
+    def __init__(self, src: Optional[Pool], dst: Optional[Pool], batch: Batch, shard: Optional[N.TkvShard] = None,
+                 flags: int = 0, transfer: Optional[Transfer] = None):
+        """``src`` and ``dst`` pools: the one-kernel handoff.  ``src`` and ``transfer``:
+        gather into a contiguous buffer (to_transfer).  ``transfer`` and ``dst``: scatter a
+        buffer into the pool (from_transfer)."""
+        self.src, self.dst, self.transfer = src, dst, transfer
         self._h = C.c_void_p()
         b = batch.c_struct()
-        check(lib().tkv_plan_create(C.byref(self._s), C.byref(self._d), C.byref(b),
-                                    C.byref(shard) if shard is not None else None, flags, C.byref(self._h)))
+        sh = C.byref(shard) if shard is not None else None
+        if transfer is None:
+            self._s, self._d = src.c_struct(), dst.c_struct()
+            self.launch_device = src.device
+            check(lib().tkv_plan_create(C.byref(self._s), C.byref(self._d), C.byref(b), sh, flags, C.byref(self._h)))
+        elif dst is None:
+            self._s, self._x = src.c_struct(), transfer.c_struct()
+            self.launch_device = src.device
+            check(lib().tkv_plan_create_to_transfer(C.byref(self._s), C.byref(self._x), C.byref(b), sh, flags,
+                                                    C.byref(self._h)))
+        else:
+            assert src is None, "give either two pools, or one pool and a transfer buffer"
+            self._d, self._x = dst.c_struct(), transfer.c_struct()
+            self.launch_device = transfer.device
+            check(lib().tkv_plan_create_from_transfer(C.byref(self._x), C.byref(self._d), C.byref(b), sh, flags,
+                                                      C.byref(self._h)))
+
+    @staticmethod
+    def to_transfer(src: Pool, transfer: Transfer, batch: Batch, shard: Optional[N.TkvShard] = None, flags: int = 0) -> "Plan":
+        return Plan(src, None, batch, shard, flags, transfer)
+
+    @staticmethod
+    def from_transfer(transfer: Transfer, dst: Pool, batch: Batch, shard: Optional[N.TkvShard] = None, flags: int = 0) -> "Plan":
+        return Plan(None, dst, batch, shard, flags, transfer)
 
     def update(self, batch: Batch) -> None:
         b = batch.c_struct()
@@ -171,12 +241,12 @@ class Plan:
 
     def enqueue(self, stream: Optional[torch.cuda.Stream] = None, done_flag: int = 0, flag_value: int = 0) -> None:
         if stream is None:
-            stream = torch.cuda.current_stream(self.src.device)
+            stream = torch.cuda.current_stream(self.launch_device)
         check(lib().tkv_handoff_enqueue(self._h, C.c_void_p(stream.cuda_stream), done_flag, flag_value))
 
     def refcount_apply(self, delta: int, stream: Optional[torch.cuda.Stream] = None) -> None:
         if stream is None:
-            stream = torch.cuda.current_stream(self.src.device)
+            stream = torch.cuda.current_stream(self.launch_device)
         check(lib().tkv_refcount_apply(self._h, delta, C.c_void_p(stream.cuda_stream)))
 
     def tune_bulk(self, stages: int, ctas_per_sm: int, stage_bytes: int = 32768) -> None:

@@ -47,3 +47,4 @@ def test_struct_layout_matches_header():
     assert C.sizeof(_native.TkvShard) == 24
     assert C.sizeof(_native.TkvPairing) == 32
     assert C.sizeof(_native.TkvStats) == 80
+    assert C.sizeof(_native.TkvTransfer) == 40
