@@ -309,12 +309,14 @@ def run_ours(args):
     multi = world > 1
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    pairs = max(1, world // 2)
-    is_prefill = rank < pairs
-    partner = rank + pairs if is_prefill else rank - pairs
-
+    if world > 1 and world % 2:
+        raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
     wname = args.workload or "cfg2"
     w = pick_workload(wname, world, args.pool_blocks, layers=args.layers)
+    from tempura_b200 import disagg
+    role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode)
+    pairs = max(1, world // 2)
+    is_prefill, partner = role.is_prefill, role.partner
     dst_dtype = w.dst_dtype
     scales = dst_dtype == "e4m3"
     flags = 0
@@ -332,8 +334,6 @@ def run_ours(args):
                               scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
         fill_source(src, w, 1234)
     else:
-        if world % 2:
-            raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
         info = None
         if not is_prefill:
             dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
