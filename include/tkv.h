@@ -134,12 +134,12 @@ typedef struct tkv_plan tkv_plan;
 enum {
     TKV_PLAN_DEFAULT = 0,
     TKV_PLAN_ALLOW_SHARED_DST = 1,  /* skip the "destination block ids are unique" check   */
-    TKV_PLAN_FORCE_VECTOR = 2,      /* use the register/vector copy kernel (no bulk copies) */
-    TKV_PLAN_FORCE_BULK = 4,        /* use the shared-memory bulk-copy pipeline             */
+    TKV_PLAN_FORCE_VECTOR = 2,      /* use the register kernels (vector copy, warp-per-head FP8) */
+    TKV_PLAN_FORCE_BULK = 4,        /* use the shared-memory bulk-copy pipelines (copy ring, staged FP8) */
     TKV_PLAN_INT_QUANTIZER = 8      /* FP8: integer bit-math encoder instead of cvt + flush */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
-       TKV_VARIANT_CAST_GENERIC = 5 };
+       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6 };
 
 /* ---- library -------------------------------------------------------------- */
 /* Copies the calling thread's last error text (NUL-terminated) into buf. */
@@ -233,7 +233,9 @@ int32_t tkv_handoff_noalloc(const TkvPool* src, const TkvPool* dst, const TkvBat
                             const TkvShard* shard /* NULL = everything */, void* stream);
 
 /* Tuning of the bulk-copy variant (ring depth per CTA, CTAs per SM, bytes per ring
- * stage); ctas_per_sm 0 derives it from the stage size.  No reference counterpart.
+ * stage); ctas_per_sm 0 derives it from the stage size.  The staged FP8 kernel takes the
+ * ring depth and the CTA cap from the same call (its stage is one chunk).  No reference
+ * counterpart.
  * Takes effect at the next enqueue.                                             */
 int32_t tkv_plan_tune_bulk(tkv_plan* plan, uint32_t stages, uint32_t ctas_per_sm, uint32_t stage_bytes);
 /* Caps the resident CTAs per SM of the register (non-bulk) kernels; 0 = as many as fit. */

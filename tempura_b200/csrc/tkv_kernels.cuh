@@ -478,6 +478,187 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
     signal_done(a);
 }
 
+// ---------------------------------------------------------------------------------
+// F16 -> E4M3 handoff, shared-memory staged (whole rows on the source side, 16 tokens
+// per block).  Thread 0 keeps a ring of source chunks in flight with the bulk async-copy
+// engine (cp.async.bulk global->shared completing on an mbarrier); the CTA's 8 warps
+// encode one kv head each out of shared memory into an output tile; the tile leaves as
+// ONE bulk store (destination on this device, whole rows) or as coalesced 16-byte stores
+// (peer destination or strided rows).  Memory latency is hidden by the ring, not by
+// registers.  Every wait is bounded: on a timeout the CTA records an error, drains its
+// copies and leaves.
+// ---------------------------------------------------------------------------------
+struct StagedItem {
+    uint64_t src, dst;
+    uint32_t n_valid, layer, is_v, dst_block;
+};
+
+template <int D, bool HW, bool SCALED>
+__global__ void __launch_bounds__(256) handoff_f16_e4m3_staged(const HandoffArgs a, uint32_t n_stages, uint32_t bulk_store,
+                                                               uint32_t* error_flag) {
+    constexpr int BS = 16;
+    constexpr int LPR = D / 8;         // lanes per token row
+    constexpr int RPP = 32 / LPR;      // token rows per pass
+    constexpr int NP = BS / RPP;
+    static_assert(D % 8 == 0 && LPR >= 2 && LPR <= 32 && (32 % LPR) == 0, "head_dim");
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                      // up to 8 barriers
+    uint32_t* fail_word = reinterpret_cast<uint32_t*>(smem + 64);
+    StagedItem* items = reinterpret_cast<StagedItem*>(smem + 128);           // 64 decoded items
+    const uint32_t in_bytes = BS * a.src_row_bytes, out_bytes = BS * a.dst_row_bytes;
+    unsigned char* in_base = smem + 128 + 64 * sizeof(StagedItem);           // 2176: 128-byte aligned
+    unsigned char* out_base = in_base + (size_t)n_stages * in_bytes;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t r0 = lane / LPR, col = lane % LPR;
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t n_mine = blockIdx.x < chunks ? (chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < n_stages; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bars + s)));
+        *fail_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // items [32*b, 32*b + 32) of this CTA, decoded by warp 0 into the half of the table batch b owns
+    auto decode_batch = [&](uint32_t b) {
+        uint32_t k = b * 32u + lane;
+        if (warp == 0 && k < n_mine) {
+            Chunk c = decode_chunk(a, blockIdx.x + k * gridDim.x);
+            StagedItem it;
+            it.src = reinterpret_cast<uint64_t>(c.src);
+            it.dst = reinterpret_cast<uint64_t>(c.dst);
+            it.n_valid = c.n_valid;
+            it.layer = c.layer;
+            it.is_v = c.is_v;
+            it.dst_block = c.dst_block;
+            items[(b & 1u) * 32u + lane] = it;
+        }
+    };
+    auto issue_load = [&](uint32_t k) {                                      // thread 0 only
+        const StagedItem it = items[k & 63u];
+        const uint32_t s = k % n_stages, bar = smem_u32(bars + s), bytes = it.n_valid * a.src_row_bytes;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_u32(in_base + (size_t)s * in_bytes)), "l"(it.src), "r"(bytes), "r"(bar) : "memory");
+    };
+
+    uint32_t decoded = 0;
+    if (n_mine) {
+        decode_batch(0);
+        decoded = 1;
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (uint32_t k = 0; k < min(n_stages, n_mine); k++) issue_load(k);
+
+    uint32_t failed = 0, k_fail = 0;
+    for (uint32_t k = 0; k < n_mine; k++) {
+        const uint32_t s = k % n_stages, o = k & 1u;
+        const uint32_t refill = k + n_stages;
+        if (refill < n_mine && refill / 32u >= decoded) {
+            decode_batch(refill / 32u);                                      // visible to thread 0 after the barrier below
+            decoded = refill / 32u + 1u;
+        }
+        const StagedItem it = items[k & 63u];
+        const bool ok = mbar_wait_bounded(smem_u32(bars + s), (k / n_stages) & 1u);
+        if (!ok) *fail_word = 1u;
+        const unsigned char* in = in_base + (size_t)s * in_bytes;
+        unsigned char* out = out_base + (size_t)o * out_bytes;
+        if (ok) {
+            for (uint32_t h = warp; h < a.n_heads; h += 8u) {
+                const unsigned char* sp = in + (size_t)h * D * 2 + col * 16;
+                unsigned char* dp = out + (size_t)h * D + col * 8;
+                uint4 v[NP];
+                uint32_t m = 0, amax = 0x7C00u;
+#pragma unroll
+                for (int p = 0; p < NP; p++) {
+                    uint32_t row = p * RPP + r0;
+                    if (row < it.n_valid) v[p] = *reinterpret_cast<const uint4*>(sp + (size_t)row * a.src_row_bytes);
+                    else v[p] = make_uint4(0, 0, 0, 0);
+                }
+                float inv = 1.0f;
+                if (SCALED) {
+#pragma unroll
+                    for (int p = 0; p < NP; p++) {
+                        m = amax_h2(m, v[p].x);
+                        m = amax_h2(m, v[p].y);
+                        m = amax_h2(m, v[p].z);
+                        m = amax_h2(m, v[p].w);
+                    }
+                    amax = max(m & 0xFFFFu, m >> 16);
+                    amax = __reduce_max_sync(0xFFFFFFFFu, amax);
+                    float scale = block_scale(amax, inv);
+                    if (lane == 0) {
+                        float* sc = it.is_v ? a.dst_v_scales : a.dst_k_scales;
+                        sc[((size_t)(a.dst_layer_begin + it.layer) * a.dst_total_blocks + it.dst_block) * a.dst_pool_heads +
+                           a.dst_head_begin + h] = scale;
+                    }
+                }
+                if (SCALED && HW && amax < 0x7C00u) {
+                    const uint32_t t = flush_threshold_bits(inv);
+                    const uint32_t t2u = t | (t << 16);
+                    const __half2 thr2 = *reinterpret_cast<const __half2*>(&t2u);
+#pragma unroll
+                    for (int p = 0; p < NP; p++) {
+                        uint32_t row = p * RPP + r0;
+                        uint2 q;
+                        q.x = __byte_perm(quant_h2_fast(v[p].x, inv, thr2), quant_h2_fast(v[p].y, inv, thr2), 0x5410);
+                        q.y = __byte_perm(quant_h2_fast(v[p].z, inv, thr2), quant_h2_fast(v[p].w, inv, thr2), 0x5410);
+                        if (row < it.n_valid) *reinterpret_cast<uint2*>(dp + (size_t)row * a.dst_row_bytes) = q;
+                    }
+                } else {
+#pragma unroll
+                    for (int p = 0; p < NP; p++) {
+                        uint32_t row = p * RPP + r0;
+                        uint2 q;
+                        q.x = quant_h2<HW>(v[p].x, inv) | (quant_h2<HW>(v[p].y, inv) << 16);
+                        q.y = quant_h2<HW>(v[p].z, inv) | (quant_h2<HW>(v[p].w, inv) << 16);
+                        if (row < it.n_valid) *reinterpret_cast<uint2*>(dp + (size_t)row * a.dst_row_bytes) = q;
+                    }
+                }
+            }
+            if (bulk_store) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();   // tile complete, stage s read by every warp
+        failed = *fail_word;
+        if (failed) {
+            k_fail = k;
+            break;
+        }
+        if (bulk_store) {
+            if (tid == 0) {
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(it.dst), "r"(smem_u32(out)), "r"(it.n_valid * a.dst_row_bytes) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                if (refill < n_mine) issue_load(refill);
+                // the store issued one iteration ago has read its tile: the next iteration may overwrite it
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
+        } else {
+            if (tid == 0 && refill < n_mine) issue_load(refill);
+            const uint32_t vec_per_row = a.dst_row_bytes / 16u, nvec = it.n_valid * vec_per_row;
+            for (uint32_t i = tid; i < nvec; i += 256u) {
+                uint32_t r = i / vec_per_row, c16 = i - r * vec_per_row;
+                uint4 q = *reinterpret_cast<const uint4*>(out + (size_t)i * 16);
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(it.dst) + (size_t)r * a.dst_row_stride + c16 * 16) = q;
+            }
+        }
+        __syncthreads();   // the other tile is free again
+    }
+    if (tid == 0) {
+        if (failed) {
+            // give the loads still in flight a bounded chance to land before leaving
+            for (uint32_t j = k_fail; j < n_mine && j < k_fail + n_stages; j++)
+                mbar_wait_bounded(smem_u32(bars + j % n_stages), (j / n_stages) & 1u);
+            if (error_flag) atomicExch(error_flag, 1u);
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    signal_done(a);
+}
+
 // Any head_dim / block_size: one warp per (chunk, kv head), two passes over the
 // source (the second one hits L2), element-wide accesses.
 template <bool HW, bool SCALED>

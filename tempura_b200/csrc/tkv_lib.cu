@@ -114,6 +114,7 @@ struct tkv_plan {
     TkvStats stats{};
     uint32_t grid = 0;
     uint32_t bulk_stages = 3, bulk_ctas_per_sm = 0, bulk_stage_bytes = 32768;  // ctas 0 = derive from the stage size
+    uint32_t fp8_stages = 2;         // staged FP8 kernel: ring depth per CTA
     uint32_t grid_ctas_per_sm = 0;   // cap for the register kernels (0 = occupancy limit)   // ring depth and residency of the bulk-copy kernel
     std::vector<uint8_t> seen;  // scratch bitmap over destination blocks
     std::vector<char> image;    // host image of the device block, built before any CUDA call
@@ -440,10 +441,59 @@ int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     return TKV_OK;
 }
 
+// Shared-memory staged FP8 variant: whole rows at the source (one contiguous run per chunk),
+// 16 tokens per block, device memory on the source side, and a ring that fits shared memory.
+bool staged_eligible(const tkv_plan* p, uint32_t* stages_out, size_t* smem_out) {
+    const tkv::HandoffArgs& a = p->args;
+    if (p->mode != MODE_F16_E4M3 || a.block_size != 16 || p->vec != 16) return false;
+    if (a.head_dim != 64 && a.head_dim != 128 && a.head_dim != 256) return false;
+    if (a.src_row_bytes != a.src_row_stride || p->host_side) return false;
+    const size_t in = 16 * (size_t)a.src_row_bytes, out = 16 * (size_t)a.dst_row_bytes;
+    // Measured on B200 (Llama-3.1-8B shape): the encode needs 16 resident warps per SM; two CTAs
+    // with a 2-deep ring each reach 1.00 of the copy peak, one CTA with any ring depth 0.76.
+    uint32_t stages = std::max(2u, std::min(8u, p->fp8_stages));
+    while (stages > 2 && 2176 + stages * in + 2 * out > 200 * 1024) stages--;
+    const size_t smem = 2176 + stages * in + 2 * out;
+    if (smem > 227 * 1024 || in >= (1u << 20)) return false;
+    *stages_out = stages;
+    *smem_out = smem;
+    return true;
+}
+
+template <int D, bool HW, bool SCALED> int32_t launch_fp8_staged(tkv_plan* p, uint32_t stages, size_t smem, cudaStream_t st) {
+    const tkv::HandoffArgs& a = p->args;
+    DevInfo di;
+    int32_t rc = dev_info(p->src.device, &di);
+    if (rc) return rc;
+    auto kernel = tkv::handoff_f16_e4m3_staged<D, HW, SCALED>;
+    CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    uint32_t per_sm = std::max<uint32_t>(1u, (uint32_t)((227 * 1024) / (smem + 1024)));
+    if (p->bulk_ctas_per_sm) per_sm = std::min(per_sm, p->bulk_ctas_per_sm);
+    per_sm = std::min(per_sm, 8u);
+    const uint64_t chunks = (uint64_t)a.n_pairs * a.n_layers * 2;
+    p->grid = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)di.sm_count * per_sm, chunks));
+    p->variant = TKV_VARIANT_FP8_STAGED;
+    const uint32_t bulk_store = (p->src.device == p->dst.device && a.dst_row_bytes == a.dst_row_stride) ? 1u : 0u;
+    uint32_t* err = a.done_counter + 1;
+    kernel<<<p->grid, 256, smem, st>>>(a, stages, bulk_store, err);
+    CU(cudaGetLastError());
+    return TKV_OK;
+}
+
 template <bool HW, bool SCALED> int32_t launch_fp8(tkv_plan* p, cudaStream_t st) {
     const tkv::HandoffArgs& a = p->args;
     const uint64_t warps = (uint64_t)a.n_pairs * a.n_layers * 2 * a.n_heads;
     const uint64_t ctas = (warps + 7) / 8;
+    uint32_t stages = 0;
+    size_t smem = 0;
+    const bool can_stage = staged_eligible(p, &stages, &smem);
+    if ((p->flags & TKV_PLAN_FORCE_BULK) && !can_stage)
+        return fail(TKV_ERR_INVALID_CONFIG, "the staged FP8 kernel needs whole source rows in device memory, 16-token blocks, head_dim 64/128/256 and 16-byte alignment");
+    if (can_stage && !(p->flags & TKV_PLAN_FORCE_VECTOR)) {
+        if (a.head_dim == 128) return launch_fp8_staged<128, HW, SCALED>(p, stages, smem, st);
+        if (a.head_dim == 64) return launch_fp8_staged<64, HW, SCALED>(p, stages, smem, st);
+        return launch_fp8_staged<256, HW, SCALED>(p, stages, smem, st);
+    }
     const bool fast = p->vec == 16 && a.block_size == 16;
     if (fast && a.head_dim == 128) {
         p->variant = TKV_VARIANT_FP8_WARP;
@@ -726,6 +776,7 @@ int32_t tkv_plan_tune_bulk(tkv_plan* p, uint32_t stages, uint32_t ctas_per_sm, u
     if (stage_bytes < 1024 || stage_bytes > 98304 || stage_bytes % 128)
         return fail(TKV_ERR_INVALID_CONFIG, "stage_bytes must be a multiple of 128 in [1024, 98304]");
     p->bulk_stages = stages;
+    p->fp8_stages = stages;
     p->bulk_ctas_per_sm = ctas_per_sm;
     p->bulk_stage_bytes = stage_bytes;
     return TKV_OK;

@@ -71,11 +71,39 @@ def test_config2_lengths_exact_multiple_and_single_token(H):
 
 
 # ---- config 3 shape: F16 -> E4M3 + scales ----------------------------------------------
-@pytest.mark.parametrize("flags", [0, N.PLAN_INT_QUANTIZER])
-def test_config3_shape_fp8_scaled(H, flags):
+@pytest.mark.parametrize("flags,variant", [(0, 6), (N.PLAN_INT_QUANTIZER, 6), (N.PLAN_FORCE_VECTOR, 3),
+                                           (N.PLAN_FORCE_VECTOR | N.PLAN_INT_QUANTIZER, 3), (N.PLAN_FORCE_BULK, 6)])
+def test_config3_shape_fp8_scaled(H, flags, variant):
     w = reduced_8b(dst_dtype="e4m3", outlier_channels=(5, 77), outlier_gain=20.0, seed=2)
     plan, *_ = run_case(H, w, flags=flags)
-    assert plan.stats().kernel_variant == 3      # warp-per-(block, head) register kernel
+    # 6: shared-memory staged kernel (default for whole rows); 3: warp-per-(block, head) register kernel
+    assert plan.stats().kernel_variant == variant and plan.device_error() == 0
+
+
+@pytest.mark.parametrize("tune", [(2, 0), (2, 1), (4, 1), (8, 1)])
+def test_fp8_staged_ring_depths_and_completion_flag(H, tune):
+    import torch
+    w = reduced_8b(n_layers=2, n_seqs=9, lo=1, hi=200, dst_dtype="e4m3", outlier_channels=(9,), outlier_gain=20.0, seed=21)
+    hs, hd = host_pools(w)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "e4m3")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "f16_e4m3")
+    plan = H.Plan(ds, dd, device_batch(w), None, N.PLAN_FORCE_BULK)
+    plan.tune_bulk(tune[0], tune[1], 32768)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for gen in (1, 2):                                   # twice: the completion counter re-arms itself
+        plan.enqueue(done_flag=flag.data_ptr(), flag_value=gen)
+        H.flag_wait_host(0, flag.data_ptr(), gen, 5_000_000)
+    assert plan.stats().kernel_variant == 6 and plan.device_error() == 0
+    assert_pool_equals_host(dd, hd, f"staged fp8 {tune}")
+
+
+def test_fp8_staged_into_strided_destination_rows(H):
+    """Whole source rows, destination pool with more heads than the source: the staged
+    kernel leaves through plain stores instead of one bulk store."""
+    w = W.Workload("fp8-staged-strided", 2, 4, 128, 16, 64, 64, np.array([40, 33, 7], dtype=np.uint32), dst_dtype="e4m3", seed=22).build_tables()
+    sh, osh = H.Shard(0, 2, 4, 0, 0, 2), oracle.OrcShard(0, 2, 4, 0, 0, 2)
+    p, *_ = run_case(H, w, shard=sh, oshard=osh, dst_heads=8)
+    assert p.stats().kernel_variant == 6
 
 
 def test_config3_fp8_special_blocks(H):
@@ -101,7 +129,11 @@ def test_config3_fp8_special_blocks(H):
     hv[t[5], :, 5, :] = np.float16(448.0).view(np.uint16)    # amax exactly 448 -> inv exactly 1
     ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "e4m3")
     oracle.handoff(hs, hd, oracle_batch(w), None, "f16_e4m3")
-    for flags in (0, N.PLAN_INT_QUANTIZER):
+    for flags in (0, N.PLAN_INT_QUANTIZER, N.PLAN_FORCE_VECTOR, N.PLAN_FORCE_VECTOR | N.PLAN_INT_QUANTIZER):
+        dd.k[0].fill_(0x5A)                                  # every variant starts from an unwritten pool
+        dd.v[0].fill_(0x5A)
+        dd.k_scales.fill_(-123.0)
+        dd.v_scales.fill_(-123.0)
         plan = H.Plan(ds, dd, device_batch(w), None, flags)
         plan.enqueue()
         torch.cuda.synchronize()
@@ -185,6 +217,8 @@ def test_head_dim_64_and_256_fp8(H):
     for d, seed in ((64, 13), (256, 14)):
         w = W.Workload(f"d{d}", 2, 4, d, 16, 64, 64, np.array([37, 16, 5], dtype=np.uint32), dst_dtype="e4m3", seed=seed).build_tables()
         p, *_ = run_case(H, w)
+        assert p.stats().kernel_variant == 6
+        p, *_ = run_case(H, w, flags=N.PLAN_FORCE_VECTOR)
         assert p.stats().kernel_variant == 3
 
 
