@@ -324,6 +324,8 @@ def run_ours(args):
         flags |= H.N.PLAN_FORCE_VECTOR
     elif args.variant == "bulk":
         flags |= H.N.PLAN_FORCE_BULK
+    if args.peer_bulk:
+        flags |= H.N.PLAN_PEER_BULK_STORES
 
     sampler = ClockSampler(local)
     src = dst = None
@@ -563,6 +565,7 @@ def main():
     ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
+    ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")
     ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")

@@ -55,6 +55,18 @@ def test_peer_bulk_refused(H):
         plan.enqueue(torch.cuda.current_stream(0))
 
 
+def test_peer_bulk_stores_opt_in(H):
+    """With TKV_PLAN_PEER_BULK_STORES the shared-memory pipelines store into the peer pool
+    with bulk copies; same bytes as the register path."""
+    w = W.Workload("peer-bulk-f16", 3, 8, 128, 16, 256, 256, W.lengths(6, 40, 300, 54, 7), seed=54).build_tables()
+    plan = _run(H, w, "copy", flags=N.PLAN_PEER_BULK_STORES)
+    assert plan.stats().kernel_variant == 2 and plan.device_error() == 0
+    w = W.Workload("peer-bulk-fp8", 2, 8, 128, 16, 256, 256, W.lengths(5, 30, 200, 55, 7), dst_dtype="e4m3",
+                   outlier_channels=(9,), outlier_gain=20.0, seed=55).build_tables()
+    plan = _run(H, w, "f16_e4m3", flags=N.PLAN_PEER_BULK_STORES)
+    assert plan.stats().kernel_variant == 6 and plan.device_error() == 0
+
+
 def test_peer_fp8_scaled_cast_before_the_wire(H):
     w = W.Workload("peer-fp8", 2, 8, 128, 16, 256, 256, W.lengths(5, 30, 200, 52, 7), dst_dtype="e4m3",
                    outlier_channels=(9,), outlier_gain=20.0, seed=52).build_tables()
