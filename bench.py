@@ -419,7 +419,7 @@ def run_ours(args):
         ms = ev0.elapsed_time(ev1)
     else:
         gen += args.steps
-        H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+        H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
         ms = (time.perf_counter() - t_wall0) * 1e3
     barrier()
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
@@ -439,7 +439,7 @@ def run_ours(args):
             if not multi:
                 H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
         else:
-            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+            H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
     torch.cuda.synchronize()
     res_s = time.perf_counter() - t0
     barrier()
@@ -479,9 +479,9 @@ def run_ours(args):
             plan_h.update(batch)
             plan_h.enqueue(stream, done_flag, gen)
             if not multi:
-                H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+                H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
         else:
-            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+            H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
     torch.cuda.synchronize()
     host_s = time.perf_counter() - t0
     barrier()

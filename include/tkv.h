@@ -249,7 +249,10 @@ int32_t tkv_plan_tune_grid(tkv_plan* plan, uint32_t ctas_per_sm);
 int32_t tkv_plan_error(const tkv_plan* plan, uint32_t* device_error);
 
 /* Bounded waits on a completion flag (uint32_t in device memory of the
- * waiting side).  Host form polls with small device->host copies; device form
+ * waiting side).  Flag values are generations: successive handoffs publish increasing
+ * values, and a wait for `expected` returns once the flag has reached OR PASSED it
+ * ((int32_t)(flag - expected) >= 0), so a waiter that polls late cannot miss a
+ * generation that a following handoff has already overwritten.  Host form polls with small device->host copies; device form
  * enqueues a one-thread kernel that spins at most max_spins times and records
  * TKV_OK or TKV_ERR_TIMEOUT in *status (device uint32_t).  Neither can hang.   */
 int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uint64_t timeout_us);

@@ -750,7 +750,7 @@ __global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, unsign
     uint32_t v = 0;
     for (unsigned long long i = 0; i < max_spins; i++) {
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (v == expected) {
+        if ((int32_t)(v - expected) >= 0) {   // generation reached or already passed
             if (status) *status = 0u;  // TKV_OK
             return;
         }

@@ -814,10 +814,10 @@ int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uin
         uint32_t v = 0;
         CU(cudaMemcpyAsync(&v, reinterpret_cast<const void*>(flag), 4, cudaMemcpyDeviceToHost, cs));
         CU(cudaStreamSynchronize(cs));
-        if (v == expected) return TKV_OK;
+        if ((int32_t)(v - expected) >= 0) return TKV_OK;   // generation reached or already passed
         auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
         if ((uint64_t)us >= timeout_us)
-            return fail(TKV_ERR_TIMEOUT, "flag still %u after %llu us (expected %u)", v, (unsigned long long)timeout_us, expected);
+            return fail(TKV_ERR_TIMEOUT, "flag still %u after %llu us (waiting for generation %u)", v, (unsigned long long)timeout_us, expected);
         std::this_thread::sleep_for(std::chrono::microseconds(20));
     }
 }

@@ -342,6 +342,12 @@ def test_done_flag_and_bounded_waits(H):
         assert int(status.item()) == 0
     oracle.handoff(hs, hd, oracle_batch(w))
     assert_pool_equals_host(dd, hd, "after flagged handoffs")
+    # a waiter that polls late: the flag (3) has passed the generation it waits for (1, 2)
+    for late in (1, 2):
+        H.flag_wait_host(0, flag.data_ptr(), late, 20_000)
+        H.flag_wait_enqueue(side, flag.data_ptr(), late, 2000, status.data_ptr())
+        side.synchronize()
+        assert int(status.item()) == 0
     # a flag nothing sets: both waits give up and say so; the context stays usable
     with pytest.raises(N.TkvError) as e:
         H.flag_wait_host(0, flag[1:].data_ptr(), 5, 20_000)
