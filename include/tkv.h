@@ -297,6 +297,33 @@ int32_t tkv_ipc_export(uint64_t devptr, uint8_t handle[64], uint64_t* offset_in_
 int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset_in_allocation, uint64_t* devptr);
 int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset_in_allocation);
 
+/* ---- the handoff's metadata on the wire -------------------------------------- */
+/* SessionTransfer {cache, position, seed, last_logits} (engine/src/session.rs:194-200)
+ * for a prefill and a decode process without a common address space: the cache is
+ * reduced to its geometry and the block table that names its blocks in the prefill
+ * pool (the K/V bytes travel through the handoff kernels, not through this message).
+ * Little-endian; layout: "TKVS", version, this header, n_blocks block ids, n_logits
+ * floats, FNV-1a-64 of everything before it.  A sequence may be announced in pieces:
+ * piece_index of piece_count names blocks [block_begin, block_begin + n_blocks).
+ * The reference derives serde traits and fixes no byte format (session.rs:194).     */
+typedef struct TkvSessionHeader {
+    uint64_t position;            /* tokens already in the cache                       */
+    uint64_t seed;                /* sampler RNG seed (StdRng::seed_from_u64)           */
+    uint32_t seq_len;
+    uint32_t n_layers, n_kv_heads, head_dim, block_size;
+    uint32_t kv_dtype;            /* TKV_DTYPE_* of the prefill pool                    */
+    uint32_t block_begin, n_blocks;
+    uint32_t piece_index, piece_count;
+    uint32_t n_logits;            /* last_logits (vocab_size floats), usually in the last piece */
+    uint32_t reserved;
+} TkvSessionHeader;
+size_t tkv_session_wire_size(const TkvSessionHeader* h);
+int32_t tkv_session_pack(const TkvSessionHeader* h, const uint32_t* blocks, const float* logits, uint8_t* out,
+                         size_t cap, size_t* written);
+/* `blocks` and `logits` point into `in` (4-byte aligned when `in` is). */
+int32_t tkv_session_unpack(const uint8_t* in, size_t len, TkvSessionHeader* h, const uint32_t** blocks,
+                           const float** logits);
+
 /* ---- host-side block bookkeeping ------------------------------------------- */
 /* PageAllocator (engine/src/kv_cache.rs:762-793) */
 typedef struct tkv_page_allocator tkv_page_allocator;

@@ -50,6 +50,12 @@ class TkvTransfer(C.Structure):
                 ("data", C.c_uint64), ("bytes", C.c_uint64), ("scales", C.c_uint64)]
 
 
+class TkvSessionHeader(C.Structure):
+    _fields_ = [("position", C.c_uint64), ("seed", C.c_uint64)] + [(n, C.c_uint32) for n in (
+        "seq_len", "n_layers", "n_kv_heads", "head_dim", "block_size", "kv_dtype", "block_begin", "n_blocks",
+        "piece_index", "piece_count", "n_logits", "reserved")]
+
+
 class TkvShard(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in (
         "src_head_begin", "dst_head_begin", "n_heads", "src_layer_begin", "dst_layer_begin", "n_layers")]
@@ -98,6 +104,9 @@ SIGNATURES = {
     "tkv_ipc_export": (_i32, [_u64, _u8p, _u64p]),
     "tkv_ipc_import": (_i32, [_u8p, _u64, _u64p]),
     "tkv_ipc_close": (_i32, [_u64, _u64]),
+    "tkv_session_wire_size": (_sz, [C.POINTER(TkvSessionHeader)]),
+    "tkv_session_pack": (_i32, [C.POINTER(TkvSessionHeader), _u32p, C.POINTER(C.c_float), _u8p, _sz, _szp]),
+    "tkv_session_unpack": (_i32, [_u8p, _sz, C.POINTER(TkvSessionHeader), C.POINTER(_u32p), C.POINTER(C.POINTER(C.c_float))]),
     "tkv_page_allocator_new": (_vp, [_sz]),
     "tkv_page_allocator_delete": (None, [_vp]),
     "tkv_page_allocator_allocate": (_i32, [_vp, _szp]),
