@@ -143,7 +143,7 @@ enum {
                                        always stores whole rows in bulk, local or peer.            */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
-       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6 };
+       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7 };
 
 /* ---- library -------------------------------------------------------------- */
 /* Copies the calling thread's last error text (NUL-terminated) into buf. */
@@ -168,7 +168,10 @@ int32_t tkv_shutdown(void);
  * dtype pairs: same dtype (byte copy), F16->E4M3 (per-block scales when the
  * destination has scale arrays, else unscaled as kernels/src/kv_scatter_write.rs:
  * 176-273), F32->F16 and F32->E4M3 (append_kv's casts, engine/src/kv_cache.rs:
- * 209-221; kernels/src/cutile_elementwise.rs:82-178).                         */
+ * 209-221; kernels/src/cutile_elementwise.rs:82-178), and E4M3->F16 / E4M3->F32,
+ * the reader's side of the FP8 cache (Fp8PagedKvCache::k_contiguous,
+ * engine/src/kv_cache.rs:1241-1271): exact decode of kernels/src/e4m3.rs:27-41 times
+ * the source pool's per-block scale when it has scale arrays.                  */
 int32_t tkv_plan_create(const TkvPool* src, const TkvPool* dst, const TkvBatch* batch,
                         const TkvShard* shard /* NULL = everything */, uint32_t flags,
                         tkv_plan** out);

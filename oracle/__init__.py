@@ -84,7 +84,8 @@ def lib() -> C.CDLL:
     sig("orc_paged_gather", None, vp, P(u32), sz, sz, sz, sz, vp)
     sig("orc_paged_scatter", None, vp, P(u32), sz, sz, sz, sz, sz, vp)
     sig("orc_transfer_layer", None, P(f32), sz, sz, C.c_int, vp)
-    for n in ("orc_handoff_copy", "orc_handoff_f16_to_e4m3", "orc_handoff_f32_to_f16"):
+    for n in ("orc_handoff_copy", "orc_handoff_f16_to_e4m3", "orc_handoff_f32_to_f16", "orc_handoff_e4m3_to_f16",
+              "orc_handoff_e4m3_to_f32"):
         sig(n, C.c_int, P(OrcPool), P(OrcPool), P(OrcBatch), P(OrcShard), C.c_int)
     sig("orc_refcount_apply", None, P(u32), P(OrcBatch), u32, C.c_int)
     sig("orc_bits_checksum_f32", u64, P(f32), sz)
@@ -196,7 +197,8 @@ def full_shard(src: HostPool, dst: HostPool) -> OrcShard:
     return OrcShard(0, 0, min(src.n_kv_heads, dst.n_kv_heads), 0, 0, min(src.n_layers, dst.n_layers))
 
 
-_MODES = {"copy": "orc_handoff_copy", "f16_e4m3": "orc_handoff_f16_to_e4m3", "f32_f16": "orc_handoff_f32_to_f16"}
+_MODES = {"copy": "orc_handoff_copy", "f16_e4m3": "orc_handoff_f16_to_e4m3", "f32_f16": "orc_handoff_f32_to_f16",
+          "e4m3_f16": "orc_handoff_e4m3_to_f16", "e4m3_f32": "orc_handoff_e4m3_to_f32"}
 
 
 def handoff(src: HostPool, dst: HostPool, batch: OrcBatch, shard: Optional[OrcShard] = None,

@@ -330,7 +330,7 @@ static int check_args(const orc_pool* s, const orc_pool* d, const orc_batch* b, 
     return 0;
 }
 
-enum { MODE_COPY = 0, MODE_F16_E4M3 = 1, MODE_F32_F16 = 2 };
+enum { MODE_COPY = 0, MODE_F16_E4M3 = 1, MODE_F32_F16 = 2, MODE_E4M3_F16 = 3, MODE_E4M3_F32 = 4 };
 
 /* One (sequence, layer, K|V) unit: gather the suffix tokens of the selected
  * heads into a contiguous buffer (k_contiguous, restricted to the shard's
@@ -369,6 +369,28 @@ static void handoff_unit(const orc_pool* s, const orc_pool* d, const orc_batch* 
             size_t off = orc_paged_row_offset(dt, bs, d_stride, pre + t, sh->dst_head_begin, D);
             uint16_t* o = (uint16_t*)dp + off;
             for (size_t i = 0; i < row; i++) o[i] = orc_f32_to_f16(f[t * row + i]);
+        }
+    } else if (mode == MODE_E4M3_F16 || mode == MODE_E4M3_F32) {
+        /* Fp8PagedKvCache::k_contiguous / v_contiguous (engine/src/kv_cache.rs:1241-1271) widen
+         * while they gather; the element decode is kernels/src/e4m3.rs:27-41 (the quantizer's
+         * own inverse, not the cache's private decoder), times the block's scale when the
+         * source pool has scale arrays: one round-to-nearest multiply, then RNE for F16.    */
+        const uint8_t* bsrc = (const uint8_t*)tmp;
+        const float* scales = is_v ? s->v_scales : s->k_scales;
+        const uint32_t sl = sh->src_layer_begin + l;
+        for (size_t t = 0; t < n_tok; t++) {
+            size_t off = orc_paged_row_offset(dt, bs, d_stride, pre + t, sh->dst_head_begin, D);
+            uint32_t blk = (uint32_t)((pre + t) / bs);
+            for (uint32_t h = 0; h < sh->n_heads; h++) {
+                float scale = scales ? scales[((size_t)sl * s->total_blocks + st[blk]) * s->n_kv_heads +
+                                              sh->src_head_begin + h]
+                                     : 1.0f;
+                for (uint32_t i = 0; i < D; i++) {
+                    volatile float x = orc_e4m3_to_f32(bsrc[t * row + (size_t)h * D + i]) * scale;
+                    if (mode == MODE_E4M3_F16) ((uint16_t*)dp)[off + (size_t)h * D + i] = orc_f32_to_f16(x);
+                    else ((float*)dp)[off + (size_t)h * D + i] = x;
+                }
+            }
         }
     } else { /* MODE_F16_E4M3 */
         const uint16_t* hsrc = (const uint16_t*)tmp;
@@ -411,6 +433,8 @@ static int handoff_run(const orc_pool* s, const orc_pool* d, const orc_batch* b,
     if (mode == MODE_F16_E4M3 && (s->elem_size != 2 || d->elem_size != 1 || (!d->k_scales != !d->v_scales)))
         return -8;
     if (mode == MODE_F32_F16 && (s->elem_size != 4 || d->elem_size != 2)) return -8;
+    if (mode == MODE_E4M3_F16 && (s->elem_size != 1 || d->elem_size != 2)) return -8;
+    if (mode == MODE_E4M3_F32 && (s->elem_size != 1 || d->elem_size != 4)) return -8;
     const long units = (long)b->n_seqs * sh->n_layers * 2;
     if (n_threads <= 1) {
         /* faithful order: the reference walks layers, K then V, with plain
@@ -440,6 +464,15 @@ int orc_handoff_f16_to_e4m3(const orc_pool* s, const orc_pool* d, const orc_batc
 int orc_handoff_f32_to_f16(const orc_pool* s, const orc_pool* d, const orc_batch* b,
                            const orc_shard* sh, int n_threads) {
     return handoff_run(s, d, b, sh, n_threads, MODE_F32_F16);
+}
+
+int orc_handoff_e4m3_to_f16(const orc_pool* s, const orc_pool* d, const orc_batch* b,
+                            const orc_shard* sh, int n_threads) {
+    return handoff_run(s, d, b, sh, n_threads, MODE_E4M3_F16);
+}
+int orc_handoff_e4m3_to_f32(const orc_pool* s, const orc_pool* d, const orc_batch* b,
+                            const orc_shard* sh, int n_threads) {
+    return handoff_run(s, d, b, sh, n_threads, MODE_E4M3_F32);
 }
 
 /* Block-level collapse of ref_count += 1 on lookup/probe

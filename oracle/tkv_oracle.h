@@ -132,6 +132,12 @@ int orc_handoff_f16_to_e4m3(const orc_pool* src, const orc_pool* dst, const orc_
 /* F32 source, F16 destination (from_transfer into a use_f16 cache).          */
 int orc_handoff_f32_to_f16(const orc_pool* src, const orc_pool* dst, const orc_batch* batch,
                            const orc_shard* shard, int n_threads);
+/* the reader's side of the FP8 cache: gather + widen (engine/src/kv_cache.rs:1241-1271),
+ * element decode kernels/src/e4m3.rs:27-41, times the source block scale if present */
+int orc_handoff_e4m3_to_f16(const orc_pool* src, const orc_pool* dst, const orc_batch* b,
+                            const orc_shard* sh, int n_threads);
+int orc_handoff_e4m3_to_f32(const orc_pool* src, const orc_pool* dst, const orc_batch* b,
+                            const orc_shard* sh, int n_threads);
 
 /* Block-level prefix refcounts: +1 (delta>0) on every dst block that lies
  * wholly inside a sequence's prefix_len, saturating -1 (delta<0).

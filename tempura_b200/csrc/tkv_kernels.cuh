@@ -721,6 +721,64 @@ __global__ void __launch_bounds__(256) handoff_f32_cast_generic(const HandoffArg
     signal_done(a);
 }
 
+__device__ __forceinline__ float e4m3_decode(uint32_t b) {
+    uint32_t sign = (b & 0x80u) << 24, exp = (b >> 3) & 0xFu, man = b & 7u;
+    return __uint_as_float(exp == 0u ? sign : (sign | ((exp + 120u) << 23) | (man << 20)));
+}
+
+// E4M3 source with a wider destination: the reader's side of the FP8 cache
+// (Fp8PagedKvCache::k_contiguous widens while it gathers).  Element rule: exact decode
+// (subnormal encodings read as signed zero), times the block's scale when the source pool
+// carries scales (one round-to-nearest multiply), then round to nearest even for F16.
+// One thread per 16 source bytes when everything is 16-byte aligned (VEC16), else per byte.
+// DST16: destination is F16 (else F32).
+template <bool DST16, bool VEC16>
+__global__ void __launch_bounds__(256) handoff_e4m3_dequant(const HandoffArgs a) {
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t D = a.head_dim;
+    constexpr uint32_t W = VEC16 ? 16u : 1u;
+    const uint32_t per_row = a.src_row_bytes / W;             // work items per token row
+    for (uint32_t w = blockIdx.x; w < chunks; w += gridDim.x) {
+        const Chunk c = decode_chunk(a, w);
+        const float* sc = c.is_v ? a.src_v_scales : a.src_k_scales;
+        const float* sc_blk = sc ? sc + ((size_t)(a.src_layer_begin + c.layer) * a.src_total_blocks + c.src_block) * a.src_pool_heads +
+                                       a.src_head_begin
+                                 : nullptr;
+        const uint32_t n = c.n_valid * per_row;
+        for (uint32_t i = threadIdx.x; i < n; i += 256u) {
+            const uint32_t r = i / per_row, e0 = (i - r * per_row) * W;   // first element of this item within the row
+            const float scale = sc_blk ? __ldg(sc_blk + e0 / D) : 1.0f;
+            const unsigned char* sp = reinterpret_cast<const unsigned char*>(c.src) + (size_t)r * a.src_row_stride + e0;
+            char* dp = c.dst + (size_t)r * a.dst_row_stride + (size_t)e0 * (DST16 ? 2 : 4);
+            if (VEC16) {
+                const uint4 q = ld_stream(reinterpret_cast<const uint4*>(sp));
+                const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+                float x[16];
+#pragma unroll
+                for (int k = 0; k < 16; k++) x[k] = __fmul_rn(e4m3_decode((words[k >> 2] >> ((k & 3) * 8)) & 0xFFu), scale);
+                if (DST16) {
+                    uint32_t h[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        h[k] = (uint32_t)__half_as_ushort(__float2half_rn(x[2 * k])) |
+                               ((uint32_t)__half_as_ushort(__float2half_rn(x[2 * k + 1])) << 16);
+                    reinterpret_cast<uint4*>(dp)[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                    reinterpret_cast<uint4*>(dp)[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        reinterpret_cast<float4*>(dp)[k] = make_float4(x[4 * k], x[4 * k + 1], x[4 * k + 2], x[4 * k + 3]);
+                }
+            } else {
+                const float x = __fmul_rn(e4m3_decode(*sp), scale);
+                if (DST16) *reinterpret_cast<__half*>(dp) = __float2half_rn(x);
+                else *reinterpret_cast<float*>(dp) = x;
+            }
+        }
+    }
+    signal_done(a);
+}
+
 // Non-template kernels have one definition per program: a second translation unit that
 // only needs the templates above defines TKV_KERNELS_TEMPLATES_ONLY before including.
 #ifndef TKV_KERNELS_TEMPLATES_ONLY
@@ -757,11 +815,6 @@ __global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, unsign
         __nanosleep(256);
     }
     if (status) *status = 4u;  // TKV_ERR_TIMEOUT
-}
-
-__device__ __forceinline__ float e4m3_decode(uint32_t b) {
-    uint32_t sign = (b & 0x80u) << 24, exp = (b >> 3) & 0xFu, man = b & 7u;
-    return __uint_as_float(exp == 0u ? sign : (sign | ((exp + 120u) << 23) | (man << 20)));
 }
 
 // dtype codes: 0 = F32, 1 = F16, 2 = E4M3

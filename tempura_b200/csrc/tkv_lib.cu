@@ -54,7 +54,7 @@ struct DeviceGuard {
 
 uint32_t elem_size(int32_t dt) { return dt == TKV_DTYPE_F32 ? 4u : dt == TKV_DTYPE_F16 ? 2u : dt == TKV_DTYPE_E4M3 ? 1u : 0u; }
 
-enum Mode { MODE_COPY, MODE_F16_E4M3, MODE_F32_F16, MODE_F32_E4M3 };
+enum Mode { MODE_COPY, MODE_F16_E4M3, MODE_F32_F16, MODE_F32_E4M3, MODE_E4M3_F16, MODE_E4M3_F32 };
 
 struct DevInfo {
     int sm_count = 0;
@@ -150,6 +150,8 @@ int32_t validate_pools(const TkvPool* s, const TkvPool* d, const TkvShard& sh, M
     else if (s->dtype == TKV_DTYPE_F16 && d->dtype == TKV_DTYPE_E4M3) *mode = MODE_F16_E4M3;
     else if (s->dtype == TKV_DTYPE_F32 && d->dtype == TKV_DTYPE_F16) *mode = MODE_F32_F16;
     else if (s->dtype == TKV_DTYPE_F32 && d->dtype == TKV_DTYPE_E4M3) *mode = MODE_F32_E4M3;
+    else if (s->dtype == TKV_DTYPE_E4M3 && d->dtype == TKV_DTYPE_F16) *mode = MODE_E4M3_F16;
+    else if (s->dtype == TKV_DTYPE_E4M3 && d->dtype == TKV_DTYPE_F32) *mode = MODE_E4M3_F32;
     else return fail(TKV_ERR_INVALID_CONFIG, "unsupported dtype pair %d -> %d", s->dtype, d->dtype);
     if ((d->k_scales == 0) != (d->v_scales == 0))
         return fail(TKV_ERR_INVALID_CONFIG, "k_scales and v_scales must both be set or both be 0");
@@ -318,7 +320,8 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     a.dst_v = dp + 3 * L;
     a.dst_k_scales = reinterpret_cast<float*>(d.k_scales);
     a.dst_v_scales = reinterpret_cast<float*>(d.v_scales);
-    const bool carry_scales = p->mode == MODE_COPY && s.dtype == TKV_DTYPE_E4M3 && s.k_scales && d.k_scales;
+    const bool dequant = p->mode == MODE_E4M3_F16 || p->mode == MODE_E4M3_F32;
+    const bool carry_scales = (p->mode == MODE_COPY && s.dtype == TKV_DTYPE_E4M3 && s.k_scales && d.k_scales) || (dequant && s.k_scales);
     a.src_k_scales = carry_scales ? reinterpret_cast<const float*>(s.k_scales) : nullptr;
     a.src_v_scales = carry_scales ? reinterpret_cast<const float*>(s.v_scales) : nullptr;
     a.src_total_blocks = s.total_blocks;
@@ -372,7 +375,7 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     if (p->mode == MODE_F16_E4M3 && d.k_scales) st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
     if (carry_scales) {
         st.bytes_read += pairs * L * 2ull * sh.n_heads * sizeof(float);
-        st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
+        if (!dequant) st.bytes_written += pairs * L * 2ull * sh.n_heads * sizeof(float);
     }
     st.worklist_bytes = need;
     st.peer = s.device != d.device;
@@ -768,6 +771,14 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         case MODE_F32_E4M3:
             p->variant = TKV_VARIANT_CAST_GENERIC;
             return launch(tkv::handoff_f32_cast_generic<1>, p, chunks, st);
+        case MODE_E4M3_F16:
+            p->variant = TKV_VARIANT_DEQUANT;
+            if (p->vec == 16 && a.head_dim % 16 == 0) return launch(tkv::handoff_e4m3_dequant<true, true>, p, chunks, st);
+            return launch(tkv::handoff_e4m3_dequant<true, false>, p, chunks, st);
+        case MODE_E4M3_F32:
+            p->variant = TKV_VARIANT_DEQUANT;
+            if (p->vec == 16 && a.head_dim % 16 == 0) return launch(tkv::handoff_e4m3_dequant<false, true>, p, chunks, st);
+            return launch(tkv::handoff_e4m3_dequant<false, false>, p, chunks, st);
     }
     return fail(TKV_ERR_INVALID_CONFIG, "unreachable mode");
 }

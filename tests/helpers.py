@@ -58,7 +58,8 @@ def oracle_batch(w: W.Workload, table_layer_stride=0):
 def mode_of(w: W.Workload) -> str:
     if w.src_dtype == w.dst_dtype:
         return "copy"
-    return {("f16", "e4m3"): "f16_e4m3", ("f32", "f16"): "f32_f16"}[(w.src_dtype, w.dst_dtype)]
+    return {("f16", "e4m3"): "f16_e4m3", ("f32", "f16"): "f32_f16", ("e4m3", "f16"): "e4m3_f16",
+            ("e4m3", "f32"): "e4m3_f32"}[(w.src_dtype, w.dst_dtype)]
 
 
 # ---- device side ------------------------------------------------------------------

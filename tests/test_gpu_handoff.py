@@ -413,3 +413,77 @@ def test_bits_checksum_matches_oracle(H):
     assert H.bits_checksum(hd, "f16") == L.orc_bits_checksum_f16_as_f32(h.ctypes.data_as(C.POINTER(C.c_uint16)), len(h))
     b = rng.integers(0, 256, 50_001, dtype=np.uint8)
     assert H.bits_checksum(torch.from_numpy(b).cuda(), "e4m3") == L.orc_bits_checksum_e4m3_as_f32(b.ctypes.data_as(C.POINTER(C.c_uint8)), len(b))
+
+
+# ---- the reader's side of the FP8 cache: gather + widen ----------------------------------------
+@pytest.mark.parametrize("dst_dtype", ["f16", "f32"])
+@pytest.mark.parametrize("scaled", [True, False])
+def test_e4m3_pool_widens_into_f16_and_f32(H, dst_dtype, scaled):
+    """Every E4M3 byte value (NaN encodings and subnormal encodings included) under seeded
+    per-block scales, against the oracle's decode * scale (kernels/src/e4m3.rs:27-41)."""
+    import torch
+    w = W.Workload("dequant", 2, 8, 128, 16, 64, 64, np.array([70, 16, 33, 1], dtype=np.uint32), src_dtype="e4m3",
+                   dst_dtype=dst_dtype, seed=31).build_tables()
+    hs, hd = host_pools(w, scales=False)
+    if scaled:
+        rng = np.random.default_rng(7)
+        hs.k_scales = (rng.random((2, 64, 8), dtype=np.float32) * 4 + 1e-3).astype(np.float32)
+        hs.v_scales = (rng.random((2, 64, 8), dtype=np.float32) * 200 + 1e-3).astype(np.float32)   # some products overflow F16
+    hs.block_view(hs.k[0])[w.src_tables[0][0], 0, 0, :] = np.arange(128, dtype=np.uint8)           # all byte values
+    hs.block_view(hs.k[0])[w.src_tables[0][0], 1, 0, :] = np.arange(128, 256, dtype=np.uint8)
+    ds, dd = to_device_pool(hs, "e4m3"), to_device_pool(hd, dst_dtype)
+    oracle.handoff(hs, hd, oracle_batch(w), None, mode_of(w))
+    plan = H.Plan(ds, dd, device_batch(w))
+    plan.enqueue()
+    torch.cuda.synchronize()
+    assert plan.stats().kernel_variant == N.VARIANT_DEQUANT
+    assert_pool_equals_host(dd, hd, f"dequant {dst_dtype} scaled={scaled}")
+
+
+def test_e4m3_widen_head_shard_and_odd_geometry(H):
+    w = W.Workload("dequant-shard", 2, 8, 128, 16, 64, 64, np.array([40, 33], dtype=np.uint32), src_dtype="e4m3", dst_dtype="f16",
+                   seed=32).build_tables()
+    hs, hd = host_pools(w, dst_heads=4, scales=False)
+    hs.k_scales = np.full((2, 64, 8), 0.5, dtype=np.float32)
+    hs.v_scales = np.linspace(0.1, 3.0, 2 * 64 * 8, dtype=np.float32).reshape(2, 64, 8)
+    ds, dd = to_device_pool(hs, "e4m3"), to_device_pool(hd, "f16")
+    osh, sh = oracle.OrcShard(3, 1, 3, 0, 0, 2), H.Shard(3, 1, 3, 0, 0, 2)
+    oracle.handoff(hs, hd, oracle_batch(w), osh, "e4m3_f16")
+    H.Plan(ds, dd, device_batch(w), sh).enqueue()
+    assert_pool_equals_host(dd, hd, "dequant shard")
+    # head_dim 24, block 4: the byte-wide form
+    w = W.Workload("dequant-odd", 1, 3, 24, 4, 16, 16, np.array([9, 4], dtype=np.uint32), src_dtype="e4m3", dst_dtype="f32", seed=33).build_tables()
+    hs, hd = host_pools(w, scales=False)
+    hs.k_scales = np.full((1, 16, 3), 2.0, dtype=np.float32)
+    hs.v_scales = np.full((1, 16, 3), 0.25, dtype=np.float32)
+    ds, dd = to_device_pool(hs, "e4m3"), to_device_pool(hd, "f32")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "e4m3_f32")
+    H.Plan(ds, dd, device_batch(w)).enqueue()
+    assert_pool_equals_host(dd, hd, "dequant odd")
+
+
+def test_quantize_then_widen_stays_within_one_e4m3_step(H):
+    """Property at the full config-3 shape of one layer: F16 -> scaled E4M3 -> F16 comes back within
+    2^-4 relative error of the block's absmax-scaled value (3 mantissa bits), exactly where the scale is 1."""
+    import torch
+    w = reduced_8b(n_layers=1, n_seqs=4, lo=100, hi=400, pool=256, dst_dtype="e4m3", outlier_channels=(3,), outlier_gain=20.0, seed=34)
+    hs, hq = host_pools(w)
+    ds, dq = to_device_pool(hs, "f16"), to_device_pool(hq, "e4m3")
+    back = H.Pool.allocate(0, 1, 8, 128, 16, 256, "f16", fill_byte=0)
+    batch = device_batch(w)
+    H.Plan(ds, dq, batch).enqueue()
+    own = H.Batch(w.seq_lens, w.dst_tables, w.dst_tables, w.table_stride)
+    H.Plan(dq, back, own, None, N.PLAN_ALLOW_SHARED_DST).enqueue()
+    torch.cuda.synchronize()
+    for q in range(len(w.seq_lens)):
+        nfull = int(w.seq_lens[q]) // 16
+        s = torch.from_numpy(w.src_tables[q, :nfull].astype(np.int64)).cuda()
+        d = torch.from_numpy(w.dst_tables[q, :nfull].astype(np.int64)).cuda()
+        x = ds.blocks(0).index_select(0, s).float()
+        y = back.blocks(0).index_select(0, d).float()
+        amax = x.abs().amax(dim=(1, 3), keepdim=True)
+        # an e4m3 step is 2^-3 of the value's binade; after scaling the largest binade is [256, 448]
+        assert bool(((x - y).abs() <= amax / 448 * 16 + amax * 2 ** -10 + 1e-6).all())   # half an E4M3 step + F16 rounding of the result
+        big = x.abs() >= amax / 448 * 2 ** -6 * 1.01            # not flushed
+        rel = ((x - y).abs() / x.abs().clamp_min(1e-9))[big]
+        assert float(rel.max()) <= 2 ** -4 + 1e-3

@@ -454,3 +454,37 @@ def test_block_scale_rule():
     s = L.orc_block_scale(0x4900, C.byref(inv))                                    # amax 10.0
     assert s == f32(np.float32(10.0) / np.float32(448.0))
     assert inv.value == f32(np.float32(448.0) / np.float32(10.0))
+
+
+def test_widening_gather_is_decode_times_scale():
+    """The reader's side of the FP8 cache: every byte value decodes as kernels/src/e4m3.rs:27-41
+    says (exp 0 -> signed zero, exp 15 through the normal path: 0x7F -> 480.0) and is multiplied
+    by the block's scale with one rounding; F16 output rounds that product to nearest even."""
+    from tempura_b200 import workloads as W
+    w = W.Workload("widen", 1, 2, 128, 16, 4, 4, np.array([16], dtype=np.uint32), src_dtype="e4m3", dst_dtype="f32", seed=1).build_tables()
+    src = oracle.HostPool.filled(1, 2, 128, 16, 4, np.uint8, 0, with_scales=True)
+    dst32 = oracle.HostPool.filled(1, 2, 128, 16, 4, np.float32, 0x5A)
+    dst16 = oracle.HostPool.filled(1, 2, 128, 16, 4, np.uint16, 0x5A)
+    sb, db = int(w.src_tables[0][0]), int(w.dst_tables[0][0])
+    view = src.block_view(src.k[0])
+    view[sb, 0, 0, :] = np.arange(128, dtype=np.uint8)
+    view[sb, 0, 1, :] = np.arange(128, 256, dtype=np.uint8)
+    src.k_scales[:] = 1.0
+    src.v_scales[:] = 1.0
+    src.k_scales[0, sb, 0] = np.float32(0.3)
+    src.k_scales[0, sb, 1] = np.float32(150.0)
+    batch = oracle.make_batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride)
+    oracle.handoff(src, dst32, batch, None, "e4m3_f32")
+    oracle.handoff(src, dst16, batch, None, "e4m3_f16")
+    got32 = dst32.block_view(dst32.k[0])[db, 0]
+    got16 = dst16.block_view(dst16.k[0])[db, 0]
+    dec = np.array([oracle.e4m3_to_f32(b) for b in range(256)], dtype=np.float32)
+    assert dec[0x7F] == 480.0 and dec[0x07] == 0.0 and dec[0x08] == 2.0 ** -6 and dec[0xFE] == -448.0
+    want0 = dec[:128] * np.float32(0.3)
+    want1 = dec[128:] * np.float32(150.0)
+    assert np.array_equal(got32[0].view(np.uint32), want0.view(np.uint32))
+    assert np.array_equal(got32[1].view(np.uint32), want1.view(np.uint32))
+    with np.errstate(over="ignore"):
+        assert np.array_equal(got16[0], want0.astype(np.float16).view(np.uint16))
+        assert np.array_equal(got16[1], want1.astype(np.float16).view(np.uint16))     # 480 * 150 overflows to -Inf / Inf
+    assert got16[1][0x7E] == 0xFC00                      # -448 * 150 -> -Inf in F16
