@@ -5,7 +5,8 @@
 The reference (Rust) cannot run in this image, so the fixtures freeze what the oracle, pinned
 to the reference's known-answer tests, produces for one small seeded handoff per dtype pair,
 special values included.  The FP8 scale rule is the one part no reference test pins; the
-fixture is what keeps it from drifting.  Files: handoff_small.npz.
+fixture is what keeps it from drifting.  Files: handoff_small.npz, and widen_small.npz (the
+E4M3 destination of the former widened back to F16 through its scales: the reader's rule).
 """
 import os
 import sys
@@ -53,6 +54,11 @@ def main():
             out["k_scales"], out["v_scales"] = hd.k_scales.copy(), hd.v_scales.copy()
     np.savez_compressed(os.path.join(HERE, "handoff_small.npz"), **out)
     print({k: (v.shape, str(v.dtype)) for k, v in out.items()})
+    # widen the E4M3 pool just produced (hd) back into an F16 pool at the same block ids
+    back = oracle.HostPool.filled(1, 2, 64, 16, 8, np.uint16, 0x5A)
+    own = oracle.make_batch(w.seq_lens, w.dst_tables, w.dst_tables, w.table_stride)
+    oracle.handoff(hd, back, own, None, "e4m3_f16")
+    np.savez_compressed(os.path.join(HERE, "widen_small.npz"), widen_dst_k=back.k[0].copy(), widen_dst_v=back.v[0].copy())
 
 
 if __name__ == "__main__":
