@@ -330,7 +330,9 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
     src = dst = None
-    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    # completion flag: page-locked host memory on one GPU (the kernel's release store lands where the
+    # host polls it, no copy per poll); device memory of the decode GPU when the waiter is another rank
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda") if multi else torch.zeros(4, dtype=torch.int32).pin_memory()
     if not multi:
         src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
         dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,

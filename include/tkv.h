@@ -200,8 +200,10 @@ uint64_t tkv_transfer_bytes(uint32_t n_layers, uint32_t n_heads, uint32_t head_d
                             int32_t dtype, uint64_t n_blocks);
 uint64_t tkv_batch_blocks(const TkvBatch* batch, uint32_t block_size);
 
-/* Re-validates and re-uploads a new batch into an existing plan (same pools,
- * shard and flags; no allocation unless the work list outgrew its capacity). */
+/* Re-validates a new batch into an existing plan (same pools, shard and flags; no allocation
+ * unless the work list outgrew its capacity).  The work list travels to the device in stream
+ * order at the head of the next tkv_handoff_enqueue, so an update may be issued while the
+ * plan's previous handoff is still running on that same stream.                          */
 int32_t tkv_plan_update(tkv_plan* plan, const TkvBatch* batch);
 int32_t tkv_plan_destroy(tkv_plan* plan);
 int32_t tkv_plan_stats(const tkv_plan* plan, TkvStats* out);
@@ -255,7 +257,9 @@ int32_t tkv_plan_error(const tkv_plan* plan, uint32_t* device_error);
  * waiting side).  Flag values are generations: successive handoffs publish increasing
  * values, and a wait for `expected` returns once the flag has reached OR PASSED it
  * ((int32_t)(flag - expected) >= 0), so a waiter that polls late cannot miss a
- * generation that a following handoff has already overwritten.  Host form polls with small device->host copies; device form
+ * generation that a following handoff has already overwritten.  The host form also accepts
+ * a flag in page-locked host memory (the kernel's system-scope store lands there) and then
+ * reads it in place instead of copying.  Host form polls with small device->host copies; device form
  * enqueues a one-thread kernel that spins at most max_spins times and records
  * TKV_OK or TKV_ERR_TIMEOUT in *status (device uint32_t).  Neither can hang.   */
 int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uint64_t timeout_us);

@@ -109,6 +109,10 @@ struct tkv_plan {
     char* h_buf = nullptr;  // pinned mirror
     size_t h_cap = 0;
     size_t off_work = 0, off_prefix = 0, used = 0;
+    // The pinned mirror goes to the device in stream order, at the head of the next enqueue (or
+    // refcount launch): `dirty` = mirror newer than the device copy, `upload_ev` = last upload.
+    bool dirty = false, upload_pending = false;
+    cudaEvent_t upload_ev = nullptr;
     uint32_t n_pairs = 0, n_prefix = 0;
     tkv::HandoffArgs args{};
     TkvStats stats{};
@@ -289,6 +293,12 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     {
         DeviceGuard g(s.device);
         if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", s.device);
+        if (!p->upload_ev) CU(cudaEventCreateWithFlags(&p->upload_ev, cudaEventDisableTiming));
+        // the previous upload must have left the pinned mirror before it is rewritten
+        if (p->upload_pending) {
+            CU(cudaEventSynchronize(p->upload_ev));
+            p->upload_pending = false;
+        }
         if (need > p->h_cap) {
             size_t cap = std::max(need, p->h_cap * 2);
             if (p->h_buf) cudaFreeHost(p->h_buf);
@@ -298,15 +308,11 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
             p->h_cap = p->d_cap = 0;
             CU(cudaMallocHost((void**)&p->h_buf, cap));
             CU(cudaMalloc((void**)&p->d_buf, cap));
+            CU(cudaMemset(p->d_buf, 0, cap));
             p->h_cap = p->d_cap = cap;
         }
-        // one pinned copy, waited for, so the plan is ready when we return
         memcpy(p->h_buf, p->image.data(), need);
-        cudaStream_t cs;
-        int32_t rc = copy_stream(s.device, &cs);
-        if (rc) return rc;
-        CU(cudaMemcpyAsync(p->d_buf, p->h_buf, need, cudaMemcpyHostToDevice, cs));
-        CU(cudaStreamSynchronize(cs));
+        p->dirty = true;
     }
 
     // kernel arguments
@@ -382,6 +388,39 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     return TKV_OK;
 }
 
+// Puts the plan's work list on the device in the order of `st`, ahead of whatever is launched
+// next on it; a stream that did not carry the upload waits for it.
+int32_t ensure_uploaded(tkv_plan* p, cudaStream_t st) {
+    if (p->dirty) {
+        CU(cudaMemcpyAsync(p->d_buf, p->h_buf, p->used, cudaMemcpyHostToDevice, st));
+        CU(cudaEventRecord(p->upload_ev, st));
+        p->dirty = false;
+        p->upload_pending = true;
+    } else if (p->upload_pending) {
+        CU(cudaStreamWaitEvent(st, p->upload_ev, 0));
+    }
+    return TKV_OK;
+}
+
+// cudaFuncSetAttribute is a driver call; remember the largest dynamic shared memory size granted
+// to each kernel on each device and only raise it.
+template <typename K> int32_t grant_smem(K kernel, int dev, size_t smem) {
+    static std::mutex mu;
+    static std::vector<std::pair<const void*, size_t>> granted[64];
+    std::lock_guard<std::mutex> lk(mu);
+    const void* key = reinterpret_cast<const void*>(kernel);
+    for (auto& g : granted[dev])
+        if (g.first == key) {
+            if (g.second >= smem) return TKV_OK;
+            CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            g.second = smem;
+            return TKV_OK;
+        }
+    CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    granted[dev].push_back({key, smem});
+    return TKV_OK;
+}
+
 template <typename K> int32_t occupancy_grid(K kernel, int dev, uint64_t work_ctas, uint32_t* grid) {
     DevInfo di;
     int32_t rc = dev_info(dev, &di);
@@ -431,7 +470,8 @@ int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     const uint32_t stages = std::max(2u, std::min(8u, p->bulk_stages));
     const size_t smem = 64 + 64 * sizeof(tkv::BulkItem) + (size_t)stages * stage;
     if (smem > 227 * 1024) return fail(TKV_ERR_INVALID_CONFIG, "bulk ring of %u x %u bytes exceeds shared memory", stages, stage);
-    CU(cudaFuncSetAttribute(tkv::handoff_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rc = grant_smem(tkv::handoff_copy_bulk, p->src.device, smem);
+    if (rc) return rc;
     // Measured on B200: throughput peaks near 96 KiB of ring per SM (3 x 32 KiB, one CTA) and
     // falls off when more is in flight, so smaller stages get proportionally more CTAs.
     uint32_t want = p->bulk_ctas_per_sm ? p->bulk_ctas_per_sm : std::max(1u, 98304u / (stages * stage));
@@ -470,7 +510,8 @@ template <int D, bool HW, bool SCALED> int32_t launch_fp8_staged(tkv_plan* p, ui
     int32_t rc = dev_info(p->src.device, &di);
     if (rc) return rc;
     auto kernel = tkv::handoff_f16_e4m3_staged<D, HW, SCALED>;
-    CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rc = grant_smem(kernel, p->src.device, smem);
+    if (rc) return rc;
     uint32_t per_sm = std::max<uint32_t>(1u, (uint32_t)((227 * 1024) / (smem + 1024)));
     if (p->bulk_ctas_per_sm) per_sm = std::min(per_sm, p->bulk_ctas_per_sm);
     per_sm = std::min(per_sm, 8u);
@@ -712,6 +753,10 @@ int32_t tkv_plan_destroy(tkv_plan* p) {
     if (!p) return TKV_OK;
     {
         DeviceGuard g(p->src.device);
+        if (p->upload_ev) {
+            if (p->upload_pending) cudaEventSynchronize(p->upload_ev);
+            cudaEventDestroy(p->upload_ev);
+        }
         if (p->h_buf) cudaFreeHost(p->h_buf);
         if (p->d_buf) cudaFree(p->d_buf);
     }
@@ -742,6 +787,10 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         if (done_flag) CU(cudaMemcpyAsync(reinterpret_cast<void*>(done_flag), &a.flag_value, 4, cudaMemcpyHostToDevice, st));
         p->grid = 0;
         return TKV_OK;
+    }
+    {
+        int32_t rc = ensure_uploaded(p, st);
+        if (rc) return rc;
     }
     switch (p->mode) {
         case MODE_COPY:
@@ -817,19 +866,31 @@ int32_t tkv_flag_wait_host(int32_t device, uint64_t flag, uint32_t expected, uin
     if (!flag) return fail(TKV_ERR_INVALID_CONFIG, "NULL flag");
     DeviceGuard g(device);
     if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", device);
-    cudaStream_t cs;
-    int32_t rc = copy_stream(device, &cs);
-    if (rc) return rc;
-    auto t0 = std::chrono::steady_clock::now();
+    // A flag in page-locked host memory is read in place; one in device memory through small copies.
+    cudaPointerAttributes attr{};
+    const bool in_host = cudaPointerGetAttributes(&attr, reinterpret_cast<const void*>(flag)) == cudaSuccess &&
+                         attr.type == cudaMemoryTypeHost && attr.hostPointer != nullptr;
+    if (!in_host) cudaGetLastError();
+    cudaStream_t cs = nullptr;
+    if (!in_host) {
+        int32_t rc = copy_stream(device, &cs);
+        if (rc) return rc;
+    }
+    const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
         uint32_t v = 0;
-        CU(cudaMemcpyAsync(&v, reinterpret_cast<const void*>(flag), 4, cudaMemcpyDeviceToHost, cs));
-        CU(cudaStreamSynchronize(cs));
+        if (in_host) {
+            v = __atomic_load_n(static_cast<const uint32_t*>(attr.hostPointer), __ATOMIC_ACQUIRE);
+        } else {
+            CU(cudaMemcpyAsync(&v, reinterpret_cast<const void*>(flag), 4, cudaMemcpyDeviceToHost, cs));
+            CU(cudaStreamSynchronize(cs));
+        }
         if ((int32_t)(v - expected) >= 0) return TKV_OK;   // generation reached or already passed
-        auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        const auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
         if ((uint64_t)us >= timeout_us)
             return fail(TKV_ERR_TIMEOUT, "flag still %u after %llu us (waiting for generation %u)", v, (unsigned long long)timeout_us, expected);
-        std::this_thread::sleep_for(std::chrono::microseconds(20));
+        // poll tightly while a handoff of ordinary size could still be finishing, then back off
+        if (us > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20));
     }
 }
 
@@ -850,6 +911,8 @@ int32_t tkv_refcount_apply(tkv_plan* p, int32_t delta, void* stream) {
     if (!p->dst.refcounts) return fail(TKV_ERR_INVALID_CONFIG, "destination pool has no refcount array");
     DeviceGuard g(p->src.device);
     if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    int32_t rc = ensure_uploaded(p, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
     uint32_t blocks = std::min<uint32_t>((p->n_prefix + 255) / 256, 1024);
     tkv::refcount_apply_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<uint32_t*>(p->dst.refcounts), reinterpret_cast<const uint32_t*>(p->d_buf + p->off_prefix),

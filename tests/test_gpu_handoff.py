@@ -348,6 +348,14 @@ def test_done_flag_and_bounded_waits(H):
         H.flag_wait_enqueue(side, flag.data_ptr(), late, 2000, status.data_ptr())
         side.synchronize()
         assert int(status.item()) == 0
+    # a flag in page-locked host memory: the kernel's release store lands there, the host reads it in place
+    hflag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    plan.enqueue(done_flag=hflag.data_ptr(), flag_value=11)
+    H.flag_wait_host(0, hflag.data_ptr(), 11, 5_000_000)
+    assert int(hflag[0]) == 11
+    with pytest.raises(N.TkvError) as e:
+        H.flag_wait_host(0, hflag.data_ptr(), 12, 20_000)
+    assert e.value.code == N.ERR_TIMEOUT
     # a flag nothing sets: both waits give up and say so; the context stays usable
     with pytest.raises(N.TkvError) as e:
         H.flag_wait_host(0, flag[1:].data_ptr(), 5, 20_000)

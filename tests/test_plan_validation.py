@@ -44,8 +44,12 @@ def test_dimension_mismatch_head_dim_and_block_size():
 
 def test_unsupported_dtype_pair_and_half_set_scales():
     b = batch([4], [[0]], [[0]], 1)
-    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(dtype="e4m3"), fake_pool(dtype="f16"), b))
     expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(dtype="f16"), fake_pool(dtype="f32"), b))
+    half = fake_pool(dtype="e4m3", scales=True)
+    half.k_scales_ptr = 0                                  # a source with only one of its two scale arrays
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(half, fake_pool(dtype="f16"), b))
+    # E4M3 -> E4M3 moves scales along: both sides carry them or neither does
+    expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(dtype="e4m3", scales=True), fake_pool(dtype="e4m3"), b))
     p = fake_pool(dtype="e4m3", scales=True)
     p.v_scales_ptr = 0
     expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), p, b))
