@@ -784,7 +784,7 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
     const uint64_t chunks = (uint64_t)a.n_pairs * a.n_layers * 2;
     if (chunks == 0) {
         // nothing moves; still publish the flag, in stream order
-        if (done_flag) CU(cudaMemcpyAsync(reinterpret_cast<void*>(done_flag), &a.flag_value, 4, cudaMemcpyHostToDevice, st));
+        if (done_flag) CU(cudaMemcpyAsync(reinterpret_cast<void*>(done_flag), &a.flag_value, 4, cudaMemcpyDefault, st));
         p->grid = 0;
         return TKV_OK;
     }

@@ -1,9 +1,9 @@
-"""BASELINE configs 2-5 at their FULL batch sizes on the GPU, checked through properties that
+"""Benchmark configurations 2-5 at their FULL batch sizes on the GPU, checked through properties that
 do not need the CPU oracle to walk gigabytes: every moved block compared with its source block
 by an independent torch gather (bit-exact), untouched memory still holding its fill pattern,
 prefix blocks unchanged with their refcounts raised, the two FP8 encoders agreeing byte for byte
 and the quantize -> widen round trip staying inside one E4M3 step.  Pools hold the blocks the
-batch needs (not BASELINE's 65 536) so two of them fit beside each other; tables stay shuffled."""
+batch needs (not the benchmark's 65 536-block free list) so two of them fit beside each other; tables stay shuffled."""
 import numpy as np
 import pytest
 
