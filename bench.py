@@ -109,7 +109,14 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------
 # workloads
 # ----------------------------------------------------------------------------------------
-def pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None, layers: int | None = None):
+def pick_workload(name: str, n_gpus: int, pool_blocks: int | None, heads: int | None = None, layers: int | None = None,
+                  single_tokens: int | None = None):
+    if single_tokens:               # latency probe: ONE prompt of that many tokens on the config-2/3 shape
+        from tempura_b200 import workloads as W
+        fn = W.llama8b_fp8 if name == "cfg3" else W.llama8b_f16
+        w = fn(pool_blocks=pool_blocks or 8192, n_seqs=1, lo=single_tokens, hi=single_tokens)
+        w.name += f"-1x{single_tokens}tok"
+        return w
     w = _pick_workload(name, n_gpus, pool_blocks, heads)
     if layers:                      # profiling aid: same batch and tables, fewer layers
         w.n_layers = layers
@@ -313,7 +320,7 @@ def run_ours(args):
     if world > 1 and world % 2:
         raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
     wname = args.workload or "cfg2"
-    w = pick_workload(wname, world, args.pool_blocks, layers=args.layers)
+    w = pick_workload(wname, world, args.pool_blocks, layers=args.layers, single_tokens=args.single_tokens)
     from tempura_b200 import disagg
     role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode)
     pairs = max(1, world // 2)
@@ -565,6 +572,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--pool-blocks", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep the batch, use fewer layers")
+    ap.add_argument("--single-tokens", type=int, default=None, help="latency probe: one prompt of this many tokens (cfg2/cfg3 shape)")
     ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
