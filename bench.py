@@ -563,13 +563,88 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------
+# the FP8 cache's consumer: decode attention over the pool the handoff filled (not the driver's line)
+# ----------------------------------------------------------------------------------------
+def run_attention(args):
+    """One decode step's attention for the config-3 batch: 32 layer launches back to back over the
+    E4M3 + scales pool (or the F16 pool with --attn-f16) that a handoff has just filled.  Bytes
+    counted: every cached K and V element of the batch once per layer, plus scales, q and out."""
+    import torch
+    from tempura_b200 import handoff as H
+    torch.cuda.set_device(0)
+    w = pick_workload("cfg3", 1, args.pool_blocks or 4096, layers=args.layers)
+    fp8 = not args.attn_f16
+    src = H.Pool.allocate(0, w.n_layers, 8, 128, 16, w.src_blocks, "f16")
+    fill_source(src, w, 77)
+    if fp8:
+        pool = H.Pool.allocate(0, w.n_layers, 8, 128, 16, w.dst_blocks, "e4m3", scales=True, fill_byte=0x5A)
+        H.Plan(src, pool, H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride)).enqueue()
+        tables_np = w.dst_tables
+    else:
+        pool, tables_np = src, w.src_tables
+    n, n_q = len(w.seq_lens), 32
+    tables = torch.from_numpy(tables_np.astype(np.int64)).to(torch.int32).cuda()
+    lens = torch.from_numpy(w.seq_lens.astype(np.int64)).to(torch.int32).cuda()
+    q = torch.randn((n, n_q, 128), device="cuda")
+    max_len = int(w.seq_lens.max())
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    attn = H.DecodeAttention(pool, q, tables, lens, max_len, split_tokens=args.attn_split, flags=1 if args.attn_per_head else 0,
+                             total_kv_tokens=0 if args.attn_no_hint else int(w.seq_lens.astype(np.int64).sum()))
+    for layer in range(w.n_layers):          # plain launches first (module load, argument structs)
+        attn.enqueue(layer)
+    torch.cuda.synchronize()
+    # one decode step's 32 attention launches as a CUDA graph, so the host's launch cost is not what is timed
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for layer in range(w.n_layers):
+            attn.enqueue(layer)
+    step = graph.replay
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler.mark()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    sampler.mark()
+    clocks = sampler.stop()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    tokens = int(w.seq_lens.astype(np.int64).sum())
+    blocks = int(((w.seq_lens.astype(np.int64) + 15) // 16).sum())
+    es = 1 if fp8 else 2
+    per_layer = tokens * 8 * 128 * 2 * es + (blocks * 8 * 2 * 4 if fp8 else 0) + 2 * n * n_q * 128 * 4
+    algo = per_layer * w.n_layers
+    peak, kind = measured_peaks()
+    achieved = algo / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "paged_decode_attention_GBps", "value": round(achieved, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 5), "us_per_layer": round(ms * 1e3 / w.n_layers, 2), "higher_is_better": True,
+        "dtype": "e4m3+scales -> f16 mma, f32 accumulate" if fp8 else "f16 mma, f32 accumulate", "data": "synthetic",
+        "config": {"workload": w.name + "-decode-attention", "layers": w.n_layers, "kv_heads": 8, "q_heads": n_q, "head_dim": 128,
+                   "n_seqs": n, "cached_tokens": tokens, "l2": "each layer's K/V is read once per step; a step reads more than L2 holds"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": None, "algorithmic_bytes": int(algo), "peak_source": f"{kind} copy peak"},
+        "gpu_launches": (args.warmup + args.steps) * w.n_layers * 2, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn"])
+    ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
+    ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
+    ap.add_argument("--attn-per-head", action="store_true", help="--workload attn: the per-(sequence, kv head) CTA form")
+    ap.add_argument("--attn-f16", action="store_true", help="--workload attn: read the F16 pool instead of the E4M3 one")
     ap.add_argument("--pool-blocks", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep the batch, use fewer layers")
     ap.add_argument("--single-tokens", type=int, default=None, help="latency probe: one prompt of this many tokens (cfg2/cfg3 shape)")
@@ -583,7 +658,9 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.workload == "attn":
+        run_attention(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -304,6 +304,40 @@ int32_t tkv_ipc_export(uint64_t devptr, uint8_t handle[64], uint64_t* offset_in_
 int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset_in_allocation, uint64_t* devptr);
 int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset_in_allocation);
 
+/* ---- decode attention over the paged pool (the FP8 cache's consumer) ---------- */
+/* One query token per sequence, grouped-query heads, K/V rows resolved through the block
+ * table, for one layer of an F16 or E4M3 pool; an E4M3 pool with scale arrays reads as
+ * decode(byte) * scale[layer][block][kv_head].  Replaces the reference's per-dtype decode
+ * twins OxideDecodeAttn::forward_d2d_ptrs_{f16,e4m3} / forward_batch_d2d_ptrs_{f16,e4m3}
+ * (kernels/src/oxide_decode_attn_host.rs:198-260,682-760), which read a contiguous run
+ * and assume unscaled E4M3; the arithmetic is paged_flash_attention
+ * (kernels/src/attention.rs:486-590) to FP16-input, FP32-accumulate tolerance.
+ * As there, kv_lens is a DEVICE array whose values are read when the kernel runs;
+ * max_kv_len (host) only sizes the grid and the scratch.  head_dim 128, 16-token blocks,
+ * 1..8 query heads per kv head.  All pointers are device memory of pool->device.       */
+typedef struct TkvDecodeAttn {
+    uint32_t n_seqs, n_q_heads, table_stride, layer, max_kv_len;
+    float sm_scale;               /* usually 1 / sqrt(head_dim)                              */
+    uint32_t split_tokens;        /* cached tokens per CTA, a multiple of 64; 0 = library's choice */
+    uint32_t flags;               /* TKV_ATTN_*                                               */
+    uint64_t q;                   /* f32 [n_seqs][n_q_heads][head_dim]                        */
+    uint64_t out;                 /* f32, same shape                                          */
+    uint64_t tables;              /* u32 [n_seqs][table_stride] block ids                     */
+    uint64_t kv_lens;             /* u32 [n_seqs]                                             */
+    uint64_t scratch;             /* tkv_decode_attn_scratch_bytes(...) bytes of device memory  */
+    uint64_t scratch_bytes;
+    uint64_t total_kv_tokens;     /* optional hint: sum of kv_lens as the host knows it (0 = unknown);
+                                     lets the library size the token ranges so the batch is one wave */
+    uint64_t status;              /* 0, or a device u32 the kernel sets to TKV_ERR_TIMEOUT if one
+                                     of its bounded waits gave up (the output is then not valid)  */
+} TkvDecodeAttn;
+enum { TKV_ATTN_DEFAULT = 0,
+       TKV_ATTN_PER_HEAD_CTAS = 1 /* one CTA per (sequence, kv head, split) with per-lane copies, the
+                                     form used when a pool has more than 8 kv heads               */ };
+uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
+                                       uint32_t split_tokens /* 0 = default */);
+int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* args, void* stream);
+
 /* ---- the handoff's metadata on the wire -------------------------------------- */
 /* SessionTransfer {cache, position, seed, last_logits} (engine/src/session.rs:194-200)
  * for a prefill and a decode process without a common address space: the cache is

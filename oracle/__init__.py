@@ -88,6 +88,7 @@ def lib() -> C.CDLL:
               "orc_handoff_e4m3_to_f32"):
         sig(n, C.c_int, P(OrcPool), P(OrcPool), P(OrcBatch), P(OrcShard), C.c_int)
     sig("orc_refcount_apply", None, P(u32), P(OrcBatch), u32, C.c_int)
+    sig("orc_paged_decode_attention", C.c_int, P(OrcPool), u32, P(f32), P(u32), u32, P(u32), u32, u32, f32, P(f32))
     sig("orc_bits_checksum_f32", u64, P(f32), sz)
     sig("orc_bits_checksum_f16_as_f32", u64, P(u16), sz)
     sig("orc_bits_checksum_e4m3_as_f32", u64, P(u8), sz)
@@ -208,6 +209,20 @@ def handoff(src: HostPool, dst: HostPool, batch: OrcBatch, shard: Optional[OrcSh
     rc = getattr(lib(), _MODES[mode])(C.byref(s), C.byref(d), C.byref(batch), C.byref(sh), n_threads)
     if rc != 0:
         raise ValueError(f"oracle rejected the handoff arguments (code {rc})")
+
+
+def paged_decode_attention(pool: HostPool, layer: int, q: np.ndarray, tables: np.ndarray, kv_lens, scale: float) -> np.ndarray:
+    """q: [n_seqs, num_heads, head_dim] f32 -> out of the same shape."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    tables = u32arr(tables)
+    kv_lens = u32arr(kv_lens)
+    out = np.empty_like(q)
+    s = pool.c_struct()
+    rc = lib().orc_paged_decode_attention(C.byref(s), layer, _p(q, C.c_float), _p(tables.reshape(-1), C.c_uint32), tables.shape[1],
+                                          _p(kv_lens, C.c_uint32), q.shape[0], q.shape[1], scale, _p(out, C.c_float))
+    if rc != 0:
+        raise ValueError(f"oracle rejected the attention arguments (code {rc})")
+    return out
 
 
 def refcount_apply(refcounts: np.ndarray, batch: OrcBatch, block_size: int, delta: int) -> None:

@@ -475,6 +475,78 @@ int orc_handoff_e4m3_to_f32(const orc_pool* s, const orc_pool* d, const orc_batc
     return handoff_run(s, d, b, sh, n_threads, MODE_E4M3_F32);
 }
 
+/* ---- decode attention over a paged pool (the FP8 cache's consumer) -------------------
+ * kernels/src/attention.rs:486-590 (paged_flash_attention) with seq_len == 1: tiles of
+ * FLASH_BC = 32 cached tokens (:343), online softmax in the reference's update order, K/V rows
+ * resolved through the block table by paged_row_offset (:472-484), GQA head h reading kv head
+ * h / (num_heads / num_kv_heads).  The pool may be F32, F16 or E4M3; an E4M3 element reads as
+ * orc_e4m3_to_f32(byte) times the block's scale when the pool has scale arrays (the rule of
+ * orc_handoff_e4m3_to_f32).  exp is libm's expf where the reference uses its own polynomial
+ * (kernels/src/portable_math.rs:5-40); the comparison with the GPU kernel is by tolerance. */
+static float pool_elem(const orc_pool* p, const char* layer, const float* scales, uint32_t l,
+                       const uint32_t* table, size_t tok, uint32_t kv_h, uint32_t d) {
+    size_t off = orc_paged_row_offset(table, p->block_size, (size_t)p->n_kv_heads * p->head_dim, tok, kv_h, p->head_dim) + d;
+    if (p->elem_size == 4) return ((const float*)layer)[off];
+    if (p->elem_size == 2) return orc_f16_to_f32(((const uint16_t*)layer)[off]);
+    float sc = scales ? scales[((size_t)l * p->total_blocks + table[tok / p->block_size]) * p->n_kv_heads + kv_h] : 1.0f;
+    volatile float x = orc_e4m3_to_f32(((const uint8_t*)layer)[off]) * sc;
+    return x;
+}
+
+int orc_paged_decode_attention(const orc_pool* p, uint32_t layer, const float* q, const uint32_t* tables,
+                               uint32_t table_stride, const uint32_t* kv_lens, uint32_t n_seqs,
+                               uint32_t num_heads, float scale, float* out) {
+    if (!p || !q || !tables || !kv_lens || !out || layer >= p->n_layers) return -1;
+    if (!num_heads || num_heads % p->n_kv_heads) return -2;
+    const uint32_t D = p->head_dim, hpg = num_heads / p->n_kv_heads, BC = 32;
+    const char* kl = p->k_layers[layer];
+    const char* vl = p->v_layers[layer];
+    float* o_acc = malloc(sizeof(float) * D);
+    float tile_scores[32];
+    for (uint32_t s = 0; s < n_seqs; s++) {
+        const uint32_t* table = tables + (size_t)s * table_stride;
+        const uint32_t kv_len = kv_lens[s];
+        if ((kv_len + p->block_size - 1) / p->block_size > table_stride) { free(o_acc); return -3; }
+        for (uint32_t h = 0; h < num_heads; h++) {
+            const uint32_t kv_h = h / hpg;
+            const float* qv = q + ((size_t)s * num_heads + h) * D;
+            float row_max = -INFINITY, row_sum = 0.0f;
+            for (uint32_t d = 0; d < D; d++) o_acc[d] = 0.0f;
+            for (uint32_t t0 = 0; t0 < kv_len; t0 += BC) {
+                const uint32_t t1 = t0 + BC < kv_len ? t0 + BC : kv_len;
+                float tile_max = -INFINITY;
+                for (uint32_t t = t0; t < t1; t++) {
+                    float dot = 0.0f;
+                    for (uint32_t d = 0; d < D; d++) dot += qv[d] * pool_elem(p, kl, p->k_scales, layer, table, t, kv_h, d);
+                    tile_scores[t - t0] = dot * scale;
+                    if (tile_scores[t - t0] > tile_max) tile_max = tile_scores[t - t0];
+                }
+                const float new_max = row_max > tile_max ? row_max : tile_max;
+                const float corr = row_max > -INFINITY ? expf(row_max - new_max) : 0.0f;
+                for (uint32_t d = 0; d < D; d++) o_acc[d] *= corr;
+                row_sum *= corr;
+                float tile_sum = 0.0f;
+                for (uint32_t t = t0; t < t1; t++) {
+                    tile_scores[t - t0] = expf(tile_scores[t - t0] - new_max);
+                    tile_sum += tile_scores[t - t0];
+                }
+                for (uint32_t t = t0; t < t1; t++) {
+                    const float w = tile_scores[t - t0];
+                    if (w == 0.0f) continue;
+                    for (uint32_t d = 0; d < D; d++) o_acc[d] += w * pool_elem(p, vl, p->v_scales, layer, table, t, kv_h, d);
+                }
+                row_sum += tile_sum;
+                row_max = new_max;
+            }
+            const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+            float* ov = out + ((size_t)s * num_heads + h) * D;
+            for (uint32_t d = 0; d < D; d++) ov[d] = o_acc[d] * inv;
+        }
+    }
+    free(o_acc);
+    return 0;
+}
+
 /* Block-level collapse of ref_count += 1 on lookup/probe
  * (engine/src/prefix_cache.rs:68, engine/src/kv_cache.rs:635) and
  * saturating_sub(1) on release (prefix_cache.rs:92, kv_cache.rs:691).       */

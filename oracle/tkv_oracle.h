@@ -150,6 +150,13 @@ uint64_t orc_bits_checksum_f32(const float* v, size_t n);
 uint64_t orc_bits_checksum_f16_as_f32(const uint16_t* v, size_t n);
 uint64_t orc_bits_checksum_e4m3_as_f32(const uint8_t* v, size_t n);
 
+/* ---- decode attention over a paged pool ---------------------------------------- */
+/* kernels/src/attention.rs:486-590 with one query token per sequence; q and out are
+ * [n_seqs][num_heads][head_dim] f32; E4M3 pools read as decode x block scale.      */
+int orc_paged_decode_attention(const orc_pool* pool, uint32_t layer, const float* q, const uint32_t* tables,
+                               uint32_t table_stride, const uint32_t* kv_lens, uint32_t n_seqs,
+                               uint32_t num_heads, float scale, float* out);
+
 /* ---- RadixTree (engine/src/prefix_cache.rs:17-149) ---------------------- */
 typedef struct orc_radix orc_radix;
 orc_radix* orc_radix_new(void);

@@ -23,6 +23,7 @@ OK, ERR_DIMENSION_MISMATCH, ERR_INVALID_CONFIG, ERR_CUDA, ERR_TIMEOUT, ERR_POOL_
 STATUS_NAMES = {0: "Ok", 1: "DimensionMismatch", 2: "InvalidConfig", 3: "CudaError", 4: "Timeout", 5: "PoolExhausted"}
 DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
 PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER, PLAN_PEER_BULK_STORES = 1, 2, 4, 8, 16
+ATTN_PER_HEAD_CTAS = 1
 VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC, VARIANT_FP8_STAGED, VARIANT_DEQUANT = 1, 2, 3, 4, 5, 6, 7
 
 
@@ -48,6 +49,11 @@ class TkvBatch(C.Structure):
 class TkvTransfer(C.Structure):
     _fields_ = [("device", C.c_int32), ("dtype", C.c_int32), ("host_memory", C.c_uint32), ("reserved", C.c_uint32),
                 ("data", C.c_uint64), ("bytes", C.c_uint64), ("scales", C.c_uint64)]
+
+
+class TkvDecodeAttn(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_seqs", "n_q_heads", "table_stride", "layer", "max_kv_len")] + [
+        ("sm_scale", C.c_float), ("split_tokens", C.c_uint32), ("flags", C.c_uint32)] + [(n, C.c_uint64) for n in ("q", "out", "tables", "kv_lens", "scratch", "scratch_bytes", "total_kv_tokens", "status")]
 
 
 class TkvSessionHeader(C.Structure):
@@ -104,6 +110,8 @@ SIGNATURES = {
     "tkv_ipc_export": (_i32, [_u64, _u8p, _u64p]),
     "tkv_ipc_import": (_i32, [_u8p, _u64, _u64p]),
     "tkv_ipc_close": (_i32, [_u64, _u64]),
+    "tkv_decode_attn_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
+    "tkv_decode_attn_enqueue": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvDecodeAttn), _vp]),
     "tkv_session_wire_size": (_sz, [C.POINTER(TkvSessionHeader)]),
     "tkv_session_pack": (_i32, [C.POINTER(TkvSessionHeader), _u32p, C.POINTER(C.c_float), _u8p, _sz, _szp]),
     "tkv_session_unpack": (_i32, [_u8p, _sz, C.POINTER(TkvSessionHeader), C.POINTER(_u32p), C.POINTER(C.POINTER(C.c_float))]),

@@ -346,3 +346,54 @@ def ipc_import(handle: bytes, offset: int) -> int:
     out = C.c_uint64(0)
     check(lib().tkv_ipc_import(h, offset, C.byref(out)))
     return out.value
+
+
+class DecodeAttention:
+    """Decode attention over the paged pool with its output and split scratch allocated once, so
+    a decode loop (or a CUDA graph capture) only issues launches.  ``q`` is f32
+    ``[n_seqs, n_q_heads, head_dim]`` on the pool's device, ``tables`` int32
+    ``[n_seqs, table_stride]`` block ids, ``kv_lens`` int32 ``[n_seqs]`` read by the kernel when
+    it runs.  (OxideDecodeAttn::forward_batch_d2d_ptrs_{f16,e4m3},
+    kernels/src/oxide_decode_attn_host.rs:682-760.)"""
+
+    def __init__(self, pool: Pool, q: torch.Tensor, tables: torch.Tensor, kv_lens: torch.Tensor, max_kv_len: int,
+                 sm_scale: Optional[float] = None, split_tokens: int = 0, flags: int = 0, total_kv_tokens: int = 0):
+        assert q.is_cuda and q.dtype == torch.float32 and q.is_contiguous() and q.dim() == 3
+        assert tables.is_cuda and tables.dtype == torch.int32 and tables.is_contiguous()
+        assert kv_lens.is_cuda and kv_lens.dtype == torch.int32
+        self.pool, self.q, self.tables, self.kv_lens = pool, q, tables, kv_lens
+        n_seqs, n_q_heads, head_dim = q.shape
+        self.sm_scale = 1.0 / float(head_dim) ** 0.5 if sm_scale is None else sm_scale
+        self.out = torch.empty_like(q)
+        need = int(lib().tkv_decode_attn_scratch_bytes(n_seqs, n_q_heads, head_dim, max_kv_len, split_tokens))
+        self.scratch = torch.empty(max(need, 4) // 4, dtype=torch.float32, device=q.device)
+        self._pool_c = pool.c_struct()
+        self._args = {}
+        self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        self._mk = lambda layer: N.TkvDecodeAttn(n_seqs, n_q_heads, tables.shape[1], layer, max_kv_len, self.sm_scale,
+                                                 split_tokens, flags, q.data_ptr(), self.out.data_ptr(), tables.data_ptr(),
+                                                 kv_lens.data_ptr(), self.scratch.data_ptr() if need else 0, need,
+                                                 total_kv_tokens, self.status.data_ptr())
+
+    def enqueue(self, layer: int, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        if stream is None:
+            stream = torch.cuda.current_stream(self.pool.device)
+        args = self._args.get(layer)
+        if args is None:
+            args = self._args[layer] = self._mk(layer)
+        check(lib().tkv_decode_attn_enqueue(C.byref(self._pool_c), C.byref(args), C.c_void_p(stream.cuda_stream)))
+        return self.out
+
+
+def decode_attention(pool: Pool, layer: int, q: torch.Tensor, tables: torch.Tensor, kv_lens: torch.Tensor,
+                     sm_scale: Optional[float] = None, max_kv_len: Optional[int] = None,
+                     stream: Optional[torch.cuda.Stream] = None, split_tokens: int = 0, flags: int = 0) -> torch.Tensor:
+    """One-shot form of :class:`DecodeAttention`; returns f32 of q's shape.  Raises if a bounded wait
+    inside the kernel gave up."""
+    if max_kv_len is None:
+        max_kv_len = int(kv_lens.max().item()) if q.shape[0] else 0
+    attn = DecodeAttention(pool, q, tables, kv_lens, max_kv_len, sm_scale, split_tokens, flags)
+    out = attn.enqueue(layer, stream)
+    if int(attn.status.item()) != 0:
+        raise TkvError(int(attn.status.item()), "decode attention: a bounded wait inside the kernel gave up")
+    return out

@@ -1,0 +1,161 @@
+"""Decode attention over the paged pool (the consumer of the FP8 cache) against the oracle's
+restatement of paged_flash_attention (kernels/src/attention.rs:486-590).  Floating point:
+the kernel feeds FP16 operands (q, probabilities; K/V are exact in FP16) to FP32-accumulating
+tensor-core MMAs, the oracle computes in FP32, so the comparison is by tolerance:
+|got - want| <= 4e-3 * max|V[:, d]| + 2e-3 * |want| per output dim d (2^-11 relative on q and on
+each probability: about 3e-3 on a score in the worst case, hence on the weights of V)."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import device_batch, host_pools, oracle_batch, to_device_pool
+from tempura_b200 import _native as N
+from tempura_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+ATOL_REL_V, RTOL = 4e-3, 2e-3
+
+
+@pytest.fixture(scope="module")
+def H():
+    import torch
+    assert torch.cuda.is_available()
+    from tempura_b200 import handoff
+    return handoff
+
+
+def close(got, want, vmax):
+    err = np.abs(got - want)
+    bound = ATOL_REL_V * vmax + RTOL * np.abs(want)
+    assert np.isfinite(got).all()
+    assert (err <= bound).all(), f"max err {err.max():.3e} at bound {bound.flat[err.argmax()]:.3e}"
+
+
+def run(H, pool_host, pool_dev, w, n_q_heads, seed, layers=None, flags=0):
+    import torch
+    rng = np.random.default_rng(seed)
+    n = len(w.seq_lens)
+    tables = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()
+    lens = torch.from_numpy(w.seq_lens.astype(np.int64)).to(torch.int32).cuda()
+    for layer in (layers if layers is not None else range(pool_host.n_layers)):
+        q = rng.standard_normal((n, n_q_heads, 128)).astype(np.float32)
+        got = H.decode_attention(pool_dev, layer, torch.from_numpy(q).cuda(), tables, lens, flags=flags).cpu().numpy()
+        want = oracle.paged_decode_attention(pool_host, layer, q, w.dst_tables, w.seq_lens, 1.0 / np.sqrt(128.0))
+        yield got, want
+
+
+def v_max_per_dim(hs, layer=0):
+    """max |V| per head_dim channel over the whole F16 source pool's seeded blocks (0xA5 filler excluded by magnitude cap)."""
+    v = hs.block_view(hs.v[layer]).view(np.float16).astype(np.float32)
+    v = np.where(np.isfinite(v) & (np.abs(v) < 1e3), v, 0.0)
+    return np.maximum(np.abs(v).max(axis=(0, 1, 2)), 1e-3)
+
+
+def quantized_pool(H, w):
+    """F16 source -> the handoff's own E4M3 + scales destination, on host (oracle) and device (CUDA)."""
+    import torch
+    hs, hd = host_pools(w)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "e4m3")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "f16_e4m3")
+    H.Plan(ds, dd, device_batch(w)).enqueue()
+    torch.cuda.synchronize()
+    return hs, hd, dd
+
+
+@pytest.mark.parametrize("flags", [0, N.ATTN_PER_HEAD_CTAS])
+def test_fp8_scaled_pool_matches_oracle_attention(H, flags):
+    # ragged lengths around the block (16), tile (32) and split (512) boundaries; 32 query heads on 8 kv heads
+    lens = np.array([1, 15, 16, 17, 33, 511, 512, 513, 1300], dtype=np.uint32)
+    w = W.Workload("attn-fp8", 2, 8, 128, 16, 512, 512, lens, dst_dtype="e4m3", outlier_channels=(7,), outlier_gain=20.0, seed=61).build_tables()
+    hs, hd, dd = quantized_pool(H, w)
+    for layer, (got, want) in enumerate(run(H, hd, dd, w, 32, seed=1, flags=flags)):
+        close(got, want, v_max_per_dim(hs, layer))          # the x20 outlier channel gets its own bound
+    # the split size only changes how partial softmaxes are merged
+    import torch
+    q = torch.randn((len(lens), 32, 128), generator=torch.Generator().manual_seed(9)).cuda()
+    tables = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()
+    lens_t = torch.from_numpy(lens.astype(np.int64)).to(torch.int32).cuda()
+    want = oracle.paged_decode_attention(hd, 1, q.cpu().numpy(), w.dst_tables, lens, 1.0 / np.sqrt(128.0))
+    for split in (64, 256, 512, 4096):
+        got = H.decode_attention(dd, 1, q, tables, lens_t, split_tokens=split, flags=flags).cpu().numpy()
+        close(got, want, v_max_per_dim(hs, 1))
+    with pytest.raises(N.TkvError):
+        H.decode_attention(dd, 1, q, tables, lens_t, split_tokens=100)
+
+
+@pytest.mark.parametrize("flags", [0, N.ATTN_PER_HEAD_CTAS])
+def test_fp8_unscaled_pool_and_f16_pool(H, flags):
+    import torch
+    lens = np.array([40, 700, 5], dtype=np.uint32)
+    w = W.Workload("attn-raw", 1, 8, 128, 16, 128, 128, lens, dst_dtype="e4m3", seed=62).build_tables()
+    hs, hd = host_pools(w, scales=False)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "e4m3")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "f16_e4m3")
+    H.Plan(ds, dd, device_batch(w)).enqueue()
+    torch.cuda.synchronize()
+    for got, want in run(H, hd, dd, w, 8, seed=2, flags=flags):          # one query head per kv head
+        close(got, want, v_max_per_dim(hs))
+    # the F16 pool the E4M3 one was made from, read in place (source tables)
+    w2 = W.Workload("attn-f16", 1, 8, 128, 16, 128, 128, lens, seed=62).build_tables()
+    w2.dst_tables = w.src_tables
+    for got, want in run(H, hs, ds, w2, 64, seed=3, flags=flags):        # 8 query heads per kv head
+        close(got, want, v_max_per_dim(hs))
+
+
+def test_four_kv_heads_and_more_than_eight(H):
+    """4 kv heads ride the whole-block form with idle consumer warps; 16 kv heads take the per-head form."""
+    import torch
+    for heads, n_q in ((4, 16), (16, 32)):
+        w = W.Workload(f"attn-h{heads}", 1, heads, 128, 16, 64, 64, np.array([90, 300], dtype=np.uint32), dst_dtype="e4m3", seed=64).build_tables()
+        hs, hd, dd = quantized_pool(H, w)
+        for got, want in run(H, hd, dd, w, n_q, seed=5):
+            close(got, want, v_max_per_dim(hs))
+
+
+def test_shuffled_tables_equal_identity_tables(H):
+    """The reference's own property (test_paged_attention_identity_and_shuffled_match_flash): where the
+    blocks sit does not change the result, bit for bit."""
+    import torch
+    lens = np.array([200, 77], dtype=np.uint32)
+    w = W.Workload("attn-perm", 1, 8, 128, 16, 64, 64, lens, dst_dtype="e4m3", seed=63).build_tables()
+    hs, hd, dd = quantized_pool(H, w)
+    q = torch.randn((2, 32, 128), generator=torch.Generator().manual_seed(4)).cuda()
+    lens_t = torch.from_numpy(lens.astype(np.int64)).to(torch.int32).cuda()
+    shuffled = H.decode_attention(dd, 0, q, torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda(), lens_t)
+    # lay the same blocks out in order in a second pool
+    ident = H.Pool.allocate(0, 1, 8, 128, 16, 64, "e4m3", scales=True)
+    order = np.full_like(w.dst_tables, 0)
+    nxt = 0
+    for qi in range(2):
+        nb = (int(lens[qi]) + 15) // 16
+        for i in range(nb):
+            src_id = int(w.dst_tables[qi, i])
+            for is_v in (False, True):
+                ident.blocks(0, is_v)[nxt].copy_(dd.blocks(0, is_v)[src_id])
+            ident.k_scales[0, nxt].copy_(dd.k_scales[0, src_id])
+            ident.v_scales[0, nxt].copy_(dd.v_scales[0, src_id])
+            order[qi, i] = nxt
+            nxt += 1
+    same = H.decode_attention(ident, 0, q, torch.from_numpy(order.astype(np.int64)).to(torch.int32).cuda(), lens_t)
+    assert torch.equal(shuffled, same)
+
+
+def test_attention_argument_errors(H):
+    import torch
+    pool = H.Pool.allocate(0, 1, 8, 64, 16, 8, "f16")
+    q = torch.zeros((1, 8, 64), device="cuda")
+    t = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    n = torch.ones(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(N.TkvError) as e:
+        H.decode_attention(pool, 0, q, t, n)
+    assert e.value.code == N.ERR_DIMENSION_MISMATCH          # head_dim 64
+    pool = H.Pool.allocate(0, 1, 8, 128, 16, 8, "f16")
+    with pytest.raises(N.TkvError) as e:
+        H.decode_attention(pool, 0, torch.zeros((1, 12, 128), device="cuda"), t, n)
+    assert e.value.code == N.ERR_DIMENSION_MISMATCH          # 12 query heads on 8 kv heads
+    with pytest.raises(N.TkvError) as e:
+        H.decode_attention(pool, 3, torch.zeros((1, 8, 128), device="cuda"), t, n)
+    assert e.value.code == N.ERR_INVALID_CONFIG               # layer outside the pool
+    with pytest.raises(N.TkvError) as e:
+        H.decode_attention(pool, 0, torch.zeros((1, 8, 128), device="cuda"), t, n, max_kv_len=40)
+    assert e.value.code == N.ERR_DIMENSION_MISMATCH          # table too short for max_kv_len

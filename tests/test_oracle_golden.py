@@ -488,3 +488,38 @@ def test_widening_gather_is_decode_times_scale():
         assert np.array_equal(got16[0], want0.astype(np.float16).view(np.uint16))
         assert np.array_equal(got16[1], want1.astype(np.float16).view(np.uint16))     # 480 * 150 overflows to -Inf / Inf
     assert got16[1][0x7E] == 0xFC00                      # -448 * 150 -> -Inf in F16
+
+
+def test_paged_attention_oracle_against_plain_softmax_and_table_invariance():
+    """The oracle's paged decode attention equals a plain numpy softmax attention over the widened
+    rows, and does not depend on where the blocks sit (the reference's own property,
+    kernels/src/attention.rs test_paged_attention_identity_and_shuffled_match_flash)."""
+    rng = np.random.default_rng(5)
+    H_, D, bs, nb = 2, 128, 16, 8
+    lens = np.array([37, 100], dtype=np.uint32)
+
+    def make(table):
+        pool = oracle.HostPool.filled(1, H_, D, bs, 32, np.uint16, 0xA5)
+        return pool
+
+    rows = [rng.standard_normal((int(n), 2, H_, D)).astype(np.float16) for n in lens]      # [token][K|V][head][dim]
+    outs = []
+    for tables in (np.array([[0, 1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12, 13]], dtype=np.uint32),
+                   np.array([[30, 2, 17, 9, 4, 25, 11], [1, 29, 3, 14, 8, 20, 6]], dtype=np.uint32)):
+        pool = make(tables)
+        for s, n in enumerate(lens):
+            for t in range(int(n)):
+                blk, off = tables[s, t // bs], t % bs
+                pool.block_view(pool.k[0])[blk, off] = rows[s][t, 0].view(np.uint16)
+                pool.block_view(pool.v[0])[blk, off] = rows[s][t, 1].view(np.uint16)
+        q = np.random.default_rng(6).standard_normal((2, 4, D)).astype(np.float32)         # 2 query heads per kv head
+        outs.append(oracle.paged_decode_attention(pool, 0, q, tables, lens, 0.125))
+    assert np.array_equal(outs[0], outs[1])
+    for s, n in enumerate(lens):
+        for h in range(4):
+            k = rows[s][:, 0, h // 2].astype(np.float64)
+            v = rows[s][:, 1, h // 2].astype(np.float64)
+            sc = k @ q[s, h].astype(np.float64) * 0.125
+            p = np.exp(sc - sc.max())
+            want = (p / p.sum()) @ v
+            assert np.allclose(outs[0][s, h], want, rtol=1e-4, atol=1e-5)
