@@ -477,7 +477,10 @@ def run_ours(args):
         for o in range(0, hv.numel(), tile.numel()):
             n = min(tile.numel(), hv.numel() - o)
             hv[o:o + n].copy_(tile[:n])
-        plan_h = H.Plan.from_transfer(xfer, dst, batch, H.Shard(0, 0, w.n_kv_heads, 0, 0, host_layers), 0)
+        plan_h = H.Plan.from_transfer(xfer, dst, batch, H.Shard(0, 0, w.n_kv_heads, 0, 0, host_layers),
+                                      H.N.PLAN_FORCE_BULK if args.host_bulk else 0)
+        if args.host_bulk and args.bulk_tune:
+            plan_h.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
     barrier()
     for it in range(1 + host_steps):             # first pass is the warm-up
         if it == 1:
@@ -654,6 +657,7 @@ def main():
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")
+    ap.add_argument("--host-bulk", action="store_true", help="host-buffer leg: bulk-copy ring reading the pinned buffer (experiment)")
     ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")
     args = ap.parse_args()
     if args.warmup < 3:

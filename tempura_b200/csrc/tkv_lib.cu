@@ -455,8 +455,9 @@ template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, 
 // Bulk-copy variant: only for same-device, contiguous, 16-byte aligned chunks.
 bool bulk_eligible(const tkv_plan* p) {
     const bool reach = p->src.device == p->dst.device || (p->flags & TKV_PLAN_PEER_BULK_STORES);
-    return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && reach && !p->host_side &&
-           p->args.src_k_scales == nullptr;
+    // a host-memory side takes the ring only when asked to (TKV_PLAN_FORCE_BULK)
+    const bool host_ok = !p->host_side || (p->flags & TKV_PLAN_FORCE_BULK);
+    return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && reach && host_ok && p->args.src_k_scales == nullptr;
 }
 
 int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {

@@ -85,7 +85,7 @@ def test_to_transfer_matches_oracle_gather(H, where):
     assert_pool_equals_host(ds, hs, "source untouched")
 
 
-@pytest.mark.parametrize("where", ["device", "host"])
+@pytest.mark.parametrize("where", ["device", "host", "host-bulk"])
 def test_from_transfer_matches_oracle_scatter(H, where):
     import torch
     w = workload(seed=4)
@@ -94,7 +94,7 @@ def test_from_transfer_matches_oracle_scatter(H, where):
     bs, D, stride = 16, 128, 8 * 128
     nb = moved_blocks(w)
     total = sum(nb)
-    x = H.Transfer.allocate(w.n_layers, 8, 128, 16, total, "f16", host=(where == "host"), fill_byte=FILL)
+    x = H.Transfer.allocate(w.n_layers, 8, 128, 16, total, "f16", host=where.startswith("host"), fill_byte=FILL)
     planes = np.full((w.n_layers, 2, total * bs * stride), 0, dtype=np.uint16)
     for l in range(w.n_layers):
         for kv, arrs in enumerate((hd.k, hd.v)):
@@ -109,9 +109,11 @@ def test_from_transfer_matches_oracle_scatter(H, where):
                 at += nb[q]
     x.data[: planes.nbytes].copy_(torch.from_numpy(planes.view(np.uint8).reshape(-1)))
     dd = to_device_pool(host_pools(w)[1], "f16")
-    plan = H.Plan.from_transfer(x, dd, device_batch(w))
+    # "host-bulk": the bulk-copy ring reading the pinned buffer (measured equal to the register kernel over PCIe)
+    plan = H.Plan.from_transfer(x, dd, device_batch(w), None, N.PLAN_FORCE_BULK if where == "host-bulk" else 0)
     plan.enqueue()
     torch.cuda.synchronize()
+    assert plan.stats().kernel_variant == (N.VARIANT_VECTOR if where == "host" else N.VARIANT_BULK) and plan.device_error() == 0
     assert_pool_equals_host(dd, hd, "from_transfer")
 
 
