@@ -72,12 +72,6 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ld_nc(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ uint32_t word_of(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 // FP8: pool elements are e4m3 bytes; else f16.
@@ -418,6 +412,96 @@ __device__ __forceinline__ void attend_block_t(const Tile<FP8>& cur, uint32_t n_
     }
 }
 
+// Two blocks (32 tokens) in one step: twice the independent MMA chains per softmax, one max / rescale per 32 tokens.
+// n_valid1 == 0 when the range ends on an odd block (the second tile is then all zeros and fully masked).
+template <bool FP8>
+__device__ __forceinline__ void kq_tile(const Tile<FP8>& t, const uint32_t (&qa)[8][2], float (&sc)[4]) {
+    float odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    sc[0] = sc[1] = sc[2] = sc[3] = 0.0f;
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+        uint32_t a0, a1, a2, a3;
+        if (FP8) {
+            const uint32_t w0 = word_of(t.k[0][s >> 2][0], s & 3), w1 = word_of(t.k[1][s >> 2][0], s & 3);
+            a0 = e4m3x2_to_h2(w0 & 0xFFFFu);
+            a2 = e4m3x2_to_h2(w0 >> 16);
+            a1 = e4m3x2_to_h2(w1 & 0xFFFFu);
+            a3 = e4m3x2_to_h2(w1 >> 16);
+        } else {
+            const int e = (s & 3) * 2;
+            a0 = word_of(t.k[0][s >> 2][e >> 2], e & 3);
+            a2 = word_of(t.k[0][s >> 2][(e + 1) >> 2], (e + 1) & 3);
+            a1 = word_of(t.k[1][s >> 2][e >> 2], e & 3);
+            a3 = word_of(t.k[1][s >> 2][(e + 1) >> 2], (e + 1) & 3);
+        }
+        mma_16816((s & 1) ? odd : sc, a0, a1, a2, a3, qa[s][0], qa[s][1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) sc[i] += odd[i];
+}
+
+template <bool FP8>
+__device__ __forceinline__ void pv_tile(const Tile<FP8>& cur, uint32_t b0, uint32_t b1, float (&o)[8][4]) {
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+        uint32_t a0, a1, a2, a3;
+        if (FP8) {
+            const uint32_t lo = 2u * (t & 1), sel0 = lo | ((4u + lo) << 4), sel1 = (lo + 1u) | ((5u + lo) << 4);
+            const uint32_t v0 = word_of(cur.v[0][0], t >> 1), v1 = word_of(cur.v[1][0], t >> 1);
+            const uint32_t v2 = word_of(cur.v[2][0], t >> 1), v3 = word_of(cur.v[3][0], t >> 1);
+            a0 = e4m3x2_to_h2(__byte_perm(v0, v1, sel0));
+            a1 = e4m3x2_to_h2(__byte_perm(v0, v1, sel1));
+            a2 = e4m3x2_to_h2(__byte_perm(v2, v3, sel0));
+            a3 = e4m3x2_to_h2(__byte_perm(v2, v3, sel1));
+        } else {
+            const uint32_t v0 = word_of(cur.v[0][t >> 2], t & 3), v1 = word_of(cur.v[1][t >> 2], t & 3);
+            const uint32_t v2 = word_of(cur.v[2][t >> 2], t & 3), v3 = word_of(cur.v[3][t >> 2], t & 3);
+            a0 = __byte_perm(v0, v1, 0x5410u);
+            a1 = __byte_perm(v0, v1, 0x7632u);
+            a2 = __byte_perm(v2, v3, 0x5410u);
+            a3 = __byte_perm(v2, v3, 0x7632u);
+        }
+        mma_16816(o[t], a0, a1, a2, a3, b0, b1);
+    }
+}
+
+template <bool FP8>
+__device__ __forceinline__ void attend_two_blocks_t(const Tile<FP8>& t0, const Tile<FP8>& t1, uint32_t n_valid0, uint32_t n_valid1, uint32_t grp,
+                                                    const uint32_t (&qa)[8][2], float (&o)[8][4], float (&m2)[2], float (&l2)[2]) {
+    float sc0[4], sc1[4];
+    kq_tile<FP8>(t0, qa, sc0);
+    kq_tile<FP8>(t1, qa, sc1);
+    float p0[4], p1[4], corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float s00 = grp < n_valid0 ? sc0[h] * t0.ks : -INFINITY, s01 = grp + 8 < n_valid0 ? sc0[2 + h] * t0.ks : -INFINITY;
+        const float s10 = grp < n_valid1 ? sc1[h] * t1.ks : -INFINITY, s11 = grp + 8 < n_valid1 ? sc1[2 + h] * t1.ks : -INFINITY;
+        float mx = fmaxf(fmaxf(s00, s01), fmaxf(s10, s11));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
+        const float m_new = fmaxf(m2[h], mx);
+        corr[h] = m2[h] == -INFINITY ? 0.0f : exp2f(m2[h] - m_new);
+        p0[h] = exp2f(s00 - m_new);
+        p0[2 + h] = exp2f(s01 - m_new);
+        p1[h] = exp2f(s10 - m_new);
+        p1[2 + h] = exp2f(s11 - m_new);
+        l2[h] = l2[h] * corr[h] + (p0[h] + p0[2 + h]) + (p1[h] + p1[2 + h]);
+        m2[h] = m_new;
+    }
+    const uint32_t b00 = movmatrix_trans(pack_h2(p0[0] * t0.vs, p0[1] * t0.vs)), b01 = movmatrix_trans(pack_h2(p0[2] * t0.vs, p0[3] * t0.vs));
+    const uint32_t b10 = movmatrix_trans(pack_h2(p1[0] * t1.vs, p1[1] * t1.vs)), b11 = movmatrix_trans(pack_h2(p1[2] * t1.vs, p1[3] * t1.vs));
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+        o[t][0] *= corr[0];
+        o[t][1] *= corr[1];
+        o[t][2] *= corr[0];
+        o[t][3] *= corr[1];
+    }
+    pv_tile<FP8>(t0, b00, b01, o);
+    pv_tile<FP8>(t1, b10, b11, o);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Whole-block form (at most 8 kv heads): a CTA owns a token range of one sequence for ALL kv
 // heads, so what it reads is whole 16-token blocks, each one contiguous run per K and per V.  A
@@ -527,8 +611,8 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
             }
         }
     } else if (warp / HALVES < a.n_kv_heads) {
-        // ---- consumer: kv head warp / HALVES, blocks k = warp % HALVES, + HALVES, ... of this CTA's range ----
-        const uint32_t kvh = warp / HALVES, half = warp % HALVES;
+        // ---- consumer: kv head `warp`, every block of this CTA's range ----
+        const uint32_t kvh = warp / HALVES, half = 0;
         uint32_t qa[8][2];
         {
             const bool live = grp < a.group;
@@ -545,16 +629,10 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 #pragma unroll
         for (int t = 0; t < 8; t++) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
         float m2[2] = {-INFINITY, -INFINITY}, l2[2] = {0.0f, 0.0f};
-        Tile<FP8> cur;
-        bool ok = true;
-        for (uint32_t k = half; k < n_blk; k += HALVES) {
+        // fragments of block k out of its ring stage, which goes back to the producer as soon as they are in registers
+        auto fetch = [&](uint32_t k, Tile<FP8>& t, uint32_t n_valid) -> bool {
             const uint32_t s = k % n_stages;
-            ok = mbar_wait(smem_addr(full + s), (k / n_stages) & 1u);
-            if (!ok || *reinterpret_cast<volatile uint32_t*>(fail_word)) {
-                ok = false;
-                break;
-            }
-            const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
+            if (!mbar_wait(smem_addr(full + s), (k / n_stages) & 1u) || *reinterpret_cast<volatile uint32_t*>(fail_word)) return false;
             const unsigned char* kb = stages + (size_t)s * stage_bytes + (size_t)kvh * D * ES;
             const unsigned char* vb = kb + block_bytes;
 #pragma unroll
@@ -563,8 +641,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 #pragma unroll
                 for (int piece = 0; piece < 2; piece++)
 #pragma unroll
-                    for (int w = 0; w < KW; w++)
-                        cur.k[nt][piece][w] = lds_once(row + (piece * 64 + 16 * j) * ES + 16 * w);
+                    for (int w = 0; w < KW; w++) t.k[nt][piece][w] = lds_once(row + (piece * 64 + 16 * j) * ES + 16 * w);
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -573,19 +650,51 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 #pragma unroll
                 for (int w = 0; w < KW; w++) {                       // rows the copy did not bring hold stale bytes: read them as zero
                     const uint4 x = lds_once(row + 16 * w);
-                    cur.v[i][w] = tok < n_valid ? x : make_uint4(0, 0, 0, 0);
+                    t.v[i][w] = tok < n_valid ? x : make_uint4(0, 0, 0, 0);
                 }
             }
             if (a.k_scales) {
                 const float* sc = reinterpret_cast<const float*>(stages + (size_t)s * stage_bytes + 2u * block_bytes);
-                cur.ks = lds_once_f32(sc + kvh);
-                cur.vs = lds_once_f32(sc + 8 + kvh);
+                t.ks = lds_once_f32(sc + kvh);
+                t.vs = lds_once_f32(sc + 8 + kvh);
             } else {
-                cur.ks = cur.vs = 1.0f;
+                t.ks = t.vs = 1.0f;
             }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + s)) : "memory");
-            attend_block_t<FP8>(cur, n_valid, grp, qa, o, m2, l2);
+            return true;
+        };
+        bool ok = true;
+        if (FP8) {
+            Tile<FP8> t0, t1;
+            for (uint32_t k = 0; k < n_blk && ok; k += 2) {           // two blocks (32 tokens) per step
+                const uint32_t n_valid0 = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
+                const uint32_t n_valid1 = k + 1 < n_blk ? min((uint32_t)BS, kv_len - (b_begin + k + 1) * BS) : 0u;
+                ok = fetch(k, t0, n_valid0);
+                if (ok && n_valid1) {
+                    ok = fetch(k + 1, t1, n_valid1);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+#pragma unroll
+                        for (int w = 0; w < KW; w++) t1.v[i][w] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                        for (int piece = 0; piece < 2; piece++)
+#pragma unroll
+                            for (int w = 0; w < KW; w++) t1.k[nt][piece][w] = make_uint4(0, 0, 0, 0);
+                    t1.ks = t1.vs = 1.0f;
+                }
+                if (ok) attend_two_blocks_t<FP8>(t0, t1, n_valid0, n_valid1, grp, qa, o, m2, l2);
+            }
+        } else {
+            Tile<FP8> cur;                                            // F16 fragments are twice the registers: one block per step
+            for (uint32_t k = 0; k < n_blk && ok; k++) {
+                const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
+                ok = fetch(k, cur, n_valid);
+                if (ok) attend_block_t<FP8>(cur, n_valid, grp, qa, o, m2, l2);
+            }
         }
         if (ok) {
             // partial of (kv head, split, half): this lane holds heads 2j, 2j+1, dims [16 grp, 16 grp + 16)
