@@ -660,8 +660,23 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
             } else {
                 t.ks = t.vs = 1.0f;
             }
+            // The stage goes back only once every fragment load of this warp has returned: the arrive takes a value
+            // folded from all of them as an (unused) operand, so it cannot issue while a load is still in flight.
+            uint32_t landed = __float_as_uint(t.ks) ^ __float_as_uint(t.vs);
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int piece = 0; piece < 2; piece++)
+#pragma unroll
+                    for (int w = 0; w < KW; w++) landed ^= t.k[nt][piece][w].x ^ t.k[nt][piece][w].w;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int w = 0; w < KW; w++) landed ^= t.v[i][w].x ^ t.v[i][w].w;
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + s)) : "memory");
+            if (lane == 0)
+                asm volatile("{\n\t.reg .b32 dep;\n\tmov.b32 dep, %1;\n\tmbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+                             ::"r"(smem_addr(empty + s)), "r"(landed) : "memory");
             return true;
         };
         bool ok = true;
