@@ -100,3 +100,41 @@ def test_null_arguments():
     assert L.tkv_handoff_enqueue(None, None, 0, 0) == N.ERR_INVALID_CONFIG
     assert L.tkv_flag_wait_enqueue(None, 0, 0, 10, 0) == N.ERR_INVALID_CONFIG
     assert L.tkv_flag_wait_enqueue(None, 0x1000, 0, 0, 0) == N.ERR_INVALID_CONFIG   # unbounded wait refused
+
+
+def test_batch_beyond_the_chunk_index_range_is_refused():
+    """Chunk indices are 32-bit: a batch with more than 2^31 / (2 * layers) block pairs is refused by
+    arithmetic on the lengths alone, before any table entry is read."""
+    n_blocks = 600_000_000                                    # x 2 layers x 2 > 2^31
+    b = H.Batch(np.array([n_blocks * 4], dtype=np.uint32), np.zeros(1, np.uint32), np.zeros(1, np.uint32), n_blocks)
+    msg = expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), b))
+    assert "too large" in msg
+
+
+def test_transfer_buffer_plans_validate_without_a_gpu():
+    small = N.TkvTransfer(0, N.DTYPE_F16, 0, 0, 0x20000000, 64, 0)          # 64 bytes for a batch that needs far more
+    pool, b = fake_pool(), batch([9], [[0, 1, 2]], [[3, 4, 5]], 3)
+    for make in (lambda: N.lib().tkv_plan_create_to_transfer(C.byref(pool.c_struct()), C.byref(small), C.byref(b.c_struct()), None, 0,
+                                                             C.byref(C.c_void_p())),
+                 lambda: N.lib().tkv_plan_create_from_transfer(C.byref(small), C.byref(pool.c_struct()), C.byref(b.c_struct()), None, 0,
+                                                               C.byref(C.c_void_p()))):
+        assert make() == N.ERR_DIMENSION_MISMATCH
+    null = N.TkvTransfer(0, N.DTYPE_F16, 0, 0, 0, 1 << 20, 0)
+    assert N.lib().tkv_plan_create_to_transfer(C.byref(pool.c_struct()), C.byref(null), C.byref(b.c_struct()), None, 0,
+                                               C.byref(C.c_void_p())) == N.ERR_INVALID_CONFIG
+    scaled_f16 = N.TkvTransfer(0, N.DTYPE_F16, 0, 0, 0x20000000, 1 << 20, 0x30000000)
+    assert N.lib().tkv_plan_create_to_transfer(C.byref(pool.c_struct()), C.byref(scaled_f16), C.byref(b.c_struct()), None, 0,
+                                               C.byref(C.c_void_p())) == N.ERR_INVALID_CONFIG
+    assert N.lib().tkv_batch_blocks(C.byref(b.c_struct()), 4) == 3
+    assert N.lib().tkv_transfer_bytes(2, 4, 16, 4, N.DTYPE_F16, 3) == 2 * 2 * 3 * 4 * 4 * 16 * 2
+
+
+def test_decode_attention_arguments_validate_without_a_gpu():
+    pool = fake_pool(layers=1, heads=8, dim=128, bs=16)
+    args = N.TkvDecodeAttn(1, 12, 1, 0, 16, 0.1, 0, 0, 0x100, 0x200, 0x300, 0x400, 0x500, 1 << 20, 0, 0)
+    assert N.lib().tkv_decode_attn_enqueue(C.byref(pool.c_struct()), C.byref(args), None) == N.ERR_DIMENSION_MISMATCH   # 12 heads on 8
+    args = N.TkvDecodeAttn(1, 8, 1, 5, 16, 0.1, 0, 0, 0x100, 0x200, 0x300, 0x400, 0x500, 1 << 20, 0, 0)
+    assert N.lib().tkv_decode_attn_enqueue(C.byref(pool.c_struct()), C.byref(args), None) == N.ERR_INVALID_CONFIG       # layer 5 of 1
+    f32 = fake_pool(layers=1, heads=8, dim=128, bs=16, dtype="f32")
+    assert N.lib().tkv_decode_attn_enqueue(C.byref(f32.c_struct()), C.byref(args), None) == N.ERR_INVALID_CONFIG
+    assert N.lib().tkv_decode_attn_scratch_bytes(16, 32, 128, 4096, 1024) == 16 * 32 * 4 * 130 * 4
