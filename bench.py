@@ -237,7 +237,9 @@ def run_reference(args):
     v = max(vals)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup,
+        # the sample's rate applied to the whole batch: what one full handoff would take on these cores
+        "ms_per_step": round(w.payload_bytes / (v * 1e9) * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u16" if w.dst_dtype != "e4m3" else "f16->e4m3", "data": "synthetic",
         "config": {"workload": w.name, "note": "reference CPU handoff restated in C (oracle port), OpenMP over (sequence, layer, K|V)"},
         "cpu_baseline": {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
