@@ -511,8 +511,7 @@ __device__ __forceinline__ void attend_two_blocks_t(const Tile<FP8>& t0, const T
 // its fragments are in registers.  No warp merges with another: each writes its own partial.
 // Every wait is bounded; a CTA that gives up reports through `status` and drains its copies.
 // ---------------------------------------------------------------------------------------------
-constexpr int MAX_KV_HEADS_PER_CTA = 8;   // consumer warps: HALVES per kv head (1 in use: a two-warp split of a head's blocks
-                                          // measured no faster, the tensor pipe being the limit, and is not launched)
+constexpr int MAX_KV_HEADS_PER_CTA = 8;   // consumer warps, one per kv head (two per head, on alternate blocks, measured no faster)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -542,10 +541,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-template <bool FP8, int HALVES>
-__global__ void __launch_bounds__((MAX_KV_HEADS_PER_CTA * HALVES + 1) * 32, 1)
+template <bool FP8>
+__global__ void __launch_bounds__((MAX_KV_HEADS_PER_CTA + 1) * 32, 1)
 decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
-    constexpr int CW = MAX_KV_HEADS_PER_CTA * HALVES;
+    constexpr int CW = MAX_KV_HEADS_PER_CTA;
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int KW = Tile<FP8>::KW;
     const uint32_t split = blockIdx.x, seq = blockIdx.y;
@@ -610,9 +609,9 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                 if (a.status) atomicExch(a.status, 4u);
             }
         }
-    } else if (warp / HALVES < a.n_kv_heads) {
+    } else if (warp < a.n_kv_heads) {
         // ---- consumer: kv head `warp`, every block of this CTA's range ----
-        const uint32_t kvh = warp / HALVES, half = 0;
+        const uint32_t kvh = warp;
         uint32_t qa[8][2];
         {
             const bool live = grp < a.group;
@@ -712,7 +711,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
             }
         }
         if (ok) {
-            // partial of (kv head, split, half): this lane holds heads 2j, 2j+1, dims [16 grp, 16 grp + 16)
+            // partial of (kv head, split): this lane holds heads 2j, 2j+1, dims [16 grp, 16 grp + 16)
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 l2[h] += __shfl_xor_sync(0xFFFFFFFFu, l2[h], 4);
@@ -720,7 +719,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                 l2[h] += __shfl_xor_sync(0xFFFFFFFFu, l2[h], 16);
                 const uint32_t g = 2 * j + h;
                 if (g < a.group) {
-                    float* pr = a.partial + ((((size_t)seq * a.n_kv_heads + kvh) * a.n_splits + HALVES * split + half) * a.group + g) * (D + 2);
+                    float* pr = a.partial + ((((size_t)seq * a.n_kv_heads + kvh) * a.n_splits + split) * a.group + g) * (D + 2);
                     if (grp == 0) {
                         pr[0] = m2[h];
                         pr[1] = l2[h];
@@ -738,7 +737,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     }
 }
 
-// merges the splits of one (sequence, query head)
+// merges the splits of one (sequence, query head); loads are issued eight splits at a time so their latencies overlap
 __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const uint32_t kvh = head / a.group, g = head % a.group;
@@ -746,13 +745,32 @@ __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t live = ((kv_len + a.split_tokens - 1) / a.split_tokens) * a.parts_per_split;
     const float* base = a.partial + (((size_t)seq * a.n_kv_heads + kvh) * a.n_splits * a.group + g) * (D + 2);
     const size_t stride = (size_t)a.group * (D + 2);
+    // running max over the splits: every thread takes a strided share, then one reduction through shared memory
+    __shared__ float red[D / 32];
     float mm = -INFINITY;
-    for (uint32_t s = 0; s < live; s++) mm = fmaxf(mm, base[s * stride]);
+    for (uint32_t s = d; s < live; s += D) mm = fmaxf(mm, __ldg(base + s * stride));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xFFFFFFFFu, mm, off));
+    if ((d & 31u) == 0) red[d >> 5] = mm;
+    __syncthreads();
+    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     float ll = 0.0f, acc = 0.0f;
-    for (uint32_t s = 0; s < live; s++) {
-        const float f = base[s * stride] == -INFINITY ? 0.0f : exp2f(base[s * stride] - mm);   // a part that saw no block
-        ll += base[s * stride + 1] * f;
-        acc += base[s * stride + 2 + d] * f;
+    for (uint32_t s0 = 0; s0 < live; s0 += 8) {
+        float pm[8], pl[8], pa[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const bool in = s0 + i < live;
+            const float* p = base + (size_t)(in ? s0 + i : 0) * stride;
+            pm[i] = in ? __ldg(p) : -INFINITY;
+            pl[i] = __ldg(p + 1);
+            pa[i] = __ldg(p + 2 + d);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float f = pm[i] == -INFINITY ? 0.0f : exp2f(pm[i] - mm);   // a part that saw no block, or padding of the group of 8
+            ll += pl[i] * f;
+            acc += pa[i] * f;
+        }
     }
     a.out[((size_t)seq * a.n_q_heads + head) * D + d] = ll > 0.0f ? acc / ll : 0.0f;
 }
@@ -857,11 +875,11 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             a.n_splits = n_splits;
             const uint32_t threads = (MAX_KV_HEADS_PER_CTA + 1) * 32;
             if (pool->dtype == TKV_DTYPE_E4M3) {
-                e = cudaFuncSetAttribute(decode_attn_blocks<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e == cudaSuccess) decode_attn_blocks<true, 1><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
+                e = cudaFuncSetAttribute(decode_attn_blocks<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e == cudaSuccess) decode_attn_blocks<true><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
             } else {
-                e = cudaFuncSetAttribute(decode_attn_blocks<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e == cudaSuccess) decode_attn_blocks<false, 1><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
+                e = cudaFuncSetAttribute(decode_attn_blocks<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e == cudaSuccess) decode_attn_blocks<false><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
             }
             if (e == cudaSuccess) e = cudaGetLastError();
             if (e == cudaSuccess) {
