@@ -134,7 +134,7 @@ typedef struct tkv_plan tkv_plan;
 enum {
     TKV_PLAN_DEFAULT = 0,
     TKV_PLAN_ALLOW_SHARED_DST = 1,  /* skip the "destination block ids are unique" check   */
-    TKV_PLAN_FORCE_VECTOR = 2,      /* use the register kernels (vector copy, warp-per-head FP8) */
+    TKV_PLAN_FORCE_VECTOR = 2,      /* use the register kernels (vector copy, warp-per-head FP8, element-wide F32 casts) */
     TKV_PLAN_FORCE_BULK = 4,        /* use the shared-memory bulk-copy pipelines (copy ring, staged FP8) */
     TKV_PLAN_INT_QUANTIZER = 8,     /* FP8: integer bit-math encoder instead of cvt + flush */
     TKV_PLAN_PEER_BULK_STORES = 16  /* same-dtype move to a peer: use the bulk-copy ring (bulk stores
@@ -143,7 +143,7 @@ enum {
                                        always stores whole rows in bulk, local or peer.            */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
-       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7 };
+       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7, TKV_VARIANT_CAST_VEC = 8 };
 
 /* ---- library -------------------------------------------------------------- */
 /* Copies the calling thread's last error text (NUL-terminated) into buf. */

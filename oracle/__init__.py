@@ -85,7 +85,7 @@ def lib() -> C.CDLL:
     sig("orc_paged_scatter", None, vp, P(u32), sz, sz, sz, sz, sz, vp)
     sig("orc_transfer_layer", None, P(f32), sz, sz, C.c_int, vp)
     for n in ("orc_handoff_copy", "orc_handoff_f16_to_e4m3", "orc_handoff_f32_to_f16", "orc_handoff_e4m3_to_f16",
-              "orc_handoff_e4m3_to_f32"):
+              "orc_handoff_e4m3_to_f32", "orc_handoff_f32_to_e4m3"):
         sig(n, C.c_int, P(OrcPool), P(OrcPool), P(OrcBatch), P(OrcShard), C.c_int)
     sig("orc_refcount_apply", None, P(u32), P(OrcBatch), u32, C.c_int)
     sig("orc_paged_decode_attention", C.c_int, P(OrcPool), u32, P(f32), P(u32), u32, P(u32), u32, u32, f32, P(f32))
@@ -199,7 +199,7 @@ def full_shard(src: HostPool, dst: HostPool) -> OrcShard:
 
 
 _MODES = {"copy": "orc_handoff_copy", "f16_e4m3": "orc_handoff_f16_to_e4m3", "f32_f16": "orc_handoff_f32_to_f16",
-          "e4m3_f16": "orc_handoff_e4m3_to_f16", "e4m3_f32": "orc_handoff_e4m3_to_f32"}
+          "e4m3_f16": "orc_handoff_e4m3_to_f16", "e4m3_f32": "orc_handoff_e4m3_to_f32", "f32_e4m3": "orc_handoff_f32_to_e4m3"}
 
 
 def handoff(src: HostPool, dst: HostPool, batch: OrcBatch, shard: Optional[OrcShard] = None,

@@ -330,7 +330,7 @@ static int check_args(const orc_pool* s, const orc_pool* d, const orc_batch* b, 
     return 0;
 }
 
-enum { MODE_COPY = 0, MODE_F16_E4M3 = 1, MODE_F32_F16 = 2, MODE_E4M3_F16 = 3, MODE_E4M3_F32 = 4 };
+enum { MODE_COPY = 0, MODE_F16_E4M3 = 1, MODE_F32_F16 = 2, MODE_E4M3_F16 = 3, MODE_E4M3_F32 = 4, MODE_F32_E4M3 = 5 };
 
 /* One (sequence, layer, K|V) unit: gather the suffix tokens of the selected
  * heads into a contiguous buffer (k_contiguous, restricted to the shard's
@@ -369,6 +369,15 @@ static void handoff_unit(const orc_pool* s, const orc_pool* d, const orc_batch* 
             size_t off = orc_paged_row_offset(dt, bs, d_stride, pre + t, sh->dst_head_begin, D);
             uint16_t* o = (uint16_t*)dp + off;
             for (size_t i = 0; i < row; i++) o[i] = orc_f32_to_f16(f[t * row + i]);
+        }
+    } else if (mode == MODE_F32_E4M3) {
+        /* the e4m3 row writer of the GPU pool (kernels/src/kv_scatter_write.rs:172-273): each element through
+         * kernels/src/e4m3.rs:50-94, no scale                                                                */
+        const float* f = (const float*)tmp;
+        for (size_t t = 0; t < n_tok; t++) {
+            size_t off = orc_paged_row_offset(dt, bs, d_stride, pre + t, sh->dst_head_begin, D);
+            uint8_t* o = (uint8_t*)dp + off;
+            for (size_t i = 0; i < row; i++) o[i] = orc_f32_to_e4m3(f[t * row + i]);
         }
     } else if (mode == MODE_E4M3_F16 || mode == MODE_E4M3_F32) {
         /* Fp8PagedKvCache::k_contiguous / v_contiguous (engine/src/kv_cache.rs:1241-1271) widen
@@ -433,6 +442,7 @@ static int handoff_run(const orc_pool* s, const orc_pool* d, const orc_batch* b,
     if (mode == MODE_F16_E4M3 && (s->elem_size != 2 || d->elem_size != 1 || (!d->k_scales != !d->v_scales)))
         return -8;
     if (mode == MODE_F32_F16 && (s->elem_size != 4 || d->elem_size != 2)) return -8;
+    if (mode == MODE_F32_E4M3 && (s->elem_size != 4 || d->elem_size != 1)) return -8;
     if (mode == MODE_E4M3_F16 && (s->elem_size != 1 || d->elem_size != 2)) return -8;
     if (mode == MODE_E4M3_F32 && (s->elem_size != 1 || d->elem_size != 4)) return -8;
     const long units = (long)b->n_seqs * sh->n_layers * 2;
@@ -466,6 +476,10 @@ int orc_handoff_f32_to_f16(const orc_pool* s, const orc_pool* d, const orc_batch
     return handoff_run(s, d, b, sh, n_threads, MODE_F32_F16);
 }
 
+int orc_handoff_f32_to_e4m3(const orc_pool* s, const orc_pool* d, const orc_batch* b,
+                            const orc_shard* sh, int n_threads) {
+    return handoff_run(s, d, b, sh, n_threads, MODE_F32_E4M3);
+}
 int orc_handoff_e4m3_to_f16(const orc_pool* s, const orc_pool* d, const orc_batch* b,
                             const orc_shard* sh, int n_threads) {
     return handoff_run(s, d, b, sh, n_threads, MODE_E4M3_F16);

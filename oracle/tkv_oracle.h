@@ -136,6 +136,9 @@ int orc_handoff_f32_to_f16(const orc_pool* src, const orc_pool* dst, const orc_b
  * element decode kernels/src/e4m3.rs:27-41, times the source block scale if present */
 int orc_handoff_e4m3_to_f16(const orc_pool* src, const orc_pool* dst, const orc_batch* b,
                             const orc_shard* sh, int n_threads);
+/* F32 rows into an unscaled E4M3 pool (kernels/src/kv_scatter_write.rs:172-273, element rule e4m3.rs:50-94) */
+int orc_handoff_f32_to_e4m3(const orc_pool* src, const orc_pool* dst, const orc_batch* b,
+                            const orc_shard* sh, int n_threads);
 int orc_handoff_e4m3_to_f32(const orc_pool* src, const orc_pool* dst, const orc_batch* b,
                             const orc_shard* sh, int n_threads);
 

@@ -779,6 +779,51 @@ __global__ void __launch_bounds__(256) handoff_e4m3_dequant(const HandoffArgs a)
     signal_done(a);
 }
 
+// The same casts, 16-byte accesses: a thread converts 8 floats into one 16-byte store of halves (MODE 0) or 16
+// floats into 16 e4m3 bytes (MODE 1).  Needs every row offset and stride to keep 16-byte alignment on both sides.
+__device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t h2_bits(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) handoff_f32_cast_vec(const HandoffArgs a) {
+    constexpr uint32_t E = MODE == 0 ? 8u : 16u;               // elements per 16-byte store
+    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t row_elems = a.n_heads * a.head_dim, per_row = row_elems / E;
+    for (uint32_t w = blockIdx.x; w < chunks; w += gridDim.x) {
+        const Chunk c = decode_chunk(a, w);
+        const uint32_t n = c.n_valid * per_row;
+        for (uint32_t i = threadIdx.x; i < n; i += 256u) {
+            const uint32_t r = i / per_row, e0 = (i - r * per_row) * E;
+            const float4* sp = reinterpret_cast<const float4*>(c.src + (size_t)r * a.src_row_stride + (size_t)e0 * 4);
+            uint4 o;
+            if (MODE == 0) {
+                const float4 x = ld_stream_f4(sp), y = ld_stream_f4(sp + 1);
+                o = make_uint4(h2_bits(x.x, x.y), h2_bits(x.z, x.w), h2_bits(y.x, y.y), h2_bits(y.z, y.w));
+                *reinterpret_cast<uint4*>(c.dst + (size_t)r * a.dst_row_stride + (size_t)e0 * 2) = o;
+            } else {
+                float4 x[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) x[k] = ld_stream_f4(sp + k);
+                uint32_t q[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    q[k] = e4m3_encode_int(x[k].x) | (e4m3_encode_int(x[k].y) << 8) | (e4m3_encode_int(x[k].z) << 16) |
+                           (e4m3_encode_int(x[k].w) << 24);
+                o = make_uint4(q[0], q[1], q[2], q[3]);
+                *reinterpret_cast<uint4*>(c.dst + (size_t)r * a.dst_row_stride + e0) = o;
+            }
+        }
+    }
+    signal_done(a);
+}
+
 // Non-template kernels have one definition per program: a second translation unit that
 // only needs the templates above defines TKV_KERNELS_TEMPLATES_ONLY before including.
 #ifndef TKV_KERNELS_TEMPLATES_ONLY

@@ -816,9 +816,17 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
             return scaled ? launch_fp8<false, true>(p, st) : launch_fp8<false, false>(p, st);
         }
         case MODE_F32_F16:
+            if (p->vec == 16 && (a.n_heads * a.head_dim) % 8 == 0 && !(p->flags & TKV_PLAN_FORCE_VECTOR)) {
+                p->variant = TKV_VARIANT_CAST_VEC;
+                return launch(tkv::handoff_f32_cast_vec<0>, p, chunks, st);
+            }
             p->variant = TKV_VARIANT_CAST_GENERIC;
             return launch(tkv::handoff_f32_cast_generic<0>, p, chunks, st);
         case MODE_F32_E4M3:
+            if (p->vec == 16 && (a.n_heads * a.head_dim) % 16 == 0 && !(p->flags & TKV_PLAN_FORCE_VECTOR)) {
+                p->variant = TKV_VARIANT_CAST_VEC;
+                return launch(tkv::handoff_f32_cast_vec<1>, p, chunks, st);
+            }
             p->variant = TKV_VARIANT_CAST_GENERIC;
             return launch(tkv::handoff_f32_cast_generic<1>, p, chunks, st);
         case MODE_E4M3_F16:

@@ -495,3 +495,21 @@ def test_quantize_then_widen_stays_within_one_e4m3_step(H):
         big = x.abs() >= amax / 448 * 2 ** -6 * 1.01            # not flushed
         rel = ((x - y).abs() / x.abs().clamp_min(1e-9))[big]
         assert float(rel.max()) <= 2 ** -4 + 1e-3
+
+
+# ---- the reference's own transfer dtype: F32 rows into an F16 (or unscaled E4M3) cache ----------
+@pytest.mark.parametrize("dst_dtype", ["f16", "e4m3"])
+@pytest.mark.parametrize("flags,variant", [(0, N.VARIANT_CAST_VEC), (N.PLAN_FORCE_VECTOR, N.VARIANT_CAST_GENERIC)])
+def test_f32_source_casts_at_the_8b_shape(H, dst_dtype, flags, variant):
+    """KvCacheTransfer is F32 (engine/src/kv_cache.rs:514-522) and the cache it lands in may be F16
+    (append_kv's cast, :209-221) or the GPU pool's unscaled E4M3 (kernels/src/kv_scatter_write.rs:172-273)."""
+    w = reduced_8b(n_layers=2, n_seqs=5, lo=1, hi=150, src_dtype="f32", dst_dtype=dst_dtype, outlier_channels=(11,), outlier_gain=2000.0, seed=71)
+    plan, *_ = run_case(H, w, flags=flags, scales=False)     # x2000: values past 448 and past 65504 saturate / overflow as the rules say
+    assert plan.stats().kernel_variant == variant
+
+
+def test_f32_cast_head_shard(H):
+    w = W.Workload("f32-shard", 2, 8, 128, 16, 64, 64, np.array([40, 33], dtype=np.uint32), src_dtype="f32", dst_dtype="f16", seed=72).build_tables()
+    sh, osh = H.Shard(2, 1, 4, 0, 0, 2), oracle.OrcShard(2, 1, 4, 0, 0, 2)
+    p, *_ = run_case(H, w, shard=sh, oshard=osh, dst_heads=6)
+    assert p.stats().kernel_variant == N.VARIANT_CAST_VEC
