@@ -154,7 +154,7 @@ def fill_source(pool, w, seed: int):
                                device=idx.device, dtype=torch.float32) * w.sigma
             for c in w.outlier_channels:
                 vals[..., c] *= w.outlier_gain
-            pool.blocks(l, is_v).index_copy_(0, idx, vals.to(torch.float16))
+            pool.blocks(l, is_v).index_copy_(0, idx, vals.to(pool.blocks(l, is_v).dtype))
     torch.cuda.synchronize()
 
 
@@ -169,8 +169,10 @@ def spot_check(src, dst, w, layer: int):
             continue
         s = torch.from_numpy(w.src_tables[q, pre:nfull].astype(np.int64)).cuda(src.device)
         d = torch.from_numpy(w.dst_tables[q, pre:nfull].astype(np.int64)).cuda(dst.device)
-        if src.dtype == dst.dtype:
+        if src.dtype == dst.dtype or src.dtype == 0:
             a = src.blocks(layer).index_select(0, s)
+            if src.dtype == 0:
+                a = a.to(torch.float16)                       # F32 -> F16, round to nearest even
             b = dst.blocks(layer).index_select(0, d).to(a.device)
             if not torch.equal(a.view(torch.int16), b.view(torch.int16)):
                 raise SystemExit("spot check failed: destination blocks differ from source blocks")
@@ -323,6 +325,11 @@ def run_ours(args):
         raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
     wname = args.workload or "cfg2"
     w = pick_workload(wname, world, args.pool_blocks, layers=args.layers, single_tokens=args.single_tokens)
+    if args.src_f32:                # the reference's own transfer dtype: F32 rows into the F16 cache (one GPU only)
+        if world != 1 or w.dst_dtype != "f16":
+            raise SystemExit("--src-f32 is a one-GPU probe of the F32 -> F16 cast")
+        w.src_dtype = "f32"
+        w.name += "-f32src"
     from tempura_b200 import disagg
     role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode)
     pairs = max(1, world // 2)
@@ -343,7 +350,7 @@ def run_ours(args):
     # host polls it, no copy per poll); device memory of the decode GPU when the waiter is another rank
     flag = torch.zeros(4, dtype=torch.int32, device="cuda") if multi else torch.zeros(4, dtype=torch.int32).pin_memory()
     if not multi:
-        src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
+        src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, w.src_dtype)
         dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
                               scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
         fill_source(src, w, 1234)
@@ -526,12 +533,14 @@ def run_ours(args):
             bound, peak_used, algo_used, peak_note = "hbm", peak, algo, f"{peak_kind} copy peak"
         achieved = algo_used / (per_launch_ms * 1e-3) / 1e9
         kname = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e4m3_warp", 4: "handoff_f16_e4m3_generic",
-                 5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged"}.get(st.kernel_variant, "?")
+                 5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant",
+                 8: "handoff_f32_cast_vec"}.get(st.kernel_variant, "?")
         ratio = NCU_TRAFFIC_RATIO.get(kname)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u16" if dst_dtype == "f16" else "f16->e4m3", "data": "synthetic",
+            "vs_baseline": None, "dtype": ("f32->f16" if w.src_dtype == "f32" else "u16") if dst_dtype == "f16" else "f16->e4m3",
+            "data": "synthetic",
             "config": {"workload": w.name, "layers": w.n_layers, "kv_heads": w.n_kv_heads, "head_dim": w.head_dim,
                        "block_size": w.block_size, "n_seqs": len(w.seq_lens), "tokens_moved": w.tokens_moved,
                        "payload_bytes_per_pair": int(st.payload_bytes), "pool_blocks": [w.src_blocks, w.dst_blocks],
@@ -652,6 +661,7 @@ def main():
     ap.add_argument("--attn-f16", action="store_true", help="--workload attn: read the F16 pool instead of the E4M3 one")
     ap.add_argument("--pool-blocks", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep the batch, use fewer layers")
+    ap.add_argument("--src-f32", action="store_true", help="probe: F32 source pool cast into the F16 pool (give --pool-blocks 8192)")
     ap.add_argument("--single-tokens", type=int, default=None, help="latency probe: one prompt of this many tokens (cfg2/cfg3 shape)")
     ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
