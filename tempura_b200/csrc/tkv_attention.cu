@@ -547,6 +547,9 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     constexpr int CW = MAX_KV_HEADS_PER_CTA;
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int KW = Tile<FP8>::KW;
+    // Under a programmatic launch the next kernel in the stream may be scheduled from here on (it waits for this
+    // grid's completion itself before it touches what this grid writes); without one both instructions do nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t split = blockIdx.x, seq = blockIdx.y;
     const uint32_t kv_len = a.kv_lens[seq];
     const uint32_t t_begin = split * a.split_tokens;
@@ -606,12 +609,16 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                 // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
                 for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
                     mbar_wait(smem_addr(full + k % n_stages), (k / n_stages) & 1u);
+                asm volatile("griddepcontrol.wait;" ::: "memory");
                 if (a.status) atomicExch(a.status, 4u);
             }
         }
     } else if (warp < a.n_kv_heads) {
         // ---- consumer: kv head `warp`, every block of this CTA's range ----
         const uint32_t kvh = warp;
+        // the producer warp is already fetching K/V (the pool, the tables and the lengths are the caller's to keep
+        // stable); q, the partials and the status word are touched only once the preceding kernel has completed
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t qa[8][2];
         {
             const bool live = grp < a.group;
@@ -741,8 +748,10 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const uint32_t kvh = head / a.group, g = head % a.group;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t kv_len = a.kv_lens[seq];
     const uint32_t live = ((kv_len + a.split_tokens - 1) / a.split_tokens) * a.parts_per_split;
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the partials are complete (no-op in a plain launch)
     const float* base = a.partial + (((size_t)seq * a.n_kv_heads + kvh) * a.n_splits * a.group + g) * (D + 2);
     const size_t stride = (size_t)a.group * (D + 2);
     // running max over the splits: every thread takes a strided share, then one reduction through shared memory
@@ -816,6 +825,10 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
     const uint32_t es = pool->dtype == TKV_DTYPE_E4M3 ? 1u : 2u;
     const uint64_t kp = pool->k_layer_ptrs[d->layer], vp = pool->v_layer_ptrs[d->layer];
     if ((kp | vp | d->q) % 16) return fail(TKV_ERR_INVALID_CONFIG, "layer tensors and q must be 16-byte aligned");
+    // whole-block form when a CTA can hold every kv head of a block (and the scale rows are bulk-copy sized)
+    const uint32_t row_bytes = pool->n_kv_heads * D * es, stage_bytes = 2u * BS * row_bytes + 128u;
+    const bool whole_blocks = pool->n_kv_heads <= (uint32_t)MAX_KV_HEADS_PER_CTA && (!pool->k_scales || pool->n_kv_heads % 4 == 0) &&
+                              !(d->flags & TKV_ATTN_PER_HEAD_CTAS) && 256u + 2u * stage_bytes <= 200u * 1024u;
     uint32_t split_tokens = d->split_tokens ? d->split_tokens : DEFAULT_SPLIT_TOKENS;
     if (!d->split_tokens && d->total_kv_tokens) {
         // one CTA per SM in the whole-block form: pick the token range so that the batch is ONE wave of CTAs
@@ -824,10 +837,13 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, pool->device) == cudaSuccess && sms > (int)d->n_seqs) {
             const uint64_t slots = (uint64_t)(sms - (int)d->n_seqs);                     // one CTA per SM
             const uint64_t per = (d->total_kv_tokens + slots - 1) / slots;
-            split_tokens = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((per + 63) / 64 * 64, 64), 1u << 20);
+            // the whole-block form walks a range two blocks at a time, the per-head form four warps' blocks at a time
+            const uint64_t step = whole_blocks ? 2u * BS : WARPS * BS;
+            split_tokens = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((per + step - 1) / step * step, 64), 1u << 20);
         }
     }
-    if (split_tokens % (WARPS * BS)) return fail(TKV_ERR_INVALID_CONFIG, "split_tokens must be a multiple of %llu", (unsigned long long)(WARPS * BS));
+    if (split_tokens % (whole_blocks ? 2u * BS : WARPS * BS))
+        return fail(TKV_ERR_INVALID_CONFIG, "split_tokens must be a multiple of %llu", (unsigned long long)(whole_blocks ? 2u * BS : WARPS * BS));
     const uint32_t n_splits = splits_for(d->max_kv_len, split_tokens);
     const uint64_t need = tkv_decode_attn_scratch_bytes(d->n_seqs, d->n_q_heads, D, d->max_kv_len, split_tokens);
     if (need > d->scratch_bytes || (need && !d->scratch))
@@ -862,11 +878,6 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
     if (e == cudaSuccess) {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         dim3 grid(n_splits, pool->n_kv_heads, d->n_seqs);
-        // whole-block form when a CTA can hold every kv head of a block (and the scale rows are bulk-copy sized)
-        const uint32_t block_bytes = BS * a.row_stride;
-        const uint32_t stage_bytes = 2u * block_bytes + 128u;
-        const bool whole_blocks = pool->n_kv_heads <= (uint32_t)MAX_KV_HEADS_PER_CTA && (!pool->k_scales || pool->n_kv_heads % 4 == 0) &&
-                                  !(d->flags & TKV_ATTN_PER_HEAD_CTAS) && 256u + 2u * stage_bytes <= 200u * 1024u;
         if (whole_blocks) {
             const uint32_t n_stages = std::min<uint32_t>(6u, (200u * 1024u - 256u) / stage_bytes);
             const size_t smem = 256 + (size_t)n_stages * stage_bytes;
@@ -874,17 +885,26 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             a.parts_per_split = 1;
             a.n_splits = n_splits;
             const uint32_t threads = (MAX_KV_HEADS_PER_CTA + 1) * 32;
-            if (pool->dtype == TKV_DTYPE_E4M3) {
-                e = cudaFuncSetAttribute(decode_attn_blocks<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e == cudaSuccess) decode_attn_blocks<true><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
-            } else {
-                e = cudaFuncSetAttribute(decode_attn_blocks<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e == cudaSuccess) decode_attn_blocks<false><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
-            }
-            if (e == cudaSuccess) e = cudaGetLastError();
+            // TKV_ATTN_PROGRAMMATIC_LAUNCH: both kernels may be scheduled before their predecessor in the stream has
+            // finished; each waits for it (griddepcontrol.wait) before reading q or the partials or writing anything
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr.val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = grid2;
+            cfg.blockDim = dim3(threads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = st;
+            cfg.attrs = &attr;
+            cfg.numAttrs = (d->flags & TKV_ATTN_PROGRAMMATIC_LAUNCH) ? 1u : 0u;
+            auto* kernel = pool->dtype == TKV_DTYPE_E4M3 ? decode_attn_blocks<true> : decode_attn_blocks<false>;
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kernel, a, n_stages, stage_bytes);
             if (e == cudaSuccess) {
-                decode_attn_combine<<<dim3(d->n_q_heads, d->n_seqs), D, 0, st>>>(a);
-                e = cudaGetLastError();
+                cfg.gridDim = dim3(d->n_q_heads, d->n_seqs);
+                cfg.blockDim = dim3(D);
+                cfg.dynamicSmemBytes = 0;
+                e = cudaLaunchKernelEx(&cfg, decode_attn_combine, a);
             }
         } else {
         constexpr size_t smem8 = (size_t)WARPS * Ring<true>::STAGES * Ring<true>::STAGE_BYTES;

@@ -140,6 +140,33 @@ def test_shuffled_tables_equal_identity_tables(H):
     assert torch.equal(shuffled, same)
 
 
+def test_programmatic_launch_chain_shares_scratch(H):
+    """Six calls back to back with TKV_ATTN_PROGRAMMATIC_LAUNCH, all merging through ONE scratch buffer: each
+    call's K/V fetch may start under its predecessor, its partial writes may not.  Bit-equal to plain launches."""
+    import torch
+    lens = np.array([900, 33, 1500, 260], dtype=np.uint32)
+    w = W.Workload("attn-pdl", 2, 8, 128, 16, 512, 512, lens, dst_dtype="e4m3", seed=66).build_tables()
+    hs, hd, dd = quantized_pool(H, w)
+    tables = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()
+    lens_t = torch.from_numpy(lens.astype(np.int64)).to(torch.int32).cuda()
+    g = torch.Generator().manual_seed(12)
+    qs = [torch.randn((len(lens), 32, 128), generator=g).cuda() for _ in range(6)]
+    plain = [H.decode_attention(dd, i % 2, q, tables, lens_t, split_tokens=128).clone() for i, q in enumerate(qs)]
+    chain = [H.DecodeAttention(dd, q, tables, lens_t, 1500, split_tokens=128, flags=N.ATTN_PROGRAMMATIC_LAUNCH) for q in qs]
+    for c in chain[1:]:
+        c.scratch = chain[0].scratch
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for i, c in enumerate(chain):
+            c.enqueue(i % 2)
+    torch.cuda.synchronize()
+    for c, want in zip(chain, plain):
+        assert int(c.status.item()) == 0
+        assert torch.equal(c.out, want)
+    want0 = oracle.paged_decode_attention(hd, 0, qs[0].cpu().numpy(), w.dst_tables, lens, 1.0 / np.sqrt(128.0))
+    close(chain[0].out.cpu().numpy(), want0, v_max_per_dim(hs, 0))
+
+
 def test_attention_argument_errors(H):
     import torch
     pool = H.Pool.allocate(0, 1, 8, 64, 16, 8, "f16")
