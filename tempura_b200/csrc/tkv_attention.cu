@@ -577,41 +577,48 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     __syncthreads();
 
     if (warp == CW) {
-        // ---- producer: one lane drives the ring ----
-        if (lane == 0) {
-            uint32_t id_ahead = __ldg(table);
-            uint32_t issued = 0;
-            bool ok = true;
-            for (uint32_t k = 0; k < n_blk && ok; k++) {
-                const uint32_t s = k % n_stages;
-                const uint32_t id = id_ahead;
-                if (k + 1 < n_blk) id_ahead = __ldg(table + k + 1);
-                if (k >= n_stages) ok = mbar_wait(smem_addr(empty + s), ((k / n_stages) - 1u) & 1u);   // every head has read the old block
-                if (!ok) break;
-                const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
-                const uint32_t bytes = n_valid * a.row_stride, sc_bytes = a.k_scales ? a.n_kv_heads * 4u : 0u;
-                const uint32_t bar = smem_addr(full + s), dst = smem_addr(stages + (size_t)s * stage_bytes);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * bytes + 2u * sc_bytes) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(dst), "l"(a.k_base + (uint64_t)id * a.block_stride), "r"(bytes), "r"(bar) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(dst + block_bytes), "l"(a.v_base + (uint64_t)id * a.block_stride), "r"(bytes), "r"(bar) : "memory");
-                if (sc_bytes) {
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(dst + 2u * block_bytes), "l"(a.k_scales + (size_t)id * a.n_kv_heads), "r"(sc_bytes), "r"(bar) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(dst + 2u * block_bytes + 32u), "l"(a.v_scales + (size_t)id * a.n_kv_heads), "r"(sc_bytes), "r"(bar) : "memory");
+        // ---- producer: lane 0 drives the ring; the warp reads the block table 32 entries at a time (one
+        // coalesced load, the next one already in flight), so no copy waits for a table entry of its own ----
+        uint32_t issued = 0;
+        bool ok = true;
+        uint32_t ids_next = lane < n_blk ? __ldg(table + lane) : 0u;
+        for (uint32_t k0 = 0; k0 < n_blk && ok; k0 += 32) {
+            const uint32_t ids = ids_next;
+            ids_next = k0 + 32 + lane < n_blk ? __ldg(table + k0 + 32 + lane) : 0u;
+            const uint32_t lim = min(32u, n_blk - k0);
+            for (uint32_t i = 0; i < lim && ok; i++) {
+                const uint32_t id = __shfl_sync(0xFFFFFFFFu, ids, i);
+                const uint32_t k = k0 + i, s = k % n_stages;
+                if (lane == 0) {
+                    if (k >= n_stages) ok = mbar_wait(smem_addr(empty + s), ((k / n_stages) - 1u) & 1u);   // every head has read the old block
+                    if (ok) {
+                        const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
+                        const uint32_t bytes = n_valid * a.row_stride, sc_bytes = a.k_scales ? a.n_kv_heads * 4u : 0u;
+                        const uint32_t bar = smem_addr(full + s), dst = smem_addr(stages + (size_t)s * stage_bytes);
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * bytes + 2u * sc_bytes) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(dst), "l"(a.k_base + (uint64_t)id * a.block_stride), "r"(bytes), "r"(bar) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(dst + block_bytes), "l"(a.v_base + (uint64_t)id * a.block_stride), "r"(bytes), "r"(bar) : "memory");
+                        if (sc_bytes) {
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(dst + 2u * block_bytes), "l"(a.k_scales + (size_t)id * a.n_kv_heads), "r"(sc_bytes), "r"(bar) : "memory");
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(dst + 2u * block_bytes + 32u), "l"(a.v_scales + (size_t)id * a.n_kv_heads), "r"(sc_bytes), "r"(bar) : "memory");
+                        }
+                        issued = k + 1;
+                    }
                 }
-                issued = k + 1;
+                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
             }
-            if (!ok) {
-                atomicExch(fail_word, 1u);
-                // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
-                for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
-                    mbar_wait(smem_addr(full + k % n_stages), (k / n_stages) & 1u);
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                if (a.status) atomicExch(a.status, 4u);
-            }
+        }
+        if (!ok && lane == 0) {
+            atomicExch(fail_word, 1u);
+            // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
+            for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
+                mbar_wait(smem_addr(full + k % n_stages), (k / n_stages) & 1u);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (a.status) atomicExch(a.status, 4u);
         }
     } else if (warp < a.n_kv_heads) {
         // ---- consumer: kv head `warp`, every block of this CTA's range ----
