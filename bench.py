@@ -605,7 +605,7 @@ def run_attention(args):
     sampler = ClockSampler(0)
     sampler.start()
 
-    attn = H.DecodeAttention(pool, q, tables, lens, max_len, split_tokens=args.attn_split, flags=(1 if args.attn_per_head else 0) | (2 if args.attn_pdl else 0),
+    attn = H.DecodeAttention(pool, q, tables, lens, max_len, split_tokens=args.attn_split, flags=1 if args.attn_per_head else 0,
                              total_kv_tokens=0 if args.attn_no_hint else int(w.seq_lens.astype(np.int64).sum()))
     for layer in range(w.n_layers):          # plain launches first (module load, argument structs)
         attn.enqueue(layer)
@@ -657,7 +657,6 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn"])
     ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
-    ap.add_argument("--attn-pdl", action="store_true", help="--workload attn: programmatic dependent launches between the layers' kernels")
     ap.add_argument("--attn-per-head", action="store_true", help="--workload attn: the per-(sequence, kv head) CTA form")
     ap.add_argument("--attn-f16", action="store_true", help="--workload attn: read the F16 pool instead of the E4M3 one")
     ap.add_argument("--pool-blocks", type=int, default=None)

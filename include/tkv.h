@@ -334,12 +334,7 @@ typedef struct TkvDecodeAttn {
 } TkvDecodeAttn;
 enum { TKV_ATTN_DEFAULT = 0,
        TKV_ATTN_PER_HEAD_CTAS = 1 /* one CTA per (sequence, kv head, split) with per-lane copies, the
-                                     form used when a pool has more than 8 kv heads               */,
-       TKV_ATTN_PROGRAMMATIC_LAUNCH = 2 /* whole-block form: launch both kernels with programmatic stream
-                                     serialization, so the K/V fetch of this call overlaps the tail of the
-                                     kernel before it in the stream.  The caller promises that the pool, the
-                                     tables and kv_lens were complete before that kernel started; q, the
-                                     scratch, out and status are touched only after it has finished       */ };
+                                     form used when a pool has more than 8 kv heads               */ };
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens /* 0 = default */);
 int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* args, void* stream);

@@ -66,8 +66,15 @@ __device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
     return r;
 }
 
+// 2^x on the special-function unit (relative error 2^-22, -inf -> 0): the softmax runs in the exp2 domain
+__device__ __forceinline__ float fast_exp2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -376,9 +383,9 @@ __device__ __forceinline__ void attend_block_t(const Tile<FP8>& cur, uint32_t n_
         mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 8));
         mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
         const float m_new = fmaxf(m2[h], mx);
-        corr[h] = m2[h] == -INFINITY ? 0.0f : exp2f(m2[h] - m_new);
-        p[h] = exp2f(s_lo - m_new);
-        p[2 + h] = exp2f(s_hi - m_new);
+        corr[h] = m2[h] == -INFINITY ? 0.0f : fast_exp2(m2[h] - m_new);
+        p[h] = fast_exp2(s_lo - m_new);
+        p[2 + h] = fast_exp2(s_hi - m_new);
         l2[h] = l2[h] * corr[h] + p[h] + p[2 + h];
         m2[h] = m_new;
     }
@@ -481,22 +488,24 @@ __device__ __forceinline__ void attend_two_blocks_t(const Tile<FP8>& t0, const T
         mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 8));
         mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
         const float m_new = fmaxf(m2[h], mx);
-        corr[h] = m2[h] == -INFINITY ? 0.0f : exp2f(m2[h] - m_new);
-        p0[h] = exp2f(s00 - m_new);
-        p0[2 + h] = exp2f(s01 - m_new);
-        p1[h] = exp2f(s10 - m_new);
-        p1[2 + h] = exp2f(s11 - m_new);
+        corr[h] = m2[h] == -INFINITY ? 0.0f : fast_exp2(m2[h] - m_new);
+        p0[h] = fast_exp2(s00 - m_new);
+        p0[2 + h] = fast_exp2(s01 - m_new);
+        p1[h] = fast_exp2(s10 - m_new);
+        p1[2 + h] = fast_exp2(s11 - m_new);
         l2[h] = l2[h] * corr[h] + (p0[h] + p0[2 + h]) + (p1[h] + p1[2 + h]);
         m2[h] = m_new;
     }
     const uint32_t b00 = movmatrix_trans(pack_h2(p0[0] * t0.vs, p0[1] * t0.vs)), b01 = movmatrix_trans(pack_h2(p0[2] * t0.vs, p0[3] * t0.vs));
     const uint32_t b10 = movmatrix_trans(pack_h2(p1[0] * t1.vs, p1[1] * t1.vs)), b11 = movmatrix_trans(pack_h2(p1[2] * t1.vs, p1[3] * t1.vs));
+    if (__any_sync(0xFFFFFFFFu, corr[0] != 1.0f || corr[1] != 1.0f)) {   // exactly 1 once the running maxima have settled
 #pragma unroll
-    for (int t = 0; t < 8; t++) {
-        o[t][0] *= corr[0];
-        o[t][1] *= corr[1];
-        o[t][2] *= corr[0];
-        o[t][3] *= corr[1];
+        for (int t = 0; t < 8; t++) {
+            o[t][0] *= corr[0];
+            o[t][1] *= corr[1];
+            o[t][2] *= corr[0];
+            o[t][3] *= corr[1];
+        }
     }
     pv_tile<FP8>(t0, b00, b01, o);
     pv_tile<FP8>(t1, b10, b11, o);
@@ -547,9 +556,6 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     constexpr int CW = MAX_KV_HEADS_PER_CTA;
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int KW = Tile<FP8>::KW;
-    // Under a programmatic launch the next kernel in the stream may be scheduled from here on (it waits for this
-    // grid's completion itself before it touches what this grid writes); without one both instructions do nothing.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t split = blockIdx.x, seq = blockIdx.y;
     const uint32_t kv_len = a.kv_lens[seq];
     const uint32_t t_begin = split * a.split_tokens;
@@ -617,15 +623,11 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
             // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
             for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
                 mbar_wait(smem_addr(full + k % n_stages), (k / n_stages) & 1u);
-            asm volatile("griddepcontrol.wait;" ::: "memory");
             if (a.status) atomicExch(a.status, 4u);
         }
     } else if (warp < a.n_kv_heads) {
         // ---- consumer: kv head `warp`, every block of this CTA's range ----
         const uint32_t kvh = warp;
-        // the producer warp is already fetching K/V (the pool, the tables and the lengths are the caller's to keep
-        // stable); q, the partials and the status word are touched only once the preceding kernel has completed
-        asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t qa[8][2];
         {
             const bool live = grp < a.group;
@@ -661,10 +663,14 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                 const uint32_t tok = 2 * j + (i & 1) + 8 * (i >> 1);
                 const unsigned char* row = vb + (size_t)tok * a.row_stride + 16 * grp * ES;
 #pragma unroll
-                for (int w = 0; w < KW; w++) {                       // rows the copy did not bring hold stale bytes: read them as zero
-                    const uint4 x = lds_once(row + 16 * w);
-                    t.v[i][w] = tok < n_valid ? x : make_uint4(0, 0, 0, 0);
-                }
+                for (int w = 0; w < KW; w++) t.v[i][w] = lds_once(row + 16 * w);
+            }
+            if (n_valid < (uint32_t)BS) {                            // rows the copy did not bring hold stale bytes: read them as zero
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int w = 0; w < KW; w++)
+                        if (2 * j + (i & 1) + 8 * (i >> 1) >= n_valid) t.v[i][w] = make_uint4(0, 0, 0, 0);
             }
             if (a.k_scales) {
                 const float* sc = reinterpret_cast<const float*>(stages + (size_t)s * stage_bytes + 2u * block_bytes);
@@ -755,10 +761,8 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const uint32_t kvh = head / a.group, g = head % a.group;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t kv_len = a.kv_lens[seq];
     const uint32_t live = ((kv_len + a.split_tokens - 1) / a.split_tokens) * a.parts_per_split;
-    asm volatile("griddepcontrol.wait;" ::: "memory");       // the partials are complete (no-op in a plain launch)
     const float* base = a.partial + (((size_t)seq * a.n_kv_heads + kvh) * a.n_splits * a.group + g) * (D + 2);
     const size_t stride = (size_t)a.group * (D + 2);
     // running max over the splits: every thread takes a strided share, then one reduction through shared memory
@@ -892,26 +896,17 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             a.parts_per_split = 1;
             a.n_splits = n_splits;
             const uint32_t threads = (MAX_KV_HEADS_PER_CTA + 1) * 32;
-            // TKV_ATTN_PROGRAMMATIC_LAUNCH: both kernels may be scheduled before their predecessor in the stream has
-            // finished; each waits for it (griddepcontrol.wait) before reading q or the partials or writing anything
-            cudaLaunchAttribute attr{};
-            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr.val.programmaticStreamSerializationAllowed = 1;
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = grid2;
-            cfg.blockDim = dim3(threads);
-            cfg.dynamicSmemBytes = smem;
-            cfg.stream = st;
-            cfg.attrs = &attr;
-            cfg.numAttrs = (d->flags & TKV_ATTN_PROGRAMMATIC_LAUNCH) ? 1u : 0u;
-            auto* kernel = pool->dtype == TKV_DTYPE_E4M3 ? decode_attn_blocks<true> : decode_attn_blocks<false>;
-            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kernel, a, n_stages, stage_bytes);
+            if (pool->dtype == TKV_DTYPE_E4M3) {
+                e = cudaFuncSetAttribute(decode_attn_blocks<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e == cudaSuccess) decode_attn_blocks<true><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
+            } else {
+                e = cudaFuncSetAttribute(decode_attn_blocks<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e == cudaSuccess) decode_attn_blocks<false><<<grid2, threads, smem, st>>>(a, n_stages, stage_bytes);
+            }
+            if (e == cudaSuccess) e = cudaGetLastError();
             if (e == cudaSuccess) {
-                cfg.gridDim = dim3(d->n_q_heads, d->n_seqs);
-                cfg.blockDim = dim3(D);
-                cfg.dynamicSmemBytes = 0;
-                e = cudaLaunchKernelEx(&cfg, decode_attn_combine, a);
+                decode_attn_combine<<<dim3(d->n_q_heads, d->n_seqs), D, 0, st>>>(a);
+                e = cudaGetLastError();
             }
         } else {
         constexpr size_t smem8 = (size_t)WARPS * Ring<true>::STAGES * Ring<true>::STAGE_BYTES;

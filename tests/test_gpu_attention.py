@@ -140,19 +140,19 @@ def test_shuffled_tables_equal_identity_tables(H):
     assert torch.equal(shuffled, same)
 
 
-def test_programmatic_launch_chain_shares_scratch(H):
-    """Six calls back to back with TKV_ATTN_PROGRAMMATIC_LAUNCH, all merging through ONE scratch buffer: each
-    call's K/V fetch may start under its predecessor, its partial writes may not.  Bit-equal to plain launches."""
+def test_back_to_back_calls_share_one_scratch(H):
+    """Eighteen calls back to back in one stream, all merging through ONE scratch buffer: each call's partials are
+    written only after the call before it has merged its own.  Bit-equal to calls run one at a time."""
     import torch
     lens = np.array([900, 33, 1500, 260], dtype=np.uint32)
-    w = W.Workload("attn-pdl", 2, 8, 128, 16, 512, 512, lens, dst_dtype="e4m3", seed=66).build_tables()
+    w = W.Workload("attn-chain", 2, 8, 128, 16, 512, 512, lens, dst_dtype="e4m3", seed=66).build_tables()
     hs, hd, dd = quantized_pool(H, w)
     tables = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()
     lens_t = torch.from_numpy(lens.astype(np.int64)).to(torch.int32).cuda()
     g = torch.Generator().manual_seed(12)
     qs = [torch.randn((len(lens), 32, 128), generator=g).cuda() for _ in range(6)]
     plain = [H.decode_attention(dd, i % 2, q, tables, lens_t, split_tokens=128).clone() for i, q in enumerate(qs)]
-    chain = [H.DecodeAttention(dd, q, tables, lens_t, 1500, split_tokens=128, flags=N.ATTN_PROGRAMMATIC_LAUNCH) for q in qs]
+    chain = [H.DecodeAttention(dd, q, tables, lens_t, 1500, split_tokens=128) for q in qs]
     for c in chain[1:]:
         c.scratch = chain[0].scratch
     torch.cuda.synchronize()
