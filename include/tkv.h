@@ -426,6 +426,49 @@ size_t tkv_prefix_table_len(const tkv_prefix_table*);
 uint64_t tkv_prefix_table_hit_count(const tkv_prefix_table*);
 uint64_t tkv_prefix_table_tokens_saved(const tkv_prefix_table*);
 
+/* ---- device-resident prefix index --------------------------------------------- */
+/* RadixTree (engine/src/prefix_cache.rs:17-149) kept in HBM and walked by the GPU, one warp per
+ * sequence, so a batch of prompts resolves its cached prefix (length, page ids, reference
+ * counts, LRU stamps) in one launch.  A node is `group_tokens` consecutive token ids below its
+ * parent (1 = the reference's per-token nodes, 16 = one node per KV block), named by a 64-bit
+ * hash chained from the root; only whole groups are indexed.  One call is one tick of the
+ * reference's clock, and its result is that of the reference's method applied to the
+ * sequences in index order at that tick.  Calls on one index must be stream-ordered.
+ * Departure kept from the host mirror above: an unlinked node is never reported twice.      */
+typedef struct tkv_prefix_index tkv_prefix_index;
+typedef struct TkvPrefixBatch {
+    uint32_t n_seqs, stride, page_stride, reserved;
+    uint64_t tokens;              /* device u32 [n_seqs][stride] token ids                        */
+    uint64_t lens;                /* device u32 [n_seqs] tokens per sequence (<= stride)         */
+    uint64_t pages;               /* insert: device u32 [n_seqs][page_stride], page of node i of a
+                                     sequence at [i]; 0 = insert without pages                  */
+    uint64_t page_lens;           /* insert: device u32 [n_seqs] valid entries per row; 0 = rows are full */
+} TkvPrefixBatch;
+typedef struct TkvPrefixIndexStats {
+    uint64_t hits, tokens_saved;  /* RadixTree::hit_count / tokens_saved                         */
+    uint64_t live_nodes, tombstones, capacity, ticks;
+    uint32_t group_tokens;
+    uint32_t table_full;          /* 1 once an insert found no free slot (nodes of that call are missing) */
+} TkvPrefixIndexStats;
+#define TKV_PREFIX_NO_PAGE 0xFFFFFFFFu
+int32_t tkv_prefix_index_create(int32_t device, uint64_t capacity /* power of two */, uint32_t group_tokens, tkv_prefix_index** out);
+void tkv_prefix_index_destroy(tkv_prefix_index*);
+/* RadixTree::insert for every sequence of the batch */
+int32_t tkv_prefix_index_insert(tkv_prefix_index*, const TkvPrefixBatch*, void* stream);
+/* RadixTree::lookup: out_matched[s] = matched nodes of sequence s (times group_tokens = its prefix
+ * length, the handoff batch's prefix_lens); out_pages[s][i] = page of matched node i or
+ * TKV_PREFIX_NO_PAGE (entries past the match are left alone).  Either output may be 0.        */
+int32_t tkv_prefix_index_lookup(tkv_prefix_index*, const TkvPrefixBatch*, uint64_t out_pages /* device u32 [n_seqs][out_stride] */,
+                                uint32_t out_stride, uint64_t out_matched /* device u32 [n_seqs] */, void* stream);
+/* RadixTree::release */
+int32_t tkv_prefix_index_release(tkv_prefix_index*, const TkvPrefixBatch*, void* stream);
+/* RadixTree::evict_lru, up to max_nodes times: *out_count = pages written to out_pages (device u32
+ * [out_cap]), *out_nodes (optional) = nodes unlinked.                                            */
+int32_t tkv_prefix_index_evict_lru(tkv_prefix_index*, uint32_t max_nodes, uint64_t out_pages, uint32_t out_cap,
+                                   uint64_t out_count /* device u32 */, uint64_t out_nodes /* device u32 or 0 */, void* stream);
+/* synchronises the stream */
+int32_t tkv_prefix_index_stats(tkv_prefix_index*, void* stream, TkvPrefixIndexStats* out);
+
 #ifdef __cplusplus
 }
 #endif

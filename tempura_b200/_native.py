@@ -56,6 +56,19 @@ class TkvDecodeAttn(C.Structure):
         ("sm_scale", C.c_float), ("split_tokens", C.c_uint32), ("flags", C.c_uint32)] + [(n, C.c_uint64) for n in ("q", "out", "tables", "kv_lens", "scratch", "scratch_bytes", "total_kv_tokens", "status")]
 
 
+class TkvPrefixBatch(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_seqs", "stride", "page_stride", "reserved")] + [
+        (n, C.c_uint64) for n in ("tokens", "lens", "pages", "page_lens")]
+
+
+class TkvPrefixIndexStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("hits", "tokens_saved", "live_nodes", "tombstones", "capacity", "ticks")] + [
+        ("group_tokens", C.c_uint32), ("table_full", C.c_uint32)]
+
+
+PREFIX_NO_PAGE = 0xFFFFFFFF
+
+
 class TkvSessionHeader(C.Structure):
     _fields_ = [("position", C.c_uint64), ("seed", C.c_uint64)] + [(n, C.c_uint32) for n in (
         "seq_len", "n_layers", "n_kv_heads", "head_dim", "block_size", "kv_dtype", "block_begin", "n_blocks",
@@ -138,6 +151,13 @@ SIGNATURES = {
     "tkv_run_allocator_free_pages": (_sz, [_vp]),
     "tkv_run_allocator_allocated_pages": (_sz, [_vp]),
     "tkv_run_allocator_free_runs": (_sz, [_vp, _szp, _szp, _sz]),
+    "tkv_prefix_index_create": (_i32, [_i32, _u64, _u32, C.POINTER(_vp)]),
+    "tkv_prefix_index_destroy": (None, [_vp]),
+    "tkv_prefix_index_insert": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _vp]),
+    "tkv_prefix_index_lookup": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _u64, _u32, _u64, _vp]),
+    "tkv_prefix_index_release": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _vp]),
+    "tkv_prefix_index_evict_lru": (_i32, [_vp, _u32, _u64, _u32, _u64, _u64, _vp]),
+    "tkv_prefix_index_stats": (_i32, [_vp, _vp, C.POINTER(TkvPrefixIndexStats)]),
     "tkv_radix_tree_new": (_vp, []),
     "tkv_radix_tree_delete": (None, [_vp]),
     "tkv_radix_tree_insert": (None, [_vp, _u32p, _sz, _szp, _sz]),

@@ -1,0 +1,479 @@
+// Device-resident prefix index: RadixTree (engine/src/prefix_cache.rs:17-149) as an open-addressing
+// hash table in HBM, walked by one warp per sequence, so that a batch of prompts resolves its cached
+// prefix (length, page ids, reference counts, LRU stamps) in one launch without a host round trip.
+//
+// A node of the reference's tree is one element of a sequence below one parent.  Here an element is
+// `group_tokens` consecutive token ids (1 reproduces the reference's per-token nodes, 16 gives one
+// node per KV block) and a node is named by a 64-bit key chained from the root:
+//     key_i = mix(key_{i-1}, hash(tokens of element i)),
+// so equal keys mean equal prefixes up to a 64-bit hash collision (the index does not store the
+// tokens; two different prefixes collide with probability 2^-64 per pair).
+//
+// Batch semantics: one call handles many sequences and is ONE tick of the reference's clock.  Its
+// result equals the reference's methods applied to the sequences in index order at that tick:
+//   insert   a node new in this call takes the page of the lowest-numbered sequence that walks it;
+//   lookup   matched nodes get stamp = tick and one more reference each, per walking sequence;
+//   release  references go down by one per walking sequence, never below zero;
+//   evict    one unreferenced childless node, oldest stamp first, earliest-created on a tie, is
+//            unlinked and its page reported (an unlinked node is never reported twice, unlike
+//            prefix_cache.rs:99-125, which leaves it eligible: a page must not be freed twice).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <new>
+
+#include "../../include/tkv.h"
+
+namespace tkv_internal {
+int32_t set_error(int32_t code, int32_t cuda_code, const char* message);
+}
+
+namespace {
+
+constexpr unsigned long long KEY_EMPTY = 0ull, KEY_TOMB = 1ull;     // real keys are >= 2
+constexpr unsigned long long ORDER_FRESH = ~0ull;
+constexpr uint32_t NO_PAGE = 0xFFFFFFFFu, NO_SLOT = 0xFFFFFFFFu;
+constexpr int WARPS_PER_CTA = 4;
+// creation order of a node: tick (34 bits) | sequence in the batch (14 bits) | depth (16 bits)
+constexpr int ORDER_SEQ_BITS = 14, ORDER_DEPTH_BITS = 16;
+
+struct Meta {                   // 32 bytes per slot
+    unsigned long long order;   // creation order; ORDER_FRESH while the slot is free
+    unsigned long long stamp;   // tick of the last insert / lookup that walked the node
+    uint32_t page;              // NO_PAGE when the node was inserted without one
+    int32_t refs;
+    uint32_t parent;            // slot of the parent node, NO_SLOT below the root
+    uint32_t children;
+};
+
+struct Counters {               // device-side statistics and the eviction scratch
+    unsigned long long hits, tokens_saved, live, tombstones;
+    uint32_t error;             // 1 = table full during an insert
+    uint32_t evict_ctas_done;
+};
+
+struct Candidate {
+    unsigned long long stamp, order;
+    uint32_t slot, valid;
+};
+
+struct View {
+    unsigned long long* keys;
+    Meta* meta;
+    Counters* ctr;
+    Candidate* cand;            // one per eviction CTA
+    uint32_t mask;              // capacity - 1
+    uint32_t group;
+};
+
+struct Batch {
+    const uint32_t* tokens;     // [n_seqs][stride]
+    const uint32_t* lens;       // [n_seqs] tokens
+    const uint32_t* pages;      // [n_seqs][page_stride] or null
+    const uint32_t* page_lens;  // [n_seqs] or null (then `pages` rows are full)
+    uint32_t n_seqs, stride, page_stride;
+};
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x ^= x >> 30;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27;
+    x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+
+__device__ __forceinline__ unsigned long long element_hash(const uint32_t* tok, uint32_t group) {
+    unsigned long long h = 0x9E3779B97F4A7C15ull;
+    for (uint32_t i = 0; i < group; i++) h = mix64(h ^ ((unsigned long long)__ldg(tok + i) + 0x632BE59BD9B4E019ull * (i + 1)));
+    return h;
+}
+
+__device__ __forceinline__ unsigned long long chain(unsigned long long parent_key, unsigned long long h) {
+    unsigned long long k = mix64(parent_key * 0xD6E8FEB86659FD93ull + h);
+    return k < 2 ? k + 2 : k;
+}
+
+// Keys of the 32 elements [base, base + 32) of one sequence, one per lane; `carry` is the key of element
+// base - 1 (the root key for base 0) and leaves as the key of element base + 31.
+__device__ __forceinline__ unsigned long long keys_of_chunk(const uint32_t* row, uint32_t base, uint32_t n_elems, uint32_t group,
+                                                            unsigned long long& carry) {
+    const uint32_t lane = threadIdx.x & 31u, i = base + lane;
+    const unsigned long long h = i < n_elems ? element_hash(row + (size_t)i * group, group) : 0ull;
+    unsigned long long key = carry, mine = 0;
+#pragma unroll 8
+    for (uint32_t l = 0; l < 32; l++) {
+        key = chain(key, __shfl_sync(0xFFFFFFFFu, h, l));
+        if (l == lane) mine = key;
+    }
+    carry = key;
+    return mine;
+}
+
+__device__ __forceinline__ uint32_t find_slot(const View& ix, unsigned long long key) {
+    uint32_t h = (uint32_t)(key >> 17) & ix.mask;
+    for (uint32_t p = 0; p <= ix.mask; p++, h = (h + 1) & ix.mask) {
+        const unsigned long long k = ix.keys[h];
+        if (k == key) return h;
+        if (k == KEY_EMPTY) return NO_SLOT;
+    }
+    return NO_SLOT;
+}
+
+// Finds the node or claims a slot for it (a tombstone on the probe path before the first empty slot is
+// reused).  Exactly one thread of the grid gets `created` for a key that was absent.
+__device__ __forceinline__ uint32_t find_or_claim(const View& ix, unsigned long long key, bool& created, bool& reused) {
+    created = reused = false;
+    uint32_t h = (uint32_t)(key >> 17) & ix.mask, first_tomb = NO_SLOT, scanned = 0;
+    volatile unsigned long long* keys = ix.keys;
+    for (uint32_t p = 0; p <= 4u * ix.mask + 3u; p++) {
+        const unsigned long long k = keys[h];
+        if (k == key) return h;
+        if (k == KEY_TOMB && first_tomb == NO_SLOT) first_tomb = h;
+        const bool path_ends = k == KEY_EMPTY || scanned == ix.mask;      // an empty slot, or the whole table seen (no empty slot left)
+        if (path_ends) {
+            if (k != KEY_EMPTY && first_tomb == NO_SLOT) return NO_SLOT;  // full of live nodes
+            const uint32_t target = first_tomb != NO_SLOT ? first_tomb : h;
+            const unsigned long long expect = first_tomb != NO_SLOT ? KEY_TOMB : KEY_EMPTY;
+            const unsigned long long old = atomicCAS(ix.keys + target, expect, key);
+            if (old == expect) {
+                created = true;
+                reused = first_tomb != NO_SLOT;
+                return target;
+            }
+            if (old == key) return target;
+            h = target;                 // somebody else's key went in: look again from there
+            first_tomb = NO_SLOT;
+            scanned = 0;
+            continue;
+        }
+        h = (h + 1) & ix.mask;
+        scanned++;
+    }
+    return NO_SLOT;
+}
+
+enum Op { OP_LOOKUP = 0, OP_INSERT_CLAIM = 1, OP_INSERT_PAGES = 2, OP_RELEASE = 3 };
+
+template <int OP>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32) prefix_walk(View ix, Batch b, unsigned long long tick, uint32_t* out_pages,
+                                                                  uint32_t out_stride, uint32_t* out_matched) {
+    const uint32_t seq = blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (seq >= b.n_seqs) return;
+    const uint32_t n_elems = min(b.lens[seq], b.stride) / ix.group;
+    const uint32_t* row = b.tokens + (size_t)seq * b.stride;
+    unsigned long long carry = 0x243F6A8885A308D3ull;       // the root's key
+    uint32_t parent_carry = NO_SLOT, matched = 0;
+    for (uint32_t base = 0; base < n_elems; base += 32) {
+        const uint32_t i = base + lane;
+        const bool active = i < n_elems;
+        const unsigned long long key = keys_of_chunk(row, base, n_elems, ix.group, carry);
+        if (OP == OP_INSERT_CLAIM) {
+            bool created = false, reused = false;
+            const uint32_t slot = active ? find_or_claim(ix, key, created, reused) : NO_SLOT;
+            if (active && slot == NO_SLOT) atomicExch(&ix.ctr->error, 1u);
+            uint32_t parent = __shfl_up_sync(0xFFFFFFFFu, slot, 1);
+            if (lane == 0) parent = parent_carry;
+            parent_carry = __shfl_sync(0xFFFFFFFFu, slot, 31);
+            if (active && slot != NO_SLOT) {
+                const unsigned long long order = (tick << (ORDER_SEQ_BITS + ORDER_DEPTH_BITS)) |
+                                                 ((unsigned long long)seq << ORDER_DEPTH_BITS) | min(i, (1u << ORDER_DEPTH_BITS) - 1u);
+                atomicMin(&ix.meta[slot].order, order);     // an older node keeps its (smaller) order
+                atomicMax(&ix.meta[slot].stamp, tick);
+                if (created) {
+                    ix.meta[slot].parent = parent;
+                    if (parent != NO_SLOT) atomicAdd(&ix.meta[parent].children, 1u);
+                    atomicAdd(&ix.ctr->live, 1ull);
+                    if (reused) atomicAdd(&ix.ctr->tombstones, ~0ull);
+                }
+            }
+        } else {
+            const uint32_t slot = active ? find_slot(ix, key) : NO_SLOT;
+            const uint32_t hit = __ballot_sync(0xFFFFFFFFu, slot != NO_SLOT);
+            const uint32_t run = hit == 0xFFFFFFFFu ? 32u : (uint32_t)__ffs(~hit) - 1u;   // matched elements of this chunk, from its start
+            if (lane < run) {
+                Meta& m = ix.meta[slot];
+                if (OP == OP_LOOKUP) {
+                    atomicAdd(&m.refs, 1);
+                    atomicMax(&m.stamp, tick);
+                    if (out_pages && i < out_stride) out_pages[(size_t)seq * out_stride + i] = m.page;
+                } else if (OP == OP_RELEASE) {
+                    if (atomicAdd(&m.refs, -1) <= 0) atomicAdd(&m.refs, 1);       // never below zero
+                } else {                                                           // OP_INSERT_PAGES: the creator writes its page
+                    const unsigned long long order = (tick << (ORDER_SEQ_BITS + ORDER_DEPTH_BITS)) |
+                                                     ((unsigned long long)seq << ORDER_DEPTH_BITS) | min(i, (1u << ORDER_DEPTH_BITS) - 1u);
+                    if (m.order == order) {
+                        const uint32_t n_pages = b.pages ? (b.page_lens ? min(b.page_lens[seq], b.page_stride) : b.page_stride) : 0u;
+                        m.page = i < n_pages ? b.pages[(size_t)seq * b.page_stride + i] : NO_PAGE;
+                    }
+                }
+            }
+            matched += run;
+            if (run < 32u) break;
+        }
+    }
+    if (OP == OP_LOOKUP && lane == 0) {
+        if (out_matched) out_matched[seq] = matched;
+        if (matched) {
+            atomicAdd(&ix.ctr->hits, 1ull);
+            atomicAdd(&ix.ctr->tokens_saved, (unsigned long long)matched * ix.group);
+        }
+    }
+}
+
+__device__ __forceinline__ bool older(const Candidate& a, const Candidate& b) {      // a before b in eviction order
+    if (a.valid != b.valid) return a.valid > b.valid;
+    if (a.stamp != b.stamp) return a.stamp < b.stamp;
+    if (a.order != b.order) return a.order < b.order;
+    return a.slot < b.slot;
+}
+
+// One victim per launch: every CTA scans a share of the table for its best candidate; the last CTA to
+// finish picks the best of those, unlinks it and appends its page to the output.
+__global__ void __launch_bounds__(256) prefix_evict_one(View ix, uint32_t* out_pages, uint32_t out_cap, uint32_t* out_count,
+                                                        uint32_t* out_nodes) {
+    __shared__ Candidate best[256];
+    __shared__ uint32_t last;
+    Candidate mine{~0ull, ~0ull, NO_SLOT, 0u};
+    for (uint32_t s = blockIdx.x * blockDim.x + threadIdx.x; s <= ix.mask; s += gridDim.x * blockDim.x) {
+        if (ix.keys[s] < 2) continue;
+        const Meta m = ix.meta[s];
+        if (m.refs > 0 || m.children != 0) continue;
+        const Candidate c{m.stamp, m.order, s, 1u};
+        if (older(c, mine)) mine = c;
+    }
+    best[threadIdx.x] = mine;
+    __syncthreads();
+    for (uint32_t off = 128; off > 0; off >>= 1) {
+        if (threadIdx.x < off && older(best[threadIdx.x + off], best[threadIdx.x])) best[threadIdx.x] = best[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        ix.cand[blockIdx.x] = best[0];
+        __threadfence();
+        last = atomicAdd(&ix.ctr->evict_ctas_done, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    mine = Candidate{~0ull, ~0ull, NO_SLOT, 0u};
+    for (uint32_t c = threadIdx.x; c < gridDim.x; c += blockDim.x) {
+        const Candidate x{__ldcg(&ix.cand[c].stamp), __ldcg(&ix.cand[c].order), __ldcg(&ix.cand[c].slot), __ldcg(&ix.cand[c].valid)};
+        if (older(x, mine)) mine = x;
+    }
+    best[threadIdx.x] = mine;
+    __syncthreads();
+    for (uint32_t off = 128; off > 0; off >>= 1) {
+        if (threadIdx.x < off && older(best[threadIdx.x + off], best[threadIdx.x])) best[threadIdx.x] = best[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        ix.ctr->evict_ctas_done = 0;
+        const Candidate v = best[0];
+        if (v.valid) {
+            Meta& m = ix.meta[v.slot];
+            if (m.page != NO_PAGE) {
+                const uint32_t at = atomicAdd(out_count, 1u);
+                if (at < out_cap) out_pages[at] = m.page;
+            }
+            if (out_nodes) atomicAdd(out_nodes, 1u);
+            if (m.parent != NO_SLOT) atomicSub(&ix.meta[m.parent].children, 1u);
+            m = Meta{ORDER_FRESH, 0ull, NO_PAGE, 0, NO_SLOT, 0u};
+            ix.keys[v.slot] = KEY_TOMB;
+            ix.ctr->live -= 1;
+            ix.ctr->tombstones += 1;
+        }
+    }
+}
+
+__global__ void prefix_index_clear(View ix) {
+    for (size_t s = blockIdx.x * (size_t)blockDim.x + threadIdx.x; s <= ix.mask; s += (size_t)gridDim.x * blockDim.x) {
+        ix.keys[s] = KEY_EMPTY;
+        ix.meta[s] = Meta{ORDER_FRESH, 0ull, NO_PAGE, 0, NO_SLOT, 0u};
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *ix.ctr = Counters{};
+}
+
+int32_t fail(int32_t code, const char* msg) { return tkv_internal::set_error(code, 0, msg); }
+int32_t fail_cuda(cudaError_t e, const char* what) {
+    char buf[200];
+    snprintf(buf, sizeof buf, "cuda error: %s: %s", what, cudaGetErrorString(e));
+    return tkv_internal::set_error(TKV_ERR_CUDA, (int32_t)e, buf);
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    cudaError_t err;
+    explicit DeviceGuard(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+        else if (err == cudaSuccess) prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+}  // namespace
+
+struct tkv_prefix_index {
+    int device = 0;
+    uint64_t capacity = 0;
+    uint32_t group = 1;
+    unsigned long long tick = 0;
+    int evict_ctas = 1;
+    View view{};
+};
+
+namespace {
+
+int32_t check_batch(const tkv_prefix_index* ix, const TkvPrefixBatch* b, Batch& out) {
+    if (!ix || !b) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (b->n_seqs == 0) return TKV_OK;
+    if (!b->tokens || !b->lens || b->stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "prefix batch: NULL tokens / lens or zero stride");
+    if (b->n_seqs >= (1u << ORDER_SEQ_BITS)) return fail(TKV_ERR_INVALID_CONFIG, "prefix batch: at most 16383 sequences per call");
+    if (b->pages && b->page_stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "prefix batch: pages without page_stride");
+    out.tokens = reinterpret_cast<const uint32_t*>(b->tokens);
+    out.lens = reinterpret_cast<const uint32_t*>(b->lens);
+    out.pages = reinterpret_cast<const uint32_t*>(b->pages);
+    out.page_lens = reinterpret_cast<const uint32_t*>(b->page_lens);
+    out.n_seqs = b->n_seqs;
+    out.stride = b->stride;
+    out.page_stride = b->page_stride;
+    return TKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t tkv_prefix_index_create(int32_t device, uint64_t capacity, uint32_t group_tokens, tkv_prefix_index** out) {
+    if (!out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    *out = nullptr;
+    if (capacity < 64 || capacity > (1ull << 31) || (capacity & (capacity - 1)))
+        return fail(TKV_ERR_INVALID_CONFIG, "prefix index: capacity must be a power of two in [64, 2^31]");
+    if (group_tokens == 0 || group_tokens > 4096) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: group_tokens must be in [1, 4096]");
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    auto* ix = new (std::nothrow) tkv_prefix_index();
+    if (!ix) return fail(TKV_ERR_POOL_EXHAUSTED, "prefix index: out of host memory");
+    ix->device = device;
+    ix->capacity = capacity;
+    ix->group = group_tokens;
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    ix->evict_ctas = (int)std::min<uint64_t>(std::max(sms, 1) * 4, (capacity + 255) / 256);
+    cudaError_t e = cudaMalloc(&ix->view.keys, capacity * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&ix->view.meta, capacity * sizeof(Meta));
+    if (e == cudaSuccess) e = cudaMalloc(&ix->view.ctr, sizeof(Counters));
+    if (e == cudaSuccess) e = cudaMalloc(&ix->view.cand, (size_t)ix->evict_ctas * sizeof(Candidate));
+    if (e == cudaSuccess) {
+        ix->view.mask = (uint32_t)(capacity - 1);
+        ix->view.group = group_tokens;
+        prefix_index_clear<<<std::max(sms, 1) * 2, 256>>>(ix->view);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    }
+    if (e != cudaSuccess) {
+        tkv_prefix_index_destroy(ix);
+        return fail_cuda(e, "prefix index allocation");
+    }
+    *out = ix;
+    return TKV_OK;
+}
+
+void tkv_prefix_index_destroy(tkv_prefix_index* ix) {
+    if (!ix) return;
+    DeviceGuard guard(ix->device);
+    cudaFree(ix->view.keys);
+    cudaFree(ix->view.meta);
+    cudaFree(ix->view.ctr);
+    cudaFree(ix->view.cand);
+    delete ix;
+}
+
+int32_t tkv_prefix_index_insert(tkv_prefix_index* ix, const TkvPrefixBatch* batch, void* stream) {
+    Batch b{};
+    if (int32_t rc = check_batch(ix, batch, b)) return rc;
+    if (b.n_seqs == 0) return TKV_OK;
+    DeviceGuard guard(ix->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    const unsigned long long tick = ++ix->tick;
+    if (tick >> (64 - ORDER_SEQ_BITS - ORDER_DEPTH_BITS)) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: call counter exhausted");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+    // two launches: every node is found or claimed first, then the sequence that created a node writes its page
+    prefix_walk<OP_INSERT_CLAIM><<<ctas, WARPS_PER_CTA * 32, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
+    prefix_walk<OP_INSERT_PAGES><<<ctas, WARPS_PER_CTA * 32, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index insert");
+}
+
+int32_t tkv_prefix_index_lookup(tkv_prefix_index* ix, const TkvPrefixBatch* batch, uint64_t out_pages, uint32_t out_stride,
+                                uint64_t out_matched, void* stream) {
+    Batch b{};
+    if (int32_t rc = check_batch(ix, batch, b)) return rc;
+    if (b.n_seqs == 0) return TKV_OK;
+    if (out_pages && out_stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: out_pages without out_stride");
+    DeviceGuard guard(ix->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    const unsigned long long tick = ++ix->tick;
+    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+    prefix_walk<OP_LOOKUP><<<ctas, WARPS_PER_CTA * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        ix->view, b, tick, reinterpret_cast<uint32_t*>(out_pages), out_stride, reinterpret_cast<uint32_t*>(out_matched));
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index lookup");
+}
+
+int32_t tkv_prefix_index_release(tkv_prefix_index* ix, const TkvPrefixBatch* batch, void* stream) {
+    Batch b{};
+    if (int32_t rc = check_batch(ix, batch, b)) return rc;
+    if (b.n_seqs == 0) return TKV_OK;
+    DeviceGuard guard(ix->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+    prefix_walk<OP_RELEASE><<<ctas, WARPS_PER_CTA * 32, 0, static_cast<cudaStream_t>(stream)>>>(ix->view, b, ix->tick, nullptr, 0, nullptr);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index release");
+}
+
+int32_t tkv_prefix_index_evict_lru(tkv_prefix_index* ix, uint32_t max_nodes, uint64_t out_pages, uint32_t out_cap, uint64_t out_count,
+                                   uint64_t out_nodes, void* stream) {
+    if (!ix) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (!out_count || (out_cap && !out_pages)) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: evict needs out_count (and out_pages for out_cap > 0)");
+    DeviceGuard guard(ix->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(reinterpret_cast<void*>(out_count), 0, sizeof(uint32_t), st);
+    if (e == cudaSuccess && out_nodes) e = cudaMemsetAsync(reinterpret_cast<void*>(out_nodes), 0, sizeof(uint32_t), st);
+    for (uint32_t i = 0; i < max_nodes && e == cudaSuccess; i++) {
+        prefix_evict_one<<<ix->evict_ctas, 256, 0, st>>>(ix->view, reinterpret_cast<uint32_t*>(out_pages), out_cap,
+                                                         reinterpret_cast<uint32_t*>(out_count), reinterpret_cast<uint32_t*>(out_nodes));
+        e = cudaGetLastError();
+    }
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index evict");
+}
+
+int32_t tkv_prefix_index_stats(tkv_prefix_index* ix, void* stream, TkvPrefixIndexStats* out) {
+    if (!ix || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    DeviceGuard guard(ix->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    Counters c{};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&c, ix->view.ctr, sizeof c, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail_cuda(e, "prefix index stats");
+    out->hits = c.hits;
+    out->tokens_saved = c.tokens_saved;
+    out->live_nodes = c.live;
+    out->tombstones = c.tombstones;
+    out->capacity = ix->capacity;
+    out->ticks = ix->tick;
+    out->group_tokens = ix->group;
+    out->table_full = c.error;
+    return TKV_OK;
+}
+
+}  // extern "C"

@@ -397,3 +397,72 @@ def decode_attention(pool: Pool, layer: int, q: torch.Tensor, tables: torch.Tens
     if int(attn.status.item()) != 0:
         raise TkvError(int(attn.status.item()), "decode attention: a bounded wait inside the kernel gave up")
     return out
+
+
+class PrefixIndex:
+    """Device-resident ``RadixTree`` (engine/src/prefix_cache.rs:17-149): insert / lookup / release /
+    evict_lru over a batch of token sequences, one launch per call, all state in HBM.  Sequences are
+    int32 tensors ``[n_seqs, stride]`` on the index's device with int32 ``lens``; a node is
+    ``group_tokens`` consecutive tokens (1 = the reference's per-token nodes, 16 = one per KV block)."""
+
+    def __init__(self, device: int, capacity: int, group_tokens: int = 1):
+        self.device, self.group_tokens = device, group_tokens
+        h = C.c_void_p()
+        check(lib().tkv_prefix_index_create(device, capacity, group_tokens, C.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if self._h:
+            lib().tkv_prefix_index_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _batch(self, tokens: torch.Tensor, lens: torch.Tensor, pages: Optional[torch.Tensor] = None,
+               page_lens: Optional[torch.Tensor] = None) -> N.TkvPrefixBatch:
+        for t in (tokens, lens, pages, page_lens):
+            assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and t.device.index == self.device)
+        assert tokens.dim() == 2 and lens.numel() == tokens.shape[0]
+        return N.TkvPrefixBatch(tokens.shape[0], tokens.shape[1], pages.shape[1] if pages is not None else 0, 0,
+                                tokens.data_ptr(), lens.data_ptr(), pages.data_ptr() if pages is not None else 0,
+                                page_lens.data_ptr() if page_lens is not None else 0)
+
+    def _stream(self, stream):
+        return C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
+
+    def insert(self, tokens, lens, pages=None, page_lens=None, stream=None) -> None:
+        b = self._batch(tokens, lens, pages, page_lens)
+        check(lib().tkv_prefix_index_insert(self._h, C.byref(b), self._stream(stream)))
+
+    def lookup(self, tokens, lens, stream=None):
+        """Returns ``(matched, pages)``: int32 ``[n_seqs]`` matched nodes and int32 ``[n_seqs, nodes]`` page
+        ids (-1 where a matched node has no page or past the match)."""
+        b = self._batch(tokens, lens)
+        n_nodes = max(tokens.shape[1] // self.group_tokens, 1)
+        pages = torch.full((tokens.shape[0], n_nodes), -1, dtype=torch.int32, device=tokens.device)
+        matched = torch.zeros(tokens.shape[0], dtype=torch.int32, device=tokens.device)
+        check(lib().tkv_prefix_index_lookup(self._h, C.byref(b), pages.data_ptr(), n_nodes, matched.data_ptr(), self._stream(stream)))
+        return matched, pages
+
+    def release(self, tokens, lens, stream=None) -> None:
+        b = self._batch(tokens, lens)
+        check(lib().tkv_prefix_index_release(self._h, C.byref(b), self._stream(stream)))
+
+    def evict_lru(self, max_nodes: int = 1, stream=None):
+        """Unlinks up to ``max_nodes`` nodes; returns ``(pages, nodes_unlinked)`` with the freed page ids on the host."""
+        dev = f"cuda:{self.device}"
+        pages = torch.full((max(max_nodes, 1),), -1, dtype=torch.int32, device=dev)
+        counts = torch.zeros(2, dtype=torch.int32, device=dev)
+        check(lib().tkv_prefix_index_evict_lru(self._h, max_nodes, pages.data_ptr(), pages.numel(), counts.data_ptr(),
+                                               counts.data_ptr() + 4, self._stream(stream)))
+        n_pages, n_nodes = (int(x) for x in counts.cpu())
+        return pages[:n_pages].cpu().tolist(), n_nodes
+
+    def stats(self, stream=None) -> N.TkvPrefixIndexStats:
+        st = N.TkvPrefixIndexStats()
+        check(lib().tkv_prefix_index_stats(self._h, self._stream(stream), C.byref(st)))
+        return st
