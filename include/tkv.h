@@ -469,6 +469,29 @@ int32_t tkv_prefix_index_evict_lru(tkv_prefix_index*, uint32_t max_nodes, uint64
 /* synchronises the stream */
 int32_t tkv_prefix_index_stats(tkv_prefix_index*, void* stream, TkvPrefixIndexStats* out);
 
+/* ---- device-side page allocator ----------------------------------------------- */
+/* PageAllocator (engine/src/kv_cache.rs:762-797), a LIFO stack of free page ids, kept in HBM so
+ * that the decode side places a batch's blocks without a host round trip and without needing
+ * contiguous runs (the reference's GPU pool hands out PageRunAllocator runs,
+ * engine/src/gpu_page_pool.rs:1-10).  One launch per batch: sequence s takes counts[s] pages
+ * into tables[s][first[s] ...] (first = its matched prefix nodes, say) and gets exactly the ids
+ * allocate() would pop for the sequences in index order; free pushes them back in table order.
+ * A batch asking for more than is free gets nothing: *status = TKV_ERR_POOL_EXHAUSTED.
+ * Rows that would overrun table_stride, or more pages returned than were handed out:
+ * *status = TKV_ERR_INVALID_CONFIG and nothing changes.  Calls must be stream-ordered.       */
+typedef struct tkv_device_page_allocator tkv_device_page_allocator;
+typedef struct TkvPageBatch {
+    uint32_t n_seqs, table_stride;
+    uint64_t tables;              /* device u32 [n_seqs][table_stride]                            */
+    uint64_t first;               /* device u32 [n_seqs] first entry of each row to fill; 0 = entry 0 */
+    uint64_t counts;              /* device u32 [n_seqs] pages per sequence                        */
+} TkvPageBatch;
+int32_t tkv_device_page_allocator_create(int32_t device, uint32_t total_pages, tkv_device_page_allocator** out);
+void tkv_device_page_allocator_destroy(tkv_device_page_allocator*);
+int32_t tkv_device_page_allocator_allocate(tkv_device_page_allocator*, const TkvPageBatch*, uint64_t status /* device u32 or 0 */, void* stream);
+int32_t tkv_device_page_allocator_free(tkv_device_page_allocator*, const TkvPageBatch*, uint64_t status /* device u32 or 0 */, void* stream);
+int32_t tkv_device_page_allocator_available(tkv_device_page_allocator*, void* stream, uint32_t* out); /* synchronises the stream */
+
 #ifdef __cplusplus
 }
 #endif

@@ -121,3 +121,31 @@ class RadixOracle:
     def batch_release(self, seqs):
         for s in seqs:
             self.release(s)
+
+
+class PageStackOracle:
+    """PageAllocator (engine/src/kv_cache.rs:762-797): a LIFO stack of free page ids, 0 on top at the start."""
+
+    def __init__(self, total_pages: int):
+        self.free_pages = list(range(total_pages))[::-1]      # (0..total).rev().collect()
+        self.total = total_pages
+
+    def allocate(self) -> Optional[int]:
+        return self.free_pages.pop() if self.free_pages else None
+
+    def free(self, page_id: int) -> None:
+        self.free_pages.append(page_id)
+
+    def available(self) -> int:
+        return len(self.free_pages)
+
+    # the device allocator's batch calls: sequences in index order, all or nothing
+    def batch_allocate(self, counts: Sequence[int]) -> Optional[List[List[int]]]:
+        if sum(counts) > len(self.free_pages):
+            return None
+        return [[self.allocate() for _ in range(c)] for c in counts]
+
+    def batch_free(self, rows: Sequence[Sequence[int]]) -> None:
+        for row in rows:
+            for p in row:
+                self.free(p)

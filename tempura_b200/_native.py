@@ -66,6 +66,10 @@ class TkvPrefixIndexStats(C.Structure):
         ("group_tokens", C.c_uint32), ("table_full", C.c_uint32)]
 
 
+class TkvPageBatch(C.Structure):
+    _fields_ = [("n_seqs", C.c_uint32), ("table_stride", C.c_uint32), ("tables", C.c_uint64), ("first", C.c_uint64), ("counts", C.c_uint64)]
+
+
 PREFIX_NO_PAGE = 0xFFFFFFFF
 
 
@@ -158,6 +162,11 @@ SIGNATURES = {
     "tkv_prefix_index_release": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _vp]),
     "tkv_prefix_index_evict_lru": (_i32, [_vp, _u32, _u64, _u32, _u64, _u64, _vp]),
     "tkv_prefix_index_stats": (_i32, [_vp, _vp, C.POINTER(TkvPrefixIndexStats)]),
+    "tkv_device_page_allocator_create": (_i32, [_i32, _u32, C.POINTER(_vp)]),
+    "tkv_device_page_allocator_destroy": (None, [_vp]),
+    "tkv_device_page_allocator_allocate": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
+    "tkv_device_page_allocator_free": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
+    "tkv_device_page_allocator_available": (_i32, [_vp, _vp, _u32p]),
     "tkv_radix_tree_new": (_vp, []),
     "tkv_radix_tree_delete": (None, [_vp]),
     "tkv_radix_tree_insert": (None, [_vp, _u32p, _sz, _szp, _sz]),

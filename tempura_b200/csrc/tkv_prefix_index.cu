@@ -296,6 +296,96 @@ __global__ void prefix_index_clear(View ix) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *ix.ctr = Counters{};
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Device-side page allocator: PageAllocator (engine/src/kv_cache.rs:762-797), a LIFO stack of free
+// page ids, kept in HBM.  One launch serves a whole batch: sequence s takes (or returns) counts[s]
+// pages into (from) row s of a block table starting at entry first[s], and gets exactly the ids the
+// reference's allocate() would pop for the sequences in index order (a fresh stack hands out 0, 1, 2 ...).
+// A batch that asks for more than is free gets nothing and the status word says so.
+// ---------------------------------------------------------------------------------------------
+struct PageStack {
+    uint32_t* ids;      // [total]
+    uint32_t* top;      // pages on the stack
+    uint32_t total;
+};
+
+struct PageBatch {
+    uint32_t* tables;           // [n_seqs][stride]
+    const uint32_t* first;      // [n_seqs] or null (0)
+    const uint32_t* counts;     // [n_seqs]
+    uint32_t n_seqs, stride;
+};
+
+__global__ void page_stack_init(PageStack st) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < st.total; i += gridDim.x * blockDim.x) st.ids[i] = st.total - 1u - i;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *st.top = st.total;
+}
+
+// offsets[s] = sum of counts before s, through shared memory in chunks of the CTA; returns the batch total
+template <bool FREE>
+__global__ void __launch_bounds__(1024) page_stack_batch(PageStack st, PageBatch b, uint32_t* status) {
+    __shared__ uint32_t scan[1024];
+    __shared__ uint32_t carry, bad;
+    const uint32_t t = threadIdx.x;
+    if (t == 0) carry = bad = 0;
+    __syncthreads();
+    // pass 1: validate rows and total the request
+    for (uint32_t s0 = 0; s0 < b.n_seqs; s0 += 1024) {
+        const uint32_t s = s0 + t;
+        const uint32_t c = s < b.n_seqs ? b.counts[s] : 0u, f = (s < b.n_seqs && b.first) ? b.first[s] : 0u;
+        if (c && ((unsigned long long)f + c > b.stride)) atomicExch(&bad, 1u);
+        scan[t] = c;
+        __syncthreads();
+        for (uint32_t off = 512; off > 0; off >>= 1) {
+            if (t < off) scan[t] += scan[t + off];
+            __syncthreads();
+        }
+        if (t == 0) carry = (carry > 0xFFFFFFFFu - scan[0]) ? 0xFFFFFFFFu : carry + scan[0];
+        __syncthreads();
+    }
+    const uint32_t total = carry, top = *st.top;
+    uint32_t verdict = 0;
+    if (bad) verdict = TKV_ERR_INVALID_CONFIG;
+    else if (!FREE && total > top) verdict = TKV_ERR_POOL_EXHAUSTED;
+    else if (FREE && total > st.total - top) verdict = TKV_ERR_INVALID_CONFIG;       // more pages returned than were ever handed out
+    __syncthreads();
+    if (verdict) {
+        if (t == 0 && status) *status = verdict;
+        return;
+    }
+    // pass 2: running offsets chunk by chunk, each thread then moves its sequence's ids
+    if (t == 0) carry = 0;
+    __syncthreads();
+    for (uint32_t s0 = 0; s0 < b.n_seqs; s0 += 1024) {
+        const uint32_t s = s0 + t;
+        const uint32_t c = s < b.n_seqs ? b.counts[s] : 0u;
+        scan[t] = c;
+        __syncthreads();
+        for (uint32_t off = 1; off < 1024; off <<= 1) {                              // inclusive scan
+            const uint32_t v = t >= off ? scan[t - off] : 0u;
+            __syncthreads();
+            scan[t] += v;
+            __syncthreads();
+        }
+        const uint32_t before = carry + scan[t] - c;
+        if (c) {
+            uint32_t* row = b.tables + (size_t)s * b.stride + (b.first ? b.first[s] : 0u);
+            for (uint32_t i = 0; i < c; i++) {
+                if (FREE) st.ids[top + before + i] = row[i];                          // push in table order
+                else row[i] = st.ids[top - 1u - before - i];                         // the i-th pop of this sequence
+            }
+        }
+        __syncthreads();
+        if (t == 1023) carry += scan[1023];
+        __syncthreads();
+    }
+    if (t == 0) {
+        *st.top = FREE ? top + total : top - total;
+        if (status) *status = 0;
+    }
+}
+
 int32_t fail(int32_t code, const char* msg) { return tkv_internal::set_error(code, 0, msg); }
 int32_t fail_cuda(cudaError_t e, const char* what) {
     char buf[200];
@@ -474,6 +564,83 @@ int32_t tkv_prefix_index_stats(tkv_prefix_index* ix, void* stream, TkvPrefixInde
     out->group_tokens = ix->group;
     out->table_full = c.error;
     return TKV_OK;
+}
+
+}  // extern "C"
+
+struct tkv_device_page_allocator {
+    int device = 0;
+    PageStack st{};
+};
+
+namespace {
+int32_t page_batch(tkv_device_page_allocator* a, const TkvPageBatch* batch, uint64_t status, void* stream, bool release) {
+    if (!a || !batch) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (batch->n_seqs == 0) return TKV_OK;
+    if (!batch->tables || !batch->counts || batch->table_stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "page batch: NULL tables / counts or zero stride");
+    DeviceGuard guard(a->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    PageBatch b{reinterpret_cast<uint32_t*>(batch->tables), reinterpret_cast<const uint32_t*>(batch->first),
+                reinterpret_cast<const uint32_t*>(batch->counts), batch->n_seqs, batch->table_stride};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (release) page_stack_batch<true><<<1, 1024, 0, st>>>(a->st, b, reinterpret_cast<uint32_t*>(status));
+    else page_stack_batch<false><<<1, 1024, 0, st>>>(a->st, b, reinterpret_cast<uint32_t*>(status));
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "device page allocator");
+}
+}  // namespace
+
+extern "C" {
+
+int32_t tkv_device_page_allocator_create(int32_t device, uint32_t total_pages, tkv_device_page_allocator** out) {
+    if (!out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    *out = nullptr;
+    if (total_pages == 0) return fail(TKV_ERR_INVALID_CONFIG, "device page allocator: zero pages");
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    auto* a = new (std::nothrow) tkv_device_page_allocator();
+    if (!a) return fail(TKV_ERR_POOL_EXHAUSTED, "device page allocator: out of host memory");
+    a->device = device;
+    a->st.total = total_pages;
+    cudaError_t e = cudaMalloc(&a->st.ids, (size_t)total_pages * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&a->st.top, sizeof(uint32_t));
+    if (e == cudaSuccess) {
+        page_stack_init<<<64, 256>>>(a->st);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    }
+    if (e != cudaSuccess) {
+        tkv_device_page_allocator_destroy(a);
+        return fail_cuda(e, "device page allocator allocation");
+    }
+    *out = a;
+    return TKV_OK;
+}
+
+void tkv_device_page_allocator_destroy(tkv_device_page_allocator* a) {
+    if (!a) return;
+    DeviceGuard guard(a->device);
+    cudaFree(a->st.ids);
+    cudaFree(a->st.top);
+    delete a;
+}
+
+int32_t tkv_device_page_allocator_allocate(tkv_device_page_allocator* a, const TkvPageBatch* batch, uint64_t status, void* stream) {
+    return page_batch(a, batch, status, stream, false);
+}
+
+int32_t tkv_device_page_allocator_free(tkv_device_page_allocator* a, const TkvPageBatch* batch, uint64_t status, void* stream) {
+    return page_batch(a, batch, status, stream, true);
+}
+
+int32_t tkv_device_page_allocator_available(tkv_device_page_allocator* a, void* stream, uint32_t* out) {
+    if (!a || !out) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    DeviceGuard guard(a->device);
+    if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(out, a->st.top, sizeof(uint32_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? TKV_OK : fail_cuda(e, "device page allocator available");
 }
 
 }  // extern "C"

@@ -466,3 +466,46 @@ class PrefixIndex:
         st = N.TkvPrefixIndexStats()
         check(lib().tkv_prefix_index_stats(self._h, self._stream(stream), C.byref(st)))
         return st
+
+
+class DevicePageAllocator:
+    """``PageAllocator`` (engine/src/kv_cache.rs:762-797) with its free stack in HBM: one launch places (or
+    returns) the pages of a whole batch straight in a device block table."""
+
+    def __init__(self, device: int, total_pages: int):
+        self.device = device
+        h = C.c_void_p()
+        check(lib().tkv_device_page_allocator_create(device, total_pages, C.byref(h)))
+        self._h = h
+        self.status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{device}")
+
+    def close(self) -> None:
+        if self._h:
+            lib().tkv_device_page_allocator_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _call(self, fn, tables, counts, first, stream):
+        for t in (tables, counts, first):
+            assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and t.device.index == self.device)
+        b = N.TkvPageBatch(tables.shape[0], tables.shape[1], tables.data_ptr(), first.data_ptr() if first is not None else 0, counts.data_ptr())
+        st = C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
+        check(fn(self._h, C.byref(b), self.status.data_ptr(), st))
+
+    def allocate(self, tables, counts, first=None, stream=None) -> None:
+        """Fills ``tables[s, first[s] : first[s] + counts[s]]``; ``self.status`` (device int32) is 0 or an error code."""
+        self._call(lib().tkv_device_page_allocator_allocate, tables, counts, first, stream)
+
+    def free(self, tables, counts, first=None, stream=None) -> None:
+        self._call(lib().tkv_device_page_allocator_free, tables, counts, first, stream)
+
+    def available(self, stream=None) -> int:
+        out = C.c_uint32()
+        st = C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
+        check(lib().tkv_device_page_allocator_available(self._h, st, C.byref(out)))
+        return int(out.value)

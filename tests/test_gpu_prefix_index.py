@@ -205,3 +205,42 @@ def test_lookup_feeds_the_handoff_plan(H):
             s_id, d_id = int(w.src_tables[q, 4]), int(dst_tables[q, 4])
             n_valid = min(16, int(w.seq_lens[q]) - 64)
             assert torch.equal(src.blocks(1)[s_id, :n_valid].view(torch.int16), dst.blocks(1)[d_id, :n_valid].view(torch.int16))
+
+
+def test_device_page_allocator_matches_the_reference_stack(H):
+    import torch
+    from oracle.prefix_oracle import PageStackOracle
+    rng = np.random.default_rng(88)
+    total, stride = 5000, 40
+    dev_alloc, ref = H.DevicePageAllocator(0, total), PageStackOracle(total)
+    held = []                                                      # (rows as lists) still allocated
+    for rnd in range(30):
+        n = int(rng.integers(1, 2500 if rnd == 7 else 60))         # one batch wider than the CTA (1 024 threads)
+        counts = rng.integers(0, 4 if n > 1024 else stride // 2, size=n).astype(np.int32)
+        first = rng.integers(0, stride // 2, size=n).astype(np.int32)
+        tables = torch.full((n, stride), -1, dtype=torch.int32, device="cuda")
+        dev_alloc.allocate(tables, torch.from_numpy(counts).cuda(), torch.from_numpy(first).cuda())
+        want = ref.batch_allocate(counts.tolist())
+        got = tables.cpu().numpy()
+        if want is None:
+            assert int(dev_alloc.status.item()) == N.ERR_POOL_EXHAUSTED and bool((got == -1).all())
+        else:
+            assert int(dev_alloc.status.item()) == 0
+            for s in range(n):
+                assert got[s, first[s]:first[s] + counts[s]].tolist() == want[s], f"round {rnd} sequence {s}"
+                assert bool((np.delete(got[s], np.s_[first[s]:first[s] + counts[s]]) == -1).all())
+            held.append((tables, counts, first, want))
+        if held and rng.random() < 0.6:                            # give one earlier batch back
+            tables, counts, first, rows = held.pop(int(rng.integers(len(held))))
+            dev_alloc.free(tables, torch.from_numpy(counts).cuda(), torch.from_numpy(first).cuda())
+            ref.batch_free(rows)
+            assert int(dev_alloc.status.item()) == 0
+        assert dev_alloc.available() == ref.available()
+    # a row that would overrun the table, and more pages returned than were handed out: refused, nothing changes
+    before = dev_alloc.available()
+    t = torch.zeros((1, 8), dtype=torch.int32, device="cuda")
+    dev_alloc.allocate(t, torch.tensor([6], dtype=torch.int32).cuda(), torch.tensor([4], dtype=torch.int32).cuda())
+    assert int(dev_alloc.status.item()) == N.ERR_INVALID_CONFIG and dev_alloc.available() == before
+    big = torch.zeros((1, total + 8), dtype=torch.int32, device="cuda")
+    dev_alloc.free(big, torch.tensor([total - before + 1], dtype=torch.int32).cuda())
+    assert int(dev_alloc.status.item()) == N.ERR_INVALID_CONFIG and dev_alloc.available() == before

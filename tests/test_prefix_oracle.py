@@ -75,3 +75,15 @@ def test_groups_and_batches():
     (n0, p0, _), (n1, p1, _) = t.batch_lookup([[1, 2, 3, 4], [1, 2, 9, 9, 5, 5]])
     assert (n0, p0) == (2, [7, 8]) and (n1, p1) == (2, [7, 80])      # the shared node keeps the first sequence's page
     assert t.tokens_saved == 8 and t.live_nodes() == 3
+
+
+def test_page_stack_oracle_follows_the_reference_allocator():
+    # kv_cache.rs:762-797: pops hand out 0, 1, 2 ...; a freed page is the next one handed out
+    from oracle.prefix_oracle import PageStackOracle
+    a = PageStackOracle(4)
+    assert [a.allocate() for _ in range(3)] == [0, 1, 2] and a.available() == 1
+    a.free(1)
+    assert a.allocate() == 1 and a.allocate() == 3 and a.allocate() is None
+    assert a.batch_allocate([1]) is None
+    a.batch_free([[2, 0], [3]])
+    assert a.batch_allocate([2, 1]) == [[3, 0], [2]]
