@@ -492,6 +492,29 @@ int32_t tkv_device_page_allocator_allocate(tkv_device_page_allocator*, const Tkv
 int32_t tkv_device_page_allocator_free(tkv_device_page_allocator*, const TkvPageBatch*, uint64_t status /* device u32 or 0 */, void* stream);
 int32_t tkv_device_page_allocator_available(tkv_device_page_allocator*, void* stream, uint32_t* out); /* synchronises the stream */
 
+/* ---- handoff from block tables that live on the device ------------------------ */
+/* The same kernels as tkv_handoff_enqueue, but the work list is built ON THE DEVICE, in stream
+ * order, from tables the device prefix index and page allocator have just filled: no block id,
+ * length or prefix length crosses to the host.  `plan` supplies the geometry and the CAPACITY:
+ * create it from a host batch with as many block pairs as a device batch may ever have (its own
+ * table contents are not used here).  Sequence q moves its blocks past prefix_lens[q], in table
+ * order, as the host path would; with apply_refcounts each shared-prefix block of each sequence
+ * gets +1 in the destination pool's refcount array (RadixTree::lookup's count).  Nothing is
+ * trusted: a misaligned or over-long prefix, a sequence longer than a table row, a block id
+ * outside a pool, or more pairs than the capacity leave an empty list -- nothing moves, no
+ * count changes, the flag is still published -- and *status = TKV_ERR_INVALID_CONFIG or
+ * TKV_ERR_DIMENSION_MISMATCH (capacity).  Destination ids are NOT checked for duplicates here.
+ * Not for transfer-buffer plans or per-layer tables.                                          */
+typedef struct TkvDeviceBatch {
+    uint32_t n_seqs, table_stride, apply_refcounts, reserved;
+    uint64_t seq_lens;            /* device u32 [n_seqs]                                          */
+    uint64_t prefix_lens;         /* device u32 [n_seqs] tokens already resident; 0 = none        */
+    uint64_t src_tables;          /* device u32 [n_seqs][table_stride]                            */
+    uint64_t dst_tables;          /* device u32 [n_seqs][table_stride]                            */
+    uint64_t status;              /* device u32 or 0                                              */
+} TkvDeviceBatch;
+int32_t tkv_handoff_enqueue_device_tables(tkv_plan* plan, const TkvDeviceBatch* batch, void* stream, uint64_t done_flag, uint32_t flag_value);
+
 #ifdef __cplusplus
 }
 #endif

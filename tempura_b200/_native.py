@@ -70,6 +70,11 @@ class TkvPageBatch(C.Structure):
     _fields_ = [("n_seqs", C.c_uint32), ("table_stride", C.c_uint32), ("tables", C.c_uint64), ("first", C.c_uint64), ("counts", C.c_uint64)]
 
 
+class TkvDeviceBatch(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_seqs", "table_stride", "apply_refcounts", "reserved")] + [
+        (n, C.c_uint64) for n in ("seq_lens", "prefix_lens", "src_tables", "dst_tables", "status")]
+
+
 PREFIX_NO_PAGE = 0xFFFFFFFF
 
 
@@ -167,6 +172,7 @@ SIGNATURES = {
     "tkv_device_page_allocator_allocate": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
     "tkv_device_page_allocator_free": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
     "tkv_device_page_allocator_available": (_i32, [_vp, _vp, _u32p]),
+    "tkv_handoff_enqueue_device_tables": (_i32, [_vp, C.POINTER(TkvDeviceBatch), _vp, _u64, _u32]),
     "tkv_radix_tree_new": (_vp, []),
     "tkv_radix_tree_delete": (None, [_vp]),
     "tkv_radix_tree_insert": (None, [_vp, _u32p, _sz, _szp, _sz]),

@@ -41,7 +41,13 @@ struct HandoffArgs {
     uint32_t src_total_blocks, src_pool_heads, src_head_begin, src_layer_begin;
     uint32_t flag_value;
     uint32_t contiguous;        // rows abut on both sides
+    const uint32_t* n_pairs_dev; // set = the work list was built on the device: its length is read here (n_pairs is the capacity)
 };
+
+// Block pairs the launch really has: the host's count, or the device-built list's (never above the capacity).
+__device__ __forceinline__ uint32_t live_pairs(const HandoffArgs& a) {
+    return a.n_pairs_dev ? min(*reinterpret_cast<const volatile uint32_t*>(a.n_pairs_dev), a.n_pairs) : a.n_pairs;
+}
 
 struct Chunk {
     const char* src;
@@ -107,7 +113,7 @@ template <typename T> __device__ __forceinline__ T ld_stream(const T* p) { retur
 template <int VEC, int UNROLL>
 __global__ void __launch_bounds__(256) handoff_copy_vec(const HandoffArgs a) {
     using V = typename VecT<VEC>::type;
-    const uint32_t total = a.n_pairs * a.n_layers * 2u;
+    const uint32_t total = live_pairs(a) * a.n_layers * 2u;
     const uint32_t vec_per_row = a.src_row_bytes / VEC;
     for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
         const Chunk c = decode_chunk(a, w);
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uin
     BulkItem* items = reinterpret_cast<BulkItem*>(smem + 64);              // 64 decoded items
     unsigned char* data = smem + 64 + 64 * sizeof(BulkItem);               // 1600: 16-byte aligned
     const uint32_t lane = threadIdx.x;
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint64_t total = (uint64_t)chunks * pieces;
     const uint32_t n_mine = blockIdx.x < total ? (uint32_t)((total - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
 
@@ -413,7 +419,7 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_warp(const HandoffArgs a
     static_assert(D % 8 == 0 && LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "head_dim");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t r0 = lane / LPR, col = lane % LPR;
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint64_t total = (uint64_t)chunks * a.n_heads;
     for (uint64_t wi = (uint64_t)blockIdx.x * 8u + warp; wi < total; wi += (uint64_t)gridDim.x * 8u) {
         const uint32_t h = (uint32_t)(wi % a.n_heads);
@@ -510,7 +516,7 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_staged(const HandoffArgs
     unsigned char* out_base = in_base + (size_t)n_stages * in_bytes;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t r0 = lane / LPR, col = lane % LPR;
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint32_t n_mine = blockIdx.x < chunks ? (chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
 
     if (tid == 0) {
@@ -664,7 +670,7 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_staged(const HandoffArgs
 template <bool HW, bool SCALED>
 __global__ void __launch_bounds__(256) handoff_f16_e4m3_generic(const HandoffArgs a) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint64_t total = (uint64_t)chunks * a.n_heads;
     const uint32_t D = a.head_dim;
     for (uint64_t wi = (uint64_t)blockIdx.x * 8u + warp; wi < total; wi += (uint64_t)gridDim.x * 8u) {
@@ -703,7 +709,7 @@ __global__ void __launch_bounds__(256) handoff_f16_e4m3_generic(const HandoffArg
 // MODE 1: F32 -> E4M3, unscaled
 template <int MODE>
 __global__ void __launch_bounds__(256) handoff_f32_cast_generic(const HandoffArgs a) {
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint32_t row_elems = a.n_heads * a.head_dim;
     for (uint32_t w = blockIdx.x; w < chunks; w += gridDim.x) {
         const Chunk c = decode_chunk(a, w);
@@ -734,7 +740,7 @@ __device__ __forceinline__ float e4m3_decode(uint32_t b) {
 // DST16: destination is F16 (else F32).
 template <bool DST16, bool VEC16>
 __global__ void __launch_bounds__(256) handoff_e4m3_dequant(const HandoffArgs a) {
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint32_t D = a.head_dim;
     constexpr uint32_t W = VEC16 ? 16u : 1u;
     const uint32_t per_row = a.src_row_bytes / W;             // work items per token row
@@ -794,7 +800,7 @@ __device__ __forceinline__ uint32_t h2_bits(float lo, float hi) {
 template <int MODE>
 __global__ void __launch_bounds__(256) handoff_f32_cast_vec(const HandoffArgs a) {
     constexpr uint32_t E = MODE == 0 ? 8u : 16u;               // elements per 16-byte store
-    const uint32_t chunks = a.n_pairs * a.n_layers * 2u;
+    const uint32_t chunks = live_pairs(a) * a.n_layers * 2u;
     const uint32_t row_elems = a.n_heads * a.head_dim, per_row = row_elems / E;
     for (uint32_t w = blockIdx.x; w < chunks; w += gridDim.x) {
         const Chunk c = decode_chunk(a, w);
@@ -830,6 +836,85 @@ __global__ void __launch_bounds__(256) handoff_f32_cast_vec(const HandoffArgs a)
 // ---------------------------------------------------------------------------------
 // small kernels
 // ---------------------------------------------------------------------------------
+// ---------------------------------------------------------------------------------
+// Work list from block tables that live on the device (one CTA): sequence q contributes its blocks
+// past the shared prefix, in table order, sequences in index order -- the list the host builder would
+// have produced.  Nothing is trusted: a prefix longer than its sequence or not block-aligned, a
+// sequence longer than its table row, a block id outside either pool, or more pairs than the plan
+// was sized for leave an EMPTY list (nothing moves, no reference count changes) and a status code.
+// ---------------------------------------------------------------------------------
+struct DeviceTables {
+    const uint32_t* seq_lens;
+    const uint32_t* prefix_lens;   // or null
+    const uint32_t* src_tables;
+    const uint32_t* dst_tables;
+    uint32_t* offsets;             // [n_seqs] scratch
+    uint4* work;
+    uint32_t* n_pairs_out;
+    uint32_t* status;              // or null
+    int32_t* refcounts;            // destination pool's, or null (no reference counting asked for)
+    uint32_t n_seqs, table_stride, block_size, capacity, src_total_blocks, dst_total_blocks;
+};
+
+__global__ void __launch_bounds__(1024) worklist_from_device_tables(const DeviceTables t) {
+    __shared__ uint32_t scan[1024];
+    __shared__ uint32_t carry, err;
+    const uint32_t tid = threadIdx.x, bs = t.block_size;
+    if (tid == 0) carry = err = 0;
+    __syncthreads();
+    for (uint32_t q0 = 0; q0 < t.n_seqs; q0 += 1024) {
+        const uint32_t q = q0 + tid;
+        uint32_t cnt = 0;
+        if (q < t.n_seqs) {
+            const uint32_t len = t.seq_lens[q], pre = t.prefix_lens ? t.prefix_lens[q] : 0u, nb = (len + bs - 1) / bs;
+            if (pre > len || pre % bs || nb > t.table_stride) atomicExch(&err, 2u);
+            else cnt = nb - pre / bs;
+        }
+        scan[tid] = cnt;
+        __syncthreads();
+        for (uint32_t off = 1; off < 1024; off <<= 1) {
+            const uint32_t v = tid >= off ? scan[tid - off] : 0u;
+            __syncthreads();
+            scan[tid] += v;
+            __syncthreads();
+        }
+        if (q < t.n_seqs) t.offsets[q] = carry + scan[tid] - cnt;
+        __syncthreads();
+        if (tid == 1023) carry = (carry > 0x7FFFFFFFu - scan[1023]) ? 0x7FFFFFFFu : carry + scan[1023];
+        __syncthreads();
+    }
+    const uint32_t total = carry;
+    if (tid == 0 && total > t.capacity && !err) err = 1u;          // more pairs than the plan was sized for
+    __syncthreads();
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
+    if (!err) {
+        for (uint32_t q = warp; q < t.n_seqs; q += 32) {
+            const uint32_t len = t.seq_lens[q], pre_b = (t.prefix_lens ? t.prefix_lens[q] : 0u) / bs, nb = (len + bs - 1) / bs;
+            const uint32_t* srow = t.src_tables + (size_t)q * t.table_stride;
+            const uint32_t* drow = t.dst_tables + (size_t)q * t.table_stride;
+            for (uint32_t i = lane; i < nb; i += 32) {
+                const uint32_t did = drow[i];
+                if (did >= t.dst_total_blocks) atomicExch(&err, 2u);
+                if (i < pre_b) continue;
+                const uint32_t sid = srow[i];
+                if (sid >= t.src_total_blocks) atomicExch(&err, 2u);
+                t.work[t.offsets[q] + (i - pre_b)] = make_uint4(sid, did, min(bs, len - i * bs), q);
+            }
+        }
+    }
+    __syncthreads();
+    if (!err && t.refcounts) {                                       // RadixTree::lookup's count, one per sequence and shared block
+        for (uint32_t q = warp; q < t.n_seqs; q += 32) {
+            const uint32_t pre_b = (t.prefix_lens ? t.prefix_lens[q] : 0u) / bs;
+            for (uint32_t i = lane; i < pre_b; i += 32) atomicAdd(t.refcounts + t.dst_tables[(size_t)q * t.table_stride + i], 1);
+        }
+    }
+    if (tid == 0) {
+        *t.n_pairs_out = err ? 0u : total;
+        if (t.status) *t.status = err;                              // 0, 1 = dimension mismatch (capacity), 2 = invalid config
+    }
+}
+
 __global__ void refcount_apply_kernel(uint32_t* refcounts, const uint32_t* ids, uint32_t n, int delta) {
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint32_t* p = refcounts + ids[i];

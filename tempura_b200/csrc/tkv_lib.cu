@@ -127,6 +127,10 @@ struct tkv_plan {
     int virt = 0;
     TkvTransfer xfer{};
     bool host_side = false;     // the transfer buffer is page-locked host memory
+    // device-built work lists (tkv_handoff_enqueue_device_tables): [u32 live pairs][pad][u32 offsets per sequence]
+    uint32_t* dev_scratch = nullptr;
+    size_t dev_scratch_seqs = 0;
+    bool layer_tables = false;  // the batch carried one table per layer
 };
 
 namespace {
@@ -340,6 +344,7 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     a.dst_block_stride = (uint64_t)bs * d.n_kv_heads * d.head_dim * de;
     a.n_pairs = (uint32_t)pairs;
     a.work_layer_stride = b->table_layer_stride ? (uint32_t)pairs : 0u;
+    p->layer_tables = b->table_layer_stride != 0;
     a.n_layers = sh.n_layers;
     a.n_heads = sh.n_heads;
     a.head_dim = s.head_dim;
@@ -563,6 +568,8 @@ template <bool HW, bool SCALED> int32_t launch_fp8(tkv_plan* p, cudaStream_t st)
 
 }  // namespace
 
+static int32_t dispatch(tkv_plan* p, uint64_t chunks, cudaStream_t st);
+
 extern "C" {
 
 void tkv_last_error(char* buf, size_t len) {
@@ -762,6 +769,7 @@ int32_t tkv_plan_destroy(tkv_plan* p) {
         }
         if (p->h_buf) cudaFreeHost(p->h_buf);
         if (p->d_buf) cudaFree(p->d_buf);
+        if (p->dev_scratch) cudaFree(p->dev_scratch);
     }
     delete p;
     return TKV_OK;
@@ -795,6 +803,15 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         int32_t rc = ensure_uploaded(p, st);
         if (rc) return rc;
     }
+    a.n_pairs_dev = nullptr;
+    return dispatch(p, chunks, st);
+}
+
+}  // extern "C"
+
+// picks and launches the kernel for the plan's mode over `chunks` (block, layer, K|V) units
+static int32_t dispatch(tkv_plan* p, uint64_t chunks, cudaStream_t st) {
+    tkv::HandoffArgs& a = p->args;
     switch (p->mode) {
         case MODE_COPY:
             if (p->flags & TKV_PLAN_FORCE_BULK) {
@@ -841,6 +858,60 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
             return launch(tkv::handoff_e4m3_dequant<false, false>, p, chunks, st);
     }
     return fail(TKV_ERR_INVALID_CONFIG, "unreachable mode");
+}
+
+extern "C" {
+
+int32_t tkv_handoff_enqueue_device_tables(tkv_plan* p, const TkvDeviceBatch* db, void* stream, uint64_t done_flag, uint32_t flag_value) {
+    if (!p || !db) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (p->virt) return fail(TKV_ERR_INVALID_CONFIG, "device tables: not for transfer-buffer plans");
+    if (p->layer_tables) return fail(TKV_ERR_INVALID_CONFIG, "device tables: the plan was made with one table per layer");
+    tkv::HandoffArgs& a = p->args;
+    if (a.n_pairs == 0) return fail(TKV_ERR_INVALID_CONFIG, "device tables: the plan has no capacity (it was made from an empty batch)");
+    if (db->n_seqs == 0 || db->table_stride == 0 || !db->seq_lens || !db->src_tables || !db->dst_tables)
+        return fail(TKV_ERR_INVALID_CONFIG, "device tables: NULL arrays or empty batch");
+    if (db->apply_refcounts && !p->dst.refcounts) return fail(TKV_ERR_INVALID_CONFIG, "device tables: apply_refcounts without a refcount array in the destination pool");
+    if (db->apply_refcounts && p->src.device != p->dst.device)
+        return fail(TKV_ERR_INVALID_CONFIG, "device tables: reference counts of a peer pool are applied by its own device");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceGuard g(p->src.device);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    if (db->n_seqs > p->dev_scratch_seqs) {                         // first use, or a wider batch than before
+        if (p->dev_scratch) CU(cudaFree(p->dev_scratch));
+        p->dev_scratch = nullptr;
+        p->dev_scratch_seqs = 0;
+        const size_t seqs = std::max<size_t>(db->n_seqs, 256);
+        CU(cudaMalloc((void**)&p->dev_scratch, (4 + seqs) * sizeof(uint32_t)));
+        p->dev_scratch_seqs = seqs;
+    }
+    {
+        int32_t rc = ensure_uploaded(p, st);
+        if (rc) return rc;
+    }
+    tkv::DeviceTables t{};
+    t.seq_lens = reinterpret_cast<const uint32_t*>(db->seq_lens);
+    t.prefix_lens = reinterpret_cast<const uint32_t*>(db->prefix_lens);
+    t.src_tables = reinterpret_cast<const uint32_t*>(db->src_tables);
+    t.dst_tables = reinterpret_cast<const uint32_t*>(db->dst_tables);
+    t.offsets = p->dev_scratch + 4;
+    t.work = reinterpret_cast<uint4*>(p->d_buf + p->off_work);
+    t.n_pairs_out = p->dev_scratch;
+    t.status = reinterpret_cast<uint32_t*>(db->status);
+    t.refcounts = db->apply_refcounts ? reinterpret_cast<int32_t*>(p->dst.refcounts) : nullptr;
+    t.n_seqs = db->n_seqs;
+    t.table_stride = db->table_stride;
+    t.block_size = a.block_size;
+    t.capacity = a.n_pairs;
+    t.src_total_blocks = p->src.total_blocks;
+    t.dst_total_blocks = p->dst.total_blocks;
+    tkv::worklist_from_device_tables<<<1, 1024, 0, st>>>(t);
+    CU(cudaGetLastError());
+    a.done_flag = reinterpret_cast<uint32_t*>(done_flag);
+    a.flag_value = flag_value;
+    a.n_pairs_dev = p->dev_scratch;
+    const int32_t rc = dispatch(p, (uint64_t)a.n_pairs * a.n_layers * 2, st);
+    a.n_pairs_dev = nullptr;
+    return rc;
 }
 
 int32_t tkv_plan_tune_bulk(tkv_plan* p, uint32_t stages, uint32_t ctas_per_sm, uint32_t stage_bytes) {

@@ -244,6 +244,29 @@ class Plan:
             stream = torch.cuda.current_stream(self.launch_device)
         check(lib().tkv_handoff_enqueue(self._h, C.c_void_p(stream.cuda_stream), done_flag, flag_value))
 
+    @staticmethod
+    def with_capacity(src: Pool, dst: Pool, n_pairs: int, shard: Optional[N.TkvShard] = None, flags: int = 0) -> "Plan":
+        """A plan sized for up to ``n_pairs`` block pairs per call, for :meth:`enqueue_device_tables`."""
+        ids = np.arange(n_pairs, dtype=np.uint32)
+        return Plan(src, dst, Batch(np.array([n_pairs * src.block_size], dtype=np.uint32), ids, ids, n_pairs), shard, flags)
+
+    def enqueue_device_tables(self, seq_lens: torch.Tensor, src_tables: torch.Tensor, dst_tables: torch.Tensor,
+                              prefix_lens: Optional[torch.Tensor] = None, apply_refcounts: bool = False,
+                              status: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None,
+                              done_flag: int = 0, flag_value: int = 0) -> None:
+        """The handoff with its work list built on the device from int32 tensors ``seq_lens [n]``, ``src_tables`` /
+        ``dst_tables [n, stride]`` and optional ``prefix_lens [n]`` (as the device prefix index and page allocator
+        leave them); ``status`` (device int32) receives 0 or an error code."""
+        for t in (seq_lens, src_tables, dst_tables, prefix_lens, status):
+            assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous())
+        assert src_tables.shape == dst_tables.shape and src_tables.shape[0] == seq_lens.numel()
+        if stream is None:
+            stream = torch.cuda.current_stream(self.launch_device)
+        b = N.TkvDeviceBatch(src_tables.shape[0], src_tables.shape[1], 1 if apply_refcounts else 0, 0, seq_lens.data_ptr(),
+                             prefix_lens.data_ptr() if prefix_lens is not None else 0, src_tables.data_ptr(), dst_tables.data_ptr(),
+                             status.data_ptr() if status is not None else 0)
+        check(lib().tkv_handoff_enqueue_device_tables(self._h, C.byref(b), C.c_void_p(stream.cuda_stream), done_flag, flag_value))
+
     def refcount_apply(self, delta: int, stream: Optional[torch.cuda.Stream] = None) -> None:
         if stream is None:
             stream = torch.cuda.current_stream(self.launch_device)
