@@ -515,6 +515,64 @@ typedef struct TkvDeviceBatch {
 } TkvDeviceBatch;
 int32_t tkv_handoff_enqueue_device_tables(tkv_plan* plan, const TkvDeviceBatch* batch, void* stream, uint64_t done_flag, uint32_t flag_value);
 
+/* ---- handoff coordinator (host logic, no CUDA) --------------------------------- */
+/* The bookkeeping a disaggregated server keeps around the handoff: which prefill worker takes a
+ * new request, which decode worker receives its cache and only when that worker's pool has the
+ * pages (the reference gates admission on pool headroom, server/src/engine_task.rs:618-660, and
+ * tracks requests in BatchScheduler, server/src/batch.rs:13-56), which handoffs are overdue, and
+ * when to give up on one and let the decode worker prefill the prompt itself.
+ *   QUEUED -> PREFILL -> WAITING -> ADMITTED -> TRANSFER -> DECODE -> (finish)
+ *                                      ^------- failed, attempts left
+ *                                   TRANSFER -> failed, none left -> REPREFILL -> DECODE
+ * The caller reports what the device calls said: free pages (tkv_device_page_allocator_available
+ * or the host allocator), completion (tkv_flag_wait_*), failures (a status word, a timeout).    */
+typedef struct tkv_coordinator tkv_coordinator;
+typedef struct TkvCoordinatorConfig {
+    uint32_t n_prefill, n_decode, block_size;
+    uint32_t max_inflight_per_decode;   /* handoffs admitted and not yet complete per decode worker; 0 = no limit */
+    uint32_t max_retries;               /* handoff attempts after the first before falling back to re-prefill     */
+    uint32_t headroom_blocks;           /* pages every decode pool keeps free for the growth of running sequences  */
+    uint64_t handoff_timeout;           /* in the caller's clock units; 0 = handoffs never time out                */
+} TkvCoordinatorConfig;
+enum { TKV_REQ_QUEUED = 0, TKV_REQ_PREFILL = 1, TKV_REQ_WAITING = 2, TKV_REQ_ADMITTED = 3, TKV_REQ_TRANSFER = 4,
+       TKV_REQ_DECODE = 5, TKV_REQ_REPREFILL = 6 };
+enum { TKV_RETRY_HANDOFF = 1, TKV_REPREFILL = 2 };
+typedef struct TkvAdmission {
+    uint64_t request_id;
+    uint32_t prefill_worker, decode_worker;
+    uint32_t blocks;                    /* pages to take from the decode worker's allocator (prompt + max_new_tokens, less the resident prefix) */
+    uint32_t prefix_tokens;
+} TkvAdmission;
+typedef struct TkvRequestInfo {
+    uint64_t request_id;
+    uint32_t state, prefill_worker, decode_worker, reserved_blocks, prefix_tokens, attempts;
+} TkvRequestInfo;
+typedef struct TkvCoordinatorStats {
+    uint64_t submitted, admitted, handoffs_completed, handoffs_failed, retries, fallbacks, finished;
+    uint64_t in_system, waiting, reserved_blocks;
+} TkvCoordinatorStats;
+tkv_coordinator* tkv_coordinator_new(const TkvCoordinatorConfig*);
+void tkv_coordinator_delete(tkv_coordinator*);
+int32_t tkv_coordinator_set_headroom(tkv_coordinator*, uint32_t decode_worker, uint64_t free_blocks);
+/* least-loaded prefill worker (prompt tokens queued or running), lowest index on a tie */
+int32_t tkv_coordinator_submit(tkv_coordinator*, uint64_t request_id, uint32_t n_tokens, uint32_t max_new_tokens, uint32_t priority,
+                               uint32_t* prefill_worker);
+/* 1 = *request_id is the worker's next prompt (highest priority, then oldest); 0 = its queue is empty; -1 = error */
+int32_t tkv_coordinator_next_prefill(tkv_coordinator*, uint32_t prefill_worker, uint64_t* request_id);
+int32_t tkv_coordinator_prefill_done(tkv_coordinator*, uint64_t request_id, uint32_t prefix_tokens_resident);
+/* oldest first; to the decode worker paired with the prefill worker (index mod n_decode) when it fits there, else to
+ * the one with the most room; a request that fits nowhere waits without blocking smaller ones behind it */
+size_t tkv_coordinator_admit(tkv_coordinator*, TkvAdmission* out, size_t cap);
+/* the pages were taken and the handoff enqueued; report the pool's new headroom before the next admit */
+int32_t tkv_coordinator_handoff_started(tkv_coordinator*, uint64_t request_id, uint64_t now);
+int32_t tkv_coordinator_handoff_complete(tkv_coordinator*, uint64_t request_id);
+int32_t tkv_coordinator_handoff_failed(tkv_coordinator*, uint64_t request_id, uint32_t* action /* TKV_RETRY_HANDOFF | TKV_REPREFILL */);
+size_t tkv_coordinator_timed_out(tkv_coordinator*, uint64_t now, uint64_t* request_ids, size_t cap);
+int32_t tkv_coordinator_reprefill_done(tkv_coordinator*, uint64_t request_id);
+int32_t tkv_coordinator_finish(tkv_coordinator*, uint64_t request_id);                 /* from any state */
+int32_t tkv_coordinator_request(const tkv_coordinator*, uint64_t request_id, TkvRequestInfo* out);   /* 1 = found */
+int32_t tkv_coordinator_stats(const tkv_coordinator*, TkvCoordinatorStats* out);
+
 #ifdef __cplusplus
 }
 #endif

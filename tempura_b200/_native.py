@@ -75,6 +75,27 @@ class TkvDeviceBatch(C.Structure):
         (n, C.c_uint64) for n in ("seq_lens", "prefix_lens", "src_tables", "dst_tables", "status")]
 
 
+class TkvCoordinatorConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_prefill", "n_decode", "block_size", "max_inflight_per_decode", "max_retries",
+                                          "headroom_blocks")] + [("handoff_timeout", C.c_uint64)]
+
+
+class TkvAdmission(C.Structure):
+    _fields_ = [("request_id", C.c_uint64)] + [(n, C.c_uint32) for n in ("prefill_worker", "decode_worker", "blocks", "prefix_tokens")]
+
+
+class TkvRequestInfo(C.Structure):
+    _fields_ = [("request_id", C.c_uint64)] + [(n, C.c_uint32) for n in (
+        "state", "prefill_worker", "decode_worker", "reserved_blocks", "prefix_tokens", "attempts")]
+
+
+class TkvCoordinatorStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("submitted", "admitted", "handoffs_completed", "handoffs_failed", "retries", "fallbacks",
+                                          "finished", "in_system", "waiting", "reserved_blocks")]
+
+
+REQ_QUEUED, REQ_PREFILL, REQ_WAITING, REQ_ADMITTED, REQ_TRANSFER, REQ_DECODE, REQ_REPREFILL = range(7)
+RETRY_HANDOFF, REPREFILL = 1, 2
 PREFIX_NO_PAGE = 0xFFFFFFFF
 
 
@@ -173,6 +194,21 @@ SIGNATURES = {
     "tkv_device_page_allocator_free": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
     "tkv_device_page_allocator_available": (_i32, [_vp, _vp, _u32p]),
     "tkv_handoff_enqueue_device_tables": (_i32, [_vp, C.POINTER(TkvDeviceBatch), _vp, _u64, _u32]),
+    "tkv_coordinator_new": (_vp, [C.POINTER(TkvCoordinatorConfig)]),
+    "tkv_coordinator_delete": (None, [_vp]),
+    "tkv_coordinator_set_headroom": (_i32, [_vp, _u32, _u64]),
+    "tkv_coordinator_submit": (_i32, [_vp, _u64, _u32, _u32, _u32, _u32p]),
+    "tkv_coordinator_next_prefill": (_i32, [_vp, _u32, _u64p]),
+    "tkv_coordinator_prefill_done": (_i32, [_vp, _u64, _u32]),
+    "tkv_coordinator_admit": (_sz, [_vp, C.POINTER(TkvAdmission), _sz]),
+    "tkv_coordinator_handoff_started": (_i32, [_vp, _u64, _u64]),
+    "tkv_coordinator_handoff_complete": (_i32, [_vp, _u64]),
+    "tkv_coordinator_handoff_failed": (_i32, [_vp, _u64, _u32p]),
+    "tkv_coordinator_timed_out": (_sz, [_vp, _u64, _u64p, _sz]),
+    "tkv_coordinator_reprefill_done": (_i32, [_vp, _u64]),
+    "tkv_coordinator_finish": (_i32, [_vp, _u64]),
+    "tkv_coordinator_request": (_i32, [_vp, _u64, C.POINTER(TkvRequestInfo)]),
+    "tkv_coordinator_stats": (_i32, [_vp, C.POINTER(TkvCoordinatorStats)]),
     "tkv_radix_tree_new": (_vp, []),
     "tkv_radix_tree_delete": (None, [_vp]),
     "tkv_radix_tree_insert": (None, [_vp, _u32p, _sz, _szp, _sz]),
