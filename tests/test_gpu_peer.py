@@ -79,3 +79,24 @@ def test_peer_head_shard_pair(H):
     """One pair of the 4 -> 4 layout: source holds 8 heads, this pair's decode pool its 2."""
     w = W.Workload("peer-shard", 4, 8, 128, 16, 128, 128, np.full(5, 70, dtype=np.uint32), seed=53).build_tables()
     _run(H, w, "copy", shard=H.Shard(2, 0, 2, 0, 0, 4), oshard=oracle.OrcShard(2, 0, 2, 0, 0, 4), dst_heads=2)
+
+
+def test_peer_handoff_from_device_tables(H):
+    """The work list built on the prefill GPU from tables in its memory, the stores going to the decode GPU."""
+    import torch
+    w = W.Workload("peer-dt", 2, 8, 128, 16, 256, 256, W.lengths(6, 20, 280, 56, 7), seed=56).build_tables()
+    hs, hd = host_pools(w)
+    src, dst = to_device_pool(hs, "f16", device=0), to_device_pool(hd, "f16", device=1)
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    n = len(w.seq_lens)
+    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(torch.int32).to("cuda:0")
+    plan = H.Plan.with_capacity(src, dst, 200)
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda:0")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda:1")
+    with torch.cuda.device(0):
+        plan.enqueue_device_tables(to_dev(w.seq_lens), to_dev(w.src_tables.reshape(n, -1)), to_dev(w.dst_tables.reshape(n, -1)),
+                                   status=status, done_flag=flag.data_ptr(), flag_value=3)
+    H.flag_wait_host(1, flag.data_ptr(), 3, 10_000_000)
+    assert int(status.item()) == 0 and plan.stats().peer == 1
+    with torch.cuda.device(1):
+        assert_pool_equals_host(dst, hd, "peer device tables")
