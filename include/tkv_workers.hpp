@@ -253,5 +253,109 @@ private:
     uint32_t generation_ = 0;
 };
 
+
+// ---- the decode side's admission kept on the device -----------------------------------------
+// RadixTree (engine/src/prefix_cache.rs:17-149) and PageAllocator (engine/src/kv_cache.rs:762-797)
+// with their state in HBM, and a receiver that goes from token ids to a finished handoff on one
+// stream: lookup -> allocate -> handoff, no block id or length crossing to the host.
+class DevicePrefixIndex {
+public:
+    DevicePrefixIndex(int device, uint64_t capacity, uint32_t group_tokens) { check(tkv_prefix_index_create(device, capacity, group_tokens, &h_)); }
+    ~DevicePrefixIndex() { tkv_prefix_index_destroy(h_); }
+    DevicePrefixIndex(const DevicePrefixIndex&) = delete;
+    DevicePrefixIndex& operator=(const DevicePrefixIndex&) = delete;
+    void insert(const TkvPrefixBatch& b, void* stream) { check(tkv_prefix_index_insert(h_, &b, stream)); }
+    void lookup(const TkvPrefixBatch& b, uint64_t out_pages, uint32_t out_stride, uint64_t out_matched, void* stream) {
+        check(tkv_prefix_index_lookup(h_, &b, out_pages, out_stride, out_matched, stream));
+    }
+    void release(const TkvPrefixBatch& b, void* stream) { check(tkv_prefix_index_release(h_, &b, stream)); }
+    void evict_lru(uint32_t max_nodes, uint64_t out_pages, uint32_t out_cap, uint64_t out_count, uint64_t out_nodes, void* stream) {
+        check(tkv_prefix_index_evict_lru(h_, max_nodes, out_pages, out_cap, out_count, out_nodes, stream));
+    }
+    TkvPrefixIndexStats stats(void* stream) {
+        TkvPrefixIndexStats st{};
+        check(tkv_prefix_index_stats(h_, stream, &st));
+        return st;
+    }
+    tkv_prefix_index* get() { return h_; }
+
+private:
+    tkv_prefix_index* h_ = nullptr;
+};
+
+class DevicePageAllocator {
+public:
+    DevicePageAllocator(int device, uint32_t total_pages) { check(tkv_device_page_allocator_create(device, total_pages, &h_)); }
+    ~DevicePageAllocator() { tkv_device_page_allocator_destroy(h_); }
+    DevicePageAllocator(const DevicePageAllocator&) = delete;
+    DevicePageAllocator& operator=(const DevicePageAllocator&) = delete;
+    void allocate(const TkvPageBatch& b, uint64_t status, void* stream) { check(tkv_device_page_allocator_allocate(h_, &b, status, stream)); }
+    void free(const TkvPageBatch& b, uint64_t status, void* stream) { check(tkv_device_page_allocator_free(h_, &b, status, stream)); }
+    uint32_t available(void* stream) {
+        uint32_t n = 0;
+        check(tkv_device_page_allocator_available(h_, stream, &n));
+        return n;
+    }
+
+private:
+    tkv_device_page_allocator* h_ = nullptr;
+};
+
+// Device arrays a batch admission works in; the caller owns them (all on the pools' device, u32):
+//   tokens [n][token_stride], seq_lens [n], src_tables / dst_tables [n][table_stride], matched / need / prefix_lens [n],
+//   status [2] (allocator, work list).  `need` and `prefix_lens` are filled by the caller's own small kernel or, as here,
+//   left to the caller: need[s] = ceil(seq_lens[s] / block) - matched[s], prefix_lens[s] = matched[s] * block.
+struct DeviceAdmissionBuffers {
+    uint64_t tokens = 0, seq_lens = 0, src_tables = 0, dst_tables = 0, matched = 0, need = 0, prefix_lens = 0, status = 0;
+    uint32_t n_seqs = 0, token_stride = 0, table_stride = 0;
+};
+
+// DecodeWorker::receive_kv for a batch, with prefix resolution and page placement on the device.  `plan` is a plan over
+// (source pool, destination pool) made from a host batch at least as large as any batch admitted here.  `derive` is
+// called between the lookup and the allocation to fill `need` and `prefix_lens` from `matched` on the same stream
+// (a two-line kernel on the caller's side; this header holds no device code).
+class DeviceKvReceiver {
+public:
+    DeviceKvReceiver(tkv_plan* plan, DevicePrefixIndex* index, DevicePageAllocator* pages, uint64_t flag)
+        : plan_(plan), index_(index), pages_(pages), flag_(flag) {}
+
+    template <typename Derive>
+    uint32_t adopt(const DeviceAdmissionBuffers& b, void* stream, Derive&& derive) {
+        TkvPrefixBatch pb{};
+        pb.n_seqs = b.n_seqs;
+        pb.stride = b.token_stride;
+        pb.tokens = b.tokens;
+        pb.lens = b.seq_lens;
+        index_->lookup(pb, b.dst_tables, b.table_stride, b.matched, stream);
+        derive(stream);
+        TkvPageBatch pg{};
+        pg.n_seqs = b.n_seqs;
+        pg.table_stride = b.table_stride;
+        pg.tables = b.dst_tables;
+        pg.first = b.matched;
+        pg.counts = b.need;
+        pages_->allocate(pg, b.status, stream);
+        TkvDeviceBatch db{};
+        db.n_seqs = b.n_seqs;
+        db.table_stride = b.table_stride;
+        db.apply_refcounts = 1;
+        db.seq_lens = b.seq_lens;
+        db.prefix_lens = b.prefix_lens;
+        db.src_tables = b.src_tables;
+        db.dst_tables = b.dst_tables;
+        db.status = b.status + 4;
+        const uint32_t gen = ++generation_;
+        check(tkv_handoff_enqueue_device_tables(plan_, &db, stream, flag_, gen));
+        return gen;       // wait for it with tkv_flag_wait_host / tkv_flag_wait_enqueue, then read the two status words
+    }
+
+private:
+    tkv_plan* plan_;
+    DevicePrefixIndex* index_;
+    DevicePageAllocator* pages_;
+    uint64_t flag_;
+    uint32_t generation_ = 0;
+};
+
 }  // namespace tkv_host
 #endif  // TKV_WORKERS_HPP

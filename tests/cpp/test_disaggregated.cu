@@ -384,6 +384,117 @@ static void test_errors(int da, int db) {
     REQUIRE(receiver.adopt(t, r.stream_a).size() == 2);
 }
 
+// what the receiver leaves to its caller between the lookup and the allocation: pages still needed, tokens resident
+__global__ void derive_need(const uint32_t* seq_lens, const uint32_t* matched, uint32_t* need, uint32_t* prefix_lens, uint32_t n, uint32_t bs) {
+    uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    need[s] = (seq_lens[s] + bs - 1) / bs - matched[s];
+    prefix_lens[s] = matched[s] * bs;
+}
+
+// The decode side's admission with the prefix index and the page allocator in device memory: the second prompt
+// shares its first two blocks with the first one, so it adopts those pages (reference count 1) and moves the rest.
+static void test_device_admission(int da) {
+    Rig r(da, da);
+    const Config& c = r.cfg;
+    const uint32_t bs = c.block_size, stride = 8;
+    DevicePrefixIndex index(da, 1024, bs);
+    DevicePageAllocator pages(da, c.total_pages);
+    // a plan sized for up to `stride` block pairs per admission (only its size matters)
+    std::vector<uint32_t> ident(stride);
+    for (uint32_t i = 0; i < stride; i++) ident[i] = i;
+    uint32_t cap_len = stride * bs;
+    TkvBatch cap{};
+    cap.n_seqs = 1;
+    cap.table_stride = stride;
+    cap.seq_lens = &cap_len;
+    cap.src_tables = ident.data();
+    cap.dst_tables = ident.data();
+    tkv_plan* plan = nullptr;
+    check(tkv_plan_create(r.a.pool.get(), r.b.pool.get(), &cap, nullptr, TKV_PLAN_DEFAULT, &plan));
+    DeviceKvReceiver receiver(plan, &index, &pages, (uint64_t)r.flag);
+
+    std::vector<uint32_t> first = prompt_of(40, 3), second(first.begin(), first.begin() + 32);
+    for (uint32_t t : prompt_of(18, 9)) second.push_back(t);
+    GpuPrefillWorker prefill(&r.model, &r.a, &r.pages_a);
+    uint32_t *d_tokens, *d_len, *d_src, *d_dst, *d_matched, *d_need, *d_prefix, *d_status;
+    CUDA_OK(cudaMalloc((void**)&d_tokens, 64 * 4));
+    CUDA_OK(cudaMalloc((void**)&d_len, 4));
+    CUDA_OK(cudaMalloc((void**)&d_src, stride * 4));
+    CUDA_OK(cudaMalloc((void**)&d_dst, stride * 4));
+    CUDA_OK(cudaMalloc((void**)&d_matched, 4));
+    CUDA_OK(cudaMalloc((void**)&d_need, 4));
+    CUDA_OK(cudaMalloc((void**)&d_prefix, 4));
+    CUDA_OK(cudaMalloc((void**)&d_status, 8));
+    std::vector<uint32_t> first_table;
+    for (int round = 0; round < 2; round++) {
+        const std::vector<uint32_t>& prompt = round ? second : first;
+        SessionTransfer t = prefill.prefill(prompt, 7);
+        const uint32_t len = (uint32_t)prompt.size(), nb = (len + bs - 1) / bs;
+        std::vector<uint32_t> src(stride, 0);
+        for (uint32_t i = 0; i < nb; i++) src[i] = t.cache.block_table[i];
+        CUDA_OK(cudaMemcpy(d_tokens, prompt.data(), len * 4, cudaMemcpyHostToDevice));
+        CUDA_OK(cudaMemcpy(d_len, &len, 4, cudaMemcpyHostToDevice));
+        CUDA_OK(cudaMemcpy(d_src, src.data(), stride * 4, cudaMemcpyHostToDevice));
+        CUDA_OK(cudaMemset(d_dst, 0xFF, stride * 4));
+        CUDA_OK(cudaMemset(d_status, 0xFF, 8));
+        DeviceAdmissionBuffers b;
+        b.tokens = (uint64_t)d_tokens;
+        b.seq_lens = (uint64_t)d_len;
+        b.src_tables = (uint64_t)d_src;
+        b.dst_tables = (uint64_t)d_dst;
+        b.matched = (uint64_t)d_matched;
+        b.need = (uint64_t)d_need;
+        b.prefix_lens = (uint64_t)d_prefix;
+        b.status = (uint64_t)d_status;
+        b.n_seqs = 1;
+        b.token_stride = 64;
+        b.table_stride = stride;
+        const uint32_t gen = receiver.adopt(b, r.stream_a, [&](void* st) {
+            derive_need<<<1, 32, 0, (cudaStream_t)st>>>(d_len, d_matched, d_need, d_prefix, 1, bs);
+        });
+        check(tkv_flag_wait_host(da, (uint64_t)r.flag, gen, 10'000'000));
+        uint32_t status[2], matched = 99;
+        std::vector<uint32_t> table(stride);
+        CUDA_OK(cudaMemcpy(status, d_status, 8, cudaMemcpyDeviceToHost));
+        CUDA_OK(cudaMemcpy(&matched, d_matched, 4, cudaMemcpyDeviceToHost));
+        CUDA_OK(cudaMemcpy(table.data(), d_dst, stride * 4, cudaMemcpyDeviceToHost));
+        REQUIRE(status[0] == 0 && status[1] == 0);
+        REQUIRE(matched == (round ? 2u : 0u));
+        table.resize(nb);
+        if (round) {
+            REQUIRE(table[0] == first_table[0] && table[1] == first_table[1]);      // adopted, not moved
+            REQUIRE(table[2] != first_table[2]);
+            uint32_t rc[2];
+            CUDA_OK(cudaMemcpy(rc, r.b.refcounts + table[0], 4, cudaMemcpyDeviceToHost));
+            CUDA_OK(cudaMemcpy(rc + 1, r.b.refcounts + table[1], 4, cudaMemcpyDeviceToHost));
+            REQUIRE(rc[0] == 1 && rc[1] == 1);
+        } else {
+            first_table = table;
+        }
+        for (uint32_t l = 0; l < c.num_layers; l++)
+            for (bool is_v : {false, true})
+                REQUIRE(read_rows(r.a, t.cache.block_table, len, l, is_v, c) == read_rows(r.b, table, len, l, is_v, c));
+        // index the whole blocks of this prompt under the pages it now has on the decode side
+        TkvPrefixBatch pb{};
+        pb.n_seqs = 1;
+        pb.stride = 64;
+        pb.page_stride = stride;
+        pb.tokens = (uint64_t)d_tokens;
+        pb.lens = (uint64_t)d_len;
+        pb.pages = (uint64_t)d_dst;
+        index.insert(pb, r.stream_a);
+        index.release(pb, r.stream_a);          // the lookup's references, given back once the prompt is indexed
+        for (uint32_t page : t.cache.block_table) r.pages_a.free(page);
+    }
+    REQUIRE(pages.available(r.stream_a) == c.total_pages - 3 - 2);   // 3 blocks for the first prompt, 2 new ones for the second
+    TkvPrefixIndexStats st = index.stats(r.stream_a);
+    REQUIRE(st.live_nodes == 2 + 1 && st.hits == 1 && st.tokens_saved == 32);
+    tkv_plan_destroy(plan);
+    for (void* p : {(void*)d_tokens, (void*)d_len, (void*)d_src, (void*)d_dst, (void*)d_matched, (void*)d_need, (void*)d_prefix, (void*)d_status})
+        cudaFree(p);
+}
+
 int main() {
     int n_dev = 0;
     CUDA_OK(cudaGetDeviceCount(&n_dev));
@@ -399,6 +510,7 @@ int main() {
     test_disaggregated_matches_single_worker(da, db);
     test_shared_prefix_pages_are_adopted_not_moved(da, db);
     test_errors(da, db);
+    test_device_admission(da);
     printf("ALL PASSED (prefill device %d, decode device %d)\n", da, db);
     return 0;
 }
