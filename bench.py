@@ -712,13 +712,117 @@ def bench_prefix_index(args) -> None:
                          "sample": "the same 64 x 8192-token lookup + release through the RadixTree oracle, once"},
         "gpu_launches": (max(args.warmup, 3) + args.steps) * 2 + 2, "clocks": clocks}), flush=True)
 
+
+def bench_admission(args) -> None:
+    """--workload admit: the decode side's admission of the prefix-reuse batch (64 prompts sharing a resident
+    2 048-token prefix, 128-512-token suffixes; 4 layers unless --layers says otherwise), wall clock from the
+    prompts' token ids to the completed handoff, two ways: everything on the device (prefix index lookup -> page
+    allocator -> handoff from device tables) and with the host in the loop (the same lookup, its answer copied
+    to the host, pages popped from a host free list, a host-built plan).  Both end with the same bytes moved."""
+    import torch
+    from tempura_b200 import handoff as H
+    from tempura_b200 import workloads as W
+    torch.cuda.set_device(0)
+    layers, blocks, bs = args.layers or 4, args.pool_blocks or 16384, 16
+    w = W.llama8b_prefix(pool_blocks=blocks)
+    n, pre = len(w.seq_lens), 2048
+    rng = np.random.default_rng(91)
+    system = rng.integers(0, 32000, size=pre)
+    stride_tok = int(w.seq_lens.max())
+    tok = np.zeros((n, stride_tok), dtype=np.int32)
+    for q, m in enumerate(w.seq_lens):
+        tok[q, :pre] = system
+        tok[q, pre:int(m)] = rng.integers(0, 32000, size=int(m) - pre)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(torch.int32).cuda()
+    src = H.Pool.allocate(0, layers, 8, 128, bs, blocks, "f16")
+    dst = H.Pool.allocate(0, layers, 8, 128, bs, blocks, "f16", refcounts=True, fill_byte=0x5A)
+    src.storage.view(torch.int16).random_(0, 15000)
+    tokens, lens = i32(tok), i32(w.seq_lens)
+    src_tables = i32(w.src_tables.reshape(n, -1))
+    stride = src_tables.shape[1]
+    # the decode side: pages 0..127 hold the shared prefix and are indexed; the allocator owns the rest
+    index, alloc = H.PrefixIndex(0, 1 << 16, bs), H.DevicePageAllocator(0, blocks)
+    pre_tab = torch.zeros((1, pre // bs), dtype=torch.int32, device="cuda")
+    alloc.allocate(pre_tab, i32([pre // bs]))
+    index.insert(i32(system[None, :]), i32([pre]), pre_tab)
+    host_free = list(range(blocks - 1, pre // bs - 1, -1))                     # the same stack, on the host
+    pairs_cap = int(((w.seq_lens.astype(np.int64) + bs - 1) // bs).sum())
+    plan_dev = H.Plan.with_capacity(src, dst, pairs_cap)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dst_tables = torch.zeros((n, stride), dtype=torch.int32, device="cuda")
+
+    def device_path():
+        matched, pages = index.lookup(tokens, lens)
+        k = min(pages.shape[1], stride)
+        dst_tables[:, :k] = pages[:, :k]
+        need = ((lens + (bs - 1)) // bs - matched).to(torch.int32)
+        alloc.allocate(dst_tables, need, matched)
+        plan_dev.enqueue_device_tables(lens, src_tables, dst_tables, (matched * bs).to(torch.int32), apply_refcounts=True, status=status)
+        torch.cuda.synchronize()
+        # undo, outside what a server would do per admission: give the pages and the references back
+        alloc.free(dst_tables, need, matched)
+        index.release(tokens, lens)
+        dst.refcounts.zero_()
+        torch.cuda.synchronize()
+
+    def host_path():
+        matched, pages = index.lookup(tokens, lens)
+        m, pg = matched.cpu().numpy(), pages.cpu().numpy()                     # the round trip
+        tab = np.zeros((n, stride), dtype=np.uint32)
+        taken = []
+        for q in range(n):
+            nb = (int(w.seq_lens[q]) + bs - 1) // bs
+            tab[q, :m[q]] = pg[q, :m[q]]
+            for i in range(m[q], nb):
+                tab[q, i] = host_free.pop()
+                taken.append(tab[q, i])
+        plan = H.Plan(src, dst, H.Batch(w.seq_lens, w.src_tables, tab, stride, (m * bs).astype(np.uint32)))
+        plan.enqueue()
+        plan.refcount_apply(+1)
+        torch.cuda.synchronize()
+        plan.destroy()
+        host_free.extend(reversed(taken))
+        index.release(tokens, lens)
+        dst.refcounts.zero_()
+        torch.cuda.synchronize()
+        return tab
+
+    def timed(fn, steps):
+        # only the admission itself is on the clock: from the call to the synchronize inside fn that follows the handoff
+        best = []
+        for _ in range(steps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            best.append(time.perf_counter() - t0)
+        return statistics.median(best)
+
+    for _ in range(max(args.warmup, 3)):
+        device_path()
+        host_path()
+    if int(status.item()) != 0:
+        raise SystemExit(f"admission: device work list refused the batch (status {int(status.item())})")
+    tab = host_path()
+    device_path()
+    steps = min(args.steps, 50)
+    t_dev, t_host = timed(device_path, steps), timed(host_path, steps)
+    suffix_tokens = int((w.seq_lens.astype(np.int64) - pre).sum())
+    payload = suffix_tokens * 8 * 128 * 2 * 2 * layers
+    print(json.dumps({
+        "metric": "admission_ms", "value": round(t_dev * 1e3, 4), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(t_dev * 1e3, 4), "higher_is_better": False, "dtype": "u16", "data": "synthetic",
+        "host_in_the_loop_ms": round(t_host * 1e3, 4),
+        "config": {"workload": w.name + f"-admission-{layers}layers", "n_seqs": n, "shared_prefix": pre, "suffix_tokens": suffix_tokens,
+                   "payload_bytes": payload, "note": "wall clock per admission including giving pages and references back (both legs do it)"},
+        "gpu_launches": None}), flush=True)
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefix"])
+    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefix", "admit"])
     ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
     ap.add_argument("--attn-per-head", action="store_true", help="--workload attn: the per-(sequence, kv head) CTA form")
@@ -740,6 +844,8 @@ def main():
         args.warmup = 3
     if args.workload == "prefix":
         return bench_prefix_index(args)
+    if args.workload == "admit":
+        return bench_admission(args)
     if args.workload == "attn":
         run_attention(args)
     elif args.impl == "reference":
