@@ -427,8 +427,8 @@ uint64_t tkv_prefix_table_hit_count(const tkv_prefix_table*);
 uint64_t tkv_prefix_table_tokens_saved(const tkv_prefix_table*);
 
 /* ---- device-resident prefix index --------------------------------------------- */
-/* RadixTree (engine/src/prefix_cache.rs:17-149) kept in HBM and walked by the GPU, one warp per
- * sequence, so a batch of prompts resolves its cached prefix (length, page ids, reference
+/* RadixTree (engine/src/prefix_cache.rs:17-149) kept in HBM and walked by the GPU, one CTA per
+ * sequence and one thread per node, so a batch of prompts resolves its cached prefix (length, page ids, reference
  * counts, LRU stamps) in one launch.  A node is `group_tokens` consecutive token ids below its
  * parent (1 = the reference's per-token nodes, 16 = one node per KV block), named by a 64-bit
  * hash chained from the root; only whole groups are indexed.  One call is one tick of the

@@ -1,13 +1,15 @@
 // Device-resident prefix index: RadixTree (engine/src/prefix_cache.rs:17-149) as an open-addressing
-// hash table in HBM, walked by one warp per sequence, so that a batch of prompts resolves its cached
-// prefix (length, page ids, reference counts, LRU stamps) in one launch without a host round trip.
+// hash table in HBM, walked by one CTA per sequence (one thread per node), so that a batch of prompts
+// resolves its cached prefix (length, page ids, reference counts, LRU stamps) in one launch without
+// a host round trip.
 //
 // A node of the reference's tree is one element of a sequence below one parent.  Here an element is
 // `group_tokens` consecutive token ids (1 reproduces the reference's per-token nodes, 16 gives one
 // node per KV block) and a node is named by a 64-bit key chained from the root:
-//     key_i = mix(key_{i-1}, hash(tokens of element i)),
-// so equal keys mean equal prefixes up to a 64-bit hash collision (the index does not store the
-// tokens; two different prefixes collide with probability 2^-64 per pair).
+//     raw_i = raw_{i-1} * C + hash(tokens of element i)  (mod 2^64),   key_i = mix(raw_i),
+// linear so that all keys of a sequence come out of one parallel scan.  Equal keys mean equal
+// prefixes up to a 64-bit hash collision (the index does not store the tokens; two different
+// prefixes collide with probability ~2^-64 per pair; the hash is not hardened against chosen tokens).
 //
 // Batch semantics: one call handles many sequences and is ONE tick of the reference's clock.  Its
 // result equals the reference's methods applied to the sequences in index order at that tick:
@@ -35,7 +37,6 @@ namespace {
 constexpr unsigned long long KEY_EMPTY = 0ull, KEY_TOMB = 1ull;     // real keys are >= 2
 constexpr unsigned long long ORDER_FRESH = ~0ull;
 constexpr uint32_t NO_PAGE = 0xFFFFFFFFu, NO_SLOT = 0xFFFFFFFFu;
-constexpr int WARPS_PER_CTA = 4;
 // creation order of a node: tick (34 bits) | sequence in the batch (14 bits) | depth (16 bits)
 constexpr int ORDER_SEQ_BITS = 14, ORDER_DEPTH_BITS = 16;
 
@@ -85,32 +86,31 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
     return x;
 }
 
+// One multiply per token, one full mix at the end: not a cryptographic hash (nothing here defends against chosen tokens).
 __device__ __forceinline__ unsigned long long element_hash(const uint32_t* tok, uint32_t group) {
     unsigned long long h = 0x9E3779B97F4A7C15ull;
-    for (uint32_t i = 0; i < group; i++) h = mix64(h ^ ((unsigned long long)__ldg(tok + i) + 0x632BE59BD9B4E019ull * (i + 1)));
-    return h;
+    for (uint32_t i = 0; i < group; i++) {
+        h = (h ^ __ldg(tok + i)) * 0xD6E8FEB86659FD93ull;
+        h ^= h >> 32;
+    }
+    return mix64(h);
 }
 
-__device__ __forceinline__ unsigned long long chain(unsigned long long parent_key, unsigned long long h) {
-    unsigned long long k = mix64(parent_key * 0xD6E8FEB86659FD93ull + h);
+// The chain from the root is LINEAR in the element hashes, raw_i = raw_{i-1} * CHAIN_MUL + h_i (mod 2^64), so the raw
+// values of a whole chunk come out of one parallel scan over affine maps x -> x * a + b; the table key is a full mix
+// of the raw value (real keys are >= 2).
+constexpr unsigned long long CHAIN_MUL = 0xBF58476D1CE4E5B9ull, ROOT_RAW = 0x243F6A8885A308D3ull;
+
+__device__ __forceinline__ unsigned long long key_of_raw(unsigned long long raw) {
+    const unsigned long long k = mix64(raw ^ 0x632BE59BD9B4E019ull);
     return k < 2 ? k + 2 : k;
 }
 
-// Keys of the 32 elements [base, base + 32) of one sequence, one per lane; `carry` is the key of element
-// base - 1 (the root key for base 0) and leaves as the key of element base + 31.
-__device__ __forceinline__ unsigned long long keys_of_chunk(const uint32_t* row, uint32_t base, uint32_t n_elems, uint32_t group,
-                                                            unsigned long long& carry) {
-    const uint32_t lane = threadIdx.x & 31u, i = base + lane;
-    const unsigned long long h = i < n_elems ? element_hash(row + (size_t)i * group, group) : 0ull;
-    unsigned long long key = carry, mine = 0;
-#pragma unroll 8
-    for (uint32_t l = 0; l < 32; l++) {
-        key = chain(key, __shfl_sync(0xFFFFFFFFu, h, l));
-        if (l == lane) mine = key;
-    }
-    carry = key;
-    return mine;
-}
+struct Affine {
+    unsigned long long a, b;
+};
+// first `p`, then `q`
+__device__ __forceinline__ Affine then(const Affine& p, const Affine& q) { return Affine{p.a * q.a, p.b * q.a + q.b}; }
 
 __device__ __forceinline__ uint32_t find_slot(const View& ix, unsigned long long key) {
     uint32_t h = (uint32_t)(key >> 17) & ix.mask;
@@ -156,27 +156,56 @@ __device__ __forceinline__ uint32_t find_or_claim(const View& ix, unsigned long 
 }
 
 enum Op { OP_LOOKUP = 0, OP_INSERT_CLAIM = 1, OP_INSERT_PAGES = 2, OP_RELEASE = 3 };
+constexpr int WALK_THREADS = 512;       // nodes one CTA handles per pass (one thread each)
 
+// One CTA per sequence, one thread per node: element hashes, the key chain by a scan, every probe of the pass in
+// flight at once, the first miss by a CTA-wide minimum.  A sequence with more nodes than threads takes more passes.
 template <int OP>
-__global__ void __launch_bounds__(WARPS_PER_CTA * 32) prefix_walk(View ix, Batch b, unsigned long long tick, uint32_t* out_pages,
-                                                                  uint32_t out_stride, uint32_t* out_matched) {
-    const uint32_t seq = blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
-    if (seq >= b.n_seqs) return;
+__global__ void __launch_bounds__(WALK_THREADS) prefix_walk(View ix, Batch b, unsigned long long tick, uint32_t* out_pages,
+                                                            uint32_t out_stride, uint32_t* out_matched) {
+    __shared__ Affine warp_total[WALK_THREADS / 32];
+    __shared__ uint32_t slots[WALK_THREADS];
+    __shared__ unsigned long long carry_raw;
+    __shared__ uint32_t first_miss, parent_carry;
+    const uint32_t seq = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t n_elems = min(b.lens[seq], b.stride) / ix.group;
     const uint32_t* row = b.tokens + (size_t)seq * b.stride;
-    unsigned long long carry = 0x243F6A8885A308D3ull;       // the root's key
-    uint32_t parent_carry = NO_SLOT, matched = 0;
-    for (uint32_t base = 0; base < n_elems; base += 32) {
-        const uint32_t i = base + lane;
+    if (tid == 0) {
+        carry_raw = ROOT_RAW;
+        parent_carry = NO_SLOT;
+    }
+    uint32_t matched = 0;
+    for (uint32_t base = 0; base < n_elems; base += WALK_THREADS) {
+        const uint32_t i = base + tid;
         const bool active = i < n_elems;
-        const unsigned long long key = keys_of_chunk(row, base, n_elems, ix.group, carry);
+        if (tid == 0) first_miss = WALK_THREADS;
+        // ---- keys of this pass ----
+        Affine f = active ? Affine{CHAIN_MUL, element_hash(row + (size_t)i * ix.group, ix.group)} : Affine{1ull, 0ull};
+#pragma unroll
+        for (uint32_t off = 1; off < 32; off <<= 1) {
+            Affine prev;
+            prev.a = __shfl_up_sync(0xFFFFFFFFu, f.a, off);
+            prev.b = __shfl_up_sync(0xFFFFFFFFu, f.b, off);
+            if (lane >= off) f = then(prev, f);
+        }
+        if (lane == 31) warp_total[warp] = f;
+        __syncthreads();
+        Affine before{1ull, 0ull};
+        for (uint32_t wv = 0; wv < warp; wv++) before = then(before, warp_total[wv]);
+        f = then(before, f);
+        const unsigned long long raw = carry_raw * f.a + f.b;
+        const unsigned long long key = key_of_raw(raw);
+        __syncthreads();                                   // everyone has read carry_raw
+        if (tid == WALK_THREADS - 1) carry_raw = raw;
+        // ---- the table ----
         if (OP == OP_INSERT_CLAIM) {
             bool created = false, reused = false;
             const uint32_t slot = active ? find_or_claim(ix, key, created, reused) : NO_SLOT;
             if (active && slot == NO_SLOT) atomicExch(&ix.ctr->error, 1u);
-            uint32_t parent = __shfl_up_sync(0xFFFFFFFFu, slot, 1);
-            if (lane == 0) parent = parent_carry;
-            parent_carry = __shfl_sync(0xFFFFFFFFu, slot, 31);
+            slots[tid] = slot;
+            const uint32_t parent_of_first = parent_carry;
+            __syncthreads();
+            const uint32_t parent = tid ? slots[tid - 1] : parent_of_first;
             if (active && slot != NO_SLOT) {
                 const unsigned long long order = (tick << (ORDER_SEQ_BITS + ORDER_DEPTH_BITS)) |
                                                  ((unsigned long long)seq << ORDER_DEPTH_BITS) | min(i, (1u << ORDER_DEPTH_BITS) - 1u);
@@ -189,11 +218,14 @@ __global__ void __launch_bounds__(WARPS_PER_CTA * 32) prefix_walk(View ix, Batch
                     if (reused) atomicAdd(&ix.ctr->tombstones, ~0ull);
                 }
             }
+            __syncthreads();
+            if (tid == WALK_THREADS - 1) parent_carry = slot;
         } else {
             const uint32_t slot = active ? find_slot(ix, key) : NO_SLOT;
-            const uint32_t hit = __ballot_sync(0xFFFFFFFFu, slot != NO_SLOT);
-            const uint32_t run = hit == 0xFFFFFFFFu ? 32u : (uint32_t)__ffs(~hit) - 1u;   // matched elements of this chunk, from its start
-            if (lane < run) {
+            if (slot == NO_SLOT) atomicMin(&first_miss, tid);
+            __syncthreads();
+            const uint32_t run = first_miss;               // matched nodes of this pass, from its start
+            if (tid < run) {
                 Meta& m = ix.meta[slot];
                 if (OP == OP_LOOKUP) {
                     atomicAdd(&m.refs, 1);
@@ -211,10 +243,12 @@ __global__ void __launch_bounds__(WARPS_PER_CTA * 32) prefix_walk(View ix, Batch
                 }
             }
             matched += run;
-            if (run < 32u) break;
+            __syncthreads();                               // first_miss is reset at the top of the next pass
+            if (run < (uint32_t)WALK_THREADS) break;
         }
+        __syncthreads();
     }
-    if (OP == OP_LOOKUP && lane == 0) {
+    if (OP == OP_LOOKUP && tid == 0) {
         if (out_matched) out_matched[seq] = matched;
         if (matched) {
             atomicAdd(&ix.ctr->hits, 1ull);
@@ -493,10 +527,10 @@ int32_t tkv_prefix_index_insert(tkv_prefix_index* ix, const TkvPrefixBatch* batc
     const unsigned long long tick = ++ix->tick;
     if (tick >> (64 - ORDER_SEQ_BITS - ORDER_DEPTH_BITS)) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: call counter exhausted");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+    const uint32_t ctas = b.n_seqs;
     // two launches: every node is found or claimed first, then the sequence that created a node writes its page
-    prefix_walk<OP_INSERT_CLAIM><<<ctas, WARPS_PER_CTA * 32, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
-    prefix_walk<OP_INSERT_PAGES><<<ctas, WARPS_PER_CTA * 32, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
+    prefix_walk<OP_INSERT_CLAIM><<<ctas, WALK_THREADS, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
+    prefix_walk<OP_INSERT_PAGES><<<ctas, WALK_THREADS, 0, st>>>(ix->view, b, tick, nullptr, 0, nullptr);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index insert");
 }
@@ -510,8 +544,8 @@ int32_t tkv_prefix_index_lookup(tkv_prefix_index* ix, const TkvPrefixBatch* batc
     DeviceGuard guard(ix->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
     const unsigned long long tick = ++ix->tick;
-    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
-    prefix_walk<OP_LOOKUP><<<ctas, WARPS_PER_CTA * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    const uint32_t ctas = b.n_seqs;
+    prefix_walk<OP_LOOKUP><<<ctas, WALK_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         ix->view, b, tick, reinterpret_cast<uint32_t*>(out_pages), out_stride, reinterpret_cast<uint32_t*>(out_matched));
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index lookup");
@@ -523,8 +557,8 @@ int32_t tkv_prefix_index_release(tkv_prefix_index* ix, const TkvPrefixBatch* bat
     if (b.n_seqs == 0) return TKV_OK;
     DeviceGuard guard(ix->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
-    const uint32_t ctas = (b.n_seqs + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
-    prefix_walk<OP_RELEASE><<<ctas, WARPS_PER_CTA * 32, 0, static_cast<cudaStream_t>(stream)>>>(ix->view, b, ix->tick, nullptr, 0, nullptr);
+    const uint32_t ctas = b.n_seqs;
+    prefix_walk<OP_RELEASE><<<ctas, WALK_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(ix->view, b, ix->tick, nullptr, 0, nullptr);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TKV_OK : fail_cuda(e, "prefix index release");
 }

@@ -176,3 +176,38 @@ def test_admission_without_a_host_round_trip(H):
     rc = np.zeros(total, dtype=np.int32)
     rc[resident] = n
     assert np.array_equal(dst.refcounts.cpu().numpy(), rc)
+
+
+def test_more_sequences_than_the_builder_has_threads(H):
+    """1 500 short prompts (the builder's scan runs in chunks of 1 024 sequences), some of them empty."""
+    rng = np.random.default_rng(36)
+    lens = rng.integers(0, 40, size=1500).astype(np.uint32)
+    lens[[0, 1023, 1024, 1499]] = [0, 17, 0, 33]
+    w = W.Workload("dt-wide", 1, 4, 64, 16, 4096, 4096, lens, seed=36).build_tables()
+    run_device_tables(H, w, "copy")
+
+
+def test_index_and_allocator_edge_cases(H):
+    import torch
+    ix = H.PrefixIndex(0, 64, 16)
+    empty_tok = torch.zeros((3, 20), dtype=torch.int32, device="cuda")
+    lens = torch.tensor([0, 15, 16], dtype=torch.int32, device="cuda")          # no whole group, no whole group, exactly one
+    ix.insert(empty_tok, lens)
+    matched, pages = ix.lookup(empty_tok, lens)
+    assert matched.tolist() == [0, 0, 1] and int(pages[2, 0]) == -1               # inserted without a page
+    st = ix.stats()
+    assert st.live_nodes == 1 and st.hits == 1 and st.tokens_saved == 16
+    assert ix.evict_lru(4) == ([], 0)                                             # still referenced by the lookup
+    ix.release(empty_tok, lens)
+    ix.release(empty_tok, lens)                                                   # a second release does not go below zero
+    assert ix.evict_lru(4) == ([], 1)                                             # unlinked; it had no page to report
+    with pytest.raises(N.TkvError):
+        H.PrefixIndex(0, 100)                                                     # capacity must be a power of two
+    alloc = H.DevicePageAllocator(0, 8)
+    t = torch.full((2, 4), -1, dtype=torch.int32, device="cuda")
+    alloc.allocate(t, torch.tensor([0, 0], dtype=torch.int32, device="cuda"))     # nothing asked for
+    assert int(alloc.status.item()) == 0 and alloc.available() == 8 and bool((t == -1).all())
+    alloc.allocate(t, torch.tensor([4, 4], dtype=torch.int32, device="cuda"))     # exactly everything
+    assert int(alloc.status.item()) == 0 and alloc.available() == 0 and sorted(t.flatten().tolist()) == list(range(8))
+    alloc.allocate(t, torch.tensor([1, 0], dtype=torch.int32, device="cuda"))
+    assert int(alloc.status.item()) == N.ERR_POOL_EXHAUSTED
