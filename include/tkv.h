@@ -504,7 +504,8 @@ int32_t tkv_device_page_allocator_available(tkv_device_page_allocator*, void* st
  * outside a pool, or more pairs than the capacity leave an empty list -- nothing moves, no
  * count changes, the flag is still published -- and *status = TKV_ERR_INVALID_CONFIG or
  * TKV_ERR_DIMENSION_MISMATCH (capacity).  Destination ids are NOT checked for duplicates here.
- * Not for transfer-buffer plans or per-layer tables.                                          */
+ * Not for transfer-buffer plans or per-layer tables.  tkv_plan_stats keeps describing the plan's
+ * capacity batch, not the device batch.                                                       */
 typedef struct TkvDeviceBatch {
     uint32_t n_seqs, table_stride, apply_refcounts, reserved;
     uint64_t seq_lens;            /* device u32 [n_seqs]                                          */

@@ -197,3 +197,45 @@ def test_config5_full_batch_and_its_head_shards(H):
     torch.cuda.synchronize()
     for l, want in zip((0, 79), whole):
         assert torch.equal(dst.blocks(l), want)
+
+
+def test_config4_full_batch_from_device_tables(H):
+    """The prefix-reuse batch at full size with the work list built on the device: the prefix comes from the device
+    index, the suffix pages from the device allocator, and the same properties hold as for the host-built plan."""
+    import torch
+    w = W.llama8b_prefix(pool_blocks=16384)
+    n, bs, pre = len(w.seq_lens), 16, 2048
+    src = H.Pool.allocate(0, 32, 8, 128, 16, 16384, "f16")
+    dst = H.Pool.allocate(0, 32, 8, 128, 16, 16384, "f16", refcounts=True, fill_byte=0x5A)
+    fill_source(src, w, 5)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(torch.int32).cuda()
+    rng = np.random.default_rng(6)
+    system = rng.integers(0, 32000, size=pre)
+    tok = np.zeros((n, int(w.seq_lens.max())), dtype=np.int32)
+    for q, m in enumerate(w.seq_lens):
+        tok[q, :pre] = system
+        tok[q, pre:int(m)] = rng.integers(0, 32000, size=int(m) - pre)
+    index, alloc = H.PrefixIndex(0, 1 << 16, bs), H.DevicePageAllocator(0, 16384)
+    pre_tab = torch.zeros((1, pre // bs), dtype=torch.int32, device="cuda")
+    alloc.allocate(pre_tab, i32([pre // bs]))                      # pages 0..127 hold the resident prefix
+    index.insert(i32(system[None, :]), i32([pre]), pre_tab)
+    lens, src_tables = i32(w.seq_lens), i32(w.src_tables.reshape(n, -1))
+    matched, pages = index.lookup(i32(tok), lens)
+    dst_tables = torch.zeros_like(src_tables)
+    k = min(pages.shape[1], dst_tables.shape[1])
+    dst_tables[:, :k] = pages[:, :k]
+    need = ((lens + (bs - 1)) // bs - matched).to(torch.int32)
+    alloc.allocate(dst_tables, need, matched)
+    plan = H.Plan.with_capacity(src, dst, int(need.sum().item()) + 64)
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    plan.enqueue_device_tables(lens, src_tables, dst_tables, (matched * bs).to(torch.int32), apply_refcounts=True, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(alloc.status.item()) == 0 and matched.tolist() == [128] * n
+    w.dst_tables = dst_tables.cpu().numpy().astype(np.uint32)      # what the device chose, for the property checks
+    assert_moved_blocks_equal(src, dst, w, 0x5A)
+    shared = torch.arange(128, device="cuda")
+    assert bool((dst.refcounts[shared] == n).all()) and int(dst.refcounts.sum()) == 128 * n
+    assert bool((dst.blocks(0).index_select(0, shared).view(torch.uint8) == 0x5A).all())      # nothing moved into the prefix
+    used = np.unique(w.dst_tables[np.arange(w.dst_tables.shape[1])[None, :] < ((w.seq_lens[:, None] + 15) // 16)])
+    assert used.size == 128 + int(need.sum().item())               # every suffix block got its own page
+    assert alloc.available() == 16384 - used.size
