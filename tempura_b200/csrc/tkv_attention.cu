@@ -757,7 +757,8 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     }
 }
 
-// merges the splits of one (sequence, query head); loads are issued eight splits at a time so their latencies overlap
+// merges the splits of one (sequence, query head): sixteen splits per round, every load of a round issued before any
+// is used (one memory round trip for up to sixteen splits), the running maximum carried from round to round
 __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const uint32_t kvh = head / a.group, g = head % a.group;
@@ -765,32 +766,32 @@ __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t live = ((kv_len + a.split_tokens - 1) / a.split_tokens) * a.parts_per_split;
     const float* base = a.partial + (((size_t)seq * a.n_kv_heads + kvh) * a.n_splits * a.group + g) * (D + 2);
     const size_t stride = (size_t)a.group * (D + 2);
-    // running max over the splits: every thread takes a strided share, then one reduction through shared memory
-    __shared__ float red[D / 32];
-    float mm = -INFINITY;
-    for (uint32_t s = d; s < live; s += D) mm = fmaxf(mm, __ldg(base + s * stride));
+    constexpr int R = 16;
+    float mm = -INFINITY, ll = 0.0f, acc = 0.0f;
+    for (uint32_t s0 = 0; s0 < live; s0 += R) {
+        float pm[R], pl[R], pa[R];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xFFFFFFFFu, mm, off));
-    if ((d & 31u) == 0) red[d >> 5] = mm;
-    __syncthreads();
-    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    float ll = 0.0f, acc = 0.0f;
-    for (uint32_t s0 = 0; s0 < live; s0 += 8) {
-        float pm[8], pl[8], pa[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < R; i++) {
             const bool in = s0 + i < live;
             const float* p = base + (size_t)(in ? s0 + i : 0) * stride;
-            pm[i] = in ? __ldg(p) : -INFINITY;
+            pm[i] = in ? __ldg(p) : -INFINITY;       // a part that saw no block also reports -inf
             pl[i] = __ldg(p + 1);
             pa[i] = __ldg(p + 2 + d);
         }
+        float m_new = mm;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float f = pm[i] == -INFINITY ? 0.0f : exp2f(pm[i] - mm);   // a part that saw no block, or padding of the group of 8
+        for (int i = 0; i < R; i++) m_new = fmaxf(m_new, pm[i]);
+        if (m_new == -INFINITY) continue;
+        const float keep = mm == -INFINITY ? 0.0f : fast_exp2(mm - m_new);
+        ll *= keep;
+        acc *= keep;
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const float f = fast_exp2(pm[i] - m_new);     // 2^-inf = 0
             ll += pl[i] * f;
             acc += pa[i] * f;
         }
+        mm = m_new;
     }
     a.out[((size_t)seq * a.n_q_heads + head) * D + d] = ll > 0.0f ? acc / ll : 0.0f;
 }
