@@ -750,17 +750,15 @@ def bench_admission(args) -> None:
     plan_dev = H.Plan.with_capacity(src, dst, pairs_cap)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     dst_tables = torch.zeros((n, stride), dtype=torch.int32, device="cuda")
+    matched_dev = torch.zeros(n, dtype=torch.int32, device="cuda")
 
     def device_path():
-        matched, pages = index.lookup(tokens, lens)
-        k = min(pages.shape[1], stride)
-        dst_tables[:, :k] = pages[:, :k]
-        need = ((lens + (bs - 1)) // bs - matched).to(torch.int32)
-        alloc.allocate(dst_tables, need, matched)
-        plan_dev.enqueue_device_tables(lens, src_tables, dst_tables, (matched * bs).to(torch.int32), apply_refcounts=True, status=status)
+        index.lookup(tokens, lens, out_pages=dst_tables, out_matched=matched_dev)
+        alloc.allocate(dst_tables, first=matched_dev, seq_lens=lens, block_size=bs)
+        plan_dev.enqueue_device_tables(lens, src_tables, dst_tables, prefix_blocks=matched_dev, apply_refcounts=True, status=status)
         torch.cuda.synchronize()
         # undo, outside what a server would do per admission: give the pages and the references back
-        alloc.free(dst_tables, need, matched)
+        alloc.free(dst_tables, first=matched_dev, seq_lens=lens, block_size=bs)
         index.release(tokens, lens)
         dst.refcounts.zero_()
         torch.cuda.synchronize()

@@ -484,7 +484,9 @@ typedef struct TkvPageBatch {
     uint32_t n_seqs, table_stride;
     uint64_t tables;              /* device u32 [n_seqs][table_stride]                            */
     uint64_t first;               /* device u32 [n_seqs] first entry of each row to fill; 0 = entry 0 */
-    uint64_t counts;              /* device u32 [n_seqs] pages per sequence                        */
+    uint64_t counts;              /* device u32 [n_seqs] pages per sequence; 0 = derive them:      */
+    uint64_t seq_lens;            /* device u32 [n_seqs] tokens: counts[s] = ceil(seq_lens[s] /    */
+    uint32_t block_size, reserved;/*   block_size) - first[s] (the blocks a lookup did not match)  */
 } TkvPageBatch;
 int32_t tkv_device_page_allocator_create(int32_t device, uint32_t total_pages, tkv_device_page_allocator** out);
 void tkv_device_page_allocator_destroy(tkv_device_page_allocator*);
@@ -509,10 +511,12 @@ int32_t tkv_device_page_allocator_available(tkv_device_page_allocator*, void* st
 typedef struct TkvDeviceBatch {
     uint32_t n_seqs, table_stride, apply_refcounts, reserved;
     uint64_t seq_lens;            /* device u32 [n_seqs]                                          */
-    uint64_t prefix_lens;         /* device u32 [n_seqs] tokens already resident; 0 = none        */
+    uint64_t prefix_lens;         /* device u32 [n_seqs] tokens already resident; 0 = none, or see prefix_blocks */
     uint64_t src_tables;          /* device u32 [n_seqs][table_stride]                            */
     uint64_t dst_tables;          /* device u32 [n_seqs][table_stride]                            */
     uint64_t status;              /* device u32 or 0                                              */
+    uint64_t prefix_blocks;       /* used when prefix_lens is 0: device u32 [n_seqs] BLOCKS already resident
+                                     (tkv_prefix_index_lookup's out_matched with group_tokens = block_size) */
 } TkvDeviceBatch;
 int32_t tkv_handoff_enqueue_device_tables(tkv_plan* plan, const TkvDeviceBatch* batch, void* stream, uint64_t done_flag, uint32_t flag_value);
 

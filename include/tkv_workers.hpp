@@ -302,45 +302,42 @@ private:
 };
 
 // Device arrays a batch admission works in; the caller owns them (all on the pools' device, u32):
-//   tokens [n][token_stride], seq_lens [n], src_tables / dst_tables [n][table_stride], matched / need / prefix_lens [n],
-//   status [2] (allocator, work list).  `need` and `prefix_lens` are filled by the caller's own small kernel or, as here,
-//   left to the caller: need[s] = ceil(seq_lens[s] / block) - matched[s], prefix_lens[s] = matched[s] * block.
+//   tokens [n][token_stride], seq_lens [n], src_tables / dst_tables [n][table_stride], matched [n], status [2]
+//   (allocator, work list).
 struct DeviceAdmissionBuffers {
-    uint64_t tokens = 0, seq_lens = 0, src_tables = 0, dst_tables = 0, matched = 0, need = 0, prefix_lens = 0, status = 0;
+    uint64_t tokens = 0, seq_lens = 0, src_tables = 0, dst_tables = 0, matched = 0, status = 0;
     uint32_t n_seqs = 0, token_stride = 0, table_stride = 0;
 };
 
-// DecodeWorker::receive_kv for a batch, with prefix resolution and page placement on the device.  `plan` is a plan over
-// (source pool, destination pool) made from a host batch at least as large as any batch admitted here.  `derive` is
-// called between the lookup and the allocation to fill `need` and `prefix_lens` from `matched` on the same stream
-// (a two-line kernel on the caller's side; this header holds no device code).
+// DecodeWorker::receive_kv for a batch, with prefix resolution and page placement on the device: three calls on one
+// stream, nothing copied to the host.  `plan` is a plan over (source pool, destination pool) made from a host batch at
+// least as large as any batch admitted here; the index's group_tokens must be the pools' block size.
 class DeviceKvReceiver {
 public:
-    DeviceKvReceiver(tkv_plan* plan, DevicePrefixIndex* index, DevicePageAllocator* pages, uint64_t flag)
-        : plan_(plan), index_(index), pages_(pages), flag_(flag) {}
+    DeviceKvReceiver(tkv_plan* plan, DevicePrefixIndex* index, DevicePageAllocator* pages, uint64_t flag, uint32_t block_size)
+        : plan_(plan), index_(index), pages_(pages), flag_(flag), block_size_(block_size) {}
 
-    template <typename Derive>
-    uint32_t adopt(const DeviceAdmissionBuffers& b, void* stream, Derive&& derive) {
+    uint32_t adopt(const DeviceAdmissionBuffers& b, void* stream) {
         TkvPrefixBatch pb{};
         pb.n_seqs = b.n_seqs;
         pb.stride = b.token_stride;
         pb.tokens = b.tokens;
         pb.lens = b.seq_lens;
-        index_->lookup(pb, b.dst_tables, b.table_stride, b.matched, stream);
-        derive(stream);
+        index_->lookup(pb, b.dst_tables, b.table_stride, b.matched, stream);      // matched pages at the head of each row
         TkvPageBatch pg{};
         pg.n_seqs = b.n_seqs;
         pg.table_stride = b.table_stride;
         pg.tables = b.dst_tables;
         pg.first = b.matched;
-        pg.counts = b.need;
+        pg.seq_lens = b.seq_lens;                                                  // the rest of each row
+        pg.block_size = block_size_;
         pages_->allocate(pg, b.status, stream);
         TkvDeviceBatch db{};
         db.n_seqs = b.n_seqs;
         db.table_stride = b.table_stride;
         db.apply_refcounts = 1;
         db.seq_lens = b.seq_lens;
-        db.prefix_lens = b.prefix_lens;
+        db.prefix_blocks = b.matched;
         db.src_tables = b.src_tables;
         db.dst_tables = b.dst_tables;
         db.status = b.status + 4;
@@ -354,6 +351,7 @@ private:
     DevicePrefixIndex* index_;
     DevicePageAllocator* pages_;
     uint64_t flag_;
+    uint32_t block_size_;
     uint32_t generation_ = 0;
 };
 

@@ -67,12 +67,13 @@ class TkvPrefixIndexStats(C.Structure):
 
 
 class TkvPageBatch(C.Structure):
-    _fields_ = [("n_seqs", C.c_uint32), ("table_stride", C.c_uint32), ("tables", C.c_uint64), ("first", C.c_uint64), ("counts", C.c_uint64)]
+    _fields_ = [("n_seqs", C.c_uint32), ("table_stride", C.c_uint32), ("tables", C.c_uint64), ("first", C.c_uint64), ("counts", C.c_uint64),
+                ("seq_lens", C.c_uint64), ("block_size", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class TkvDeviceBatch(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_seqs", "table_stride", "apply_refcounts", "reserved")] + [
-        (n, C.c_uint64) for n in ("seq_lens", "prefix_lens", "src_tables", "dst_tables", "status")]
+        (n, C.c_uint64) for n in ("seq_lens", "prefix_lens", "src_tables", "dst_tables", "status", "prefix_blocks")]
 
 
 class TkvCoordinatorConfig(C.Structure):

@@ -845,7 +845,8 @@ __global__ void __launch_bounds__(256) handoff_f32_cast_vec(const HandoffArgs a)
 // ---------------------------------------------------------------------------------
 struct DeviceTables {
     const uint32_t* seq_lens;
-    const uint32_t* prefix_lens;   // or null
+    const uint32_t* prefix_lens;   // tokens, or null
+    const uint32_t* prefix_blocks; // blocks, read when prefix_lens is null; or null
     const uint32_t* src_tables;
     const uint32_t* dst_tables;
     uint32_t* offsets;             // [n_seqs] scratch
@@ -855,6 +856,13 @@ struct DeviceTables {
     int32_t* refcounts;            // destination pool's, or null (no reference counting asked for)
     uint32_t n_seqs, table_stride, block_size, capacity, src_total_blocks, dst_total_blocks;
 };
+
+__device__ __forceinline__ uint32_t prefix_tokens_of(const DeviceTables& t, uint32_t q) {
+    if (t.prefix_lens) return t.prefix_lens[q];
+    if (!t.prefix_blocks) return 0u;
+    const uint32_t blocks = t.prefix_blocks[q];
+    return blocks > 0xFFFFFFFFu / t.block_size ? 0xFFFFFFFFu : blocks * t.block_size;      // an absurd count fails the prefix <= length check
+}
 
 __global__ void __launch_bounds__(1024) worklist_from_device_tables(const DeviceTables t) {
     __shared__ uint32_t scan[1024];
@@ -866,7 +874,7 @@ __global__ void __launch_bounds__(1024) worklist_from_device_tables(const Device
         const uint32_t q = q0 + tid;
         uint32_t cnt = 0;
         if (q < t.n_seqs) {
-            const uint32_t len = t.seq_lens[q], pre = t.prefix_lens ? t.prefix_lens[q] : 0u, nb = (len + bs - 1) / bs;
+            const uint32_t len = t.seq_lens[q], pre = prefix_tokens_of(t, q), nb = (len + bs - 1) / bs;
             if (pre > len || pre % bs || nb > t.table_stride) atomicExch(&err, 2u);
             else cnt = nb - pre / bs;
         }
@@ -889,7 +897,7 @@ __global__ void __launch_bounds__(1024) worklist_from_device_tables(const Device
     const uint32_t warp = tid >> 5, lane = tid & 31u;
     if (!err) {
         for (uint32_t q = warp; q < t.n_seqs; q += 32) {
-            const uint32_t len = t.seq_lens[q], pre_b = (t.prefix_lens ? t.prefix_lens[q] : 0u) / bs, nb = (len + bs - 1) / bs;
+            const uint32_t len = t.seq_lens[q], pre_b = (prefix_tokens_of(t, q)) / bs, nb = (len + bs - 1) / bs;
             const uint32_t* srow = t.src_tables + (size_t)q * t.table_stride;
             const uint32_t* drow = t.dst_tables + (size_t)q * t.table_stride;
             for (uint32_t i = lane; i < nb; i += 32) {
@@ -905,7 +913,7 @@ __global__ void __launch_bounds__(1024) worklist_from_device_tables(const Device
     __syncthreads();
     if (!err && t.refcounts) {                                       // RadixTree::lookup's count, one per sequence and shared block
         for (uint32_t q = warp; q < t.n_seqs; q += 32) {
-            const uint32_t pre_b = (t.prefix_lens ? t.prefix_lens[q] : 0u) / bs;
+            const uint32_t pre_b = (prefix_tokens_of(t, q)) / bs;
             for (uint32_t i = lane; i < pre_b; i += 32) atomicAdd(t.refcounts + t.dst_tables[(size_t)q * t.table_stride + i], 1);
         }
     }

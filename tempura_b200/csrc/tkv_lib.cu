@@ -891,6 +891,7 @@ int32_t tkv_handoff_enqueue_device_tables(tkv_plan* p, const TkvDeviceBatch* db,
     tkv::DeviceTables t{};
     t.seq_lens = reinterpret_cast<const uint32_t*>(db->seq_lens);
     t.prefix_lens = reinterpret_cast<const uint32_t*>(db->prefix_lens);
+    t.prefix_blocks = reinterpret_cast<const uint32_t*>(db->prefix_blocks);
     t.src_tables = reinterpret_cast<const uint32_t*>(db->src_tables);
     t.dst_tables = reinterpret_cast<const uint32_t*>(db->dst_tables);
     t.offsets = p->dev_scratch + 4;

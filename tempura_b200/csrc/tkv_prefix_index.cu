@@ -347,9 +347,16 @@ struct PageStack {
 struct PageBatch {
     uint32_t* tables;           // [n_seqs][stride]
     const uint32_t* first;      // [n_seqs] or null (0)
-    const uint32_t* counts;     // [n_seqs]
-    uint32_t n_seqs, stride;
+    const uint32_t* counts;     // [n_seqs], or null: ceil(seq_lens / block_size) - first
+    const uint32_t* seq_lens;
+    uint32_t n_seqs, stride, block_size;
 };
+
+__device__ __forceinline__ uint32_t pages_of(const PageBatch& b, uint32_t s) {
+    if (b.counts) return b.counts[s];
+    const uint32_t nb = (b.seq_lens[s] + b.block_size - 1) / b.block_size, f = b.first ? b.first[s] : 0u;
+    return nb > f ? nb - f : 0u;
+}
 
 __global__ void page_stack_init(PageStack st) {
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < st.total; i += gridDim.x * blockDim.x) st.ids[i] = st.total - 1u - i;
@@ -367,7 +374,7 @@ __global__ void __launch_bounds__(1024) page_stack_batch(PageStack st, PageBatch
     // pass 1: validate rows and total the request
     for (uint32_t s0 = 0; s0 < b.n_seqs; s0 += 1024) {
         const uint32_t s = s0 + t;
-        const uint32_t c = s < b.n_seqs ? b.counts[s] : 0u, f = (s < b.n_seqs && b.first) ? b.first[s] : 0u;
+        const uint32_t c = s < b.n_seqs ? pages_of(b, s) : 0u, f = (s < b.n_seqs && b.first) ? b.first[s] : 0u;
         if (c && ((unsigned long long)f + c > b.stride)) atomicExch(&bad, 1u);
         scan[t] = c;
         __syncthreads();
@@ -393,7 +400,7 @@ __global__ void __launch_bounds__(1024) page_stack_batch(PageStack st, PageBatch
     __syncthreads();
     for (uint32_t s0 = 0; s0 < b.n_seqs; s0 += 1024) {
         const uint32_t s = s0 + t;
-        const uint32_t c = s < b.n_seqs ? b.counts[s] : 0u;
+        const uint32_t c = s < b.n_seqs ? pages_of(b, s) : 0u;
         scan[t] = c;
         __syncthreads();
         for (uint32_t off = 1; off < 1024; off <<= 1) {                              // inclusive scan
@@ -611,11 +618,14 @@ namespace {
 int32_t page_batch(tkv_device_page_allocator* a, const TkvPageBatch* batch, uint64_t status, void* stream, bool release) {
     if (!a || !batch) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
     if (batch->n_seqs == 0) return TKV_OK;
-    if (!batch->tables || !batch->counts || batch->table_stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "page batch: NULL tables / counts or zero stride");
+    if (!batch->tables || batch->table_stride == 0) return fail(TKV_ERR_INVALID_CONFIG, "page batch: NULL tables or zero stride");
+    if (!batch->counts && (!batch->seq_lens || batch->block_size == 0))
+        return fail(TKV_ERR_INVALID_CONFIG, "page batch: give counts, or seq_lens and block_size to derive them");
     DeviceGuard guard(a->device);
     if (guard.err != cudaSuccess) return fail_cuda(guard.err, "cudaSetDevice");
     PageBatch b{reinterpret_cast<uint32_t*>(batch->tables), reinterpret_cast<const uint32_t*>(batch->first),
-                reinterpret_cast<const uint32_t*>(batch->counts), batch->n_seqs, batch->table_stride};
+                reinterpret_cast<const uint32_t*>(batch->counts), reinterpret_cast<const uint32_t*>(batch->seq_lens),
+                batch->n_seqs, batch->table_stride, batch->block_size};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (release) page_stack_batch<true><<<1, 1024, 0, st>>>(a->st, b, reinterpret_cast<uint32_t*>(status));
     else page_stack_batch<false><<<1, 1024, 0, st>>>(a->st, b, reinterpret_cast<uint32_t*>(status));

@@ -253,18 +253,19 @@ class Plan:
     def enqueue_device_tables(self, seq_lens: torch.Tensor, src_tables: torch.Tensor, dst_tables: torch.Tensor,
                               prefix_lens: Optional[torch.Tensor] = None, apply_refcounts: bool = False,
                               status: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None,
-                              done_flag: int = 0, flag_value: int = 0) -> None:
+                              done_flag: int = 0, flag_value: int = 0, prefix_blocks: Optional[torch.Tensor] = None) -> None:
         """The handoff with its work list built on the device from int32 tensors ``seq_lens [n]``, ``src_tables`` /
         ``dst_tables [n, stride]`` and optional ``prefix_lens [n]`` (as the device prefix index and page allocator
-        leave them); ``status`` (device int32) receives 0 or an error code."""
-        for t in (seq_lens, src_tables, dst_tables, prefix_lens, status):
+        leave them; ``prefix_blocks [n]`` gives the resident prefix in blocks instead); ``status`` (device int32) receives 0 or
+        an error code."""
+        for t in (seq_lens, src_tables, dst_tables, prefix_lens, status, prefix_blocks):
             assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous())
         assert src_tables.shape == dst_tables.shape and src_tables.shape[0] == seq_lens.numel()
         if stream is None:
             stream = torch.cuda.current_stream(self.launch_device)
         b = N.TkvDeviceBatch(src_tables.shape[0], src_tables.shape[1], 1 if apply_refcounts else 0, 0, seq_lens.data_ptr(),
                              prefix_lens.data_ptr() if prefix_lens is not None else 0, src_tables.data_ptr(), dst_tables.data_ptr(),
-                             status.data_ptr() if status is not None else 0)
+                             status.data_ptr() if status is not None else 0, prefix_blocks.data_ptr() if prefix_blocks is not None else 0)
         check(lib().tkv_handoff_enqueue_device_tables(self._h, C.byref(b), C.c_void_p(stream.cuda_stream), done_flag, flag_value))
 
     def refcount_apply(self, delta: int, stream: Optional[torch.cuda.Stream] = None) -> None:
@@ -461,15 +462,20 @@ class PrefixIndex:
         b = self._batch(tokens, lens, pages, page_lens)
         check(lib().tkv_prefix_index_insert(self._h, C.byref(b), self._stream(stream)))
 
-    def lookup(self, tokens, lens, stream=None):
+    def lookup(self, tokens, lens, stream=None, out_pages: Optional[torch.Tensor] = None, out_matched: Optional[torch.Tensor] = None):
         """Returns ``(matched, pages)``: int32 ``[n_seqs]`` matched nodes and int32 ``[n_seqs, nodes]`` page
-        ids (-1 where a matched node has no page or past the match)."""
+        ids (-1 where a matched node has no page or past the match).  With ``out_pages`` (say the destination block
+        tables) the pages of the matched nodes are written at the head of its rows and the rest is left alone."""
         b = self._batch(tokens, lens)
-        n_nodes = max(tokens.shape[1] // self.group_tokens, 1)
-        pages = torch.full((tokens.shape[0], n_nodes), -1, dtype=torch.int32, device=tokens.device)
-        matched = torch.zeros(tokens.shape[0], dtype=torch.int32, device=tokens.device)
-        check(lib().tkv_prefix_index_lookup(self._h, C.byref(b), pages.data_ptr(), n_nodes, matched.data_ptr(), self._stream(stream)))
-        return matched, pages
+        if out_pages is None:
+            n_nodes = max(tokens.shape[1] // self.group_tokens, 1)
+            out_pages = torch.full((tokens.shape[0], n_nodes), -1, dtype=torch.int32, device=tokens.device)
+        if out_matched is None:
+            out_matched = torch.zeros(tokens.shape[0], dtype=torch.int32, device=tokens.device)
+        assert out_pages.dtype == torch.int32 and out_pages.is_contiguous() and out_pages.shape[0] == tokens.shape[0]
+        check(lib().tkv_prefix_index_lookup(self._h, C.byref(b), out_pages.data_ptr(), out_pages.shape[1], out_matched.data_ptr(),
+                                            self._stream(stream)))
+        return out_matched, out_pages
 
     def release(self, tokens, lens, stream=None) -> None:
         b = self._batch(tokens, lens)
@@ -513,19 +519,21 @@ class DevicePageAllocator:
         except Exception:
             pass
 
-    def _call(self, fn, tables, counts, first, stream):
-        for t in (tables, counts, first):
+    def _call(self, fn, tables, counts, first, stream, seq_lens, block_size):
+        for t in (tables, counts, first, seq_lens):
             assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and t.device.index == self.device)
-        b = N.TkvPageBatch(tables.shape[0], tables.shape[1], tables.data_ptr(), first.data_ptr() if first is not None else 0, counts.data_ptr())
+        b = N.TkvPageBatch(tables.shape[0], tables.shape[1], tables.data_ptr(), first.data_ptr() if first is not None else 0,
+                           counts.data_ptr() if counts is not None else 0, seq_lens.data_ptr() if seq_lens is not None else 0, block_size, 0)
         st = C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
         check(fn(self._h, C.byref(b), self.status.data_ptr(), st))
 
-    def allocate(self, tables, counts, first=None, stream=None) -> None:
-        """Fills ``tables[s, first[s] : first[s] + counts[s]]``; ``self.status`` (device int32) is 0 or an error code."""
-        self._call(lib().tkv_device_page_allocator_allocate, tables, counts, first, stream)
+    def allocate(self, tables, counts=None, first=None, stream=None, seq_lens=None, block_size: int = 16) -> None:
+        """Fills ``tables[s, first[s] : first[s] + counts[s]]``; without ``counts`` a row gets the blocks of ``seq_lens[s]``
+        tokens that ``first[s]`` does not cover.  ``self.status`` (device int32) is 0 or an error code."""
+        self._call(lib().tkv_device_page_allocator_allocate, tables, counts, first, stream, seq_lens, block_size)
 
-    def free(self, tables, counts, first=None, stream=None) -> None:
-        self._call(lib().tkv_device_page_allocator_free, tables, counts, first, stream)
+    def free(self, tables, counts=None, first=None, stream=None, seq_lens=None, block_size: int = 16) -> None:
+        self._call(lib().tkv_device_page_allocator_free, tables, counts, first, stream, seq_lens, block_size)
 
     def available(self, stream=None) -> int:
         out = C.c_uint32()

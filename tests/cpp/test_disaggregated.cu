@@ -384,14 +384,6 @@ static void test_errors(int da, int db) {
     REQUIRE(receiver.adopt(t, r.stream_a).size() == 2);
 }
 
-// what the receiver leaves to its caller between the lookup and the allocation: pages still needed, tokens resident
-__global__ void derive_need(const uint32_t* seq_lens, const uint32_t* matched, uint32_t* need, uint32_t* prefix_lens, uint32_t n, uint32_t bs) {
-    uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= n) return;
-    need[s] = (seq_lens[s] + bs - 1) / bs - matched[s];
-    prefix_lens[s] = matched[s] * bs;
-}
-
 // The decode side's admission with the prefix index and the page allocator in device memory: the second prompt
 // shares its first two blocks with the first one, so it adopts those pages (reference count 1) and moves the rest.
 static void test_device_admission(int da) {
@@ -412,19 +404,17 @@ static void test_device_admission(int da) {
     cap.dst_tables = ident.data();
     tkv_plan* plan = nullptr;
     check(tkv_plan_create(r.a.pool.get(), r.b.pool.get(), &cap, nullptr, TKV_PLAN_DEFAULT, &plan));
-    DeviceKvReceiver receiver(plan, &index, &pages, (uint64_t)r.flag);
+    DeviceKvReceiver receiver(plan, &index, &pages, (uint64_t)r.flag, bs);
 
     std::vector<uint32_t> first = prompt_of(40, 3), second(first.begin(), first.begin() + 32);
     for (uint32_t t : prompt_of(18, 9)) second.push_back(t);
     GpuPrefillWorker prefill(&r.model, &r.a, &r.pages_a);
-    uint32_t *d_tokens, *d_len, *d_src, *d_dst, *d_matched, *d_need, *d_prefix, *d_status;
+    uint32_t *d_tokens, *d_len, *d_src, *d_dst, *d_matched, *d_status;
     CUDA_OK(cudaMalloc((void**)&d_tokens, 64 * 4));
     CUDA_OK(cudaMalloc((void**)&d_len, 4));
     CUDA_OK(cudaMalloc((void**)&d_src, stride * 4));
     CUDA_OK(cudaMalloc((void**)&d_dst, stride * 4));
     CUDA_OK(cudaMalloc((void**)&d_matched, 4));
-    CUDA_OK(cudaMalloc((void**)&d_need, 4));
-    CUDA_OK(cudaMalloc((void**)&d_prefix, 4));
     CUDA_OK(cudaMalloc((void**)&d_status, 8));
     std::vector<uint32_t> first_table;
     for (int round = 0; round < 2; round++) {
@@ -444,15 +434,11 @@ static void test_device_admission(int da) {
         b.src_tables = (uint64_t)d_src;
         b.dst_tables = (uint64_t)d_dst;
         b.matched = (uint64_t)d_matched;
-        b.need = (uint64_t)d_need;
-        b.prefix_lens = (uint64_t)d_prefix;
         b.status = (uint64_t)d_status;
         b.n_seqs = 1;
         b.token_stride = 64;
         b.table_stride = stride;
-        const uint32_t gen = receiver.adopt(b, r.stream_a, [&](void* st) {
-            derive_need<<<1, 32, 0, (cudaStream_t)st>>>(d_len, d_matched, d_need, d_prefix, 1, bs);
-        });
+        const uint32_t gen = receiver.adopt(b, r.stream_a);
         check(tkv_flag_wait_host(da, (uint64_t)r.flag, gen, 10'000'000));
         uint32_t status[2], matched = 99;
         std::vector<uint32_t> table(stride);
@@ -491,7 +477,7 @@ static void test_device_admission(int da) {
     TkvPrefixIndexStats st = index.stats(r.stream_a);
     REQUIRE(st.live_nodes == 2 + 1 && st.hits == 1 && st.tokens_saved == 32);
     tkv_plan_destroy(plan);
-    for (void* p : {(void*)d_tokens, (void*)d_len, (void*)d_src, (void*)d_dst, (void*)d_matched, (void*)d_need, (void*)d_prefix, (void*)d_status})
+    for (void* p : {(void*)d_tokens, (void*)d_len, (void*)d_src, (void*)d_dst, (void*)d_matched, (void*)d_status})
         cudaFree(p);
 }
 

@@ -140,17 +140,14 @@ def test_admission_without_a_host_round_trip(H):
     for q, p in enumerate(prompts):
         tok[q, :len(p)] = p
     lens_t = dev_i32(lens)
-    matched, pages = ix.lookup(dev_i32(tok), lens_t)
     dst_tables = torch.full((n, stride), -1, dtype=torch.int32, device="cuda")
-    k = min(pages.shape[1], stride)
-    dst_tables[:, :k] = pages[:, :k]                                 # matched nodes' pages; the rest is overwritten below or unused
-    need = (lens_t + (bs - 1)) // bs - matched
-    alloc.allocate(dst_tables, need.to(torch.int32), matched)
+    matched, _ = ix.lookup(dev_i32(tok), lens_t, out_pages=dst_tables)     # matched nodes' pages at the head of each row
+    alloc.allocate(dst_tables, first=matched, seq_lens=lens_t, block_size=bs)   # the rest of each row
     hs2, hd2 = host_pools(w)
     src, dst = to_device_pool(hs2, "f16"), to_device_pool(hd2, "f16", refcounts=np.zeros(total, dtype=np.int32))
     plan = H.Plan.with_capacity(src, dst, n * stride)
     status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
-    plan.enqueue_device_tables(lens_t, dev_i32(w.src_tables.reshape(n, -1)[:, :stride]), dst_tables, (matched * bs).to(torch.int32),
+    plan.enqueue_device_tables(lens_t, dev_i32(w.src_tables.reshape(n, -1)[:, :stride]), dst_tables, prefix_blocks=matched,
                                apply_refcounts=True, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and int(alloc.status.item()) == 0
