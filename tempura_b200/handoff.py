@@ -540,3 +540,18 @@ class DevicePageAllocator:
         st = C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
         check(lib().tkv_device_page_allocator_available(self._h, st, C.byref(out)))
         return int(out.value)
+
+
+def causal_chunk_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.Tensor, start_pos: int,
+                           sm_scale: Optional[float] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Causal attention of ``T`` consecutive new tokens of ONE sequence over the paged pool (their K/V rows already
+    written at positions ``start_pos .. start_pos + T - 1``): query token ``t`` attends to positions ``0 .. start_pos + t``.
+    ``q`` is f32 ``[T, n_q_heads, head_dim]``, ``table_row`` the sequence's int32 block table.  Each query token is one
+    row of the decode kernel (the rows share the table and differ in length), which is the right shape for a few
+    tokens at a time -- speculative verification, short prefill chunks -- and reads the scaled E4M3 pool exactly as
+    decode does; it is not a prefill-throughput kernel (K/V is fetched once per query token, mostly from L2).
+    (cutile_flash_attn_heads_paged_e4m3, kernels/src/cutile_flash_attention.rs:868, is the reference's unscaled form.)"""
+    t = q.shape[0]
+    tables = table_row.reshape(1, -1).expand(t, -1).contiguous()
+    kv_lens = torch.arange(start_pos + 1, start_pos + t + 1, dtype=torch.int32, device=q.device)
+    return decode_attention(pool, layer, q, tables, kv_lens, sm_scale, max_kv_len=start_pos + t, stream=stream)

@@ -186,3 +186,23 @@ def test_attention_argument_errors(H):
     with pytest.raises(N.TkvError) as e:
         H.decode_attention(pool, 0, torch.zeros((1, 8, 128), device="cuda"), t, n, max_kv_len=40)
     assert e.value.code == N.ERR_DIMENSION_MISMATCH          # table too short for max_kv_len
+
+
+def test_causal_chunk_of_new_tokens_matches_oracle(H):
+    """A few new tokens of one sequence at once (speculative verification, a short prefill chunk): token t sees
+    positions 0 .. start + t.  Checked against the oracle run once per query token with that length."""
+    import torch
+    lens = np.array([300], dtype=np.uint32)
+    w = W.Workload("attn-chunk", 1, 8, 128, 16, 64, 64, lens, dst_dtype="e4m3", outlier_channels=(5,), outlier_gain=20.0, seed=67).build_tables()
+    hs, hd, dd = quantized_pool(H, w)
+    start, t = 300 - 7, 7
+    q = torch.randn((t, 32, 128), generator=torch.Generator().manual_seed(13)).cuda()
+    row = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()[0]
+    got = H.causal_chunk_attention(dd, 0, q, row, start).cpu().numpy()
+    tables = np.repeat(w.dst_tables.reshape(1, -1), t, axis=0)
+    kv = np.arange(start + 1, start + t + 1, dtype=np.uint32)
+    want = oracle.paged_decode_attention(hd, 0, q.cpu().numpy(), tables, kv, 1.0 / np.sqrt(128.0))
+    close(got, want, v_max_per_dim(hs, 0))
+    # the last row is plain decode attention over the whole sequence
+    one = H.decode_attention(dd, 0, q[-1:].contiguous(), row.reshape(1, -1), torch.tensor([300], dtype=torch.int32).cuda())
+    assert torch.equal(one.cpu(), torch.from_numpy(got[-1:]))
