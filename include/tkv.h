@@ -519,6 +519,12 @@ typedef struct TkvDeviceBatch {
                                      (tkv_prefix_index_lookup's out_matched with group_tokens = block_size) */
 } TkvDeviceBatch;
 int32_t tkv_handoff_enqueue_device_tables(tkv_plan* plan, const TkvDeviceBatch* batch, void* stream, uint64_t done_flag, uint32_t flag_value);
+/* The prefix reference counts of a device batch alone (+1 or -1 per sequence and shared block, never below zero),
+ * launched on the pool's own device: for a destination pool on a peer GPU, whose counts the prefill side's
+ * handoff does not touch (apply_refcounts is for same-device plans), and for giving the references back.
+ * Reads dst_tables and prefix_lens or prefix_blocks of `batch`; ids outside the pool are skipped and set
+ * *status = TKV_ERR_INVALID_CONFIG.                                                                          */
+int32_t tkv_refcount_apply_device_tables(const TkvPool* dst, const TkvDeviceBatch* batch, int32_t delta, void* stream);
 
 /* ---- handoff coordinator (host logic, no CUDA) --------------------------------- */
 /* The bookkeeping a disaggregated server keeps around the handoff: which prefill worker takes a

@@ -195,6 +195,7 @@ SIGNATURES = {
     "tkv_device_page_allocator_free": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),
     "tkv_device_page_allocator_available": (_i32, [_vp, _vp, _u32p]),
     "tkv_handoff_enqueue_device_tables": (_i32, [_vp, C.POINTER(TkvDeviceBatch), _vp, _u64, _u32]),
+    "tkv_refcount_apply_device_tables": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvDeviceBatch), _i32, _vp]),
     "tkv_coordinator_new": (_vp, [C.POINTER(TkvCoordinatorConfig)]),
     "tkv_coordinator_delete": (None, [_vp]),
     "tkv_coordinator_set_headroom": (_i32, [_vp, _u32, _u64]),

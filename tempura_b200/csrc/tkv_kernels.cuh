@@ -939,6 +939,36 @@ __global__ void refcount_apply_kernel(uint32_t* refcounts, const uint32_t* ids, 
     }
 }
 
+// The shared-prefix reference counts of a device batch, applied by the pool's own device: one warp per sequence over the
+// first prefix_blocks[q] (or prefix_lens[q] / block_size) entries of its destination table row.  Ids outside the pool
+// are skipped and reported through `status`.
+__global__ void __launch_bounds__(256) refcount_apply_tables_kernel(uint32_t* refcounts, const uint32_t* dst_tables, const uint32_t* prefix_lens,
+                                                                    const uint32_t* prefix_blocks, uint32_t n_seqs, uint32_t table_stride,
+                                                                    uint32_t block_size, uint32_t total_blocks, int delta, uint32_t* status) {
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t q = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; q < n_seqs; q += warps) {
+        const uint32_t pre = min(prefix_lens ? prefix_lens[q] / block_size : prefix_blocks[q], table_stride);
+        for (uint32_t i = lane; i < pre; i += 32) {
+            const uint32_t id = dst_tables[(size_t)q * table_stride + i];
+            if (id >= total_blocks) {
+                if (status) atomicExch(status, 2u);
+                continue;
+            }
+            uint32_t* p = refcounts + id;
+            if (delta > 0) {
+                atomicAdd(p, 1u);
+            } else {
+                uint32_t old = *p;
+                while (old != 0u) {
+                    const uint32_t seen = atomicCAS(p, old, old - 1u);
+                    if (seen == old) break;
+                    old = seen;
+                }
+            }
+        }
+    }
+}
+
 // Bounded wait: gives up after max_spins polls and records a status instead of
 // spinning forever.
 __global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, unsigned long long max_spins,

@@ -1004,6 +1004,23 @@ int32_t tkv_refcount_apply(tkv_plan* p, int32_t delta, void* stream) {
     return TKV_OK;
 }
 
+int32_t tkv_refcount_apply_device_tables(const TkvPool* dst, const TkvDeviceBatch* b, int32_t delta, void* stream) {
+    if (!dst || !b) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (!dst->refcounts) return fail(TKV_ERR_INVALID_CONFIG, "destination pool has no refcount array");
+    if (delta == 0 || b->n_seqs == 0) return TKV_OK;
+    if (!b->dst_tables || b->table_stride == 0 || (!b->prefix_lens && !b->prefix_blocks) || dst->block_size == 0)
+        return fail(TKV_ERR_INVALID_CONFIG, "device tables: need dst_tables and prefix_lens or prefix_blocks");
+    DeviceGuard g(dst->device);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", dst->device);
+    const uint32_t blocks = std::min<uint32_t>((b->n_seqs + 7) / 8, 1024);
+    tkv::refcount_apply_tables_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<uint32_t*>(dst->refcounts), reinterpret_cast<const uint32_t*>(b->dst_tables),
+        reinterpret_cast<const uint32_t*>(b->prefix_lens), reinterpret_cast<const uint32_t*>(b->prefix_blocks), b->n_seqs, b->table_stride,
+        dst->block_size, dst->total_blocks, delta, reinterpret_cast<uint32_t*>(b->status));
+    CU(cudaGetLastError());
+    return TKV_OK;
+}
+
 int32_t tkv_pairing_make(int32_t n_gpus, uint32_t n_layers, uint32_t n_kv_heads, TkvPairing* out, int32_t cap,
                          int32_t* n_pairs) {
     if (!out || !n_pairs) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");

@@ -542,6 +542,19 @@ class DevicePageAllocator:
         return int(out.value)
 
 
+def refcount_apply_device_tables(dst: Pool, dst_tables: torch.Tensor, prefix_blocks: torch.Tensor, delta: int,
+                                 status: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """+1 / -1 on ``dst``'s reference counts for the first ``prefix_blocks[q]`` entries of every row of ``dst_tables``
+    (int32 device tensors), launched on the pool's device."""
+    for t in (dst_tables, prefix_blocks, status):
+        assert t is None or (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous())
+    b = N.TkvDeviceBatch(dst_tables.shape[0], dst_tables.shape[1], 0, 0, 0, 0, 0, dst_tables.data_ptr(),
+                         status.data_ptr() if status is not None else 0, prefix_blocks.data_ptr())
+    s = dst.c_struct()
+    st = stream or torch.cuda.current_stream(dst.device)
+    check(lib().tkv_refcount_apply_device_tables(C.byref(s), C.byref(b), delta, C.c_void_p(st.cuda_stream)))
+
+
 def causal_chunk_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.Tensor, start_pos: int,
                            sm_scale: Optional[float] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Causal attention of ``T`` consecutive new tokens of ONE sequence over the paged pool (their K/V rows already

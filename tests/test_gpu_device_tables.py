@@ -208,3 +208,22 @@ def test_index_and_allocator_edge_cases(H):
     assert int(alloc.status.item()) == 0 and alloc.available() == 0 and sorted(t.flatten().tolist()) == list(range(8))
     alloc.allocate(t, torch.tensor([1, 0], dtype=torch.int32, device="cuda"))
     assert int(alloc.status.item()) == N.ERR_POOL_EXHAUSTED
+
+
+def test_refcounts_from_device_tables_up_and_down(H):
+    import torch
+    dst = H.Pool.allocate(0, 1, 4, 64, 16, 64, "f16", refcounts=True)
+    dst.refcounts.zero_()
+    tables = dev_i32([[3, 4, 5, 9], [3, 4, 7, 8], [60, 61, 62, 63]])
+    pre = dev_i32([2, 3, 0])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    H.refcount_apply_device_tables(dst, tables, pre, +1, status)
+    want = np.zeros(64, dtype=np.int32)
+    want[[3, 4]] = 2
+    want[7] = 1
+    assert np.array_equal(dst.refcounts.cpu().numpy(), want) and int(status.item()) == 0
+    H.refcount_apply_device_tables(dst, tables, pre, -1)
+    H.refcount_apply_device_tables(dst, tables, pre, -1)             # never below zero
+    assert int(dst.refcounts.abs().sum()) == 0
+    H.refcount_apply_device_tables(dst, dev_i32([[64, 1]]), dev_i32([2]), +1, status)     # id 64 is outside the pool
+    assert int(status.item()) == N.ERR_INVALID_CONFIG and int(dst.refcounts[1]) == 1

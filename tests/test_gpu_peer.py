@@ -100,3 +100,65 @@ def test_peer_handoff_from_device_tables(H):
     assert int(status.item()) == 0 and plan.stats().peer == 1
     with torch.cuda.device(1):
         assert_pool_equals_host(dst, hd, "peer device tables")
+
+
+def test_peer_admission_on_the_decode_gpu_handoff_from_the_prefill_gpu(H):
+    """Two GPUs: the decode GPU resolves the prefix, places the pages and counts the references in its own memory;
+    the prefill GPU's handoff builds its work list from those tables over NVLink and stores into the decode pool."""
+    import torch
+    from oracle.prefix_oracle import PageStackOracle
+    rng = np.random.default_rng(57)
+    bs, n, total = 16, 5, 256
+    system = rng.integers(0, 32000, size=48).tolist()                # 3 blocks resident on the decode side
+    lens = rng.integers(60, 150, size=n)
+    prompts = [system + rng.integers(0, 32000, size=int(m) - 48).tolist() for m in lens]
+    w = W.Workload("peer-admit", 2, 8, 128, 16, total, total, lens.astype(np.uint32), seed=57).build_tables()
+    stride = w.table_stride
+    hs, hd = host_pools(w)
+    src = to_device_pool(hs, "f16", device=0)
+    dst = to_device_pool(hd, "f16", device=1, refcounts=np.zeros(total, dtype=np.int32))
+    d1 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(torch.int32).to("cuda:1")
+    d0 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(torch.int32).to("cuda:0")
+    tok = np.zeros((n, int(lens.max())), dtype=np.int32)
+    for q, p in enumerate(prompts):
+        tok[q, :len(p)] = p
+    with torch.cuda.device(1):
+        alloc, ix = H.DevicePageAllocator(1, total), H.PrefixIndex(1, 2048, bs)
+        pre_tab = torch.full((1, 3), -1, dtype=torch.int32, device="cuda:1")
+        alloc.allocate(pre_tab, d1([3]))
+        ix.insert(d1([system]), d1([48]), pre_tab)
+        lens1 = d1(lens)
+        dst_tables = torch.full((n, stride), -1, dtype=torch.int32, device="cuda:1")
+        matched, _ = ix.lookup(d1(tok), lens1, out_pages=dst_tables)
+        alloc.allocate(dst_tables, first=matched, seq_lens=lens1, block_size=bs)
+        H.refcount_apply_device_tables(dst, dst_tables, matched, +1)
+        ready = torch.cuda.Event()
+        ready.record()
+    plan = H.Plan.with_capacity(src, dst, n * stride)
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda:0")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda:1")
+    with torch.cuda.device(0):
+        s0 = torch.cuda.current_stream(0)
+        s0.wait_event(ready)                                          # the tables are complete before the prefill GPU reads them
+        plan.enqueue_device_tables(d0(lens), d0(w.src_tables.reshape(n, -1)), dst_tables, prefix_blocks=matched, status=status,
+                                   done_flag=flag.data_ptr(), flag_value=11)
+    H.flag_wait_host(1, flag.data_ptr(), 11, 10_000_000)
+    assert int(status.item()) == 0 and int(alloc.status.item()) == 0 and matched.tolist() == [3] * n
+    ref = PageStackOracle(total)
+    resident = ref.batch_allocate([3])[0]
+    fresh = ref.batch_allocate([(int(m) + bs - 1) // bs - 3 for m in lens])
+    want = np.zeros((n, stride), dtype=np.uint32)
+    for q in range(n):
+        want[q, :3] = resident
+        want[q, 3:3 + len(fresh[q])] = fresh[q]
+    got = dst_tables.cpu().numpy()
+    for q in range(n):
+        nb = (int(lens[q]) + bs - 1) // bs
+        assert got[q, :nb].tolist() == want[q, :nb].tolist()
+    w.dst_tables, w.prefix_lens = want, np.full(n, 48, dtype=np.uint32)
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    with torch.cuda.device(1):
+        assert_pool_equals_host(dst, hd, "peer admission")
+        rc = np.zeros(total, dtype=np.int32)
+        rc[resident] = n
+        assert np.array_equal(dst.refcounts.cpu().numpy(), rc)
