@@ -745,10 +745,8 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                         pr[1] = l2[h];
                     }
 #pragma unroll
-                    for (int t = 0; t < 8; t++) {
-                        pr[2 + 16 * grp + 2 * t] = o[t][h];
-                        pr[2 + 16 * grp + 2 * t + 1] = o[t][2 + h];
-                    }
+                    for (int t = 0; t < 8; t++)          // a partial row is 8-byte aligned (130 floats per row, 2 ahead of the dims)
+                        *reinterpret_cast<float2*>(pr + 2 + 16 * grp + 2 * t) = make_float2(o[t][h], o[t][2 + h]);
                 }
             }
         } else if (lane == 0 && a.status) {
@@ -836,7 +834,7 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
                     (unsigned long long)((d->max_kv_len + BS - 1) / BS), (unsigned long long)d->table_stride);
     const uint32_t es = pool->dtype == TKV_DTYPE_E4M3 ? 1u : 2u;
     const uint64_t kp = pool->k_layer_ptrs[d->layer], vp = pool->v_layer_ptrs[d->layer];
-    if ((kp | vp | d->q) % 16) return fail(TKV_ERR_INVALID_CONFIG, "layer tensors and q must be 16-byte aligned");
+    if ((kp | vp | d->q | d->scratch) % 16) return fail(TKV_ERR_INVALID_CONFIG, "layer tensors, q and scratch must be 16-byte aligned");
     // whole-block form when a CTA can hold every kv head of a block (and the scale rows are bulk-copy sized)
     const uint32_t row_bytes = pool->n_kv_heads * D * es, stage_bytes = 2u * BS * row_bytes + 128u;
     const bool whole_blocks = pool->n_kv_heads <= (uint32_t)MAX_KV_HEADS_PER_CTA && (!pool->k_scales || pool->n_kv_heads % 4 == 0) &&
