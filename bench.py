@@ -587,7 +587,14 @@ def run_attention(args):
     import torch
     from tempura_b200 import handoff as H
     torch.cuda.set_device(0)
-    w = pick_workload("cfg3", 1, args.pool_blocks or 4096, layers=args.layers)
+    if args.attn_seqs:              # a wider batch of the same length distribution (how the kernel scales with bytes per launch)
+        from tempura_b200 import workloads as W
+        w = W.llama8b_fp8(pool_blocks=args.pool_blocks or 256 * args.attn_seqs + 64, n_seqs=args.attn_seqs)
+        if args.layers:
+            w.n_layers = args.layers
+            w.name += f"-{args.layers}layers"
+    else:
+        w = pick_workload("cfg3", 1, args.pool_blocks or 4096, layers=args.layers)
     fp8 = not args.attn_f16
     src = H.Pool.allocate(0, w.n_layers, 8, 128, 16, w.src_blocks, "f16")
     fill_source(src, w, 77)
@@ -823,6 +830,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefix", "admit"])
     ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
+    ap.add_argument("--attn-seqs", type=int, default=None, help="--workload attn: this many prompts instead of the configuration's 16")
     ap.add_argument("--attn-per-head", action="store_true", help="--workload attn: the per-(sequence, kv head) CTA form")
     ap.add_argument("--attn-f16", action="store_true", help="--workload attn: read the F16 pool instead of the E4M3 one")
     ap.add_argument("--pool-blocks", type=int, default=None)

@@ -17,6 +17,8 @@
 // wants it and the permutation is undone once, at the output.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <cmath>
 #include <stdint.h>
 
 #include <algorithm>
@@ -841,15 +843,24 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
                               !(d->flags & TKV_ATTN_PER_HEAD_CTAS) && 256u + 2u * stage_bytes <= 200u * 1024u;
     uint32_t split_tokens = d->split_tokens ? d->split_tokens : DEFAULT_SPLIT_TOKENS;
     if (!d->split_tokens && d->total_kv_tokens) {
-        // one CTA per SM in the whole-block form: pick the token range so that the batch is ONE wave of CTAs
-        // (sum over sequences of ceil(len / split) <= total / split + n_seqs <= SM count)
+        // Two candidates, the cheaper by a simple makespan estimate (in tokens of work per SM, a CTA's start-up counted as
+        // START tokens, the ragged end of the last wave as TAIL ranges): ONE wave of CTAs (sum over sequences of ceil(len / split) <= total / split + n_seqs <= SM count),
+        // good while the sequences are few; or several waves of short ranges, whose tail is one short CTA instead of the
+        // slack of n_seqs reserved slots, better when the batch has many sequences.
         int sms = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, pool->device) == cudaSuccess && sms > (int)d->n_seqs) {
-            const uint64_t slots = (uint64_t)(sms - (int)d->n_seqs);                     // one CTA per SM
-            const uint64_t per = (d->total_kv_tokens + slots - 1) / slots;
-            // the whole-block form walks a range two blocks at a time, the per-head form four warps' blocks at a time
-            const uint64_t step = whole_blocks ? 2u * BS : WARPS * BS;
-            split_tokens = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((per + step - 1) / step * step, 64), 1u << 20);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, pool->device) == cudaSuccess && sms > 0) {
+            const uint64_t step = whole_blocks ? 2u * BS : WARPS * BS;    // a range is walked two blocks (per-head form: four warps' blocks) at a time
+            // START and TAIL are fitted to measurements on B200 (64 and 128 prompts of 512-4096 tokens, ranges of 128-416 tokens)
+            const double START = 96.0, TAIL = 0.7, total = (double)d->total_kv_tokens, per_sm = total / sms;
+            auto round_up = [&](double x) { return std::min<uint64_t>(std::max<uint64_t>(((uint64_t)x + step - 1) / step * step, 64), 1u << 20); };
+            const uint64_t many = std::max<uint64_t>(round_up(std::sqrt(per_sm * START / TAIL)), 128);
+            const double t_many = per_sm * (1.0 + START / (double)many) + TAIL * (double)many;
+            uint64_t pick = many;
+            if (sms > (int)d->n_seqs) {
+                const uint64_t one = round_up(total / (sms - (int)d->n_seqs) + 0.999);
+                if ((double)one + START <= t_many) pick = one;
+            }
+            split_tokens = (uint32_t)pick;
         }
     }
     if (split_tokens % (whole_blocks ? 2u * BS : WARPS * BS))
