@@ -328,7 +328,8 @@ typedef struct TkvDecodeAttn {
     uint64_t scratch;             /* tkv_decode_attn_scratch_bytes(...) bytes of device memory  */
     uint64_t scratch_bytes;
     uint64_t total_kv_tokens;     /* optional hint: sum of kv_lens as the host knows it (0 = unknown);
-                                     lets the library size the token ranges so the batch is one wave */
+                                     lets the library size the token ranges: one wave of CTAs for a
+                                     few sequences, several waves of short ranges for many            */
     uint64_t status;              /* 0, or a device u32 the kernel sets to TKV_ERR_TIMEOUT if one
                                      of its bounded waits gave up (the output is then not valid)  */
 } TkvDecodeAttn;
