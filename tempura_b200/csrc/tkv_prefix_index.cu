@@ -579,6 +579,7 @@ int32_t tkv_prefix_index_evict_lru(tkv_prefix_index* ix, uint32_t max_nodes, uin
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemsetAsync(reinterpret_cast<void*>(out_count), 0, sizeof(uint32_t), st);
     if (e == cudaSuccess && out_nodes) e = cudaMemsetAsync(reinterpret_cast<void*>(out_nodes), 0, sizeof(uint32_t), st);
+    max_nodes = (uint32_t)std::min<uint64_t>(max_nodes, ix->capacity);      // one launch per node: never more than the table holds
     for (uint32_t i = 0; i < max_nodes && e == cudaSuccess; i++) {
         prefix_evict_one<<<ix->evict_ctas, 256, 0, st>>>(ix->view, reinterpret_cast<uint32_t*>(out_pages), out_cap,
                                                          reinterpret_cast<uint32_t*>(out_count), reinterpret_cast<uint32_t*>(out_nodes));
