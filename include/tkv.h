@@ -223,14 +223,20 @@ int32_t tkv_handoff_enqueue(tkv_plan* plan, void* stream, uint64_t done_flag, ui
  * library a fixed memory budget.  Instead of a plan's device buffer, the layer
  * pointers and the work list live in ONE fixed array compiled into the library
  * (TKV_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads it, held until
- * the process exits).  The call validates exactly like tkv_plan_create, copies the
+ * the process exits).  The call checks its arguments the way tkv_plan_create does
+ * (geometry, shard, table ids, duplicate and shared-prefix destinations, and that a
+ * destination on another device was mapped by tkv_init or tkv_ipc_import), copies the
  * work list into that array on `stream` and launches the copy kernel behind it; it
- * calls no cudaMalloc, cudaFree or other allocating routine.
+ * calls no cudaMalloc, cudaFree or other allocating routine.  What it does not do that
+ * a plan does: casts (both pools must have one dtype), E4M3 pools with scale arrays
+ * (refused; a plan carries the scales along), completion flags, reference counts.
  *   - Limits: at most TKV_NOALLOC_MAX_BLOCK_PAIRS (source block, destination block)
  *     pairs and TKV_NOALLOC_MAX_LAYERS layers per call; more is refused with
  *     TKV_ERR_INVALID_CONFIG and nothing is launched.
  *   - The first call on a device looks up the array's device address; make that call
- *     before any stream capture begins on that device.
+ *     before any stream capture begins on that device.  A call on a stream that is being
+ *     captured is refused with TKV_ERR_INVALID_CONFIG: the work list is uploaded from host
+ *     memory that the next call rewrites.
  *   - Every call on a device shares the array and overwrites the previous call's
  *     contents: calls whose GPU work may overlap (different streams, or different
  *     threads) race on it.  Order them on one stream or with events.
@@ -313,7 +319,7 @@ int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset_in_allocation);
  * and assume unscaled E4M3; the arithmetic is paged_flash_attention
  * (kernels/src/attention.rs:486-590) to FP16-input, FP32-accumulate tolerance.
  * As there, kv_lens is a DEVICE array whose values are read when the kernel runs;
- * max_kv_len (host) only sizes the grid and the scratch.  head_dim 128, 16-token blocks,
+ * max_kv_len (host) sizes the grid, the table rows and the scratch, and bounds every length read.  head_dim 128, 16-token blocks,
  * 1..8 query heads per kv head.  All pointers are device memory of pool->device.       */
 typedef struct TkvDecodeAttn {
     uint32_t n_seqs, n_q_heads, table_stride, layer, max_kv_len;
@@ -330,8 +336,10 @@ typedef struct TkvDecodeAttn {
     uint64_t total_kv_tokens;     /* optional hint: sum of kv_lens as the host knows it (0 = unknown);
                                      lets the library size the token ranges: one wave of CTAs for a
                                      few sequences, several waves of short ranges for many            */
-    uint64_t status;              /* 0, or a device u32 the kernel sets to TKV_ERR_TIMEOUT if one
-                                     of its bounded waits gave up (the output is then not valid)  */
+    uint64_t status;              /* 0, or a device u32 (zero it before the launch) that receives the first
+                                     failure: TKV_ERR_TIMEOUT if a bounded wait gave up, TKV_ERR_INVALID_CONFIG
+                                     if kv_lens held a value above max_kv_len (clamped to it) or a table entry
+                                     named a block outside the pool (never read); the output is then not valid */
 } TkvDecodeAttn;
 enum { TKV_ATTN_DEFAULT = 0,
        TKV_ATTN_PER_HEAD_CTAS = 1 /* one CTA per (sequence, kv head, split) with per-lane copies, the

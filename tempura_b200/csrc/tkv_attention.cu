@@ -52,8 +52,16 @@ struct AttnArgs {
     uint32_t n_q_heads, n_kv_heads, group, table_stride, n_splits, split_tokens;   // n_splits counts partial slots
     uint32_t parts_per_split;     // partial slots one token range writes (2 in the whole-block form)
     float q_scale;                // softmax scale * log2(e), folded into q
-    uint32_t* status;             // optional: set to TKV_ERR_TIMEOUT when a bounded wait gave up
+    uint32_t max_kv_len;          // the host's bound: sized the grid, the table rows and the scratch; device lengths are clamped to it
+    uint32_t total_blocks;        // blocks in the pool: a table entry at or above it is never dereferenced
+    uint32_t* status;             // optional: first failure wins -- TKV_ERR_TIMEOUT (a bounded wait gave up) or
+                                  // TKV_ERR_INVALID_CONFIG (a length above max_kv_len, a block id outside the pool)
 };
+
+// first failure wins; the output of a launch that reports one is not valid
+__device__ __forceinline__ void report(const AttnArgs& a, uint32_t code) {
+    if (a.status) atomicCAS(a.status, 0u, code);
+}
 
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
@@ -243,7 +251,8 @@ __device__ __forceinline__ void attend_block(const Tile<FP8>& cur, uint32_t n_va
 template <bool FP8>
 __global__ void __launch_bounds__(WARPS * 32) decode_attn_paged(const AttnArgs a) {
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-    const uint32_t kv_len = a.kv_lens[seq];
+    const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len);
+    if (split == 0 && kvh == 0 && threadIdx.x == 0 && a.kv_lens[seq] > a.max_kv_len) report(a, 2u);
     const uint32_t t_begin = split * a.split_tokens;
     if (t_begin >= kv_len) return;
     const uint32_t t_end = min(kv_len, t_begin + a.split_tokens);
@@ -283,7 +292,14 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_paged(const AttnArgs a
         }
         asm volatile("cp.async.commit_group;" ::: "memory");          // one group per k, empty past the end
     };
-    auto table_entry = [&](uint32_t k) { return k < n_mine ? __ldg(table + b_begin + warp + WARPS * k) : 0u; };
+    auto table_entry = [&](uint32_t k) {
+        const uint32_t id = k < n_mine ? __ldg(table + b_begin + warp + WARPS * k) : 0u;
+        if (id >= a.total_blocks) {                                    // never dereferenced: block 0 is read instead and the launch reports it
+            report(a, 2u);
+            return 0u;
+        }
+        return id;
+    };
     for (uint32_t k = 0; k + 1 < (uint32_t)STAGES; k++) issue(k, table_entry(k));
     uint32_t id_ahead = table_entry(STAGES - 1);                       // block ids are fetched one iteration before they are needed
     Tile<FP8> cur;
@@ -552,6 +568,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
+// the same wait, given up early once another warp of the CTA has recorded a failure
+__device__ __forceinline__ bool mbar_wait_unless(uint32_t bar, uint32_t parity, const uint32_t* fail_word) {
+    for (uint32_t it = 0; it < (1u << 22); it++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 15u) == 15u && *reinterpret_cast<const volatile uint32_t*>(fail_word)) return false;
+    }
+    return false;
+}
+
 template <bool FP8>
 __global__ void __launch_bounds__((MAX_KV_HEADS_PER_CTA + 1) * 32, 1)
 decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
@@ -559,7 +590,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int KW = Tile<FP8>::KW;
     const uint32_t split = blockIdx.x, seq = blockIdx.y;
-    const uint32_t kv_len = a.kv_lens[seq];
+    const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len);
     const uint32_t t_begin = split * a.split_tokens;
     if (t_begin >= kv_len) return;
     const uint32_t t_end = min(kv_len, t_begin + a.split_tokens);
@@ -587,7 +618,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
     if (warp == CW) {
         // ---- producer: lane 0 drives the ring; the warp reads the block table 32 entries at a time (one
         // coalesced load, the next one already in flight), so no copy waits for a table entry of its own ----
-        uint32_t issued = 0;
+        uint32_t issued = 0, why = 4u;
         bool ok = true;
         uint32_t ids_next = lane < n_blk ? __ldg(table + lane) : 0u;
         for (uint32_t k0 = 0; k0 < n_blk && ok; k0 += 32) {
@@ -598,7 +629,11 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                 const uint32_t id = __shfl_sync(0xFFFFFFFFu, ids, i);
                 const uint32_t k = k0 + i, s = k % n_stages;
                 if (lane == 0) {
-                    if (k >= n_stages) ok = mbar_wait(smem_addr(empty + s), ((k / n_stages) - 1u) & 1u);   // every head has read the old block
+                    if (id >= a.total_blocks) {                      // a stale or foreign id is never turned into an address
+                        ok = false;
+                        why = 2u;
+                    }
+                    if (ok && k >= n_stages) ok = mbar_wait(smem_addr(empty + s), ((k / n_stages) - 1u) & 1u);   // every head has read the old block
                     if (ok) {
                         const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + k) * BS);
                         const uint32_t bytes = n_valid * a.row_stride, sc_bytes = a.k_scales ? a.n_kv_heads * 4u : 0u;
@@ -621,11 +656,11 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
             }
         }
         if (!ok && lane == 0) {
-            atomicExch(fail_word, 1u);
+            atomicExch(fail_word, why);
             // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
             for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
                 mbar_wait(smem_addr(full + k % n_stages), (k / n_stages) & 1u);
-            if (a.status) atomicExch(a.status, 4u);
+            report(a, why);
         }
     } else if (warp < a.n_kv_heads) {
         // ---- consumer: kv head `warp`, every block of this CTA's range ----
@@ -649,7 +684,7 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
         // fragments of block k out of its ring stage, which goes back to the producer as soon as they are in registers
         auto fetch = [&](uint32_t k, Tile<FP8>& t, uint32_t n_valid) -> bool {
             const uint32_t s = k % n_stages;
-            if (!mbar_wait(smem_addr(full + s), (k / n_stages) & 1u) || *reinterpret_cast<volatile uint32_t*>(fail_word)) return false;
+            if (!mbar_wait_unless(smem_addr(full + s), (k / n_stages) & 1u, fail_word) || *reinterpret_cast<volatile uint32_t*>(fail_word)) return false;
             const unsigned char* kb = stages + (size_t)s * stage_bytes + (size_t)kvh * D * ES;
             const unsigned char* vb = kb + block_bytes;
 #pragma unroll
@@ -751,8 +786,9 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
                         *reinterpret_cast<float2*>(pr + 2 + 16 * grp + 2 * t) = make_float2(o[t][h], o[t][2 + h]);
                 }
             }
-        } else if (lane == 0 && a.status) {
-            atomicExch(a.status, 4u);
+        } else if (lane == 0) {
+            const uint32_t why = *reinterpret_cast<volatile uint32_t*>(fail_word);
+            report(a, why ? why : 4u);
         }
     }
 }
@@ -762,7 +798,8 @@ decode_attn_blocks(const AttnArgs a, uint32_t n_stages, uint32_t stage_bytes) {
 __global__ void __launch_bounds__(D) decode_attn_combine(const AttnArgs a) {
     const uint32_t head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const uint32_t kvh = head / a.group, g = head % a.group;
-    const uint32_t kv_len = a.kv_lens[seq];
+    const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len);
+    if (head == 0 && d == 0 && a.kv_lens[seq] > a.max_kv_len) report(a, 2u);   // the tokens past max_kv_len were not attended to
     const uint32_t live = ((kv_len + a.split_tokens - 1) / a.split_tokens) * a.parts_per_split;
     const float* base = a.partial + (((size_t)seq * a.n_kv_heads + kvh) * a.n_splits * a.group + g) * (D + 2);
     const size_t stride = (size_t)a.group * (D + 2);
@@ -837,6 +874,9 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
     const uint32_t es = pool->dtype == TKV_DTYPE_E4M3 ? 1u : 2u;
     const uint64_t kp = pool->k_layer_ptrs[d->layer], vp = pool->v_layer_ptrs[d->layer];
     if ((kp | vp | d->q | d->scratch) % 16) return fail(TKV_ERR_INVALID_CONFIG, "layer tensors, q and scratch must be 16-byte aligned");
+    // the scale rows of a block are bulk-copy sources too
+    if (pool->k_scales && ((pool->k_scales | pool->v_scales) % 16 || ((uint64_t)pool->total_blocks * pool->n_kv_heads * 4u) % 16))
+        return fail(TKV_ERR_INVALID_CONFIG, "scale arrays (and each layer's slice of them) must be 16-byte aligned");
     // whole-block form when a CTA can hold every kv head of a block (and the scale rows are bulk-copy sized)
     const uint32_t row_bytes = pool->n_kv_heads * D * es, stage_bytes = 2u * BS * row_bytes + 128u;
     const bool whole_blocks = pool->n_kv_heads <= (uint32_t)MAX_KV_HEADS_PER_CTA && (!pool->k_scales || pool->n_kv_heads % 4 == 0) &&
@@ -891,6 +931,8 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
     a.parts_per_split = 1;
     a.split_tokens = split_tokens;
     a.q_scale = d->sm_scale * 1.4426950408889634f;
+    a.max_kv_len = d->max_kv_len;
+    a.total_blocks = pool->total_blocks;
     a.status = reinterpret_cast<uint32_t*>(d->status);
 
     int prev = -1;

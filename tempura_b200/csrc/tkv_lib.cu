@@ -62,6 +62,9 @@ struct DevInfo {
 std::mutex g_mu;
 DevInfo g_dev[64];
 cudaStream_t g_copy_stream[64] = {};
+// g_peer[a][b]: device a may store into device b's memory because THIS library enabled the mapping
+// (tkv_init) or opened it (tkv_ipc_import).  cudaDeviceCanAccessPeer only says the hardware could.
+bool g_peer[64][64] = {};
 
 int32_t dev_info(int dev, DevInfo* out) {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -88,6 +91,17 @@ int32_t copy_stream(int dev, cudaStream_t* out) {
 
 // Lets other translation units of this library report through tkv_last_error().
 namespace tkv_internal {
+bool peer_reachable(int from, int to) {
+    if (from == to) return true;
+    if (from < 0 || to < 0 || from >= 64 || to >= 64) return false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_peer[from][to];
+}
+void mark_peer(int from, int to) {
+    if (from < 0 || to < 0 || from >= 64 || to >= 64) return;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_peer[from][to] = true;
+}
 int32_t set_error(int32_t code, int32_t cuda_code, const char* text) {
     g_err = text ? text : "";
     if (cuda_code) g_cuda_err = cuda_code;
@@ -112,6 +126,7 @@ struct tkv_plan {
     // The pinned mirror goes to the device in stream order, at the head of the next enqueue (or
     // refcount launch): `dirty` = mirror newer than the device copy, `upload_ev` = last upload.
     bool dirty = false, upload_pending = false;
+    bool list_clobbered = false;   // a device-built work list sits where the host-built one was uploaded
     cudaEvent_t upload_ev = nullptr;
     uint32_t n_pairs = 0, n_prefix = 0;
     tkv::HandoffArgs args{};
@@ -288,12 +303,12 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     p->n_pairs = (uint32_t)pairs;
     p->n_prefix = (uint32_t)prefix_refs;
 
+    // A kernel on the source device stores into the destination pool: refuse a pair whose peer mapping this
+    // library has not set up, rather than launch stores at addresses the device cannot reach.
+    if (!tkv_internal::peer_reachable(s.device, d.device))
+        return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot store into device %d: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
+                    s.device, d.device);
     // ---- everything above is pure host logic; CUDA starts here ----
-    if (s.device != d.device) {
-        int can = 0;
-        CU(cudaDeviceCanAccessPeer(&can, s.device, d.device));
-        if (!can) return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot store into device %d", s.device, d.device);
-    }
     {
         DeviceGuard g(s.device);
         if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", s.device);
@@ -395,11 +410,12 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
 
 // Puts the plan's work list on the device in the order of `st`, ahead of whatever is launched
 // next on it; a stream that did not carry the upload waits for it.
-int32_t ensure_uploaded(tkv_plan* p, cudaStream_t st) {
-    if (p->dirty) {
+int32_t ensure_uploaded(tkv_plan* p, cudaStream_t st, bool need_host_list = true) {
+    if (p->dirty || (need_host_list && p->list_clobbered)) {
         CU(cudaMemcpyAsync(p->d_buf, p->h_buf, p->used, cudaMemcpyHostToDevice, st));
         CU(cudaEventRecord(p->upload_ev, st));
         p->dirty = false;
+        p->list_clobbered = false;
         p->upload_pending = true;
     } else if (p->upload_pending) {
         CU(cudaStreamWaitEvent(st, p->upload_ev, 0));
@@ -605,6 +621,7 @@ int32_t tkv_init(const int32_t* devices, int32_t n) {
                 cudaSetDevice(prev);
                 return cuda_fail(e, "cudaDeviceEnablePeerAccess");
             }
+            tkv_internal::mark_peer(devices[i], devices[j]);
         }
     }
     CU(cudaSetDevice(prev));
@@ -885,7 +902,7 @@ int32_t tkv_handoff_enqueue_device_tables(tkv_plan* p, const TkvDeviceBatch* db,
         p->dev_scratch_seqs = seqs;
     }
     {
-        int32_t rc = ensure_uploaded(p, st);
+        int32_t rc = ensure_uploaded(p, st, false);   // layer pointers and counter; the list is built below
         if (rc) return rc;
     }
     tkv::DeviceTables t{};
@@ -912,6 +929,9 @@ int32_t tkv_handoff_enqueue_device_tables(tkv_plan* p, const TkvDeviceBatch* db,
     a.n_pairs_dev = p->dev_scratch;
     const int32_t rc = dispatch(p, (uint64_t)a.n_pairs * a.n_layers * 2, st);
     a.n_pairs_dev = nullptr;
+    // the device builder wrote over the slot that holds the plan's host-built list: the next host-table
+    // enqueue uploads the pinned mirror again, in stream order
+    p->list_clobbered = true;
     return rc;
 }
 
@@ -994,7 +1014,7 @@ int32_t tkv_refcount_apply(tkv_plan* p, int32_t delta, void* stream) {
     if (!p->dst.refcounts) return fail(TKV_ERR_INVALID_CONFIG, "destination pool has no refcount array");
     DeviceGuard g(p->src.device);
     if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
-    int32_t rc = ensure_uploaded(p, static_cast<cudaStream_t>(stream));
+    int32_t rc = ensure_uploaded(p, static_cast<cudaStream_t>(stream), false);   // the prefix ids sit past the work list
     if (rc) return rc;
     uint32_t blocks = std::min<uint32_t>((p->n_prefix + 255) / 256, 1024);
     tkv::refcount_apply_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -1144,6 +1164,13 @@ int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset, uint64_t* devp
     void* base = nullptr;
     CU(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
     *devptr = reinterpret_cast<uint64_t>(base) + offset;
+    // the mapping is usable from the importing (current) device; remember which device owns the memory
+    int cur = -1;
+    cudaPointerAttributes attr{};
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaPointerGetAttributes(&attr, base) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
+        tkv_internal::mark_peer(cur, attr.device);
+    else
+        cudaGetLastError();
     return TKV_OK;
 }
 

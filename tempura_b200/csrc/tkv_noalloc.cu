@@ -16,6 +16,7 @@
 
 namespace tkv_internal {
 int32_t set_error(int32_t code, int32_t cuda_code, const char* text);
+bool peer_reachable(int from, int to);
 }
 
 namespace {
@@ -180,6 +181,10 @@ extern "C" int32_t tkv_handoff_noalloc(const TkvPool* s, const TkvPool* d, const
             }
         }
     }
+    // as for a plan: a destination on another device must have been mapped by tkv_init or tkv_ipc_import
+    if (!tkv_internal::peer_reachable(s->device, d->device))
+        return fail(TKV_ERR_INVALID_CONFIG, "device %llu cannot store into device %llu: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
+                    (unsigned long long)s->device, (unsigned long long)d->device);
     if (pairs == 0) return TKV_OK;
 
     // ---- CUDA from here on; nothing below allocates ----
@@ -190,6 +195,15 @@ extern "C" int32_t tkv_handoff_noalloc(const TkvPool* s, const TkvPool* d, const
     PerDevice pd;
     int32_t rc = setup(s->device, &pd);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rc == TKV_OK) {
+        // The work list is uploaded from this thread's host image, which the next call rewrites: a stream that
+        // is recording a graph would keep a pointer to it, so such a call is refused.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        e = cudaStreamIsCapturing(st, &cap);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaStreamIsCapturing");
+        else if (cap != cudaStreamCaptureStatusNone)
+            rc = fail(TKV_ERR_INVALID_CONFIG, "no-alloc handoff: the stream is being captured; the call uploads from host memory that the next call rewrites");
+    }
     if (rc == TKV_OK) {
         unsigned char* base = static_cast<unsigned char*>(pd.scratch);
         e = cudaMemcpyAsync(base, image.data(), used, cudaMemcpyHostToDevice, st);

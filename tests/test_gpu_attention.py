@@ -206,3 +206,37 @@ def test_causal_chunk_of_new_tokens_matches_oracle(H):
     # the last row is plain decode attention over the whole sequence
     one = H.decode_attention(dd, 0, q[-1:].contiguous(), row.reshape(1, -1), torch.tensor([300], dtype=torch.int32).cuda())
     assert torch.equal(one.cpu(), torch.from_numpy(got[-1:]))
+
+
+@pytest.mark.parametrize("flags", [0, N.ATTN_PER_HEAD_CTAS])
+def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faulting(H, flags):
+    """kv_lens is device memory read when the kernel runs: a value above max_kv_len (which sized the grid, the
+    table rows and the scratch) is clamped, and a table entry outside the pool is never turned into an
+    address.  Both launches finish, report TKV_ERR_INVALID_CONFIG, and leave the context usable."""
+    import torch
+    lens = np.array([40, 200], dtype=np.uint32)
+    w = W.Workload("attn-guard", 1, 8, 128, 16, 64, 64, lens, seed=5).build_tables()
+    hs, _ = host_pools(w)
+    ds = to_device_pool(hs, "f16")
+    q = torch.randn((2, 32, 128), generator=torch.Generator().manual_seed(3)).cuda()
+    tables = torch.from_numpy(w.src_tables.astype(np.int64)).to(torch.int32).cuda()
+    good = torch.from_numpy(lens.astype(np.int64)).to(torch.int32).cuda()
+    want = H.decode_attention(ds, 0, q, tables, good, max_kv_len=200, flags=flags).cpu().numpy()
+
+    # a device length far above the bound: attended up to the bound, reported
+    long = torch.tensor([40, 100000], dtype=torch.int32).cuda()
+    attn = H.DecodeAttention(ds, q, tables, long, 200, flags=flags)
+    got = attn.enqueue(0).cpu().numpy()
+    assert int(attn.status.item()) == N.ERR_INVALID_CONFIG
+    np.testing.assert_array_equal(got, want)           # the clamp makes it the max_kv_len answer
+
+    # one table entry outside the pool
+    bad = tables.clone()
+    bad[1, 3] = 1 << 20
+    attn = H.DecodeAttention(ds, q, bad, good, 200, flags=flags)
+    attn.enqueue(0)
+    torch.cuda.synchronize()
+    assert int(attn.status.item()) == N.ERR_INVALID_CONFIG
+    # the context still works
+    again = H.decode_attention(ds, 0, q, tables, good, max_kv_len=200, flags=flags).cpu().numpy()
+    np.testing.assert_array_equal(again, want)

@@ -227,3 +227,37 @@ def test_refcounts_from_device_tables_up_and_down(H):
     assert int(dst.refcounts.abs().sum()) == 0
     H.refcount_apply_device_tables(dst, dev_i32([[64, 1]]), dev_i32([2]), +1, status)     # id 64 is outside the pool
     assert int(status.item()) == N.ERR_INVALID_CONFIG and int(dst.refcounts[1]) == 1
+
+
+def test_host_tables_and_device_tables_alternate_on_one_plan(H):
+    """The device builder writes its list where the plan's host-built list was uploaded.  A host-table enqueue
+    that follows must move the plan's own batch again (the list is uploaded anew, in stream order), and a
+    device-table enqueue after that its device batch: both against the oracle, twice round."""
+    import torch
+    w_host = W.Workload("alt-host", 2, 8, 128, 16, 256, 256, W.lengths(6, 20, 200, 41, 7), seed=41).build_tables()
+    w_dev = W.Workload("alt-dev", 2, 8, 128, 16, 256, 256, W.lengths(4, 5, 90, 42, 7), seed=42).build_tables()
+    hs, hd0 = host_pools(w_host)
+    src = to_device_pool(hs, "f16")
+    # the device batch reads the same source pool through its own tables
+    for q in range(len(w_dev.seq_lens)):
+        nb = (int(w_dev.seq_lens[q]) + 15) // 16
+        w_dev.src_tables[q, :nb] = w_host.src_tables[q, :nb]
+    dst = to_device_pool(hd0, "f16")
+    fresh = dst.storage.clone()
+    plan = H.Plan(src, dst, device_batch(w_host))
+    n = len(w_dev.seq_lens)
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    for rnd in range(2):
+        for which in ("host", "device"):
+            _, hd = host_pools(w_host)                               # the oracle's fresh 0x5A destination
+            oracle.handoff(hs, hd, oracle_batch(w_host if which == "host" else w_dev), None, "copy")
+            dst.storage.copy_(fresh)
+            if which == "host":
+                plan.enqueue()
+            else:
+                plan.enqueue_device_tables(dev_i32(w_dev.seq_lens), dev_i32(w_dev.src_tables.reshape(n, -1)),
+                                           dev_i32(w_dev.dst_tables.reshape(n, -1)), status=status)
+            torch.cuda.synchronize()
+            if which == "device":
+                assert int(status.item()) == 0
+            assert_pool_equals_host(dst, hd, f"round {rnd} {which} tables")

@@ -138,3 +138,35 @@ def test_decode_attention_arguments_validate_without_a_gpu():
     f32 = fake_pool(layers=1, heads=8, dim=128, bs=16, dtype="f32")
     assert N.lib().tkv_decode_attn_enqueue(C.byref(f32.c_struct()), C.byref(args), None) == N.ERR_INVALID_CONFIG
     assert N.lib().tkv_decode_attn_scratch_bytes(16, 32, 128, 4096, 1024) == 16 * 32 * 4 * 130 * 4
+
+
+def test_unmapped_peer_destination_is_refused_on_the_host():
+    """A kernel on the source device stores into the destination pool.  Two ordinals the library never
+    paired (no tkv_init, no tkv_ipc_import) are refused before any CUDA call, by the planned handoff and
+    by the allocation-free one alike: nothing is launched at addresses the source device cannot reach."""
+    b = batch([8], [[0, 1]], [[2, 3]], 2)
+    src, dst = fake_pool(), fake_pool()
+    dst.device = 5
+    for call in (lambda: H.Plan(src, dst, b), lambda: H.handoff_noalloc(src, dst, b, stream=_NoStream())):
+        msg = expect(N.ERR_INVALID_CONFIG, call)
+        assert "device 0 cannot store into device 5" in msg and "tkv_init" in msg
+    # the transfer-buffer forms go through the same gate (buffer on one device, pool on another)
+    x = H.Transfer(_FakeTensor(0x20000000, 1 << 20), N.DTYPE_F16, 3)
+    msg = expect(N.ERR_INVALID_CONFIG, lambda: H.Plan.from_transfer(x, dst, b))
+    assert "device 3 cannot store into device 5" in msg
+
+
+class _NoStream:
+    cuda_stream = 0
+
+
+class _FakeTensor:
+    """Address and size of a buffer that is never dereferenced (validation fails first)."""
+    def __init__(self, ptr, n):
+        self._p, self._n = ptr, n
+
+    def data_ptr(self):
+        return self._p
+
+    def numel(self):
+        return self._n

@@ -4,13 +4,15 @@ Some callers cannot allocate device memory when a handoff happens: the KV pools 
 serving engine already own nearly all of HBM, and a cudaMalloc in the steady-state loop
 stalls every stream of the device.  For them the work list lives in a fixed array inside
 the library.  This file checks that entry point against the planned handoff
-(tkv_plan_create + tkv_handoff_enqueue) on the same inputs, byte for byte, on two calls
-in a row, and that oversized batches are refused.  It is named to be collected last.
+(tkv_plan_create + tkv_handoff_enqueue) and against the CPU oracle on the same inputs,
+byte for byte, on two calls in a row, and that oversized batches are refused.  It is
+named to be collected last.
 """
 import numpy as np
 import pytest
 
-from helpers import device_batch, host_pools, to_device_pool
+import oracle
+from helpers import assert_pool_equals_host, device_batch, host_pools, oracle_batch, to_device_pool
 from tempura_b200 import _native as N
 from tempura_b200 import workloads as W
 
@@ -52,6 +54,8 @@ def test_noalloc_matches_planned_handoff_twice_in_a_row():
         want, got = _pool_bytes(dst_plan), _pool_bytes(dst_noalloc)
         for i, (a, b) in enumerate(zip(want, got)):
             assert np.array_equal(a, b), f"call {call}: tensor {i} differs from the planned handoff"
+        oracle.handoff(hs, hd, oracle_batch(w), None, "copy")           # and directly against the checker
+        assert_pool_equals_host(dst_noalloc, hd, f"no-alloc call {call}")
         assert any((a != 0x5A).any() for a in got)          # something was actually moved
 
 
