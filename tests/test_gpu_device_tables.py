@@ -238,10 +238,7 @@ def test_host_tables_and_device_tables_alternate_on_one_plan(H):
     w_dev = W.Workload("alt-dev", 2, 8, 128, 16, 256, 256, W.lengths(4, 5, 90, 42, 7), seed=42).build_tables()
     hs, hd0 = host_pools(w_host)
     src = to_device_pool(hs, "f16")
-    # the device batch reads the same source pool through its own tables
-    for q in range(len(w_dev.seq_lens)):
-        nb = (int(w_dev.seq_lens[q]) + 15) // 16
-        w_dev.src_tables[q, :nb] = w_host.src_tables[q, :nb]
+    # the device batch reads the same source pool through its own tables (seeded blocks or the 0xA5 filler alike)
     dst = to_device_pool(hd0, "f16")
     fresh = dst.storage.clone()
     plan = H.Plan(src, dst, device_batch(w_host))
