@@ -3,10 +3,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A step is one handoff of the whole batch.  N = 1 moves the batch between a prefill pool and
-a decode pool on the same GPU (HBM-bound); N = 2, 4, 8 is one process per GPU, ranks
-[0, N/2) prefill and ranks [N/2, N) decode, every pair moving its own batch with peer stores
-over NVLink (weak scaling: work per pair is fixed).  Prints ONE JSON line on rank 0.
+A step is one handoff of the whole batch.  The default workload is the benchmark's scaling configuration
+(Llama-3.1-70B shape, 80 layers, 32 prompts of 4096 tokens, 42.9 GB of F16 K/V) at every N: N = 1 moves it
+between a prefill pool and a decode pool on the same GPU (HBM-bound); N = 2, 4, 8 is one process per GPU,
+ranks [0, N/2) prefill and ranks [N/2, N) decode, the batch's KV heads split evenly over the pairs
+(tkv_pairing_make) and every pair moving its share with stores into the peer pool over NVLink (strong scaling:
+the batch is fixed).  --workload cfg1..cfg4 select the other configurations (at N > 1 every pair then moves its
+own batch: weak scaling).  Every run ends with a parity step outside the timed region: every moved row of every
+layer on the destination against the source, bit for bit, or the run exits non-zero.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -158,28 +162,182 @@ def fill_source(pool, w, seed: int):
     torch.cuda.synchronize()
 
 
-def spot_check(src, dst, w, layer: int):
-    """Not timed: destination blocks of one layer equal the source blocks they came from."""
-    import torch
-    bs = w.block_size
-    for q in (0, len(w.seq_lens) - 1):
+# ----------------------------------------------------------------------------------------
+# parity inside the run (not timed)
+# ----------------------------------------------------------------------------------------
+def _moved_block_ids(w, tables):
+    """Block ids of every moved block, in work-list order (sequence by sequence, past the shared prefix)."""
+    bs, out = w.block_size, []
+    for q in range(len(w.seq_lens)):
         pre = int(w.prefix_lens[q]) // bs if w.prefix_lens is not None else 0
-        nfull = int(w.seq_lens[q]) // bs
-        if nfull <= pre:
-            continue
-        s = torch.from_numpy(w.src_tables[q, pre:nfull].astype(np.int64)).cuda(src.device)
-        d = torch.from_numpy(w.dst_tables[q, pre:nfull].astype(np.int64)).cuda(dst.device)
-        if src.dtype == dst.dtype or src.dtype == 0:
-            a = src.blocks(layer).index_select(0, s)
-            if src.dtype == 0:
-                a = a.to(torch.float16)                       # F32 -> F16, round to nearest even
-            b = dst.blocks(layer).index_select(0, d).to(a.device)
-            if not torch.equal(a.view(torch.int16), b.view(torch.int16)):
-                raise SystemExit("spot check failed: destination blocks differ from source blocks")
-        else:
-            sc = dst.k_scales[layer].index_select(0, d)
-            if not bool((sc > 0).all()):
-                raise SystemExit("spot check failed: scales not written")
+        nb = (int(w.seq_lens[q]) + bs - 1) // bs
+        out.append(tables[q, pre:nb])
+    return np.concatenate(out).astype(np.int64)
+
+
+def _compact_batch(w):
+    """The same moved blocks described against a transfer buffer: identity tables in work-list order, no prefix."""
+    bs = w.block_size
+    pre = w.prefix_lens.astype(np.int64) if w.prefix_lens is not None else np.zeros(len(w.seq_lens), dtype=np.int64)
+    lens = w.seq_lens.astype(np.int64) - pre
+    nb = (lens + bs - 1) // bs
+    stride = int(max(1, nb.max()))
+    tab = np.zeros((len(lens), stride), dtype=np.uint32)
+    off = 0
+    for q, k in enumerate(nb):
+        tab[q, :k] = np.arange(off, off + k, dtype=np.uint32)
+        off += int(k)
+    return lens.astype(np.uint32), tab, stride, off
+
+
+def parity_step(H, w, batch, src, dst, is_prefill, partner, multi, local, scales):
+    """Not timed.  Every moved row of every layer, destination against source, bit for bit.
+
+    Both sides gather their rows of a few layers at a time into a contiguous buffer (source pool through the
+    source tables, cast as the handoff casts; destination pool through the destination tables) and the buffers
+    must be byte-equal, scales included.  For same-dtype moves the reference's bits checksum (wrapping sum of
+    the f32 bit patterns, engine/src/cutile_kv_cache.rs:1274-1368) of each side is reported as well, and one
+    layer is also compared through torch indexing, which shares no code with the library.  For an E4M3
+    destination the first and the last layer are compared with the CPU oracle's bytes and scales.  With two
+    or more GPUs the decode rank sends its gathered rows to the prefill rank of its pair over NCCL.
+    Returns a dict for the JSON line, or raises SystemExit."""
+    import torch
+    import torch.distributed as dist
+    L, bs = w.n_layers, w.block_size
+    n_blocks = H.batch_blocks(batch, bs)
+    if n_blocks == 0:
+        return {"parity": "bit-exact", "layers": 0, "bytes_compared_per_pair": 0}
+    es_dst = {"f32": 4, "f16": 2, "e4m3": 1}[w.dst_dtype]
+    half = n_blocks * bs * w.n_kv_heads * w.head_dim          # elements of one K or V plane
+    per_layer = 2 * half * es_dst
+    chunk = int(max(1, min(L, (3 << 29) // per_layer)))
+    same = w.src_dtype == w.dst_dtype
+    fp8_cast = w.src_dtype == "f16" and w.dst_dtype == "e4m3"
+    own_dst = H.Batch(batch.seq_lens, batch.dst_tables, batch.dst_tables, batch.table_stride, batch.prefix_lens)
+    have_src = is_prefill
+    have_dst = (not multi) or (not is_prefill)
+    dev = torch.device("cuda", local)
+    M64 = (1 << 64) - 1
+    ok, compared, sum_src, sum_dst = True, 0, 0, 0
+    mk = lambda fill: H.Transfer.allocate(chunk, w.n_kv_heads, w.head_dim, bs, n_blocks, w.dst_dtype, device=local, scales=scales, fill_byte=fill)
+    xa = mk(0x5A) if have_src else None
+    xb = mk(0x5A) if have_dst else None
+    xr = mk(None) if (multi and have_src) else None
+    n_sc = lambda nl: 2 * nl * n_blocks * w.n_kv_heads       # scales of nl layers: K of every layer, then V
+
+    def gather_both(l0, nl):
+        """Rows of layers [l0, l0 + nl): the source's in xa, the destination's in the returned buffer (on the prefill rank)."""
+        shard = H.Shard(0, 0, w.n_kv_heads, l0, 0, nl)
+        pa = pb = None
+        if have_src:
+            xa.data.fill_(0x5A)
+            pa = H.Plan.to_transfer(src, xa, batch, shard)
+            pa.enqueue()
+        if have_dst:
+            xb.data.fill_(0x5A)
+            pb = H.Plan.to_transfer(dst, xb, own_dst, shard)
+            pb.enqueue()
+        torch.cuda.synchronize()
+        del pa, pb
+        if not multi:
+            return xb
+        if have_dst:
+            dist.send(xb.data[:nl * per_layer], partner)
+            if scales:
+                dist.send(xb.scales, partner)
+            return xb
+        dist.recv(xr.data[:nl * per_layer], partner)
+        if scales:
+            dist.recv(xr.scales, partner)
+        return xr
+
+    for l0 in range(0, L, chunk):
+        nl = min(chunk, L - l0)
+        used = nl * per_layer
+        got = gather_both(l0, nl)
+        if have_src:
+            ok = ok and torch.equal(xa.data[:used], got.data[:used])
+            if scales:
+                ok = ok and torch.equal(xa.scales.view(-1)[:n_sc(nl)].view(torch.int32), got.scales.view(-1)[:n_sc(nl)].view(torch.int32))
+            compared += used
+        if same and w.dst_dtype in ("f16", "f32"):
+            view = torch.float16 if w.dst_dtype == "f16" else torch.float32
+            if have_src:
+                sum_src = (sum_src + H.bits_checksum(xa.data[:used].view(view), w.dst_dtype)) & M64
+            if have_dst:
+                sum_dst = (sum_dst + H.bits_checksum(xb.data[:used].view(view), w.dst_dtype)) & M64
+
+    # ---- an E4M3 destination against the oracle's own bytes and scales, first and last layer ----
+    oracle_checked = []
+    for layer in (sorted({0, L - 1}) if fp8_cast else []):
+        got = gather_both(layer, 1)
+        if have_src:
+            import oracle
+            xf = H.Transfer.allocate(1, w.n_kv_heads, w.head_dim, bs, n_blocks, "f16", device=local, fill_byte=0xA5)
+            pf = H.Plan.to_transfer(src, xf, batch, H.Shard(0, 0, w.n_kv_heads, layer, 0, 1))
+            pf.enqueue()
+            torch.cuda.synchronize()
+            rows = xf.data[:4 * half].cpu().numpy().view(np.uint16)
+            hs = oracle.HostPool(1, w.n_kv_heads, w.head_dim, bs, n_blocks, np.dtype(np.uint16), [rows[:half]], [rows[half:2 * half]])
+            hd = oracle.HostPool.filled(1, w.n_kv_heads, w.head_dim, bs, n_blocks, np.uint8, 0x5A, with_scales=True)
+            lens, tab, stride, _ = _compact_batch(w)
+            oracle.handoff(hs, hd, oracle.make_batch(lens, tab, tab, stride), None, "f16_e4m3", n_threads=os.cpu_count() or 1)
+            dev_bytes = got.data[:2 * half].cpu().numpy()
+            dev_scales = got.scales.view(-1)[:n_sc(1)].cpu().numpy().view(np.uint32)
+            ok = ok and np.array_equal(dev_bytes[:half], hd.k[0]) and np.array_equal(dev_bytes[half:], hd.v[0])
+            ok = ok and np.array_equal(dev_scales[:n_sc(1) // 2], hd.k_scales.view(np.uint32).reshape(-1))
+            ok = ok and np.array_equal(dev_scales[n_sc(1) // 2:], hd.v_scales.view(np.uint32).reshape(-1))
+            del xf, pf
+        oracle_checked.append(layer)
+
+    # ---- one layer through torch indexing (no library code on either side): the whole blocks of every sequence ----
+    indep = None
+    if same:
+        layer = L - 1
+        s_ids, d_ids = _moved_block_ids(w, w.src_tables), _moved_block_ids(w, w.dst_tables)
+        whole = []
+        for q in range(len(w.seq_lens)):                       # a ragged last block keeps the destination's fill in its tail rows
+            pre = int(w.prefix_lens[q]) // bs if w.prefix_lens is not None else 0
+            nb = (int(w.seq_lens[q]) + bs - 1) // bs
+            whole += [True] * (nb - pre)
+            if int(w.seq_lens[q]) % bs and nb > pre:
+                whole[-1] = False
+        whole = np.asarray(whole, dtype=bool)
+        for is_v in (False, True):
+            b = None
+            if have_dst:
+                b = dst.blocks(layer, is_v).index_select(0, torch.from_numpy(d_ids[whole]).to(dev)).contiguous()
+                if multi:
+                    dist.send(b.view(torch.uint8).reshape(-1), partner)
+            if have_src:
+                a = src.blocks(layer, is_v).index_select(0, torch.from_numpy(s_ids[whole]).to(dev)).contiguous()
+                if multi:
+                    b = torch.empty_like(a)
+                    dist.recv(b.view(torch.uint8).reshape(-1), partner)
+                ok = ok and torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+        indep = layer
+    del xa, xb, xr
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    if multi:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        sums = torch.tensor([sum_src >> 32, sum_src & 0xFFFFFFFF, sum_dst >> 32, sum_dst & 0xFFFFFFFF], dtype=torch.int64, device=dev)
+        gathered = [torch.zeros_like(sums) for _ in range(dist.get_world_size())]
+        dist.all_gather(gathered, sums)
+        pairs = dist.get_world_size() // 2
+        sum_src = sum((int(g[0]) << 32) | int(g[1]) for g in gathered[:pairs]) & M64
+        sum_dst = sum((int(g[2]) << 32) | int(g[3]) for g in gathered[pairs:]) & M64
+    if not bool(flag.item()) or sum_src != sum_dst:
+        raise SystemExit(f"PARITY FAILED: destination rows differ from source rows (bits checksum {sum_src:#x} vs {sum_dst:#x})")
+    out = {"parity": "bit-exact", "layers": L, "bytes_compared_per_pair": int(compared),
+           "how": "destination rows gathered through the destination tables == source rows gathered through the source tables"
+                  + ("" if same else " and cast as the handoff casts") + ", every layer, bytes" + (" and scales" if scales else "")}
+    if same and w.dst_dtype in ("f16", "f32"):
+        out["bits_checksum"] = f"{sum_src:#018x}"
+    if oracle_checked:
+        out["oracle_layers"] = oracle_checked
+    if indep is not None:
+        out["torch_indexing_layer"] = indep
+    return out
 
 
 # ----------------------------------------------------------------------------------------
@@ -193,57 +351,109 @@ def cpu_sample_workload(w, layers: int, pool_blocks: int):
     return s.build_tables()
 
 
-def time_cpu(w, threads: int, layers: int, reps: int):
-    """Times the oracle's handoff (the reference's CPU path restated) on `layers` layers of
-    the workload with all its sequences; pool shrunk so two pools fit host RAM."""
-    import oracle
-    need = int(((w.seq_lens.astype(np.int64) + w.block_size - 1) // w.block_size).sum()) + 256
-    pool_blocks = 1 << int(np.ceil(np.log2(need)))
-    s = cpu_sample_workload(w, layers, pool_blocks)
-    npdt = {"f16": np.uint16, "e4m3": np.uint8, "f32": np.float32}
-    src = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.src_dtype], 0xA5)
-    dst = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.dst_dtype], 0x5A,
-                                 with_scales=(s.dst_dtype == "e4m3"))
-    for l in range(layers if s.dst_dtype == "e4m3" else 0):   # values only matter to the FP8 path
-        for kv, arrs in enumerate((src.k, src.v)):
-            arrs[l][:] = oracle.gen_normal_f16(arrs[l].size, s.seed, 2 * l + kv, s.sigma, s.head_dim,
-                                               s.outlier_channels, s.outlier_gain)
-    batch = oracle.make_batch(s.seq_lens, s.src_tables, s.dst_tables, s.table_stride, s.prefix_lens)
-    mode = "copy" if s.src_dtype == s.dst_dtype else "f16_e4m3"
-    best = float("inf")
-    for _ in range(reps + 1):        # first pass is the warm-up
+class CpuSample:
+    """The oracle's handoff (the reference's CPU path restated) on `layers` layers of the workload with all its
+    sequences and full tables; pools shrunk to the next power of two above the batch so two of them fit host RAM."""
+
+    def __init__(self, w, layers: int):
+        import oracle
+        self.oracle = oracle
+        need = int(((w.seq_lens.astype(np.int64) + w.block_size - 1) // w.block_size).sum()) + 256
+        pool_blocks = 1 << int(np.ceil(np.log2(need)))
+        s = self.s = cpu_sample_workload(w, layers, pool_blocks)
+        npdt = {"f16": np.uint16, "e4m3": np.uint8, "f32": np.float32}
+        self.src = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.src_dtype], 0xA5)
+        self.dst = oracle.HostPool.filled(layers, s.n_kv_heads, s.head_dim, s.block_size, pool_blocks, npdt[s.dst_dtype], 0x5A,
+                                          with_scales=(s.dst_dtype == "e4m3"))
+        for l in range(layers if s.dst_dtype == "e4m3" else 0):   # values only matter to the FP8 path
+            for kv, arrs in enumerate((self.src.k, self.src.v)):
+                arrs[l][:] = oracle.gen_normal_f16(arrs[l].size, s.seed, 2 * l + kv, s.sigma, s.head_dim,
+                                                   s.outlier_channels, s.outlier_gain)
+        self.batch = oracle.make_batch(s.seq_lens, s.src_tables, s.dst_tables, s.table_stride, s.prefix_lens)
+        self.mode = "copy" if s.src_dtype == s.dst_dtype else "f16_e4m3"
+        self.payload = s.payload_bytes
+        self.what = (f"{layers} of {w.n_layers} layers, all {len(w.seq_lens)} sequences ({self.payload / 1e6:.0f} MB payload per step), "
+                     f"pools shrunk to {pool_blocks} blocks")
+
+    def step(self, threads: int) -> float:
         t0 = time.perf_counter()
-        oracle.handoff(src, dst, batch, None, mode, n_threads=threads)
-        dt = time.perf_counter() - t0
-        best = min(best, dt)
-    payload = s.payload_bytes
-    return payload / best / 1e9, f"{layers} of {w.n_layers} layers, all {len(w.seq_lens)} sequences ({payload / 1e6:.0f} MB payload), pools shrunk to {pool_blocks} blocks; best of {reps}"
+        self.oracle.handoff(self.src, self.dst, self.batch, None, self.mode, n_threads=threads)
+        return time.perf_counter() - t0
+
+
+def time_cpu(w, threads: int, layers: int, reps: int):
+    c = CpuSample(w, layers)
+    c.step(threads)                    # warm-up: page faults of the pools
+    best = min(c.step(threads) for _ in range(reps))
+    return c.payload / best / 1e9, c.what + f"; best of {reps}"
+
+
+def sample_layers(w) -> int:
+    """Layers of the CPU sample: about 2 GB of payload per step for a copy, about 0.3 GB for the FP8 cast."""
+    per_layer = max(1, w.payload_bytes // w.n_layers)
+    budget = 300_000_000 if w.dst_dtype == "e4m3" else 2_200_000_000
+    return int(max(1, min(w.n_layers, budget // per_layer)))
+
+
+def describe(w, world: int, small: bool) -> dict:
+    """The `config` object, the same in both arms."""
+    pairs = max(1, world // 2)
+    strong = w.name.startswith("llama3.1-70b")
+    return {"workload": w.name, "layers": w.n_layers, "kv_heads": w.n_kv_heads * (pairs if strong else 1),
+            "kv_heads_per_pair": w.n_kv_heads, "head_dim": w.head_dim, "block_size": w.block_size, "n_seqs": len(w.seq_lens),
+            "tokens_moved": w.tokens_moved, "payload_bytes": int(w.payload_bytes) * pairs, "pool_blocks": [w.src_blocks, w.dst_blocks],
+            "pairs": pairs,
+            "placement": ("intra-device: prefill pool -> decode pool on one GPU" if world == 1 else
+                          ("one batch, KV heads split over the pairs; " if strong else "every pair its own batch; ") +
+                          "prefill rank i -> decode rank i+N/2, stores into the peer pool from inside the kernel"),
+            "l2": ("256 MB written between timed launches (batch fits L2)" if small else "inputs larger than L2 (no flush needed)")}
+
+
+def is_small(w) -> bool:
+    return w.payload_bytes * 2 < 4 * 126_000_000
+
+
+def default_workload(args) -> str:
+    return args.workload or "cfg5"
 
 
 def run_reference(args):
-    """The reference's CPU handoff (its Rust cannot be built here: the oracle port stands in),
-    on all host cores, on a bounded sample of the same workload."""
+    """The reference's CPU handoff (its Rust cannot be built here: the oracle port stands in), on all host cores.
+    A step is one handoff of a bounded sample of the workload (some of its layers, every sequence, full tables);
+    K steps are timed after W warm-up steps, and `ms_per_step` is the measured time of such a step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    w = pick_workload(args.workload or "cfg2", args.gpus, 4096)
+    world = max(1, args.gpus)
+    w = pick_workload(default_workload(args), world, 4096 if default_workload(args) != "cfg5" else None)
+    pairs = max(1, world // 2)
+    strong = w.name.startswith("llama3.1-70b")
+    # the CPU moves the whole batch (every kv head): the unsharded workload is what it is timed on
+    w_cpu = pick_workload(default_workload(args), 1, 4096 if default_workload(args) != "cfg5" else None) if strong else w
     cores = os.cpu_count() or 1
-    layers = 2 if w.dst_dtype == "e4m3" else 4
-    vals = []
-    t0 = time.perf_counter()
-    for _ in range(max(1, min(args.steps, 5))):
-        v, sample = time_cpu(w, cores, layers, 2)
-        vals.append(v)
-        if time.perf_counter() - t0 > 120:
+    c = CpuSample(w_cpu, sample_layers(w_cpu))
+    for _ in range(max(1, args.warmup)):
+        c.step(cores)
+    steps, t_total, t0 = 0, 0.0, time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        t_total += c.step(cores)
+        steps += 1
+        if time.perf_counter() - t0 > 150:            # bounded: a slow host stops early and says so
             break
-    v = max(vals)
+    ms = t_total / steps * 1e3
+    v = c.payload / (ms * 1e-3) / 1e9
+    sample = c.what + f"; {steps} timed steps after {max(1, args.warmup)} warm-up"
+    full_ms = w_cpu.payload_bytes / (v * 1e9) * 1e3
+    cfg = describe(pick_workload(default_workload(args), world, None), world, is_small(w))
     line = {
         "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup,
-        # the sample's rate applied to the whole batch: what one full handoff would take on these cores
-        "ms_per_step": round(w.payload_bytes / (v * 1e9) * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "steps": steps, "warmup": max(1, args.warmup), "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "strong" if strong else "weak",
         "vs_baseline": None, "dtype": "u16" if w.dst_dtype != "e4m3" else "f16->e4m3", "data": "synthetic",
-        "config": {"workload": w.name, "note": "reference CPU handoff restated in C (oracle port), OpenMP over (sequence, layer, K|V)"},
+        "config": cfg,
+        "note": "reference CPU handoff restated in C (oracle port; the Rust reference has no toolchain here), OpenMP over (sequence, layer, K|V); "
+                "a step moves the sample, not the whole batch",
+        "ms_per_whole_batch_at_this_rate": round(full_ms, 2),
         "cpu_baseline": {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(v, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -299,12 +509,76 @@ def nccl_baseline(H, w, batch, src, dst, is_prefill, partner, local, scales, ste
     payload = w.payload_bytes * pairs
     return {"value": round(payload / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms, 5), "steps": steps,
             "wire_bytes_per_pair": int(used.numel()) + (int(x.scales.numel()) * 4 if scales else 0),
-            "what": "tkv to_transfer kernel -> ncclSend/ncclRecv (torch.distributed) -> tkv from_transfer kernel"}
+            "what": "tkv to_transfer kernel -> ncclSend/ncclRecv (torch.distributed) -> tkv from_transfer kernel, the three stages "
+                    "strictly one after another per step (not pipelined across layers): the plain library route, for comparison only"}
 
 
 # ----------------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------------
+KERNEL_NAMES = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e4m3_warp", 4: "handoff_f16_e4m3_generic",
+                5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant", 8: "handoff_f32_cast_vec"}
+
+
+def time_handoffs(H, plan, w, steps, stream, done_flag, gen):
+    """K handoffs, inputs resident in HBM, device-timed on the launching stream.  A batch whose bytes would fit L2
+    (126 MB) is timed launch by launch with a 256 MB write in between, so every timed launch starts with a cold
+    L2; larger batches run back to back.  Returns (total ms, next flag generation)."""
+    import torch
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if is_small(w):
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        ms = 0.0
+        for i in range(steps):
+            gen += 1
+            flush.fill_(i & 0xFF)
+            ev0.record(stream)
+            plan.enqueue(stream, done_flag, gen)
+            ev1.record(stream)
+            torch.cuda.synchronize()
+            ms += ev0.elapsed_time(ev1)
+        return ms, gen
+    ev0.record(stream)
+    for _ in range(steps):
+        gen += 1
+        plan.enqueue(stream, done_flag, gen)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1), gen
+
+
+def quick_config(H, name, steps, peak):
+    """One of the other benchmark configurations on one GPU, device-timed the same way (no end-to-end legs):
+    extra keys of the line, not the line's value."""
+    import torch
+    w = pick_workload(name, 1, None)
+    scales = w.dst_dtype == "e4m3"
+    src = H.Pool.allocate(0, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, w.src_dtype)
+    dst = H.Pool.allocate(0, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, w.dst_dtype,
+                          scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
+    fill_source(src, w, 4321)
+    batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens)
+    plan = H.Plan(src, dst, batch)
+    stream = torch.cuda.current_stream()
+    for _ in range(3):
+        plan.enqueue(stream)
+    torch.cuda.synchronize()
+    ms, _ = time_handoffs(H, plan, w, steps, stream, 0, 0)
+    par = parity_step(H, w, batch, src, dst, True, 0, False, 0, scales)
+    st = plan.stats()
+    per = ms / steps
+    out = {"workload": w.name, "value": round(st.payload_bytes / (per * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(per, 5),
+           "steps": steps, "frac": round((st.bytes_read + st.bytes_written) / (per * 1e-3) / 1e9 / peak, 4),
+           "kernel": KERNEL_NAMES.get(st.kernel_variant, "?"), "pool_blocks": [w.src_blocks, w.dst_blocks], "parity": par["parity"],
+           "l2": "flushed between launches" if is_small(w) else "inputs larger than L2"}
+    if "oracle_layers" in par:
+        out["oracle_layers"] = par["oracle_layers"]
+    plan.destroy()
+    del src, dst, plan
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -323,7 +597,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if world > 1 and world % 2:
         raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
-    wname = args.workload or "cfg2"
+    wname = default_workload(args)
     w = pick_workload(wname, world, args.pool_blocks, layers=args.layers, single_tokens=args.single_tokens)
     if args.src_f32:                # the reference's own transfer dtype: F32 rows into the F16 cache (one GPU only)
         if world != 1 or w.dst_dtype != "f16":
@@ -331,8 +605,11 @@ def run_ours(args):
         w.src_dtype = "f32"
         w.name += "-f32src"
     from tempura_b200 import disagg
-    role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode)
+    role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode); heads split by tkv_pairing_make
     pairs = max(1, world // 2)
+    strong = wname == "cfg5"                         # one batch, its KV heads split over the pairs
+    if strong and multi and not args.single_tokens:
+        assert w.n_kv_heads == role.n_heads, "the pools hold exactly the pair's share of the KV heads"
     is_prefill, partner = role.is_prefill, role.partner
     dst_dtype = w.dst_dtype
     scales = dst_dtype == "e4m3"
@@ -346,6 +623,7 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
     src = dst = None
+    remote_base = 0
     # completion flag: page-locked host memory on one GPU (the kernel's release store lands where the
     # host polls it, no copy per poll); device memory of the decode GPU when the waiter is another rank
     flag = torch.zeros(4, dtype=torch.int32, device="cuda") if multi else torch.zeros(4, dtype=torch.int32).pin_memory()
@@ -355,13 +633,15 @@ def run_ours(args):
                               scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
         fill_source(src, w, 1234)
     else:
+        # The decode rank announces its pool; the prefill rank of its pair maps it.  What crosses between the
+        # processes is the wire message of the handoff's metadata (tkv_session_pack) plus the IPC handles.
         info = None
         if not is_prefill:
             dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
                                   scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
             hs, off = H.ipc_export(dst.storage.data_ptr())
             hf, foff = H.ipc_export(flag.data_ptr())
-            info = {"pool": (hs, off), "flag": (hf, foff), "base": dst.storage.data_ptr(),
+            info = {"pool": (hs, off), "flag": (hf, foff), "base": dst.storage.data_ptr(), "bytes": dst.storage.numel(),
                     "k": [int(p) for p in dst.k_ptrs], "v": [int(p) for p in dst.v_ptrs], "device": local}
             if scales:
                 info["ks"] = H.ipc_export(dst.k_scales.data_ptr())
@@ -375,6 +655,7 @@ def run_ours(args):
             fill_source(src, w, 1234 + rank)
             pi = infos[partner]
             base = H.ipc_import(*pi["pool"])
+            remote_base, remote_bytes = base, pi["bytes"]
             remote_flag = H.ipc_import(*pi["flag"])
             rel = lambda p: base + (p - pi["base"])
             dst = H.Pool.from_pointers(pi["device"], dst_dtype, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks,
@@ -398,6 +679,36 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- N > 1: the link's own yardstick, measured in this run: a copy-engine copy of 1 GiB from the prefill
+    # pool into the paired decode pool, every pair at once, CUDA events, best of 5 (slowest pair reported) ----
+    peer_copy = None
+    if multi:
+        nbytes = int(min(1 << 30, src.storage.numel() if is_prefill else 1 << 62, remote_bytes if is_prefill else 1 << 62))
+        best = float("inf")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(6):
+            barrier()
+            if is_prefill:
+                e0.record(stream)
+                H.memcpy_enqueue(remote_base, src.storage.data_ptr(), nbytes, stream)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                if it:
+                    best = min(best, e0.elapsed_time(e1))
+        barrier()
+        t = torch.tensor([(nbytes / (best * 1e-3) / 1e9) if is_prefill else 1e30], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        peer_copy = float(t.item())
+        if not is_prefill:                           # the copy wrote over the head of the pool: restore the fill pattern
+            dst.storage[: 1 << 30].fill_(0x5A)
+        barrier()
+
     sampler.start()
     # ---- warm-up -------------------------------------------------------------------------
     gen = 0
@@ -411,42 +722,20 @@ def run_ours(args):
     sampler.mark()
 
     # ---- timed: K handoffs, inputs resident in HBM -------------------------------------------
-    # A batch whose bytes would fit L2 (126 MB) is timed launch by launch with a 256 MB write
-    # in between, so every timed launch starts with a cold L2; larger batches run back to back.
-    small = w.payload_bytes * 2 < 4 * 126_000_000
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if small else None
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    small = is_small(w)
     t_wall0 = time.perf_counter()
-    if is_prefill and small:
-        ms = 0.0
-        for i in range(args.steps):
-            gen += 1
-            flush.fill_(i & 0xFF)
-            ev0.record(stream)
-            plan.enqueue(stream, done_flag, gen)
-            ev1.record(stream)
-            torch.cuda.synchronize()
-            ms += ev0.elapsed_time(ev1)
-    elif is_prefill:
-        ev0.record(stream)
-        for _ in range(args.steps):
-            gen += 1
-            plan.enqueue(stream, done_flag, gen)
-        ev1.record(stream)
-        torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1)
+    if is_prefill:
+        ms, gen = time_handoffs(H, plan, w, args.steps, stream, done_flag, gen)
     else:
         gen += args.steps
-        H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
-        ms = (time.perf_counter() - t_wall0) * 1e3
+        H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+        ms = 0.0                                      # the prefill rank's CUDA events time the pair
     barrier()
-    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-    if multi:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
+    sampler.mark()
+    ms_total = max_over_ranks(ms)
 
     # ---- end to end, device-resident pools: host tables -> plan update (H2D work list) -> kernel -> D2H flag
-    e2e_steps = args.steps
+    e2e_steps = max(1, min(args.steps, 50))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -457,17 +746,15 @@ def run_ours(args):
             if not multi:
                 H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
         else:
-            H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
+            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
     torch.cuda.synchronize()
     res_s = time.perf_counter() - t0
     barrier()
-    t = torch.tensor([res_s], dtype=torch.float64, device="cuda")
-    if multi:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    res_s = float(t.item())
+    res_s = max_over_ranks(res_s)
 
-    if not multi:
-        spot_check(src, dst, w, w.n_layers - 1)
+    # ---- parity, not timed: every moved row of every layer, at every N ------------------------
+    parity = parity_step(H, w, batch, src, dst, is_prefill, partner, multi, local, scales)
+    barrier()
 
     # ---- end to end, HOST buffers: the prompts' K/V sit in page-locked host memory in the contiguous
     # transfer layout (the reference's KvCacheTransfer); every step uploads the tables, runs the
@@ -506,71 +793,83 @@ def run_ours(args):
     torch.cuda.synchronize()
     host_s = time.perf_counter() - t0
     barrier()
-    t = torch.tensor([host_s], dtype=torch.float64, device="cuda")
-    if multi:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    host_s = float(t.item())
+    host_s = max_over_ranks(host_s)
     host_h2d = (plan_h.stats().payload_bytes + plan_h.stats().worklist_bytes) if is_prefill else 0
+    per_rank_h2d = torch.tensor([host_h2d * host_steps / host_s / 1e9 if is_prefill else 0.0], dtype=torch.float64, device="cuda")
+    h2d_rates = [per_rank_h2d.clone() for _ in range(world)] if multi else [per_rank_h2d]
+    if multi:
+        dist.all_gather(h2d_rates, per_rank_h2d)
     del plan_h, xfer
 
     # ---- comparison baseline (N > 1): pack kernel -> NCCL send/recv -> scatter kernel ------------------
     nccl = None
     if multi and not args.no_nccl:
         nccl = nccl_baseline(H, w, batch, src, dst, is_prefill, partner, local, scales, max(3, min(args.steps, 10)), barrier)
-    sampler.mark()
     clocks = sampler.stop()
 
     if rank == 0:
         st = plan.stats()
-        payload_all = st.payload_bytes * pairs                      # every pair moves its own batch
+        payload_all = st.payload_bytes * pairs       # strong: the pairs' shares add up to the one batch; weak: every pair its own batch
         per_launch_ms = ms_total / args.steps
         value = payload_all / (per_launch_ms * 1e-3) / 1e9
         peak, peak_kind = measured_peaks()
         algo = st.bytes_read + st.bytes_written                     # one launch, one GPU
-        if multi:
-            bound, peak_used, algo_used, peak_note = "nvlink", 770.0, st.bytes_written, "measured peer copy, per direction"
-        else:
-            bound, peak_used, algo_used, peak_note = "hbm", peak, algo, f"{peak_kind} copy peak"
-        achieved = algo_used / (per_launch_ms * 1e-3) / 1e9
-        kname = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e4m3_warp", 4: "handoff_f16_e4m3_generic",
-                 5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant",
-                 8: "handoff_f32_cast_vec"}.get(st.kernel_variant, "?")
+        kname = KERNEL_NAMES.get(st.kernel_variant, "?")
         ratio = NCU_TRAFFIC_RATIO.get(kname)
+        if multi:
+            wire = st.bytes_written                                  # what one prefill GPU stores into its decode GPU per launch
+            achieved = wire / (per_launch_ms * 1e-3) / 1e9
+            roofline = {"bound": "nvlink", "achieved": round(achieved, 1), "peak": round(peer_copy, 1), "unit": "GB/s",
+                        "frac": round(achieved / peer_copy, 4), "traffic": int(wire), "algorithmic_bytes": int(wire),
+                        "peak_source": "copy-engine copy of 1 GiB prefill pool -> paired decode pool measured in this run, every pair at once, best of 5, slowest pair",
+                        "traffic_source": "wire bytes: what one prefill GPU stores into its decode GPU per launch (no ncu capture wraps a multi-rank run)",
+                        "frac_of_nominal_900": round(achieved / 900.0, 4), "per": "pair, one direction"}
+        else:
+            achieved = algo / (per_launch_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                        "frac": round(achieved / peak, 4), "traffic": (int(ratio * algo) if ratio else None),
+                        "algorithmic_bytes": int(algo), "peak_source": f"{peak_kind} copy peak (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+                        "frac_of_nominal_8000": round(achieved / 8000.0, 4)}
+        cfg = describe(w, world, small)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": ("f32->f16" if w.src_dtype == "f32" else "u16") if dst_dtype == "f16" else "f16->e4m3",
-            "data": "synthetic",
-            "config": {"workload": w.name, "layers": w.n_layers, "kv_heads": w.n_kv_heads, "head_dim": w.head_dim,
-                       "block_size": w.block_size, "n_seqs": len(w.seq_lens), "tokens_moved": w.tokens_moved,
-                       "payload_bytes_per_pair": int(st.payload_bytes), "pool_blocks": [w.src_blocks, w.dst_blocks],
-                       "pairs": pairs, "placement": "intra-device" if not multi else "prefill rank i -> decode rank i+N/2, peer stores",
-                       "l2": ("256 MB written between timed launches (batch fits L2)" if small else "inputs larger than L2 (no flush needed)"), "kernel": kname, "grid": [st.grid, st.block]},
-            "roofline": {"bound": bound, "achieved": round(achieved, 1), "peak": peak_used, "unit": "GB/s",
-                         "frac": round(achieved / peak_used, 4), "traffic": (int(ratio * algo) if ratio else None),
-                         "algorithmic_bytes": int(algo_used), "peak_source": peak_note,
-                         "frac_of_nominal_8000": round(achieved / 8000.0, 4) if not multi else None},
+            "data": "synthetic", "config": cfg,
+            "launch": {"kernel": kname, "grid": [st.grid, st.block]},
+            "parity": parity["parity"], "parity_detail": {k: v for k, v in parity.items() if k != "parity"},
+            "roofline": roofline,
             "e2e": {"value": round(payload_all * host_layers / w.n_layers * host_steps / host_s / 1e9, 2), "unit": UNIT,
                     "h2d_bytes_per_step": int(host_h2d), "d2h_bytes_per_step": 4, "steps": host_steps,
-                    "layers": host_layers,
+                    "layers": host_layers, "h2d_GBps_per_prefill_rank": [round(float(r.item()), 2) for r in h2d_rates[:pairs]],
                     "what": "K/V of the batch in page-locked HOST memory (contiguous transfer layout) + host block tables -> "
                             "tkv_plan_update -> tkv_handoff_enqueue of a from_transfer plan (the kernel reads the host buffer "
                             "over PCIe and stores into the decode pool) -> flag read back"},
             "e2e_resident": {"value": round(payload_all * e2e_steps / res_s / 1e9, 2), "unit": UNIT,
-                             "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4,
+                             "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                              "what": "same call sequence with the K/V already in the prefill GPU's paged pool (where prefill "
                                      "wrote it): host block tables -> tkv_plan_update -> tkv_handoff_enqueue -> flag read back"},
-            "gpu_launches": args.warmup + args.steps + e2e_steps + 1 + host_steps,
+            "gpu_launches": args.steps,              # one handoff kernel per timed step
+            "gpu_launches_whole_run": args.warmup + args.steps + e2e_steps + 1 + host_steps,
             "clocks": clocks,
         }
         if nccl is not None:
             line["nccl_baseline"] = nccl
         if not multi and not args.no_cpu:
-            layers = 2 if dst_dtype == "e4m3" else 4
+            layers = sample_layers(w)
             v1, sample = time_cpu(w, 1, layers, 3)
             vall, _ = time_cpu(w, os.cpu_count() or 1, layers, 3)
             line["cpu_baseline"] = {"value": round(v1, 3), "unit": UNIT, "cores": 1, "kind": "port", "sample": sample,
                                     "all_cores": {"value": round(vall, 3), "cores": os.cpu_count() or 1}}
+    if not multi and args.others and not (args.workload or args.single_tokens or args.layers or args.src_f32):
+        # the other benchmark configurations on this GPU, device-timed and parity-checked the same way
+        plan.destroy()
+        del src, dst, plan
+        torch.cuda.empty_cache()
+        peak, _ = measured_peaks()
+        line["other_configs"] = {name: quick_config(H, name, 20, peak) for name in ("cfg1", "cfg2", "cfg3", "cfg4")}
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if multi:
         dist.barrier()
@@ -842,6 +1141,8 @@ def main():
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-others", dest="others", action="store_false",
+                    help="N = 1 default run: skip the other four configurations (extra keys of the line)")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")
     ap.add_argument("--host-bulk", action="store_true", help="host-buffer leg: bulk-copy ring reading the pinned buffer (experiment)")
     ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")

@@ -299,6 +299,14 @@ int32_t tkv_selfcheck_e4m3(uint32_t skip_bits, uint64_t* mismatches);
  * every finite non-zero block amax and every F16 value of magnitude <= amax.       */
 int32_t tkv_selfcheck_scaled_quant(uint64_t* mismatches);
 
+/* ---- contiguous copies (engine/src/cutile_kv_cache.rs:449-468,619-631) ------- */
+/* The copy-engine route: one asynchronous copy of `bytes` on `stream` between any two
+ * addresses the stream's device can reach (its own memory, a peer pool mapped by tkv_init
+ * or tkv_ipc_import, page-locked host memory).  This is what the reference's per-layer
+ * cuMemcpyDtoDAsync / DtoHAsync / HtoDAsync calls are; contiguous runs (a GpuKvRun's live
+ * prefix) can keep using it, and the benchmark uses it as its peer-copy yardstick.       */
+int32_t tkv_memcpy_enqueue(uint64_t dst, uint64_t src, uint64_t bytes, void* stream);
+
 /* ---- bits checksum (engine/src/cutile_kv_cache.rs:1274-1368) --------------- */
 /* Wrapping sum of the f32 bit patterns of n elements (narrow dtypes widened). */
 int32_t tkv_bits_checksum(uint64_t data, int32_t dtype, uint64_t n, void* stream, uint64_t* out);

@@ -150,6 +150,7 @@ SIGNATURES = {
     "tkv_cast": (_i32, [_u64, _i32, _u64, _i32, _u64, _vp]),
     "tkv_selfcheck_e4m3": (_i32, [_u32, _u64p]),
     "tkv_selfcheck_scaled_quant": (_i32, [_u64p]),
+    "tkv_memcpy_enqueue": (_i32, [_u64, _u64, _u64, _vp]),
     "tkv_bits_checksum": (_i32, [_u64, _i32, _u64, _vp, _u64p]),
     "tkv_ipc_export": (_i32, [_u64, _u8p, _u64p]),
     "tkv_ipc_import": (_i32, [_u8p, _u64, _u64p]),

@@ -1111,6 +1111,14 @@ int32_t tkv_selfcheck_scaled_quant(uint64_t* mismatches) {
     return TKV_OK;
 }
 
+int32_t tkv_memcpy_enqueue(uint64_t dst, uint64_t src, uint64_t bytes, void* stream) {
+    if (bytes == 0) return TKV_OK;
+    if (!dst || !src) return fail(TKV_ERR_INVALID_CONFIG, "NULL buffer");
+    CU(cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), bytes, cudaMemcpyDefault,
+                       static_cast<cudaStream_t>(stream)));
+    return TKV_OK;
+}
+
 int32_t tkv_bits_checksum(uint64_t data, int32_t dtype, uint64_t n, void* stream, uint64_t* out) {
     if (!out || (!data && n)) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -339,6 +339,14 @@ def cast(src: torch.Tensor, dst: torch.Tensor, src_dtype: str, dst_dtype: str) -
                          C.c_void_p(st.cuda_stream)))
 
 
+def memcpy_enqueue(dst_ptr: int, src_ptr: int, nbytes: int, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """One asynchronous copy-engine copy between two addresses the current device can reach (local memory, a mapped
+    peer pool, pinned host memory): the reference's cuMemcpyDtoDAsync call sites (engine/src/cutile_kv_cache.rs:449-468)."""
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    check(lib().tkv_memcpy_enqueue(dst_ptr, src_ptr, nbytes, C.c_void_p(stream.cuda_stream)))
+
+
 def bits_checksum(t: torch.Tensor, dtype: str) -> int:
     out = C.c_uint64(0)
     st = torch.cuda.current_stream(t.device)
