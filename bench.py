@@ -62,7 +62,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
         except OSError:
             self.proc = None
             return
@@ -671,6 +671,8 @@ def run_ours(args):
             plan.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
         if args.grid_tune:
             plan.tune_grid(args.grid_tune)
+        if args.vec_tune:
+            plan.tune_vector(*[int(x) for x in args.vec_tune.split(",")])
     stream = torch.cuda.current_stream()
     done_flag = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
 
@@ -733,6 +735,22 @@ def run_ours(args):
     barrier()
     sampler.mark()
     ms_total = max_over_ranks(ms)
+
+    if args.sweep:
+        if rank == 0:
+            st = plan.stats()
+            per = ms_total / args.steps
+            bytes_moved = st.bytes_written if multi else st.bytes_read + st.bytes_written
+            print(json.dumps({"sweep": True, "workload": w.name, "n_gpus": world, "ms_per_step": round(per, 5),
+                              "value": round(st.payload_bytes * pairs / (per * 1e-3) / 1e9, 2),
+                              "achieved": round(bytes_moved / (per * 1e-3) / 1e9, 1), "peer_copy_GBps": peer_copy,
+                              "kernel": KERNEL_NAMES.get(st.kernel_variant, "?"), "grid": [st.grid, st.block], "clocks": sampler.stop()}), flush=True)
+        else:
+            sampler.stop()
+        if multi:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---- end to end, device-resident pools: host tables -> plan update (H2D work list) -> kernel -> D2H flag
     e2e_steps = max(1, min(args.steps, 50))
@@ -911,7 +929,8 @@ def run_attention(args):
     sampler = ClockSampler(0)
     sampler.start()
 
-    attn = H.DecodeAttention(pool, q, tables, lens, max_len, split_tokens=args.attn_split, flags=1 if args.attn_per_head else 0,
+    attn = H.DecodeAttention(pool, q, tables, lens, max_len, split_tokens=args.attn_split,
+                             flags=(1 if args.attn_per_head else 0) | (2 if args.attn_mma_sync else 0),
                              total_kv_tokens=0 if args.attn_no_hint else int(w.seq_lens.astype(np.int64).sum()))
     for layer in range(w.n_layers):          # plain launches first (module load, argument structs)
         attn.enqueue(layer)
@@ -946,7 +965,9 @@ def run_attention(args):
     print(json.dumps({
         "metric": "paged_decode_attention_GBps", "value": round(achieved, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 5), "us_per_layer": round(ms * 1e3 / w.n_layers, 2), "higher_is_better": True,
-        "dtype": "e4m3+scales -> f16 mma, f32 accumulate" if fp8 else "f16 mma, f32 accumulate", "data": "synthetic",
+        "dtype": ("e4m3+scales -> f16 mma.sync, f32 accumulate" if fp8 else "f16 mma.sync, f32 accumulate") if (args.attn_mma_sync or args.attn_per_head)
+                 else ("e4m3 x e4m3 / e4m3 x e5m2 tcgen05.mma, f32 accumulate in tensor memory" if fp8 else "f16 tcgen05.mma, f32 accumulate in tensor memory"),
+        "data": "synthetic",
         "config": {"workload": w.name + "-decode-attention", "layers": w.n_layers, "kv_heads": 8, "q_heads": n_q, "head_dim": 128,
                    "n_seqs": n, "cached_tokens": tokens, "l2": "each layer's K/V is read once per step; a step reads more than L2 holds"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
@@ -1131,6 +1152,7 @@ def main():
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
     ap.add_argument("--attn-seqs", type=int, default=None, help="--workload attn: this many prompts instead of the configuration's 16")
     ap.add_argument("--attn-per-head", action="store_true", help="--workload attn: the per-(sequence, kv head) CTA form")
+    ap.add_argument("--attn-mma-sync", action="store_true", help="--workload attn: the warp-level mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--attn-f16", action="store_true", help="--workload attn: read the F16 pool instead of the E4M3 one")
     ap.add_argument("--pool-blocks", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep the batch, use fewer layers")
@@ -1139,8 +1161,10 @@ def main():
     ap.add_argument("--variant", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
+    ap.add_argument("--vec-tune", default=None, help="bytes_per_access,unroll,store_hint for the register copy kernel (e.g. 32,8,0)")
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sweep", action="store_true", help="tuning aid: the device-timed region only (no end-to-end legs, no parity step, no baselines)")
     ap.add_argument("--no-others", dest="others", action="store_false",
                     help="N = 1 default run: skip the other four configurations (extra keys of the line)")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")

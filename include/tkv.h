@@ -253,6 +253,11 @@ int32_t tkv_handoff_noalloc(const TkvPool* src, const TkvPool* dst, const TkvBat
  * counterpart.
  * Takes effect at the next enqueue.                                             */
 int32_t tkv_plan_tune_bulk(tkv_plan* plan, uint32_t stages, uint32_t ctas_per_sm, uint32_t stage_bytes);
+/* The register copy kernel's access shape: bytes per load / store (16, or 32 where every address keeps
+ * 32-byte alignment and chunks are contiguous; 0 = the library's choice), loads a thread keeps in flight
+ * (4, 8, 16; the 32-byte kernel only), cache policy of the stores (0 default, 1 streaming, 2 no L1
+ * allocation; the 32-byte kernel only).  No reference counterpart.  Takes effect at the next enqueue. */
+int32_t tkv_plan_tune_vector(tkv_plan* plan, uint32_t bytes_per_access, uint32_t unroll, uint32_t store_hint);
 /* Caps the resident CTAs per SM of the register (non-bulk) kernels; 0 = as many as fit. */
 int32_t tkv_plan_tune_grid(tkv_plan* plan, uint32_t ctas_per_sm);
 /* Reads the plan's device-side error word (synchronous): 0, or 1 when a kernel of
@@ -313,7 +318,10 @@ int32_t tkv_bits_checksum(uint64_t data, int32_t dtype, uint64_t n, void* stream
 
 /* ---- cross-process mapping of a destination pool --------------------------- */
 /* One process per GPU: the decode process exports its pool allocation, the
- * prefill process imports it and uses the mapped address in TkvPool.          */
+ * prefill process imports it and uses the mapped address in TkvPool.  The
+ * import is made on the current device and its address range is remembered:
+ * a plan whose destination layer pointers lie inside it passes the peer check
+ * whatever ordinal the pool gives the owning device.                          */
 int32_t tkv_ipc_export(uint64_t devptr, uint8_t handle[64], uint64_t* offset_in_allocation);
 int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset_in_allocation, uint64_t* devptr);
 int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset_in_allocation);
@@ -350,11 +358,19 @@ typedef struct TkvDecodeAttn {
                                      named a block outside the pool (never read); the output is then not valid */
 } TkvDecodeAttn;
 enum { TKV_ATTN_DEFAULT = 0,
-       TKV_ATTN_PER_HEAD_CTAS = 1 /* one CTA per (sequence, kv head, split) with per-lane copies, the
-                                     form used when a pool has more than 8 kv heads               */ };
+       TKV_ATTN_PER_HEAD_CTAS = 1, /* one CTA per (sequence, kv head, split) with per-lane copies, the
+                                      form used when a pool has more than 8 kv heads               */
+       TKV_ATTN_MMA_SYNC = 2       /* whole-block form on warp-level mma.sync instead of tcgen05 with
+                                      tensor-memory accumulators (the default where the shape allows:
+                                      8 kv heads, 4 query heads per kv head)                        */ };
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens /* 0 = default */);
 int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* args, void* stream);
+/* Device self-check of the tcgen05 path's operand plumbing (tensor-map copy with the 128-byte swizzle,
+ * shared-memory and instruction descriptors, tensor-memory reads) on operands of small dyadic values whose
+ * products and sums are exact: mismatches[0..3] count wrong accumulators for E4M3 K-major, E4M3 x E5M2
+ * MN-major, F16 K-major and F16 MN-major operands.  No reference counterpart.                        */
+int32_t tkv_selfcheck_tensor_cores(uint64_t mismatches[4]);
 
 /* ---- the handoff's metadata on the wire -------------------------------------- */
 /* SessionTransfer {cache, position, seed, last_logits} (engine/src/session.rs:194-200)

@@ -24,6 +24,7 @@ STATUS_NAMES = {0: "Ok", 1: "DimensionMismatch", 2: "InvalidConfig", 3: "CudaErr
 DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
 PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER, PLAN_PEER_BULK_STORES = 1, 2, 4, 8, 16
 ATTN_PER_HEAD_CTAS = 1
+ATTN_MMA_SYNC = 2
 VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC, VARIANT_FP8_STAGED, VARIANT_DEQUANT, VARIANT_CAST_VEC = 1, 2, 3, 4, 5, 6, 7, 8
 
 
@@ -141,6 +142,7 @@ SIGNATURES = {
     "tkv_handoff_enqueue": (_i32, [_vp, _vp, _u64, _u32]),
     "tkv_handoff_noalloc": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPool), C.POINTER(TkvBatch), C.POINTER(TkvShard), _vp]),
     "tkv_plan_tune_bulk": (_i32, [_vp, _u32, _u32, _u32]),
+    "tkv_plan_tune_vector": (_i32, [_vp, _u32, _u32, _u32]),
     "tkv_plan_tune_grid": (_i32, [_vp, _u32]),
     "tkv_plan_error": (_i32, [_vp, _u32p]),
     "tkv_flag_wait_host": (_i32, [_i32, _u64, _u32, _u64]),
@@ -157,6 +159,7 @@ SIGNATURES = {
     "tkv_ipc_close": (_i32, [_u64, _u64]),
     "tkv_decode_attn_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
     "tkv_decode_attn_enqueue": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvDecodeAttn), _vp]),
+    "tkv_selfcheck_tensor_cores": (_i32, [_u64p]),
     "tkv_session_wire_size": (_sz, [C.POINTER(TkvSessionHeader)]),
     "tkv_session_pack": (_i32, [C.POINTER(TkvSessionHeader), _u32p, C.POINTER(C.c_float), _u8p, _sz, _szp]),
     "tkv_session_unpack": (_i32, [_u8p, _sz, C.POINTER(TkvSessionHeader), C.POINTER(_u32p), C.POINTER(C.POINTER(C.c_float))]),

@@ -25,6 +25,7 @@
 #include <cstdio>
 
 #include "../../include/tkv.h"
+#include "tkv_attention_tc.h"
 
 namespace tkv_internal {
 int32_t set_error(int32_t code, int32_t cuda_code, const char* text);
@@ -852,6 +853,17 @@ uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint
     return (uint64_t)n_seqs * n_q_heads * splits_for(max_kv_len, split_tokens) * (head_dim + 2) * sizeof(float);
 }
 
+int32_t tkv_selfcheck_tensor_cores(uint64_t mismatches[4]) {
+    if (!mismatches) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    const cudaError_t e = tkv_tc::selfcheck(mismatches);
+    if (e != cudaSuccess) {
+        char buf[256];
+        snprintf(buf, sizeof buf, "tensor-core self-check: %s (cuda error %d)", cudaGetErrorString(e), (int)e);
+        return tkv_internal::set_error(TKV_ERR_CUDA, (int32_t)e, buf);
+    }
+    return TKV_OK;
+}
+
 int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, void* stream) {
     if (!pool || !d) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
     if (pool->dtype != TKV_DTYPE_F16 && pool->dtype != TKV_DTYPE_E4M3)
@@ -941,7 +953,31 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
     if (e == cudaSuccess) {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         dim3 grid(n_splits, pool->n_kv_heads, d->n_seqs);
-        if (whole_blocks) {
+        const bool tensor_memory = whole_blocks && !(d->flags & TKV_ATTN_MMA_SYNC) &&
+                                   tkv_tc::eligible(pool->n_kv_heads, a.group, pool->k_scales != 0, pool->total_blocks);
+        if (tensor_memory) {
+            // the tcgen05 kernel: K and V tiles straight from shared memory into the tensor cores, accumulators in tensor memory
+            tkv_tc::Args t{};
+            t.k_scales = a.k_scales;
+            t.v_scales = a.v_scales;
+            t.q = a.q;
+            t.tables = a.tables;
+            t.kv_lens = a.kv_lens;
+            t.partial = a.partial;
+            t.n_q_heads = a.n_q_heads;
+            t.table_stride = a.table_stride;
+            t.n_splits = n_splits;
+            t.split_tokens = split_tokens;
+            t.max_kv_len = a.max_kv_len;
+            t.total_blocks = a.total_blocks;
+            t.q_scale = a.q_scale;
+            t.status = a.status;
+            e = tkv_tc::launch(pool->dtype == TKV_DTYPE_E4M3, a.group, kp, vp, t, n_splits, d->n_seqs, st);
+            if (e == cudaSuccess) {
+                decode_attn_combine<<<dim3(d->n_q_heads, d->n_seqs), D, 0, st>>>(a);
+                e = cudaGetLastError();
+            }
+        } else if (whole_blocks) {
             const uint32_t n_stages = std::min<uint32_t>(6u, (200u * 1024u - 256u) / stage_bytes);
             const size_t smem = 256 + (size_t)n_stages * stage_bytes;
             dim3 grid2(n_splits, d->n_seqs);

@@ -1,0 +1,29 @@
+// Interface between the decode-attention entry point (tkv_attention.cu) and its tcgen05 kernel (tkv_attention_tc.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tkv_tc {
+
+struct Args {
+    const float* k_scales;        // [total_blocks][8] of this layer, or null
+    const float* v_scales;
+    const float* q;               // [n_seqs][n_q_heads][128]
+    const uint32_t* tables;       // [n_seqs][table_stride]
+    const uint32_t* kv_lens;
+    float* partial;               // [n_seqs][8][n_splits][group][128 + 2]: running maximum, row sum, 128 numerators
+    uint32_t n_q_heads, table_stride, n_splits, split_tokens, max_kv_len, total_blocks;
+    float q_scale;                // softmax scale * log2(e)
+    uint32_t* status;             // optional device word: first failure wins
+};
+
+// 8 kv heads of 128 dims in 16-token blocks (one block = one 128-row operand tile), 4 query heads per kv head
+bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t total_blocks);
+// launches on the current device; layer tensors as raw device addresses
+cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer, const Args& a, uint32_t n_splits, uint32_t n_seqs, cudaStream_t st);
+
+// operand plumbing of the tcgen05 path (tensor-map copy, swizzle, descriptors, tensor-memory reads) on exact small cases:
+// out[0..3] = mismatches of {E4M3 K-major, E4M3 x E5M2 MN-major, F16 K-major, F16 MN-major}
+cudaError_t selfcheck(uint64_t out[4]);
+
+}  // namespace tkv_tc

@@ -170,6 +170,58 @@ __global__ void __launch_bounds__(256) handoff_copy_vec(const HandoffArgs a) {
 }
 
 // ---------------------------------------------------------------------------------
+// Same-dtype handoff, 32 bytes per access (contiguous chunks, everything 32-byte aligned):
+// a warp's load or store instruction covers 1 KiB of one chunk, so a store that leaves the
+// GPU travels in the widest packets the link takes.  Built for peer destinations; HINT picks
+// the store's cache policy (0 default, 1 streaming, 2 no L1 allocation).
+// ---------------------------------------------------------------------------------
+struct Vec32 {
+    uint32_t r[8];
+};
+__device__ __forceinline__ Vec32 ld_stream32(const void* p) {
+    Vec32 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
+                 : "l"(p));
+    return v;
+}
+template <int HINT> __device__ __forceinline__ void st32(void* p, const Vec32& v) {
+    if (HINT == 1)
+        asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]), "r"(v.r[1]), "r"(v.r[2]), "r"(v.r[3]),
+                     "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7]) : "memory");
+    else if (HINT == 2)
+        asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]), "r"(v.r[1]), "r"(v.r[2]),
+                     "r"(v.r[3]), "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7]) : "memory");
+    else
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]), "r"(v.r[1]), "r"(v.r[2]), "r"(v.r[3]),
+                     "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7]) : "memory");
+}
+
+template <int UNROLL, int HINT>
+__global__ void __launch_bounds__(256) handoff_copy_wide(const HandoffArgs a) {
+    const uint32_t total = live_pairs(a) * a.n_layers * 2u;
+    const uint32_t vec_per_row = a.src_row_bytes / 32u;
+    for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
+        const Chunk c = decode_chunk(a, w);
+        const uint32_t nvec = c.n_valid * vec_per_row;
+        for (uint32_t base = 0; base < nvec; base += 256u * UNROLL) {
+            Vec32 v[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const uint32_t i = base + u * 256u + threadIdx.x;
+                if (i < nvec) v[u] = ld_stream32(c.src + (size_t)i * 32u);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const uint32_t i = base + u * 256u + threadIdx.x;
+                if (i < nvec) st32<HINT>(c.dst + (size_t)i * 32u, v[u]);
+            }
+        }
+    }
+    signal_done(a);
+}
+
+// ---------------------------------------------------------------------------------
 // Same-dtype handoff, bulk-copy path (same device, contiguous chunks): one warp per
 // CTA; lane 0 drives a ring of shared-memory stages with the bulk async-copy engine
 // (cp.async.bulk global->shared completing on an mbarrier, then shared->global as a

@@ -65,6 +65,12 @@ cudaStream_t g_copy_stream[64] = {};
 // g_peer[a][b]: device a may store into device b's memory because THIS library enabled the mapping
 // (tkv_init) or opened it (tkv_ipc_import).  cudaDeviceCanAccessPeer only says the hardware could.
 bool g_peer[64][64] = {};
+// Allocations of other processes opened by tkv_ipc_import: [base, base + size) as seen from `device`.
+struct Imported {
+    int device;
+    uint64_t base, size;
+};
+std::vector<Imported> g_imported;
 
 int32_t dev_info(int dev, DevInfo* out) {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -96,6 +102,32 @@ bool peer_reachable(int from, int to) {
     if (from < 0 || to < 0 || from >= 64 || to >= 64) return false;
     std::lock_guard<std::mutex> lk(g_mu);
     return g_peer[from][to];
+}
+// Every address lies in an allocation that `from` opened through tkv_ipc_import (the mapping itself is what makes it reachable).
+bool imported_on(int from, const uint64_t* ptrs, size_t n) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (size_t i = 0; i < n; i++) {
+        bool hit = false;
+        for (const Imported& m : g_imported)
+            if (m.device == from && ptrs[i] >= m.base && ptrs[i] < m.base + m.size) {
+                hit = true;
+                break;
+            }
+        if (!hit) return false;
+    }
+    return n > 0;
+}
+void note_import(int device, uint64_t base, uint64_t size) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_imported.push_back(Imported{device, base, size});
+}
+void forget_import(uint64_t base) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (size_t i = 0; i < g_imported.size(); i++)
+        if (g_imported[i].base == base) {
+            g_imported.erase(g_imported.begin() + i);
+            break;
+        }
 }
 void mark_peer(int from, int to) {
     if (from < 0 || to < 0 || from >= 64 || to >= 64) return;
@@ -134,6 +166,7 @@ struct tkv_plan {
     uint32_t grid = 0;
     uint32_t bulk_stages = 3, bulk_ctas_per_sm = 0, bulk_stage_bytes = 32768;  // ctas 0 = derive from the stage size
     uint32_t fp8_stages = 2;         // staged FP8 kernel: ring depth per CTA
+    uint32_t vec_bytes = 0, vec_unroll = 8, vec_hint = 0;   // register copy kernel: bytes per access (0 = the library's choice), loads in flight per thread, store cache policy
     uint32_t grid_ctas_per_sm = 0;   // cap for the register kernels (0 = occupancy limit)   // ring depth and residency of the bulk-copy kernel
     std::vector<uint8_t> seen;  // scratch bitmap over destination blocks
     std::vector<char> image;    // host image of the device block, built before any CUDA call
@@ -305,7 +338,8 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
 
     // A kernel on the source device stores into the destination pool: refuse a pair whose peer mapping this
     // library has not set up, rather than launch stores at addresses the device cannot reach.
-    if (!tkv_internal::peer_reachable(s.device, d.device))
+    if (!tkv_internal::peer_reachable(s.device, d.device) && !(tkv_internal::imported_on(s.device, p->dst_k.data(), p->dst_k.size()) &&
+                                                               tkv_internal::imported_on(s.device, p->dst_v.data(), p->dst_v.size())))
         return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot store into device %d: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
                     s.device, d.device);
     // ---- everything above is pure host logic; CUDA starts here ----
@@ -582,6 +616,26 @@ template <bool HW, bool SCALED> int32_t launch_fp8(tkv_plan* p, cudaStream_t st)
     return launch(tkv::handoff_f16_e4m3_generic<HW, SCALED>, p, ctas, st);
 }
 
+// 32-byte accesses: contiguous chunks whose addresses and strides all keep 32-byte alignment, no scales riding along.
+bool wide_eligible(const tkv_plan* p) {
+    const tkv::HandoffArgs& a = p->args;
+    if (p->vec_bytes != 32 || p->mode != MODE_COPY || !a.contiguous || p->vec != 16 || a.src_k_scales != nullptr) return false;
+    if (a.src_row_bytes % 32 || a.src_block_stride % 32 || a.dst_block_stride % 32 || a.src_head_off % 32 || a.dst_head_off % 32) return false;
+    const uint64_t* ptrs = reinterpret_cast<const uint64_t*>(p->h_buf);
+    for (size_t l = 0; l < 4 * (size_t)a.n_layers; l++)
+        if (ptrs[l] % 32) return false;
+    return true;
+}
+
+int32_t launch_wide(tkv_plan* p, uint64_t chunks, cudaStream_t st) {
+    const uint32_t u = p->vec_unroll, h = p->vec_hint;
+#define TKV_WIDE(U, H) \
+    if (u == U && h == H) return launch(tkv::handoff_copy_wide<U, H>, p, chunks, st);
+    TKV_WIDE(4, 0) TKV_WIDE(4, 1) TKV_WIDE(4, 2) TKV_WIDE(8, 0) TKV_WIDE(8, 1) TKV_WIDE(8, 2) TKV_WIDE(16, 0) TKV_WIDE(16, 1) TKV_WIDE(16, 2)
+#undef TKV_WIDE
+    return fail(TKV_ERR_INVALID_CONFIG, "no 32-byte copy kernel for unroll %u, store hint %u", u, h);
+}
+
 }  // namespace
 
 static int32_t dispatch(tkv_plan* p, uint64_t chunks, cudaStream_t st);
@@ -838,6 +892,7 @@ static int32_t dispatch(tkv_plan* p, uint64_t chunks, cudaStream_t st) {
             }
             if (!(p->flags & TKV_PLAN_FORCE_VECTOR) && bulk_eligible(p)) return launch_bulk(p, st);
             p->variant = TKV_VARIANT_VECTOR;
+            if (wide_eligible(p)) return launch_wide(p, chunks, st);
             switch (p->vec) {
                 case 16: return launch(tkv::handoff_copy_vec<16, 8>, p, chunks, st);
                 case 8: return launch(tkv::handoff_copy_vec<8, 8>, p, chunks, st);
@@ -945,6 +1000,16 @@ int32_t tkv_plan_tune_bulk(tkv_plan* p, uint32_t stages, uint32_t ctas_per_sm, u
     p->fp8_stages = stages;
     p->bulk_ctas_per_sm = ctas_per_sm;
     p->bulk_stage_bytes = stage_bytes;
+    return TKV_OK;
+}
+
+int32_t tkv_plan_tune_vector(tkv_plan* p, uint32_t bytes_per_access, uint32_t unroll, uint32_t store_hint) {
+    if (!p) return fail(TKV_ERR_INVALID_CONFIG, "NULL plan");
+    if ((bytes_per_access != 0 && bytes_per_access != 16 && bytes_per_access != 32) || (unroll != 4 && unroll != 8 && unroll != 16) || store_hint > 2)
+        return fail(TKV_ERR_INVALID_CONFIG, "bytes_per_access must be 0, 16 or 32, unroll 4, 8 or 16, store_hint 0, 1 or 2");
+    p->vec_bytes = bytes_per_access;
+    p->vec_unroll = unroll;
+    p->vec_hint = store_hint;
     return TKV_OK;
 }
 
@@ -1172,18 +1237,28 @@ int32_t tkv_ipc_import(const uint8_t handle[64], uint64_t offset, uint64_t* devp
     void* base = nullptr;
     CU(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
     *devptr = reinterpret_cast<uint64_t>(base) + offset;
-    // the mapping is usable from the importing (current) device; remember which device owns the memory
+    // the mapping is usable from the importing (current) device: remember its extent, so that a plan whose destination
+    // pointers lie inside it is accepted whatever ordinal the caller gives the owning device
     int cur = -1;
-    cudaPointerAttributes attr{};
-    if (cudaGetDevice(&cur) == cudaSuccess && cudaPointerGetAttributes(&attr, base) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
-        tkv_internal::mark_peer(cur, attr.device);
-    else
-        cudaGetLastError();
+    if (cudaGetDevice(&cur) == cudaSuccess) {
+        typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        unsigned long long lo = 0;
+        size_t size = 0;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr) == cudaSuccess && fn &&
+            reinterpret_cast<range_fn>(fn)(&lo, &size, (unsigned long long)reinterpret_cast<uint64_t>(base)) == 0 && size)
+            tkv_internal::note_import(cur, (uint64_t)lo, (uint64_t)size);
+        else
+            tkv_internal::note_import(cur, reinterpret_cast<uint64_t>(base), ~0ull - reinterpret_cast<uint64_t>(base));   // extent unknown: from the base on
+    }
+    cudaGetLastError();
     return TKV_OK;
 }
 
 int32_t tkv_ipc_close(uint64_t devptr, uint64_t offset) {
     if (!devptr) return TKV_OK;
+    tkv_internal::forget_import(devptr - offset);
     CU(cudaIpcCloseMemHandle(reinterpret_cast<void*>(devptr - offset)));
     return TKV_OK;
 }

@@ -17,6 +17,7 @@
 namespace tkv_internal {
 int32_t set_error(int32_t code, int32_t cuda_code, const char* text);
 bool peer_reachable(int from, int to);
+bool imported_on(int from, const uint64_t* ptrs, size_t n);
 }
 
 namespace {
@@ -182,7 +183,8 @@ extern "C" int32_t tkv_handoff_noalloc(const TkvPool* s, const TkvPool* d, const
         }
     }
     // as for a plan: a destination on another device must have been mapped by tkv_init or tkv_ipc_import
-    if (!tkv_internal::peer_reachable(s->device, d->device))
+    if (!tkv_internal::peer_reachable(s->device, d->device) &&
+        !(tkv_internal::imported_on(s->device, d->k_layer_ptrs, d->n_layers) && tkv_internal::imported_on(s->device, d->v_layer_ptrs, d->n_layers)))
         return fail(TKV_ERR_INVALID_CONFIG, "device %llu cannot store into device %llu: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
                     (unsigned long long)s->device, (unsigned long long)d->device);
     if (pairs == 0) return TKV_OK;

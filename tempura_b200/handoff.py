@@ -276,6 +276,9 @@ class Plan:
     def tune_bulk(self, stages: int, ctas_per_sm: int, stage_bytes: int = 32768) -> None:
         check(lib().tkv_plan_tune_bulk(self._h, stages, ctas_per_sm, stage_bytes))
 
+    def tune_vector(self, bytes_per_access: int, unroll: int = 8, store_hint: int = 0) -> None:
+        check(lib().tkv_plan_tune_vector(self._h, bytes_per_access, unroll, store_hint))
+
     def tune_grid(self, ctas_per_sm: int) -> None:
         check(lib().tkv_plan_tune_grid(self._h, ctas_per_sm))
 
@@ -364,6 +367,13 @@ def selfcheck_scaled_quant() -> int:
     out = C.c_uint64(0)
     check(lib().tkv_selfcheck_scaled_quant(C.byref(out)))
     return out.value
+
+
+def selfcheck_tensor_cores():
+    """Mismatch counts of the tcgen05 operand plumbing self-check: E4M3 K-major, E4M3 x E5M2 MN-major, F16 K-major, F16 MN-major."""
+    out = (C.c_uint64 * 4)()
+    check(lib().tkv_selfcheck_tensor_cores(out))
+    return [int(v) for v in out]
 
 
 def ipc_export(ptr: int):

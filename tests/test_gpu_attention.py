@@ -62,7 +62,13 @@ def quantized_pool(H, w):
     return hs, hd, dd
 
 
-@pytest.mark.parametrize("flags", [0, N.ATTN_PER_HEAD_CTAS])
+def test_tensor_core_operand_plumbing_is_exact(H):
+    """The tcgen05 path's tensor-map copy, swizzle, descriptors and tensor-memory reads on operands whose products and
+    sums are exact in FP32: E4M3 K-major, E4M3 x E5M2 MN-major, F16 K-major, F16 MN-major."""
+    assert H.selfcheck_tensor_cores() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("flags", [0, N.ATTN_MMA_SYNC, N.ATTN_PER_HEAD_CTAS])
 def test_fp8_scaled_pool_matches_oracle_attention(H, flags):
     # ragged lengths around the block (16), tile (32) and split (512) boundaries; 32 query heads on 8 kv heads
     lens = np.array([1, 15, 16, 17, 33, 511, 512, 513, 1300], dtype=np.uint32)
@@ -208,7 +214,7 @@ def test_causal_chunk_of_new_tokens_matches_oracle(H):
     assert torch.equal(one.cpu(), torch.from_numpy(got[-1:]))
 
 
-@pytest.mark.parametrize("flags", [0, N.ATTN_PER_HEAD_CTAS])
+@pytest.mark.parametrize("flags", [0, N.ATTN_MMA_SYNC, N.ATTN_PER_HEAD_CTAS])
 def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faulting(H, flags):
     """kv_lens is device memory read when the kernel runs: a value above max_kv_len (which sized the grid, the
     table rows and the scratch) is clamped, and a table entry outside the pool is never turned into an

@@ -65,6 +65,22 @@ def test_config2_shape_f16_copy(H, seed, flags, variant):
     assert plan.stats().kernel_variant == variant     # 2 = bulk-copy ring, 1 = register copy
 
 
+@pytest.mark.parametrize("unroll,hint", [(4, 0), (8, 1), (16, 2)])
+def test_config2_shape_f16_copy_32_byte_accesses(H, unroll, hint):
+    """The 32-byte register kernel (the peer path's store shape), here on one GPU: same bytes, ragged tails included."""
+    import torch
+    w = reduced_8b(seed=2)
+    hs, hd = host_pools(w)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "f16")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    plan = H.Plan(ds, dd, device_batch(w), None, N.PLAN_FORCE_VECTOR)
+    plan.tune_vector(32, unroll, hint)
+    plan.enqueue()
+    torch.cuda.synchronize()
+    assert_pool_equals_host(dd, hd, f"32-byte copy unroll {unroll} hint {hint}")
+    assert plan.stats().kernel_variant == 1
+
+
 def test_config2_lengths_exact_multiple_and_single_token(H):
     w = W.Workload("edge-lens", 2, 8, 128, 16, 64, 64, np.array([16, 1, 17, 32, 15], dtype=np.uint32), seed=3).build_tables()
     run_case(H, w)

@@ -45,6 +45,22 @@ def test_peer_f16_copy_uses_register_stores(H):
     assert plan.stats().kernel_variant == 1          # peer destinations never take the bulk-copy path
 
 
+def test_peer_f16_copy_32_byte_stores(H):
+    import torch
+    w = W.Workload("peer-f16-wide", 3, 8, 128, 16, 256, 256, W.lengths(6, 40, 300, 52, 7), seed=52).build_tables()
+    hs, hd = host_pools(w)
+    src, dst = to_device_pool(hs, "f16", device=0), to_device_pool(hd, "f16", device=1)
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    plan = H.Plan(src, dst, device_batch(w))
+    plan.tune_vector(32, 8, 0)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda:1")
+    with torch.cuda.device(0):
+        plan.enqueue(torch.cuda.current_stream(0), done_flag=flag.data_ptr(), flag_value=3)
+    H.flag_wait_host(1, flag.data_ptr(), 3, 10_000_000)
+    with torch.cuda.device(1):
+        assert_pool_equals_host(dst, hd, "peer 32-byte stores")
+
+
 def test_peer_bulk_refused(H):
     import torch
     w = W.Workload("peer-bulk", 1, 8, 128, 16, 32, 32, np.array([20], dtype=np.uint32), seed=51).build_tables()
