@@ -395,17 +395,20 @@ def sample_layers(w) -> int:
     return int(max(1, min(w.n_layers, budget // per_layer)))
 
 
-def describe(w, world: int, small: bool) -> dict:
+def describe(w, world: int, small: bool, push: bool = False) -> dict:
     """The `config` object, the same in both arms."""
     pairs = max(1, world // 2)
     strong = w.name.startswith("llama3.1-70b")
+    pulled = w.src_dtype == w.dst_dtype and not push
     return {"workload": w.name, "layers": w.n_layers, "kv_heads": w.n_kv_heads * (pairs if strong else 1),
             "kv_heads_per_pair": w.n_kv_heads, "head_dim": w.head_dim, "block_size": w.block_size, "n_seqs": len(w.seq_lens),
             "tokens_moved": w.tokens_moved, "payload_bytes": int(w.payload_bytes) * pairs, "pool_blocks": [w.src_blocks, w.dst_blocks],
             "pairs": pairs,
             "placement": ("intra-device: prefill pool -> decode pool on one GPU" if world == 1 else
                           ("one batch, KV heads split over the pairs; " if strong else "every pair its own batch; ") +
-                          "prefill rank i -> decode rank i+N/2, stores into the peer pool from inside the kernel"),
+                          "prefill rank i -> decode rank i+N/2, " +
+                          ("the decode GPU's kernel loads from the prefill pool over NVLink and stores into its own pool" if pulled else
+                           "the prefill GPU's kernel stores into the decode pool over NVLink")),
             "l2": ("256 MB written between timed launches (batch fits L2)" if small else "inputs larger than L2 (no flush needed)")}
 
 
@@ -444,7 +447,7 @@ def run_reference(args):
     v = c.payload / (ms * 1e-3) / 1e9
     sample = c.what + f"; {steps} timed steps after {max(1, args.warmup)} warm-up"
     full_ms = w_cpu.payload_bytes / (v * 1e9) * 1e3
-    cfg = describe(pick_workload(default_workload(args), world, None), world, is_small(w))
+    cfg = describe(pick_workload(default_workload(args), world, None), world, is_small(w), getattr(args, "push", False))
     line = {
         "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": max(1, args.warmup), "ms_per_step": round(ms, 3), "higher_is_better": True,
@@ -624,49 +627,57 @@ def run_ours(args):
     sampler = ClockSampler(local)
     src = dst = None
     remote_base = 0
+    # Across GPUs a same-dtype batch is PULLED: the kernel runs on the decode GPU, fetches the prefill pool's blocks with
+    # ordinary loads over NVLink and stores into its own pool (measured 786 GB/s per pair against 718 GB/s for stores pushed
+    # from the prefill GPU, whatever their shape).  A cast to E4M3 is PUSHED: the prefill GPU encodes first, so half the
+    # bytes cross the link.  --push forces the store form for the same-dtype case as well.
+    pull = multi and w.src_dtype == dst_dtype and not args.push
+    mover = (not is_prefill) if pull else is_prefill          # the rank whose GPU runs the handoff kernel
     # completion flag: page-locked host memory on one GPU (the kernel's release store lands where the
-    # host polls it, no copy per poll); device memory of the decode GPU when the waiter is another rank
+    # host polls it, no copy per poll); device memory of the decode GPU when two ranks are involved
     flag = torch.zeros(4, dtype=torch.int32, device="cuda") if multi else torch.zeros(4, dtype=torch.int32).pin_memory()
+    remote_flag = 0
     if not multi:
         src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, w.src_dtype)
         dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
                               scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
         fill_source(src, w, 1234)
     else:
-        # The decode rank announces its pool; the prefill rank of its pair maps it.  What crosses between the
-        # processes is the wire message of the handoff's metadata (tkv_session_pack) plus the IPC handles.
-        info = None
-        if not is_prefill:
-            dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
-                                  scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
-            hs, off = H.ipc_export(dst.storage.data_ptr())
-            hf, foff = H.ipc_export(flag.data_ptr())
-            info = {"pool": (hs, off), "flag": (hf, foff), "base": dst.storage.data_ptr(), "bytes": dst.storage.numel(),
-                    "k": [int(p) for p in dst.k_ptrs], "v": [int(p) for p in dst.v_ptrs], "device": local}
-            if scales:
-                info["ks"] = H.ipc_export(dst.k_scales.data_ptr())
-                info["vs"] = H.ipc_export(dst.v_scales.data_ptr())
-            if dst.refcounts is not None:
-                info["rc"] = H.ipc_export(dst.refcounts.data_ptr())
+        # Every rank announces its pool (IPC handles, layer addresses); its partner maps it.
+        if is_prefill:
+            mine = src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
+            fill_source(src, w, 1234 + rank)
+        else:
+            mine = dst = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks, dst_dtype,
+                                         scales=scales, refcounts=w.prefix_lens is not None, fill_byte=0x5A)
+        hs, off = H.ipc_export(mine.storage.data_ptr())
+        hf, foff = H.ipc_export(flag.data_ptr())
+        info = {"pool": (hs, off), "flag": (hf, foff), "base": mine.storage.data_ptr(), "bytes": mine.storage.numel(),
+                "k": [int(p) for p in mine.k_ptrs], "v": [int(p) for p in mine.v_ptrs], "device": local}
+        if mine.k_scales is not None:
+            info["ks"] = H.ipc_export(mine.k_scales.data_ptr())
+            info["vs"] = H.ipc_export(mine.v_scales.data_ptr())
+        if mine.refcounts is not None:
+            info["rc"] = H.ipc_export(mine.refcounts.data_ptr())
         infos = [None] * world
         dist.all_gather_object(infos, info)
+        pi = infos[partner]
+        base = H.ipc_import(*pi["pool"])
+        rel = lambda p: base + (p - pi["base"])
+        theirs = H.Pool.from_pointers(pi["device"], dst_dtype if is_prefill else "f16", w.n_kv_heads, w.head_dim, w.block_size,
+                                      w.dst_blocks if is_prefill else w.src_blocks, [rel(p) for p in pi["k"]], [rel(p) for p in pi["v"]],
+                                      H.ipc_import(*pi["ks"]) if "ks" in pi else 0, H.ipc_import(*pi["vs"]) if "vs" in pi else 0,
+                                      H.ipc_import(*pi["rc"]) if "rc" in pi else 0)
         if is_prefill:
-            src = H.Pool.allocate(local, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, "f16")
-            fill_source(src, w, 1234 + rank)
-            pi = infos[partner]
-            base = H.ipc_import(*pi["pool"])
-            remote_base, remote_bytes = base, pi["bytes"]
+            dst, remote_base, remote_bytes = theirs, base, pi["bytes"]
             remote_flag = H.ipc_import(*pi["flag"])
-            rel = lambda p: base + (p - pi["base"])
-            dst = H.Pool.from_pointers(pi["device"], dst_dtype, w.n_kv_heads, w.head_dim, w.block_size, w.dst_blocks,
-                                       [rel(p) for p in pi["k"]], [rel(p) for p in pi["v"]],
-                                       H.ipc_import(*pi["ks"]) if scales else 0, H.ipc_import(*pi["vs"]) if scales else 0,
-                                       H.ipc_import(*pi["rc"]) if "rc" in pi else 0)
+        else:
+            src_remote = theirs
 
     batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens)
     plan = None
-    if is_prefill:
-        plan = H.Plan(src, dst, batch, None, flags)
+    if mover:
+        plan = H.Plan(src_remote, dst, batch, None, flags | H.N.PLAN_PULL) if pull else H.Plan(src, dst, batch, None, flags)
         if args.bulk_tune:
             plan.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
         if args.grid_tune:
@@ -674,7 +685,10 @@ def run_ours(args):
         if args.vec_tune:
             plan.tune_vector(*[int(x) for x in args.vec_tune.split(",")])
     stream = torch.cuda.current_stream()
-    done_flag = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
+    # where the kernel publishes completion: the host-visible flag on one GPU; the decode GPU's flag across GPUs (its own
+    # memory when it pulls, the mapped peer word when the prefill GPU pushes)
+    done_flag = flag.data_ptr() if (not multi or pull) else (remote_flag if is_prefill else 0)
+    waits_on_flag = multi and not pull and not is_prefill     # a pushed handoff is awaited by the decode rank
 
     def barrier():
         if multi:
@@ -716,9 +730,9 @@ def run_ours(args):
     gen = 0
     for _ in range(args.warmup):
         gen += 1
-        if is_prefill:
+        if mover:
             plan.enqueue(stream, done_flag, gen)
-        else:
+        elif waits_on_flag:
             H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
     barrier()
     sampler.mark()
@@ -726,19 +740,27 @@ def run_ours(args):
     # ---- timed: K handoffs, inputs resident in HBM -------------------------------------------
     small = is_small(w)
     t_wall0 = time.perf_counter()
-    if is_prefill:
+    if mover:
         ms, gen = time_handoffs(H, plan, w, args.steps, stream, done_flag, gen)
     else:
         gen += args.steps
-        H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
-        ms = 0.0                                      # the prefill rank's CUDA events time the pair
+        if waits_on_flag:
+            H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
+        ms = 0.0                                      # the moving rank's CUDA events time the pair
     barrier()
     sampler.mark()
     ms_total = max_over_ranks(ms)
 
+    stats_src = [plan.stats() if mover else None]
+    if multi:                                       # rank 0 prints; the plan may live on its partner
+        gathered = [None] * world
+        dist.all_gather_object(gathered, None if stats_src[0] is None else
+                               {f: getattr(stats_src[0], f) for f, _ in H.N.TkvStats._fields_})
+        first = next(g for g in gathered if g is not None)
+        stats_src = [type("Stats", (), first)]
     if args.sweep:
         if rank == 0:
-            st = plan.stats()
+            st = stats_src[0]
             per = ms_total / args.steps
             bytes_moved = st.bytes_written if multi else st.bytes_read + st.bytes_written
             print(json.dumps({"sweep": True, "workload": w.name, "n_gpus": world, "ms_per_step": round(per, 5),
@@ -758,12 +780,12 @@ def run_ours(args):
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         gen += 1
-        if is_prefill:
+        if mover:
             plan.update(batch)
             plan.enqueue(stream, done_flag, gen)
-            if not multi:
+            if not multi or pull:
                 H.flag_wait_host(local, flag.data_ptr(), gen, 60_000_000)
-        else:
+        elif waits_on_flag:
             H.flag_wait_host(local, flag.data_ptr(), gen, 600_000_000)
     torch.cuda.synchronize()
     res_s = time.perf_counter() - t0
@@ -795,6 +817,8 @@ def run_ours(args):
                                       H.N.PLAN_FORCE_BULK if args.host_bulk else 0)
         if args.host_bulk and args.bulk_tune:
             plan_h.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
+    # this leg's kernel runs on the prefill GPU (its host holds the buffer) and publishes to the decode rank's flag
+    host_done = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
     barrier()
     for it in range(1 + host_steps):             # first pass is the warm-up
         if it == 1:
@@ -803,7 +827,7 @@ def run_ours(args):
         gen += 1
         if is_prefill:
             plan_h.update(batch)
-            plan_h.enqueue(stream, done_flag, gen)
+            plan_h.enqueue(stream, host_done, gen)
             if not multi:
                 H.flag_wait_host(local, flag.data_ptr(), gen, 120_000_000)
         else:
@@ -826,7 +850,7 @@ def run_ours(args):
     clocks = sampler.stop()
 
     if rank == 0:
-        st = plan.stats()
+        st = stats_src[0]
         payload_all = st.payload_bytes * pairs       # strong: the pairs' shares add up to the one batch; weak: every pair its own batch
         per_launch_ms = ms_total / args.steps
         value = payload_all / (per_launch_ms * 1e-3) / 1e9
@@ -840,7 +864,7 @@ def run_ours(args):
             roofline = {"bound": "nvlink", "achieved": round(achieved, 1), "peak": round(peer_copy, 1), "unit": "GB/s",
                         "frac": round(achieved / peer_copy, 4), "traffic": int(wire), "algorithmic_bytes": int(wire),
                         "peak_source": "copy-engine copy of 1 GiB prefill pool -> paired decode pool measured in this run, every pair at once, best of 5, slowest pair",
-                        "traffic_source": "wire bytes: what one prefill GPU stores into its decode GPU per launch (no ncu capture wraps a multi-rank run)",
+                        "traffic_source": "wire bytes: what crosses from one prefill GPU to its decode GPU per launch (no ncu capture wraps a multi-rank run)",
                         "frac_of_nominal_900": round(achieved / 900.0, 4), "per": "pair, one direction"}
         else:
             achieved = algo / (per_launch_ms * 1e-3) / 1e9
@@ -848,14 +872,15 @@ def run_ours(args):
                         "frac": round(achieved / peak, 4), "traffic": (int(ratio * algo) if ratio else None),
                         "algorithmic_bytes": int(algo), "peak_source": f"{peak_kind} copy peak (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                         "frac_of_nominal_8000": round(achieved / 8000.0, 4)}
-        cfg = describe(w, world, small)
+        cfg = describe(w, world, small, args.push)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True,
             "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": ("f32->f16" if w.src_dtype == "f32" else "u16") if dst_dtype == "f16" else "f16->e4m3",
             "data": "synthetic", "config": cfg,
-            "launch": {"kernel": kname, "grid": [st.grid, st.block]},
+            "launch": {"kernel": kname, "grid": [st.grid, st.block],
+                       "runs_on": "the one GPU" if not multi else ("decode GPU (pull: loads over NVLink)" if pull else "prefill GPU (push: stores over NVLink)")},
             "parity": parity["parity"], "parity_detail": {k: v for k, v in parity.items() if k != "parity"},
             "roofline": roofline,
             "e2e": {"value": round(payload_all * host_layers / w.n_layers * host_steps / host_s / 1e9, 2), "unit": UNIT,
@@ -1162,6 +1187,7 @@ def main():
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--vec-tune", default=None, help="bytes_per_access,unroll,store_hint for the register copy kernel (e.g. 32,8,0)")
+    ap.add_argument("--push", action="store_true", help="N > 1: the prefill GPU's kernel stores into the decode pool (default for a same-dtype batch: the decode GPU pulls)")
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sweep", action="store_true", help="tuning aid: the device-timed region only (no end-to-end legs, no parity step, no baselines)")

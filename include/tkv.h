@@ -137,10 +137,16 @@ enum {
     TKV_PLAN_FORCE_VECTOR = 2,      /* use the register kernels (vector copy, warp-per-head FP8, element-wide F32 casts) */
     TKV_PLAN_FORCE_BULK = 4,        /* use the shared-memory bulk-copy pipelines (copy ring, staged FP8) */
     TKV_PLAN_INT_QUANTIZER = 8,     /* FP8: integer bit-math encoder instead of cvt + flush */
-    TKV_PLAN_PEER_BULK_STORES = 16  /* same-dtype move to a peer: use the bulk-copy ring (bulk stores
+    TKV_PLAN_PEER_BULK_STORES = 16, /* same-dtype move to a peer: use the bulk-copy ring (bulk stores
                                        shared -> peer global) instead of register stores; measured
                                        equal over NVLink, so it is opt-in.  The staged FP8 kernel
                                        always stores whole rows in bulk, local or peer.            */
+    TKV_PLAN_PULL = 32              /* pools on two devices, same dtype: the kernel runs on the DESTINATION
+                                       pool's device (enqueue on one of its streams), fetches the source
+                                       blocks with ordinary loads over the peer mapping and stores locally;
+                                       the completion flag is then local to the receiver.  Needs the
+                                       destination device to reach the source pool (tkv_init, or
+                                       tkv_ipc_import on the destination side).                     */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
        TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7, TKV_VARIANT_CAST_VEC = 8 };

@@ -146,6 +146,7 @@ struct tkv_plan {
     std::vector<uint64_t> src_k, src_v, dst_k, dst_v;  // owned copies of the layer pointers
     TkvShard shard{};
     uint32_t flags = 0;
+    int launch_dev = 0;   // the device whose kernel moves the bytes: the source pool's, or (TKV_PLAN_PULL) the destination pool's
     Mode mode = MODE_COPY;
     uint32_t variant = 0;
     int vec = 16;
@@ -338,14 +339,20 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
 
     // A kernel on the source device stores into the destination pool: refuse a pair whose peer mapping this
     // library has not set up, rather than launch stores at addresses the device cannot reach.
-    if (!tkv_internal::peer_reachable(s.device, d.device) && !(tkv_internal::imported_on(s.device, p->dst_k.data(), p->dst_k.size()) &&
-                                                               tkv_internal::imported_on(s.device, p->dst_v.data(), p->dst_v.size())))
-        return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot store into device %d: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
-                    s.device, d.device);
+    const bool pull = (p->flags & TKV_PLAN_PULL) != 0;
+    p->launch_dev = pull ? d.device : s.device;
+    const int far_dev = pull ? s.device : d.device;
+    const std::vector<uint64_t>&far_k = pull ? p->src_k : p->dst_k, &far_v = pull ? p->src_v : p->dst_v;
+    if (!tkv_internal::peer_reachable(p->launch_dev, far_dev) && !(tkv_internal::imported_on(p->launch_dev, far_k.data(), far_k.size()) &&
+                                                                  tkv_internal::imported_on(p->launch_dev, far_v.data(), far_v.size())))
+        return fail(TKV_ERR_INVALID_CONFIG, "device %d cannot %s device %d: no peer mapping (call tkv_init with both devices, or map the pool with tkv_ipc_import)",
+                    p->launch_dev, pull ? "load from" : "store into", far_dev);
+    if (pull && (p->mode != MODE_COPY || p->virt || (p->flags & (TKV_PLAN_FORCE_BULK | TKV_PLAN_PEER_BULK_STORES))))
+        return fail(TKV_ERR_INVALID_CONFIG, "TKV_PLAN_PULL is for same-dtype pool-to-pool moves with the register kernels (no bulk copy reads a peer's memory)");
     // ---- everything above is pure host logic; CUDA starts here ----
     {
-        DeviceGuard g(s.device);
-        if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", s.device);
+        DeviceGuard g(p->launch_dev);
+        if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->launch_dev);
         if (!p->upload_ev) CU(cudaEventCreateWithFlags(&p->upload_ev, cudaEventDisableTiming));
         // the previous upload must have left the pinned mirror before it is rewritten
         if (p->upload_pending) {
@@ -490,7 +497,7 @@ template <typename K> int32_t occupancy_grid(K kernel, int dev, uint64_t work_ct
 
 template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, cudaStream_t st) {
     uint32_t grid = 0;
-    int32_t rc = occupancy_grid(kernel, p->src.device, work_ctas, &grid);
+    int32_t rc = occupancy_grid(kernel, p->launch_dev, work_ctas, &grid);
     if (rc) return rc;
     // Measured on B200 (Llama-3.1-8B shape): the FP8 warp kernel peaks at 3 resident CTAs per
     // SM (90.7 % of the copy peak against 83 % at the occupancy limit of 4).
@@ -499,7 +506,7 @@ template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, 
                                        : (p->variant == TKV_VARIANT_FP8_WARP ? 3u : p->variant == TKV_VARIANT_CAST_VEC ? 4u : 0u);
     if (cap) {
         DevInfo di;
-        rc = dev_info(p->src.device, &di);
+        rc = dev_info(p->launch_dev, &di);
         if (rc) return rc;
         grid = std::max(1u, std::min(grid, (uint32_t)di.sm_count * cap));
     }
@@ -511,7 +518,7 @@ template <typename K> int32_t launch(K kernel, tkv_plan* p, uint64_t work_ctas, 
 
 // Bulk-copy variant: only for same-device, contiguous, 16-byte aligned chunks.
 bool bulk_eligible(const tkv_plan* p) {
-    const bool reach = p->src.device == p->dst.device || (p->flags & TKV_PLAN_PEER_BULK_STORES);
+    const bool reach = (p->src.device == p->dst.device || (p->flags & TKV_PLAN_PEER_BULK_STORES)) && !(p->flags & TKV_PLAN_PULL);
     // a host-memory side takes the ring only when asked to (TKV_PLAN_FORCE_BULK)
     const bool host_ok = !p->host_side || (p->flags & TKV_PLAN_FORCE_BULK);
     return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && reach && host_ok && p->args.src_k_scales == nullptr;
@@ -520,7 +527,7 @@ bool bulk_eligible(const tkv_plan* p) {
 int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     const tkv::HandoffArgs& a = p->args;
     DevInfo di;
-    int32_t rc = dev_info(p->src.device, &di);
+    int32_t rc = dev_info(p->launch_dev, &di);
     if (rc) return rc;
     const uint32_t chunk = a.block_size * a.src_row_bytes;
     const uint32_t stage = std::min<uint32_t>(p->bulk_stage_bytes, (chunk + 127u) & ~127u);
@@ -528,7 +535,7 @@ int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     const uint32_t stages = std::max(2u, std::min(8u, p->bulk_stages));
     const size_t smem = 64 + 64 * sizeof(tkv::BulkItem) + (size_t)stages * stage;
     if (smem > 227 * 1024) return fail(TKV_ERR_INVALID_CONFIG, "bulk ring of %u x %u bytes exceeds shared memory", stages, stage);
-    rc = grant_smem(tkv::handoff_copy_bulk, p->src.device, smem);
+    rc = grant_smem(tkv::handoff_copy_bulk, p->launch_dev, smem);
     if (rc) return rc;
     // Measured on B200: throughput peaks near 96 KiB of ring per SM (3 x 32 KiB, one CTA) and
     // falls off when more is in flight, so smaller stages get proportionally more CTAs.
@@ -565,10 +572,10 @@ bool staged_eligible(const tkv_plan* p, uint32_t* stages_out, size_t* smem_out) 
 template <int D, bool HW, bool SCALED> int32_t launch_fp8_staged(tkv_plan* p, uint32_t stages, size_t smem, cudaStream_t st) {
     const tkv::HandoffArgs& a = p->args;
     DevInfo di;
-    int32_t rc = dev_info(p->src.device, &di);
+    int32_t rc = dev_info(p->launch_dev, &di);
     if (rc) return rc;
     auto kernel = tkv::handoff_f16_e4m3_staged<D, HW, SCALED>;
-    rc = grant_smem(kernel, p->src.device, smem);
+    rc = grant_smem(kernel, p->launch_dev, smem);
     if (rc) return rc;
     uint32_t per_sm = std::max<uint32_t>(1u, (uint32_t)((227 * 1024) / (smem + 1024)));
     if (p->bulk_ctas_per_sm) per_sm = std::min(per_sm, p->bulk_ctas_per_sm);
@@ -732,6 +739,12 @@ static int32_t create_plan(const TkvPool* src, const TkvPool* dst, const TkvBatc
     p->flags = flags;
     p->mode = mode;
     p->virt = virt;
+    if (flags & TKV_PLAN_PULL) {
+        // measured over NVLink (Llama-3.1-70B shape, one pair): 32-byte loads, 16 in flight per thread, one CTA per SM
+        // fetch 786 GB/s; 16-byte loads 770; stores pushed the other way stop at 718 whatever their shape
+        p->vec_bytes = 32;
+        p->vec_unroll = 16;
+    }
     if (xfer) {
         p->xfer = *xfer;
         p->host_side = xfer->host_memory != 0;
@@ -833,7 +846,7 @@ int32_t tkv_plan_update(tkv_plan* p, const TkvBatch* batch) {
 int32_t tkv_plan_destroy(tkv_plan* p) {
     if (!p) return TKV_OK;
     {
-        DeviceGuard g(p->src.device);
+        DeviceGuard g(p->launch_dev);
         if (p->upload_ev) {
             if (p->upload_pending) cudaEventSynchronize(p->upload_ev);
             cudaEventDestroy(p->upload_ev);
@@ -858,8 +871,8 @@ int32_t tkv_plan_stats(const tkv_plan* p, TkvStats* out) {
 int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint32_t flag_value) {
     if (!p) return fail(TKV_ERR_INVALID_CONFIG, "NULL plan");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    DeviceGuard g(p->src.device);
-    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    DeviceGuard g(p->launch_dev);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->launch_dev);
     tkv::HandoffArgs& a = p->args;
     a.done_flag = reinterpret_cast<uint32_t*>(done_flag);
     a.flag_value = flag_value;
@@ -1024,8 +1037,8 @@ int32_t tkv_plan_error(const tkv_plan* p, uint32_t* device_error) {
     if (!p || !device_error) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
     *device_error = 0;
     if (!p->d_buf) return TKV_OK;
-    DeviceGuard g(p->src.device);
-    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->src.device);
+    DeviceGuard g(p->launch_dev);
+    if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->launch_dev);
     CU(cudaMemcpy(device_error, p->args.done_counter + 1, 4, cudaMemcpyDeviceToHost));
     return TKV_OK;
 }

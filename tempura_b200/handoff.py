@@ -213,7 +213,7 @@ class Plan:
         sh = C.byref(shard) if shard is not None else None
         if transfer is None:
             self._s, self._d = src.c_struct(), dst.c_struct()
-            self.launch_device = src.device
+            self.launch_device = dst.device if flags & N.PLAN_PULL else src.device
             check(lib().tkv_plan_create(C.byref(self._s), C.byref(self._d), C.byref(b), sh, flags, C.byref(self._h)))
         elif dst is None:
             self._s, self._x = src.c_struct(), transfer.c_struct()

@@ -1,12 +1,17 @@
-"""Benchmark configurations 2-5 at their FULL batch sizes on the GPU, checked through properties that
-do not need the CPU oracle to walk gigabytes: every moved block compared with its source block
-by an independent torch gather (bit-exact), untouched memory still holding its fill pattern,
-prefix blocks unchanged with their refcounts raised, the two FP8 encoders agreeing byte for byte
-and the quantize -> widen round trip staying inside one E4M3 step.  Pools hold the blocks the
-batch needs (not the benchmark's 65 536-block free list) so two of them fit beside each other; tables stay shuffled."""
+"""Benchmark configurations 2-5 at their FULL batch sizes on the GPU.  Two layers of every configuration
+(the first and the last, with the full batch and the full tables) are compared with the CPU oracle byte
+for byte, scales and untouched fill included; all layers are checked through properties that do not need
+the oracle to walk gigabytes: every moved block compared with its source block by an independent torch
+gather (bit-exact), untouched memory still holding its fill pattern, prefix blocks unchanged with their
+refcounts raised, the two FP8 encoders agreeing byte for byte and the quantize -> widen round trip staying
+inside one E4M3 step.  Pools hold the blocks the batch needs (not the benchmark's 65 536-block free list)
+so two of them fit beside each other; tables stay shuffled."""
+import os
+
 import numpy as np
 import pytest
 
+import oracle
 from tempura_b200 import _native as N
 from tempura_b200 import workloads as W
 
@@ -36,6 +41,47 @@ def fill_source(pool, w, seed):
             for c in w.outlier_channels:
                 vals[..., c] *= w.outlier_gain
             pool.blocks(l, is_v).index_copy_(0, idx, vals.to(torch.float16))
+
+
+_NP = {N.DTYPE_F32: np.float32, N.DTYPE_F16: np.uint16, N.DTYPE_E4M3: np.uint8}
+
+
+def snapshot_layers(pool, layers):
+    """The named layers of a device pool as a host pool of len(layers) layers (what the oracle reads and writes)."""
+    import torch
+    torch.cuda.synchronize()
+    dt = _NP[pool.dtype]
+    grab = lambda t: t.view(torch.uint8).cpu().numpy().view(dt).copy()
+    hp = oracle.HostPool(len(layers), pool.n_kv_heads, pool.head_dim, pool.block_size, pool.total_blocks, np.dtype(dt),
+                         [grab(pool.k[l]) for l in layers], [grab(pool.v[l]) for l in layers])
+    if pool.k_scales is not None:
+        hp.k_scales = np.stack([pool.k_scales[l].cpu().numpy() for l in layers])
+        hp.v_scales = np.stack([pool.v_scales[l].cpu().numpy() for l in layers])
+    return hp
+
+
+def assert_layers_equal_oracle(pool, hp, layers, what):
+    """Every byte of the named device layers (moved rows, ragged tails, untouched fill) and every scale bit pattern."""
+    import torch
+    torch.cuda.synchronize()
+    for i, l in enumerate(layers):
+        for name, dev, host in (("K", pool.k[l], hp.k[i]), ("V", pool.v[l], hp.v[i])):
+            got = dev.view(torch.uint8).cpu().numpy()
+            want = host.view(np.uint8)
+            if not np.array_equal(got, want):
+                bad = np.flatnonzero(got != want)
+                raise AssertionError(f"{what} layer {l} {name}: {bad.size} bytes differ from the oracle, first at {bad[0]}")
+        if hp.k_scales is not None:
+            for name, dev, host in (("k_scales", pool.k_scales[l], hp.k_scales[i]), ("v_scales", pool.v_scales[l], hp.v_scales[i])):
+                assert np.array_equal(dev.cpu().numpy().view(np.uint32), host.view(np.uint32)), f"{what} layer {l} {name} differ from the oracle"
+
+
+def oracle_on_layers(src, dst_before, w, layers, mode):
+    """The oracle's handoff of the FULL batch over the snapshot of the named layers; returns the host destination."""
+    hs = snapshot_layers(src, layers)
+    oracle.handoff(hs, dst_before, oracle.make_batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens), None, mode,
+                   n_threads=os.cpu_count() or 1)
+    return dst_before
 
 
 def moved(w):
@@ -91,6 +137,7 @@ def test_config2_full_batch_bit_exact(H):
     src = H.Pool.allocate(0, 32, 8, 128, 16, 4096, "f16")
     dst = H.Pool.allocate(0, 32, 8, 128, 16, 4096, "f16", fill_byte=0x5A)
     fill_source(src, w, 1)
+    want = oracle_on_layers(src, snapshot_layers(dst, (0, 31)), w, (0, 31), "copy")
     for flags, variant in ((0, N.VARIANT_BULK), (N.PLAN_FORCE_VECTOR, N.VARIANT_VECTOR)):
         dst.storage.fill_(0x5A)
         plan = H.Plan(src, dst, H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride), None, flags)
@@ -98,6 +145,7 @@ def test_config2_full_batch_bit_exact(H):
         torch.cuda.synchronize()
         st = plan.stats()
         assert st.kernel_variant == variant and st.payload_bytes == w.payload_bytes and plan.device_error() == 0
+        assert_layers_equal_oracle(dst, want, (0, 31), "config 2")
         assert_moved_blocks_equal(src, dst, w, 0x5A)
         untouched_blocks_keep_fill(dst, w, 0x5A)
 
@@ -117,6 +165,11 @@ def test_config3_full_batch_two_encoders_agree_and_round_trip(H):
         assert plan.stats().kernel_variant == variant and plan.device_error() == 0
         pools.append(dst)
     a, b = pools
+    # the oracle's own bytes and scales for the first and the last layer of the full batch
+    fresh = H.Pool.allocate(0, 32, 8, 128, 16, 4096, "e4m3", scales=True, fill_byte=0x5A)
+    want = oracle_on_layers(src, snapshot_layers(fresh, (0, 31)), w, (0, 31), "f16_e4m3")
+    del fresh
+    assert_layers_equal_oracle(a, want, (0, 31), "config 3")
     # staged kernel + hardware conversion == register kernel + integer bit-math encoder, every byte and scale
     assert torch.equal(a.storage, b.storage)
     assert torch.equal(a.k_scales.view(torch.int32), b.k_scales.view(torch.int32))
@@ -156,10 +209,12 @@ def test_config4_full_batch_prefix_untouched_and_refcounted(H):
     r0 = torch.randint(0, 5, (16384,), generator=g, device="cuda", dtype=torch.int32)
     dst.refcounts.copy_(r0)
     before = [dst.blocks(l).index_select(0, shared).clone() for l in (0, 31)]
+    want = oracle_on_layers(src, snapshot_layers(dst, (0, 31)), w, (0, 31), "copy")
     plan = H.Plan(src, dst, H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens))
     plan.enqueue()
     plan.refcount_apply(+1)
     torch.cuda.synchronize()
+    assert_layers_equal_oracle(dst, want, (0, 31), "config 4")
     st = plan.stats()
     assert st.n_prefix_refs == 64 * 128 and st.n_tokens == w.tokens_moved
     assert_moved_blocks_equal(src, dst, w, 0x5A)
@@ -184,10 +239,12 @@ def test_config5_full_batch_and_its_head_shards(H):
     dst = H.Pool.allocate(0, 80, 8, 128, 16, 8192, "f16", fill_byte=0x5A)
     fill_source(src, w, 4)
     batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride)
+    want = oracle_on_layers(src, snapshot_layers(dst, (0, 79)), w, (0, 79), "copy")
     plan = H.Plan(src, dst, batch)
     plan.enqueue()
     torch.cuda.synchronize()
     assert plan.stats().n_chunks == 8192 * 80 * 2 and plan.device_error() == 0
+    assert_layers_equal_oracle(dst, want, (0, 79), "config 5")
     assert_moved_blocks_equal(src, dst, w, 0x5A)
     whole = [dst.blocks(l).clone() for l in (0, 79)]
     dst.storage.fill_(0x5A)

@@ -61,6 +61,33 @@ def test_peer_f16_copy_32_byte_stores(H):
         assert_pool_equals_host(dst, hd, "peer 32-byte stores")
 
 
+@pytest.mark.parametrize("tune", [None, (16, 8, 0), (32, 4, 0)])
+def test_peer_pull_kernel_on_the_decode_gpu_loads_over_nvlink(H, tune):
+    """TKV_PLAN_PULL: the kernel runs on the destination pool's GPU, fetches the source blocks with ordinary loads over
+    the peer mapping and stores locally; the flag it publishes is local to the receiver.  Same bytes as the oracle,
+    ragged tails and untouched fill included; the source pool is not written."""
+    import torch
+    w = W.Workload("peer-pull", 3, 8, 128, 16, 256, 256, W.lengths(6, 40, 300, 53, 7), seed=53).build_tables()
+    hs, hd = host_pools(w)
+    src, dst = to_device_pool(hs, "f16", device=0), to_device_pool(hd, "f16", device=1)
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    plan = H.Plan(src, dst, device_batch(w), None, N.PLAN_PULL)
+    if tune:
+        plan.tune_vector(*tune)
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    with torch.cuda.device(1):
+        plan.enqueue(torch.cuda.current_stream(1), done_flag=flag.data_ptr(), flag_value=4)
+    H.flag_wait_host(1, flag.data_ptr(), 4, 10_000_000)
+    with torch.cuda.device(1):
+        assert_pool_equals_host(dst, hd, "peer pull")
+    with torch.cuda.device(0):
+        assert_pool_equals_host(src, hs, "peer pull (source untouched)")
+    assert plan.stats().peer == 1 and plan.stats().kernel_variant == 1
+    # a pull cannot use the bulk-copy pipelines (they would load a peer's memory with the bulk engine) nor cast
+    with pytest.raises(N.TkvError):
+        H.Plan(src, dst, device_batch(w), None, N.PLAN_PULL | N.PLAN_FORCE_BULK)
+
+
 def test_peer_bulk_refused(H):
     import torch
     w = W.Workload("peer-bulk", 1, 8, 128, 16, 32, 32, np.array([20], dtype=np.uint32), seed=51).build_tables()
