@@ -11,17 +11,18 @@
 //
 // with the accumulators in tensor memory.  The K and V bytes are never touched by a thread: a producer
 // warp brings whole blocks in with 2-D tensor-map copies (128-byte swizzle, the layout the MMA's shared
-// memory descriptors name), one thread issues the MMAs, and the four softmax warps own one
-// (token, kv head) row each: they read their row of S^T from tensor memory, keep the columns of their
-// own kv head, and write the probabilities into P^T, whose entries for other kv heads stay zero.
+// memory descriptors name), one thread issues the MMAs, and two groups of four softmax warps take
+// alternate blocks (each group with its own accumulators, merged at the end).  A softmax thread owns one
+// (token, kv head) row: it reads its row of S^T from tensor memory, keeps the columns of its own kv
+// head, and writes the probabilities into P^T, whose entries for other kv heads stay zero.
 // A row's columns of the other seven kv heads are computed and dropped: that is 7/8 of the tensor work
 // and still a fifth of the time the block takes to arrive from HBM, which is the bound.
 //
 // Operand precision.  F16 pool: q and the probabilities are F16 (as the mma.sync kernel feeds them).
 // E4M3 pool: both operands of an MMA must be 8-bit, so q is split into two E4M3 terms (per-head power
-// of two scale, residual in the second term: 2^-8 relative) and a probability into four E5M2 terms
-// (E5M2 for its range: weights down to 2^-31 of the running maximum survive; four 3-bit terms give
-// 2^-12 relative).  The terms are separate columns of Q^T / P^T, summed after the MMA.
+// of two scale, residual in the second term: 2^-8 relative) and a probability into three E5M2 terms
+// (E5M2 for its range: weights down to 2^-31 of the running maximum survive; three 3-bit terms give
+// 2^-9 relative).  The terms are separate columns of Q^T / P^T, summed after the MMA.
 //
 // The running maximum is kept per query head in shared memory and only raised when a block exceeds it
 // by more than 2^6 (weights stay below 2^6 * 2^9 < the E5M2 maximum); raising it rescales O^T in tensor
@@ -109,6 +110,10 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt
 }
 template <bool FP8>
 __device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+#if defined(TKV_TC_ABLATE) && TKV_TC_ABLATE >= 11
+    // debug builds 11 / 12 / 13: no PV / no QK / no MMA at all (the PV form is the one with an MN-major A operand: bit 15 of the descriptor)
+    if ((TKV_TC_ABLATE == 11 && (idesc & (1u << 15))) || (TKV_TC_ABLATE == 12 && !(idesc & (1u << 15))) || TKV_TC_ABLATE == 13) return;
+#endif
     if (FP8)
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
                      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
@@ -176,33 +181,75 @@ __device__ __forceinline__ int ordered(float f) {
 }
 __device__ __forceinline__ float unordered(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7FFFFFFF); }
 
-// Control block at the head of shared memory.
-struct Control {
-    uint64_t full[8], empty[8];       // ring stages: copies landed / both MMAs of the block done
-    uint64_t s_full[2], s_free[2];    // S^T buffers: QK done / every softmax warp has read it
-    uint64_t p_full[2], p_free[2];    // P^T buffers: written / the PV MMA has read it
-    uint64_t drained;                 // teardown: every MMA issued so far has completed
-    uint32_t tmem_base, fail;
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {        // one non-blocking look
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]),
+          "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]),
+          "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr) : "memory");
+}
+
+#ifndef TKV_TC_ABLATE
+#define TKV_TC_ABLATE 9      // debug builds drop parts of the softmax to time the rest (their output is wrong on purpose): 1 = waits, loads and
+#endif                       // barriers only, 2 = + column selection and scores, 3 = + weights without the P^T stores, 9 = everything
+#ifdef TKV_TC_TIMING
+// Debug builds: cycle stamps of one softmax thread (CTA 0, group 0, row 0) through its fourth block.
+__device__ unsigned long long g_tc_stamps[16];
+#define TKV_STAMP(k) do { if (stamp_on) g_tc_stamps[k] = clock64(); } while (0)
+#else
+#define TKV_STAMP(k) do { } while (0)
+#endif
+
+// Control block at the head of shared memory.  Two softmax groups (warps 0-3 and 4-7) take alternate blocks; each
+// has its own S^T buffers, P^T buffer, O^T accumulator, running maxima and row sums, merged once at the end.
+struct Group {
+    uint64_t s_full[2], s_free[2];    // S^T buffers: QK done / every warp of the group has read it
+    uint64_t p_full, p_free;          // P^T buffer: written / the PV MMA has read it
     int block_max[2][32];             // per block parity: ordered-int maxima of the query heads that asked for a raise
     uint32_t raise[2];
-    float m_used[32], factor[32], q_inv[32], l_sum[4][32];
+    float m_used[32], factor[32], l_sum[4][32];
 };
+struct Control {
+    uint64_t full[8], empty[8];       // ring stages: copies landed / both MMAs of the block done
+    uint64_t drained;                 // teardown: every MMA issued so far has completed
+    uint32_t tmem_base, fail;
+    float q_inv[32];
+    float scales[8][16];              // per stage: 8 K scales, 8 V scales
+    Group g[2];
+};
+static_assert(sizeof(Control) <= 3072, "control block");
 
 template <bool FP8, int G>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a, const uint32_t n_stages) {
     constexpr int ES = FP8 ? 1 : 2;                    // bytes per pool element = 128-byte column groups per row
-    constexpr int QT = FP8 ? 2 : 1, PT = FP8 ? 4 : 1;  // terms a query element / a probability is split into
-    constexpr int CQ = (G * QT < 2) ? 2 : G * QT;      // columns per kv head in S^T and in O^T (N must be a multiple of 16)
-    constexpr int CP = (G * PT < 2) ? 2 : G * PT;
+    constexpr int PT = FP8 ? 3 : 1;                    // terms a probability is split into (a query element: two, accumulated by two MMA passes)
+    constexpr int CQ = (G < 2) ? 2 : G;                // columns per kv head in S^T: the q terms accumulate into the same column (two MMA passes)
+    constexpr int CP = (G * PT < 2) ? 2 : G * PT;      // columns per kv head in O^T: the probability terms are separate columns (N must be a multiple of 16)
     constexpr int NQ = HKV * CQ, NP = HKV * CP;
-    static_assert(NQ % 16 == 0 && NP % 16 == 0 && NQ <= 256 && NP <= 256 && NP + 2 * NQ <= 512, "MMA N and tensor memory columns");
-    static_assert(NQ % 32 == 0 || NQ == 16, "S^T is read 32 columns at a time");
+    static_assert(NQ % 16 == 0 && NP % 16 == 0 && NQ <= 64 && NP <= 128, "MMA N; a group owns 256 tensor-memory columns: O^T at 0, S^T at 128 and 192");
+    static_assert(NQ == 32, "S^T is read as one 32-column load");
     constexpr int KV_TILE = TILE * ES;                 // K (or V) of one block in shared memory
-    constexpr int QT_BYTES = NQ * 128 * ES, PT_BYTES = NP * 128 * ES;
-    constexpr uint32_t FMT_KV = 0u, FMT_P = FP8 ? 1u : 0u;          // kind::f8f6f4: E4M3 = 0, E5M2 = 1; kind::f16: F16 = 0
-    constexpr uint32_t IDESC_QK = instr_desc(FMT_KV, 0u, 0u, NQ), IDESC_PV = instr_desc(FMT_KV, FMT_P, 1u, NP);
+    constexpr int Q_SUB = NQ * 128;                    // one [NQ rows][128 B] tile of Q^T: per q term (E4M3) or per 64-dim column group (F16)
+    constexpr int QT_BYTES = 2 * Q_SUB, PT_BYTES = NP * 128 * ES;
+    constexpr uint32_t FMT_P = FP8 ? 1u : 0u;          // kind::f8f6f4: E4M3 = 0, E5M2 = 1; kind::f16: F16 = 0
+    constexpr uint32_t IDESC_QK = instr_desc(0u, 0u, 0u, NQ), IDESC_PV = instr_desc(0u, FMT_P, 1u, NP);
     constexpr int KSTEPS = 4 * ES;                     // 32 bytes of the contraction per MMA: 4 steps per 128-byte group
+    // operand descriptors: everything but the start address is constant (stride between 8-row groups 1024 B, version 1, 128-byte swizzle)
+    constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+    constexpr uint64_t DESC_K = DESC_HI | ((uint64_t)1u << 16);                       // leading offset unused by K-major operands
+    constexpr uint64_t DESC_V = DESC_HI | ((uint64_t)(TILE >> 4) << 16);              // MN-major: the second 64-dim column group one tile further
 
     const uint32_t split = blockIdx.x, seq = blockIdx.y;
     const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len);
@@ -212,14 +259,16 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const uint32_t b_begin = t_begin / BS, n_blk = (t_end + BS - 1) / BS - b_begin;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t* table = a.tables + (size_t)seq * a.table_stride + b_begin;
+#ifdef TKV_TC_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[13] = clock64();
+#endif
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     Control* c = reinterpret_cast<Control*>(smem);
-    unsigned char* q_tile = smem + 2048;                          // Q^T: [NQ rows][128 B] per column group
-    unsigned char* p_tile = q_tile + QT_BYTES;                    // P^T: two buffers
-    float* scales = reinterpret_cast<float*>(p_tile + 2 * PT_BYTES);   // per stage: 8 K scales, 8 V scales
-    unsigned char* stages = reinterpret_cast<unsigned char*>(scales) + 1024;   // per stage: K tile(s), V tile(s)
+    unsigned char* q_tile = smem + 3072;                          // Q^T: [NQ rows][128 B] per column group
+    unsigned char* p_tile = q_tile + QT_BYTES;                    // P^T: one buffer per group
+    unsigned char* stages = p_tile + 2 * PT_BYTES;                // per stage: K tile(s), V tile(s)
     const volatile uint32_t* fail_word = &c->fail;
     const uint32_t stage_bytes = 2 * KV_TILE;
 
@@ -228,86 +277,90 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             mbar_init(c->full + s, 1);
             mbar_init(c->empty + s, 1);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(c->s_full + b, 1);
-            mbar_init(c->s_free + b, 4);
-            mbar_init(c->p_full + b, 4);
-            mbar_init(c->p_free + b, 1);
-            c->raise[b] = 0;
+        for (int g = 0; g < 2; g++) {
+            for (int b = 0; b < 2; b++) {
+                mbar_init(c->g[g].s_full + b, 1);
+                mbar_init(c->g[g].s_free + b, 4);
+                c->g[g].raise[b] = 0;
+            }
+            mbar_init(&c->g[g].p_full, 4);
+            mbar_init(&c->g[g].p_free, 1);
         }
         mbar_init(&c->drained, 1);
         c->fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < 64) c->block_max[tid >> 5][tid & 31] = ordered(-INFINITY);
-    if (tid < 32) c->m_used[tid] = -INFINITY;
-    if (warp == 5) {                                               // tensor memory: 512 columns, this CTA alone on its SM
+    if (tid < 128) c->g[tid >> 6].block_max[(tid >> 5) & 1][tid & 31] = ordered(-INFINITY);
+    if (tid < 64) c->g[tid >> 5].m_used[tid & 31] = -INFINITY;
+    if (warp == 9) {                                               // tensor memory: 512 columns, this CTA alone on its SM
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&c->tmem_base)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp < 4) {
-        // ---- Q^T: thread (query head qh = tid / 4, dims [32 * (tid % 4), +32)) ----
-        const uint32_t qh = tid >> 2, part = tid & 3u, kvh = qh / G, g = qh % G;
-        float x[32];
-        const bool live = qh < a.n_q_heads;
-        const float* qrow = a.q + ((size_t)seq * a.n_q_heads + (live ? qh : 0)) * D + part * 32;
+    if (warp < 8) {
+        // zero Q^T and both P^T buffers (entries of other kv heads stay zero for good), then group 0 writes Q^T:
+        // thread (query head qh = t / 4, dims [32 * (t % 4), +32))
+        for (uint32_t i = tid; i < (2 * PT_BYTES + QT_BYTES) / 16; i += 256) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (warp < 4) {
+            const uint32_t qh = tid >> 2, part = tid & 3u, kvh = qh / G, g = qh % G;
+            float x[32];
+            const bool live = qh < a.n_q_heads;
+            const float* qrow = a.q + ((size_t)seq * a.n_q_heads + (live ? qh : 0)) * D + part * 32;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float4 f = live ? *reinterpret_cast<const float4*>(qrow + 4 * i) : make_float4(0, 0, 0, 0);
-            x[4 * i] = f.x * a.q_scale;
-            x[4 * i + 1] = f.y * a.q_scale;
-            x[4 * i + 2] = f.z * a.q_scale;
-            x[4 * i + 3] = f.w * a.q_scale;
-        }
-        // zero both P^T buffers and the unused rows of Q^T first (entries of other kv heads stay zero for good)
-        for (uint32_t i = tid; i < (2 * PT_BYTES + QT_BYTES) / 16; i += 128) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
-        named_barrier_softmax();
-        if (FP8) {
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-            // power of two that brings the head's largest element into [128, 256): exact to apply and to undo
-            int e = 0;
-            if (amax > 0.0f && amax < INFINITY) e = 7 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
-            e = max(-60, min(60, e));
-            const float up = __uint_as_float((uint32_t)(127 + e) << 23);
-            if (part == 0 && live) c->q_inv[qh] = __uint_as_float((uint32_t)(127 - e) << 23);
-            if (live) {
-#pragma unroll
-                for (int ch = 0; ch < 2; ch++) {                    // two 16-byte chunks of the row per term
-                    uint32_t hi[4], lo[4];
-#pragma unroll
-                    for (int wd = 0; wd < 4; wd++) {
-                        hi[wd] = lo[wd] = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            const float v = x[ch * 16 + wd * 4 + b] * up;
-                            const uint32_t h = e4m3_of(v);
-                            const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
-                            hi[wd] |= h << (8 * b);
-                            lo[wd] |= l << (8 * b);
-                        }
-                    }
-                    const uint32_t chunk = part * 2 + ch;
-                    *reinterpret_cast<uint4*>(q_tile + swz(kvh * CQ + g, chunk)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(q_tile + swz(kvh * CQ + G + g, chunk)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                }
+            for (int i = 0; i < 8; i++) {
+                const float4 f = live ? *reinterpret_cast<const float4*>(qrow + 4 * i) : make_float4(0, 0, 0, 0);
+                x[4 * i] = f.x * a.q_scale;
+                x[4 * i + 1] = f.y * a.q_scale;
+                x[4 * i + 2] = f.z * a.q_scale;
+                x[4 * i + 3] = f.w * a.q_scale;
             }
-        } else {
-            if (part == 0 && live) c->q_inv[qh] = 1.0f;
-            if (live) {
+            if (FP8) {
+                float amax = 0.0f;
 #pragma unroll
-                for (int ch = 0; ch < 4; ch++) {                    // 32 dims * 2 B = four 16-byte chunks; dims [64, 128) live in the second column group
-                    uint32_t wv[4];
+                for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+                // power of two that brings the head's largest element into [128, 256): exact to apply and to undo
+                int e = 0;
+                if (amax > 0.0f && amax < INFINITY) e = 7 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
+                e = max(-60, min(60, e));
+                const float up = __uint_as_float((uint32_t)(127 + e) << 23);
+                if (part == 0 && live) c->q_inv[qh] = __uint_as_float((uint32_t)(127 - e) << 23);
+                if (live) {
 #pragma unroll
-                    for (int wd = 0; wd < 4; wd++) {
-                        __half2 h = __floats2half2_rn(x[ch * 8 + wd * 2], x[ch * 8 + wd * 2 + 1]);
-                        wv[wd] = *reinterpret_cast<uint32_t*>(&h);
+                    for (int ch = 0; ch < 2; ch++) {                // two 16-byte chunks of the row per term
+                        uint32_t hi[4], lo[4];
+#pragma unroll
+                        for (int wd = 0; wd < 4; wd++) {
+                            hi[wd] = lo[wd] = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; b++) {
+                                const float v = x[ch * 16 + wd * 4 + b] * up;
+                                const uint32_t h = e4m3_of(v);
+                                const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
+                                hi[wd] |= h << (8 * b);
+                                lo[wd] |= l << (8 * b);
+                            }
+                        }
+                        const uint32_t chunk = part * 2 + ch;
+                        *reinterpret_cast<uint4*>(q_tile + swz(kvh * CQ + g, chunk)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        *reinterpret_cast<uint4*>(q_tile + Q_SUB + swz(kvh * CQ + g, chunk)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     }
-                    const uint32_t group = part >> 1, chunk = (part & 1u) * 4 + ch;
-                    *reinterpret_cast<uint4*>(q_tile + group * (NQ * 128) + swz(kvh * CQ + g, chunk)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            } else {
+                if (part == 0 && live) c->q_inv[qh] = 1.0f;
+                if (live) {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {                // 32 dims * 2 B = four 16-byte chunks; dims [64, 128) live in the second column group
+                        uint32_t wv[4];
+#pragma unroll
+                        for (int wd = 0; wd < 4; wd++) {
+                            __half2 h = __floats2half2_rn(x[ch * 8 + wd * 2], x[ch * 8 + wd * 2 + 1]);
+                            wv[wd] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        const uint32_t group = part >> 1, chunk = (part & 1u) * 4 + ch;
+                        *reinterpret_cast<uint4*>(q_tile + group * Q_SUB + swz(kvh * CQ + g, chunk)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    }
                 }
             }
         }
@@ -317,9 +370,11 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = c->tmem_base;
-    const uint32_t tmem_o = tmem, tmem_s0 = tmem + NP;            // O^T at column 0, the two S^T buffers behind it
+#ifdef TKV_TC_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[14] = clock64();
+#endif
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---- producer: the block table 32 entries at a time; lane 0 issues the copies ----
         uint32_t issued = 0, why = 4u;
         bool ok = true;
@@ -347,8 +402,8 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             tma_box(dst + KV_TILE + grp * TILE, &map_v, grp * 128, (int32_t)(id * ROWS), c->full + s);
                         }
                         if (sc_bytes) {
-                            bulk_copy(smem_u32(scales + s * 16), a.k_scales + (size_t)id * HKV, sc_bytes, c->full + s);
-                            bulk_copy(smem_u32(scales + s * 16 + 8), a.v_scales + (size_t)id * HKV, sc_bytes, c->full + s);
+                            bulk_copy(smem_u32(&c->scales[s][0]), a.k_scales + (size_t)id * HKV, sc_bytes, c->full + s);
+                            bulk_copy(smem_u32(&c->scales[s][8]), a.v_scales + (size_t)id * HKV, sc_bytes, c->full + s);
                         }
                         issued = k + 1;
                     }
@@ -359,164 +414,174 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         if (!ok && lane == 0) {
             atomicCAS(&c->fail, 0u, why);
             // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
-            for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++) {
-                const uint32_t addr = smem_u32(c->full + k % n_stages), parity = (k / n_stages) & 1u;
-                for (uint32_t it = 0; it < (1u << 20); it++) {
-                    uint32_t done;
-                    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-                    if (done) break;
-                }
-            }
+            for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
+                for (uint32_t it = 0; it < (1u << 20); it++)
+                    if (mbar_test(c->full + k % n_stages, (k / n_stages) & 1u)) break;
         }
-    } else if (warp == 5) {
-        // ---- MMA issuer: one thread ----
+    } else if (warp == 9) {
+        // ---- MMA issuer: one thread; QK of block k as soon as its copies have landed and its S^T buffer is free,
+        // PV of block k as soon as its P^T is written.  Block k belongs to group k & 1 (its j-th block, j = k >> 1). ----
         if (lane == 0) {
+            const uint32_t q_lo = smem_u32(q_tile) >> 4, st_lo = smem_u32(stages) >> 4, p_lo = smem_u32(p_tile) >> 4;
+            uint32_t qk = 0, pv = 0, idle = 0;
             bool ok = true;
-            auto issue_pv = [&](uint32_t j) {
-                const uint32_t s = j % n_stages, b = j & 1u;
-                if (!mbar_wait(c->p_full + b, (j >> 1) & 1u, fail_word)) return false;
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(stages + (size_t)s * stage_bytes + KV_TILE), p_addr = smem_u32(p_tile + b * PT_BYTES);
+            while (pv < n_blk && ok) {
+                bool did = false;
+                if (qk < n_blk) {
+                    const uint32_t g = qk & 1u, j = qk >> 1, sb = j & 1u, s = qk % n_stages;
+                    if (mbar_test(c->full + s, (qk / n_stages) & 1u) && (j < 2 || mbar_test(c->g[g].s_free + sb, ((j >> 1) - 1u) & 1u))) {
+                        tc_fence_after();
+                        const uint32_t d = tmem + g * 256u + 128u + sb * 64u, k_lo = st_lo + s * (stage_bytes >> 4);
+                        if (FP8) {
+                            // q = hi + lo: two passes over the K tile into the same accumulator columns
 #pragma unroll
-                for (int ks = 0; ks < KSTEPS; ks++) {
-                    // V^T (A, MN-major): 32 / ES block rows per step, 128 B each; dims beyond 64 (F16) in the second column group
-                    const uint64_t da = smem_desc(v_addr + ks * (32 / ES) * 128, TILE, 1024);
-                    // P^T (B, K-major): 32 bytes of the row per step
-                    const uint64_t db = smem_desc(p_addr + (ks / 4) * (NP * 128) + (ks % 4) * 32, 16, 1024);
-                    mma<FP8>(tmem_o, da, db, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                }
-                tc_commit(c->empty + s);
-                tc_commit(c->p_free + b);
-                return true;
-            };
-            const uint32_t q_addr = smem_u32(q_tile);
-            for (uint32_t i = 0; i < n_blk && ok; i++) {
-                const uint32_t s = i % n_stages, b = i & 1u;
-                ok = mbar_wait(c->full + s, (i / n_stages) & 1u, fail_word);
-                if (ok && i >= 2) ok = mbar_wait(c->s_free + b, ((i >> 1) - 1u) & 1u, fail_word);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(stages + (size_t)s * stage_bytes);
+                            for (int term = 0; term < 2; term++)
 #pragma unroll
-                for (int ks = 0; ks < KSTEPS; ks++) {
-                    const uint64_t da = smem_desc(k_addr + (ks / 4) * TILE + (ks % 4) * 32, 16, 1024);
-                    const uint64_t db = smem_desc(q_addr + (ks / 4) * (NQ * 128) + (ks % 4) * 32, 16, 1024);
-                    mma<FP8>(tmem_s0 + b * NQ, da, db, IDESC_QK, ks > 0 ? 1u : 0u);
+                                for (int ks = 0; ks < 4; ks++)
+                                    mma<FP8>(d, DESC_K | (k_lo + ks * 2), DESC_K | (q_lo + term * (Q_SUB >> 4) + ks * 2), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                        } else {
+#pragma unroll
+                            for (int ks = 0; ks < KSTEPS; ks++)
+                                mma<FP8>(d, DESC_K | (k_lo + (ks / 4) * (TILE >> 4) + (ks % 4) * 2), DESC_K | (q_lo + (ks / 4) * (Q_SUB >> 4) + (ks % 4) * 2),
+                                         IDESC_QK, ks > 0 ? 1u : 0u);
+                        }
+                        tc_commit(c->g[g].s_full + sb);
+                        qk++;
+                        did = true;
+                    }
                 }
-                tc_commit(c->s_full + b);
-                if (i >= 1) ok = issue_pv(i - 1);
+                if (pv < qk) {
+                    const uint32_t g = pv & 1u, j = pv >> 1, s = pv % n_stages;
+                    if (mbar_test(&c->g[g].p_full, j & 1u)) {
+                        tc_fence_after();
+                        const uint32_t v_lo = st_lo + s * (stage_bytes >> 4) + (KV_TILE >> 4), pg_lo = p_lo + g * (PT_BYTES >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < KSTEPS; ks++)     // V^T MN-major: 32 / ES block rows of 128 B per step; P^T K-major: 32 bytes of the row per step
+                            mma<FP8>(tmem + g * 256u, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
+                                     IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                        tc_commit(c->empty + s);
+                        tc_commit(&c->g[g].p_free);
+                        pv++;
+                        did = true;
+                    }
+                }
+                if (did) idle = 0;
+                else if (++idle > (1u << 24) || ((idle & 63u) == 63u && *fail_word)) ok = false;
             }
-            if (ok) ok = issue_pv(n_blk - 1);
             if (!ok) atomicCAS(&c->fail, 0u, 4u);
             // nothing of this CTA may still be writing tensor memory when it is freed
             tc_commit(&c->drained);
-            const uint32_t addr = smem_u32(&c->drained);
-            for (uint32_t it = 0; it < (1u << 22); it++) {
-                uint32_t done;
-                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(done) : "r"(addr), "r"(0u) : "memory");
-                if (done) break;
-            }
+            for (uint32_t it = 0; it < (1u << 22); it++)
+                if (mbar_test(&c->drained, 0u)) break;
         }
         __syncwarp();
     } else {
-        // ---- softmax: thread tid owns block row tid = (token tid / 8, kv head tid % 8) and tensor-memory lane tid ----
-        const uint32_t kvh = tid & 7u, tok = tid >> 3;
-        const uint32_t lane_base = (warp * 32u) << 16;
+        // ---- softmax: group grp = warp / 4 takes blocks grp, grp + 2, ...; thread t of the group owns block row
+        // t = (token t / 8, kv head t % 8) and tensor-memory lane t ----
+        const uint32_t grp = warp >> 2, t = tid & 127u, kvh = t & 7u, tok = t >> 3;
+        Group* gs = &c->g[grp];
+        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
+        const uint32_t tmem_o = tmem + grp * 256u, tmem_s = tmem_o + 128u;
+        const uint32_t n_mine = n_blk > grp ? (n_blk - grp + 1u) / 2u : 0u;
+        unsigned char* pt = p_tile + grp * PT_BYTES;
         float m_used[G], l[G], q_inv[G];
+        uint32_t p_off[G][PT];                                      // where this row's probabilities go in P^T (row = kv head, term, query head; column = this row)
 #pragma unroll
         for (int g = 0; g < G; g++) {
             m_used[g] = -INFINITY;
             l[g] = 0.0f;
             q_inv[g] = c->q_inv[kvh * G + g];
+#pragma unroll
+            for (int term = 0; term < PT; term++)
+                p_off[g][term] = FP8 ? swz(kvh * CP + term * G + g, t >> 4) + (t & 15u)
+                                     : (t >> 6) * (NP * 128) + swz(kvh * CP + g, (t & 63u) >> 3) + (t & 7u) * 2;
         }
         bool ok = true;
-        for (uint32_t i = 0; i < n_blk; i++) {
-            const uint32_t s = i % n_stages, b = i & 1u;
+        for (uint32_t j = 0; j < n_mine; j++) {
+            const uint32_t i = 2u * j + grp, s = i % n_stages, b = j & 1u;
+#ifdef TKV_TC_TIMING
+            const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && j == 3;
+#endif
+            TKV_STAMP(0);
             const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + i) * BS);
             const bool valid = tok < n_valid;
             float sc[G];                                            // this row's scores against its own kv head's query heads (log2 domain)
             float lv = 0.0f, inv_vs = 1.0f;
             if (ok) {
-                ok = mbar_wait(c->s_full + b, (i >> 1) & 1u, fail_word) && mbar_wait(c->full + s, (i / n_stages) & 1u, fail_word);
+                ok = mbar_wait(gs->s_full + b, (j >> 1) & 1u, fail_word) && mbar_wait(c->full + s, (i / n_stages) & 1u, fail_word);
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
             }
+            TKV_STAMP(1);
             if (ok) {
                 tc_fence_after();
                 float part[CQ];
-                // the row's NQ columns, 32 at a time (16 when that is all there is); keep the CQ columns of this row's kv head
-                if (NQ >= 32) {
-#pragma unroll
-                    for (int c0 = 0; c0 < NQ; c0 += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem_s0 + b * NQ + lane_base + c0, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int h = 0; h < 32 / CQ; h++)
-                            if ((uint32_t)(c0 / CQ + h) == kvh) {
-#pragma unroll
-                                for (int j = 0; j < CQ; j++) part[j] = __uint_as_float(r[h * CQ + j]);
-                            }
-                    }
-                } else {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_s0 + b * NQ + lane_base, r);     // NQ = 16: the upper 16 columns read belong to the next buffer and are ignored
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int h = 0; h < 16 / CQ; h++)
-                        if ((uint32_t)h == kvh) {
-#pragma unroll
-                            for (int j = 0; j < CQ; j++) part[j] = __uint_as_float(r[h * CQ + j]);
-                        }
-                }
+                uint32_t r[32];
+                tmem_ld32(tmem_s + b * 64u + lane_base, r);
+                tmem_wait_ld();
+                TKV_STAMP(2);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(c->s_free + b);
+                if (lane == 0) mbar_arrive(gs->s_free + b);
+                TKV_STAMP(3);
+                // keep the CQ columns of this row's kv head
+#if TKV_TC_ABLATE >= 2
+#pragma unroll
+                for (int h = 0; h < HKV; h++)
+                    if ((uint32_t)h == kvh) {
+#pragma unroll
+                        for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[h * CQ + q]);
+                    }
+#else
+#pragma unroll
+                for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[q]);
+#endif
                 float ks = 1.0f, vs = 1.0f;
                 if (a.k_scales) {
-                    ks = scales[s * 16 + kvh];
-                    vs = scales[s * 16 + 8 + kvh];
+                    ks = c->scales[s][kvh];
+                    vs = c->scales[s][8 + kvh];
                     lv = fast_log2(vs);
-                    inv_vs = __frcp_rn(vs);
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));   // scales the row sum only
                 }
 #pragma unroll
-                for (int g = 0; g < G; g++) {
-                    const float raw = FP8 ? part[g] + part[G + g] : part[g];
-                    sc[g] = valid ? raw * (ks * q_inv[g]) : -INFINITY;
-                }
+                for (int g = 0; g < G; g++) sc[g] = valid ? part[g] * (ks * q_inv[g]) + lv : -INFINITY;   // the V scale rides in the exponent
             } else {
 #pragma unroll
                 for (int g = 0; g < G; g++) sc[g] = -INFINITY;
             }
+            TKV_STAMP(4);
             // does any query head of this kv head exceed its running maximum by more than 2^RAISE in this block?
             bool want = false;
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                float bm = sc[g] + lv;                              // the weight's exponent carries the V scale
-                bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 8));
-                bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 16));
-                if (bm > m_used[g] + RAISE) {
-                    want = true;
-                    if (lane < 8) atomicMax(&c->block_max[b][kvh * G + g], ordered(bm));
+            for (int g = 0; g < G; g++) want = want || sc[g] > m_used[g] + RAISE;
+            if (__any_sync(0xFFFFFFFFu, want)) {                    // rare: post this warp's maxima
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    float bm = sc[g];
+                    bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 8));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 16));
+                    if (lane < 8 && bm > m_used[g] + RAISE) {
+                        atomicMax(&gs->block_max[b][kvh * G + g], ordered(bm));
+                        gs->raise[b] = 1u;
+                    }
                 }
             }
-            if (want && lane < 8) c->raise[b] = 1u;
-            named_barrier_softmax();
-            if (c->raise[b]) {
-                // ---- raise the maxima: rescale O^T in tensor memory and the row sums; rare ----
-                if (tid < 32) {
-                    const float bm = unordered(c->block_max[b][tid]), mo = c->m_used[tid];
+            TKV_STAMP(5);
+            asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
+            TKV_STAMP(6);
+            if (gs->raise[b]) {
+                // ---- raise the maxima: rescale O^T in tensor memory and the row sums; a few times per sequence at most ----
+                if (t < 32) {
+                    const float bm = unordered(gs->block_max[b][t]), mo = gs->m_used[t];
                     const float mn = fmaxf(mo, bm);
-                    c->factor[tid] = (mn == mo) ? 1.0f : (mo == -INFINITY ? 0.0f : fast_exp2(mo - mn));
-                    c->m_used[tid] = mn;
-                    c->block_max[b][tid] = ordered(-INFINITY);
+                    gs->factor[t] = (mn == mo) ? 1.0f : (mo == -INFINITY ? 0.0f : fast_exp2(mo - mn));
+                    gs->m_used[t] = mn;
+                    gs->block_max[b][t] = ordered(-INFINITY);
                 }
-                named_barrier_softmax();
-                if (tid == 0) c->raise[b] = 0u;
-                if (i > 0) {
-                    // the PV MMA of the previous block must have finished with O^T; none follows until this block's P^T is published
-                    if (ok) ok = mbar_wait(c->p_free + ((i - 1) & 1u), ((i - 1) >> 1) & 1u, fail_word);
+                asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
+                if (t == 0) gs->raise[b] = 0u;
+                if (j > 0) {
+                    // the PV MMA of the group's previous block must have finished with O^T; none follows until this block's P^T is published
+                    if (ok) ok = mbar_wait(&gs->p_free, (j - 1u) & 1u, fail_word);
                     if (ok) {
                         tc_fence_after();
 #pragma unroll
@@ -525,9 +590,9 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             tmem_ld32(tmem_o + lane_base + c0, r);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int col = c0 + j, head = (col / CP) * G + (col % CP) % G;
-                                r[j] = __float_as_uint(__uint_as_float(r[j]) * c->factor[head]);
+                            for (int q = 0; q < 32; q++) {
+                                const int col = c0 + q, head = (col / CP) * G + (col % CP) % G;
+                                r[q] = __float_as_uint(__uint_as_float(r[q]) * gs->factor[head]);
                             }
                             tmem_st32(tmem_o + lane_base + c0, r);
                         }
@@ -537,99 +602,153 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
 #pragma unroll
                 for (int g = 0; g < G; g++) {
-                    l[g] *= c->factor[kvh * G + g];
-                    m_used[g] = c->m_used[kvh * G + g];
+                    l[g] *= gs->factor[kvh * G + g];
+                    m_used[g] = gs->m_used[kvh * G + g];
                 }
-                named_barrier_softmax();                            // factor[] and m_used[] are read before the next raise rewrites them
+                asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");   // factor[] and m_used[] are read before the next raise rewrites them
             }
-            if (ok && i >= 2) ok = mbar_wait(c->p_free + b, ((i >> 1) - 1u) & 1u, fail_word);
+            TKV_STAMP(7);
+            if (ok && j >= 1) ok = mbar_wait(&gs->p_free, (j - 1u) & 1u, fail_word);
+            TKV_STAMP(8);
             if (ok) {
-                unsigned char* pt = p_tile + b * PT_BYTES;
+                // weights 2^(score - maximum + SHIFT), two query heads at a time in half2.  E4M3 pool: an E5M2 byte is the top
+                // byte of an F16, so the three terms are peeled off by masking the low byte and subtracting (exact in F16: the
+                // weights are non-negative and every residual fits); the row sum takes the value the three terms add up to.
+                const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
+#if TKV_TC_ABLATE >= 3
 #pragma unroll
-                for (int g = 0; g < G; g++) {
-                    const float e = sc[g] + lv - m_used[g];          // <= RAISE; -inf for a row past the sequence end
-                    const float w = fast_exp2(e);
-                    l[g] += w * inv_vs;
-                    float x = fast_exp2(e + SHIFT);
+                for (int g = 0; g < G; g += 2) {
+                    const float x0 = fast_exp2(sc[g] - m_used[g] + SHIFT);                         // <= 2^(RAISE + SHIFT); 0 for a row past the sequence end
+                    const float x1 = (g + 1 < G) ? fast_exp2(sc[g + 1 < G ? g + 1 : g] - m_used[g + 1 < G ? g + 1 : g] + SHIFT) : 0.0f;
+                    __half2 h = __floats2half2_rn(x0, x1);
                     if (FP8) {
-#pragma unroll
-                        for (int t = 0; t < PT; t++) {
-                            const uint32_t byte = e5m2_of(x);
-                            x -= e5m2_to_f32(byte);
-                            const uint32_t row = kvh * CP + t * G + g;
-                            pt[swz(row, tid >> 4) + (tid & 15u)] = (unsigned char)byte;
+                        const uint32_t t1 = *reinterpret_cast<uint32_t*>(&h) & 0xFF00FF00u;
+                        const __half2 r1 = __hsub2(h, *reinterpret_cast<const __half2*>(&t1));
+                        const uint32_t t2 = *reinterpret_cast<const uint32_t*>(&r1) & 0xFF00FF00u;
+                        const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
+                        const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
+                        h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));         // = t1 + t2 + t3
+#if TKV_TC_ABLATE >= 9
+                        pt[p_off[g][0]] = (unsigned char)(t1 >> 8);
+                        pt[p_off[g][1]] = (unsigned char)(t2 >> 8);
+                        pt[p_off[g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 8);
+                        if (g + 1 < G) {
+                            pt[p_off[g + 1 < G ? g + 1 : g][0]] = (unsigned char)(t1 >> 24);
+                            pt[p_off[g + 1 < G ? g + 1 : g][1]] = (unsigned char)(t2 >> 24);
+                            pt[p_off[g + 1 < G ? g + 1 : g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 24);
                         }
+#else
+                        l[g] += __uint_as_float(t1 ^ t2 ^ t3);
+#endif
                     } else {
-                        const uint32_t row = kvh * CP + g, el = tid & 63u;        // element tid of the row: column group tid / 64
-                        *reinterpret_cast<__half*>(pt + (tid >> 6) * (NP * 128) + swz(row, el >> 3) + (el & 7u) * 2) = __float2half_rn(x);
+                        *reinterpret_cast<__half*>(pt + p_off[g][0]) = __low2half(h);
+                        if (g + 1 < G) *reinterpret_cast<__half*>(pt + p_off[g + 1 < G ? g + 1 : g][0]) = __high2half(h);
                     }
+                    const float2 q = __half22float2(h);
+                    l[g] += q.x * l_scale;
+                    if (g + 1 < G) l[g + 1 < G ? g + 1 : g] += q.y * l_scale;
                 }
+#else
+                l[0] += l_scale + sc[0] + sc[1] + sc[2 < G ? 2 : 0] + sc[3 < G ? 3 : 0];
+#endif
                 if (!valid) {
                     // a row past the sequence end holds whatever the pool held there: 0 * NaN must not reach O^T
                     unsigned char* vt = stages + (size_t)s * stage_bytes + KV_TILE;
 #pragma unroll
-                    for (int grp = 0; grp < ES; grp++)
+                    for (int cg = 0; cg < ES; cg++)
 #pragma unroll
-                        for (int ch = 0; ch < 8; ch++) *reinterpret_cast<uint4*>(vt + grp * TILE + swz(tid, ch)) = make_uint4(0, 0, 0, 0);
+                        for (int ch = 0; ch < 8; ch++) *reinterpret_cast<uint4*>(vt + cg * TILE + swz(t, ch)) = make_uint4(0, 0, 0, 0);
                 }
+                TKV_STAMP(9);
                 fence_async_smem();
+                TKV_STAMP(10);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(c->p_full + b);              // also after a failure: the issuer's wait then ends through the fail word
+            if (lane == 0) mbar_arrive(&gs->p_full);                // also after a failure: the issuer then ends through the fail word
+            TKV_STAMP(11);
         }
-        // ---- the partial of this (sequence, token range): wait for the last PV MMA, then O^T rows back out ----
-        if (ok) ok = mbar_wait(c->p_free + ((n_blk - 1) & 1u), ((n_blk - 1) >> 1) & 1u, fail_word);
+#ifdef TKV_TC_TIMING
+        if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[12] = clock64();
+#endif
+        // ---- the group's result: wait for its last PV MMA, row sums over the group, O^T rows out of tensor memory ----
+        if (ok && n_mine) {
+            ok = mbar_wait(&gs->p_free, (n_mine - 1u) & 1u, fail_word);
+            if (!ok) atomicCAS(&c->fail, 0u, 4u);
+        }
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float x = l[g];
             x += __shfl_xor_sync(0xFFFFFFFFu, x, 8);
             x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);
-            if (lane < 8) c->l_sum[warp][kvh * G + g] = x;
+            if (lane < 8) gs->l_sum[warp & 3u][kvh * G + g] = x;
         }
-        named_barrier_softmax();
-        if (ok) {
+        float acc[HKV * G];                                         // this thread's output dim t, every query head
+#pragma unroll
+        for (int q = 0; q < HKV * G; q++) acc[q] = 0.0f;
+        if (ok && n_mine) {
             tc_fence_after();
-            const float down = __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
-            const uint32_t d = tid;                                  // this thread's tensor-memory lane is output dim d
 #pragma unroll
             for (int c0 = 0; c0 < NP; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_o + lane_base + c0, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int h = 0; h < 32 / CP; h++) {
-                    const uint32_t head_kv = c0 / CP + h;
-#pragma unroll
-                    for (int g = 0; g < G; g++) {
-                        float acc = 0.0f;
-#pragma unroll
-                        for (int t = 0; t < PT; t++) acc += __uint_as_float(r[h * CP + t * G + g]);
-                        const uint32_t qh = head_kv * G + g;
-                        if (qh < a.n_q_heads) {
-                            float* pr = a.partial + ((((size_t)seq * HKV + head_kv) * a.n_splits + split) * G + g) * (D + 2);
-                            pr[2 + d] = acc * down;
-                        }
-                    }
+                for (int q = 0; q < 32; q++) {
+                    const int col = c0 + q;
+                    if (col < NP) acc[(col / CP) * G + (col % CP) % G] += __uint_as_float(r[q]);
                 }
             }
             tc_fence_before();
-            if (tid < 32 && tid < a.n_q_heads) {
-                const uint32_t head_kv = tid / G, g = tid % G;
-                float* pr = a.partial + ((((size_t)seq * HKV + head_kv) * a.n_splits + split) * G + g) * (D + 2);
-                pr[0] = c->m_used[tid];
-                pr[1] = c->l_sum[0][tid] + c->l_sum[1][tid] + c->l_sum[2][tid] + c->l_sum[3][tid];
+        }
+        // group 1 hands its numerators over through shared memory (the ring is idle by now); group 0 merges and writes the partial
+        float* other = reinterpret_cast<float*>(stages);            // [query head][dim]
+        float* merge = other + HKV * G * D;                         // per query head: weight of group 0, weight of group 1
+        asm volatile("bar.sync 3, 256;" ::: "memory");              // both groups have seen their last MMA complete: no copy or MMA touches the ring any more
+        if (grp == 1) {
+#pragma unroll
+            for (int q = 0; q < HKV * G; q++) other[q * D + t] = acc[q];
+        } else if (t < HKV * G && t < a.n_q_heads) {                // one thread per query head: the two groups' maxima and row sums
+            const float m0 = c->g[0].m_used[t], m1 = c->g[1].m_used[t], mm = fmaxf(m0, m1);
+            const float f0 = m0 == -INFINITY ? 0.0f : fast_exp2(m0 - mm), f1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - mm);
+            float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                l0 += c->g[0].l_sum[w][t];
+                l1 += c->g[1].l_sum[w][t];
             }
-        } else if (tid == 0) {
-            atomicCAS(&c->fail, 0u, 4u);
+            const float down = __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
+            merge[2 * t] = f0 * down;
+            merge[2 * t + 1] = f1 * down;
+            if (ok) {
+                float* pr = a.partial + ((((size_t)seq * HKV + t / G) * a.n_splits + split) * G + t % G) * (D + 2);
+                pr[0] = mm;
+                pr[1] = l0 * f0 + l1 * f1;
+            }
+        }
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (grp == 0 && ok) {
+            float* pr0 = a.partial + (((size_t)seq * HKV * a.n_splits + split) * G) * (D + 2) + 2 + t;
+            const size_t head_stride = (size_t)a.n_splits * G * (D + 2);
+#pragma unroll
+            for (int q = 0; q < HKV * G; q++) {
+                if ((uint32_t)q < a.n_q_heads) {
+                    const float2 f = *reinterpret_cast<const float2*>(merge + 2 * q);
+                    const float v1 = f.y != 0.0f ? other[q * D + t] * f.y : 0.0f;
+                    pr0[(size_t)(q / G) * head_stride + (size_t)(q % G) * (D + 2)] = acc[q] * f.x + v1;
+                }
+            }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
     if (tid == 0 && c->fail && a.status) atomicCAS(a.status, 0u, c->fail);
+#ifdef TKV_TC_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[15] = clock64();
+#endif
 }
 
 // ---- self-check of the operand plumbing ---------------------------------------------------------------
@@ -762,9 +881,10 @@ bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t tot
 }
 
 template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t st) {
-    constexpr int ES = FP8 ? 1 : 2, QT = FP8 ? 2 : 1, PT = FP8 ? 4 : 1;
-    constexpr int CQ = (G * QT < 2) ? 2 : G * QT, CP = (G * PT < 2) ? 2 : G * PT;
-    constexpr size_t fixed = 1024 /* alignment slack */ + 2048 + (size_t)HKV * CQ * 128 * ES + 2 * (size_t)HKV * CP * 128 * ES + 1024;
+    constexpr int ES = FP8 ? 1 : 2, QT = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;
+    constexpr int CQ = (G < 2) ? 2 : G, CP = (G * PT < 2) ? 2 : G * PT;
+    (void)QT;
+    constexpr size_t fixed = 1024 /* alignment slack */ + 3072 + 2 * (size_t)HKV * CQ * 128 + 2 * (size_t)HKV * CP * 128 * ES;
     constexpr size_t stage = 2 * (size_t)TILE * ES;
     const uint32_t n_stages = (uint32_t)std::min<size_t>(8, (227 * 1024 - fixed) / stage);
     if (n_stages < 2) return cudaErrorInvalidConfiguration;
@@ -783,7 +903,7 @@ template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, 
             granted[dev] = true;
         }
     }
-    kernel<<<grid, 192, smem, st>>>(mk, mv, a, n_stages);
+    kernel<<<grid, 320, smem, st>>>(mk, mv, a, n_stages);
     return cudaGetLastError();
 }
 
@@ -852,4 +972,11 @@ cudaError_t selfcheck(uint64_t out[4]) {
     return e;
 }
 
+#ifdef TKV_TC_TIMING
+cudaError_t read_stamps(unsigned long long out[16]) { return cudaMemcpyFromSymbol(out, g_tc_stamps, 16 * sizeof(unsigned long long)); }
+#endif
+
 }  // namespace tkv_tc
+#ifdef TKV_TC_TIMING
+extern "C" int32_t tkv_debug_tc_stamps(unsigned long long* out) { return tkv_tc::read_stamps(out) == cudaSuccess ? 0 : 3; }
+#endif
