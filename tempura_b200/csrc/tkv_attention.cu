@@ -848,9 +848,10 @@ extern "C" {
 
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens) {
-    // sized for the smallest token range the library may choose (64) unless the caller fixes one
+    // sized for the smallest token range the library may choose (64) unless the caller fixes one; two partial results per
+    // range (the tcgen05 kernel's two softmax groups each write their own)
     if (split_tokens == 0) split_tokens = 64;
-    return (uint64_t)n_seqs * n_q_heads * splits_for(max_kv_len, split_tokens) * (head_dim + 2) * sizeof(float);
+    return 2ull * n_seqs * n_q_heads * splits_for(max_kv_len, split_tokens) * (head_dim + 2) * sizeof(float);
 }
 
 int32_t tkv_selfcheck_tensor_cores(uint64_t mismatches[4]) {
@@ -964,6 +965,7 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             t.tables = a.tables;
             t.kv_lens = a.kv_lens;
             t.partial = a.partial;
+            t.n_seqs = d->n_seqs;
             t.n_q_heads = a.n_q_heads;
             t.table_stride = a.table_stride;
             t.n_splits = n_splits;
@@ -972,7 +974,9 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             t.total_blocks = a.total_blocks;
             t.q_scale = a.q_scale;
             t.status = a.status;
-            e = tkv_tc::launch(pool->dtype == TKV_DTYPE_E4M3, a.group, kp, vp, t, n_splits, d->n_seqs, st);
+            e = tkv_tc::launch(pool->dtype == TKV_DTYPE_E4M3, a.group, kp, vp, t, st);
+            a.n_splits = 2u * n_splits;              // partial slots per (sequence, kv head): two per token range
+            a.parts_per_split = 2;
             if (e == cudaSuccess) {
                 decode_attn_combine<<<dim3(d->n_q_heads, d->n_seqs), D, 0, st>>>(a);
                 e = cudaGetLastError();

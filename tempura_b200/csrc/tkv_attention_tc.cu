@@ -110,10 +110,6 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt
 }
 template <bool FP8>
 __device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-#if defined(TKV_TC_ABLATE) && TKV_TC_ABLATE >= 11
-    // debug builds 11 / 12 / 13: no PV / no QK / no MMA at all (the PV form is the one with an MN-major A operand: bit 15 of the descriptor)
-    if ((TKV_TC_ABLATE == 11 && (idesc & (1u << 15))) || (TKV_TC_ABLATE == 12 && !(idesc & (1u << 15))) || TKV_TC_ABLATE == 13) return;
-#endif
     if (FP8)
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
                      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
@@ -200,49 +196,47 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
         : "r"(taddr) : "memory");
 }
 
-#ifndef TKV_TC_ABLATE
-#define TKV_TC_ABLATE 9      // debug builds drop parts of the softmax to time the rest (their output is wrong on purpose): 1 = waits, loads and
-#endif                       // barriers only, 2 = + column selection and scores, 3 = + weights without the P^T stores, 9 = everything
-#ifdef TKV_TC_TIMING
-// Debug builds: cycle stamps of one softmax thread (CTA 0, group 0, row 0) through its fourth block.
-__device__ unsigned long long g_tc_stamps[16];
-#define TKV_STAMP(k) do { if (stamp_on) g_tc_stamps[k] = clock64(); } while (0)
-#else
-#define TKV_STAMP(k) do { } while (0)
-#endif
-
-// Control block at the head of shared memory.  Two softmax groups (warps 0-3 and 4-7) take alternate blocks; each
-// has its own S^T buffers, P^T buffer, O^T accumulator, running maxima and row sums, merged once at the end.
+// Control block at the head of shared memory.  Two softmax groups (warps 0-3 and 4-7) take alternate blocks of a token
+// range; each has its own S^T buffers, P^T buffers, O^T accumulator, running maxima and row sums, and writes its own
+// partial result (the split-merge kernel folds them together with the other ranges').
+constexpr int MAX_ITEMS = 128;        // token ranges one CTA walks
 struct Group {
     uint64_t s_full[2], s_free[2];    // S^T buffers: QK done / every warp of the group has read it
-    uint64_t p_full, p_free;          // P^T buffer: written / the PV MMA has read it
+    uint64_t p_full[2], p_free[2];    // P^T buffers: written / the PV MMA has read it
     int block_max[2][32];             // per block parity: ordered-int maxima of the query heads that asked for a raise
     uint32_t raise[2];
     float m_used[32], factor[32], l_sum[4][32];
 };
 struct Control {
-    uint64_t full[8], empty[8];       // ring stages: copies landed / both MMAs of the block done
-    uint64_t drained;                 // teardown: every MMA issued so far has completed
-    uint32_t tmem_base, fail;
-    float q_inv[32];
-    float scales[8][16];              // per stage: 8 K scales, 8 V scales
+    uint64_t k_full[8], k_empty[8];   // K ring: tile landed / the QK MMAs that read it are done (a K tile is held only that long)
+    uint64_t v_full[8], v_empty[8];   // V ring (the block's scales travel with it): landed / the PV MMAs are done
+    uint64_t q_full, q_free;          // Q^T: written for the next range / every QK MMA of the current range done
+    uint64_t drained[2];              // teardown: every MMA an issuer has issued has completed
+    uint32_t tmem_base, fail, n_items, pad;
+    float q_inv[2][32];               // per range parity: what undoes the power-of-two scale of each query head
+    float scales[8][16];              // per V slot: 8 K scales, 8 V scales
     Group g[2];
+    uint32_t item_id[MAX_ITEMS];      // sequence * ranges per sequence + range
+    uint16_t item_blocks[MAX_ITEMS];
 };
-static_assert(sizeof(Control) <= 3072, "control block");
+static_assert(sizeof(Control) <= 5120, "control block");
 
+// A persistent CTA per SM walks token ranges (sequence, range) c, c + gridDim.x, ...: barriers, tensor memory and the ring
+// are set up once, and the producer runs ahead across range boundaries, so the ring never drains between ranges.
 template <bool FP8, int G>
-__global__ void __launch_bounds__(320, 1)
-decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a, const uint32_t n_stages) {
+__global__ void __launch_bounds__(352, 1)
+decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a, const uint32_t n_k, const uint32_t n_v) {
     constexpr int ES = FP8 ? 1 : 2;                    // bytes per pool element = 128-byte column groups per row
-    constexpr int PT = FP8 ? 3 : 1;                    // terms a probability is split into (a query element: two, accumulated by two MMA passes)
-    constexpr int CQ = (G < 2) ? 2 : G;                // columns per kv head in S^T: the q terms accumulate into the same column (two MMA passes)
-    constexpr int CP = (G * PT < 2) ? 2 : G * PT;      // columns per kv head in O^T: the probability terms are separate columns (N must be a multiple of 16)
+    constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;   // terms a query element / a probability is split into
+    constexpr int PBUF = FP8 ? 2 : 1;                  // P^T buffers per group
+    constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS;   // columns per kv head in S^T and in O^T (N must be a multiple of 16)
+    constexpr int CP = (G * PT < 2) ? 2 : G * PT;
     constexpr int NQ = HKV * CQ, NP = HKV * CP;
     static_assert(NQ % 16 == 0 && NP % 16 == 0 && NQ <= 64 && NP <= 128, "MMA N; a group owns 256 tensor-memory columns: O^T at 0, S^T at 128 and 192");
-    static_assert(NQ == 32, "S^T is read as one 32-column load");
+    static_assert(NQ == 64 || NQ == 32, "S^T is read as one 64- or 32-column load");
     constexpr int KV_TILE = TILE * ES;                 // K (or V) of one block in shared memory
-    constexpr int Q_SUB = NQ * 128;                    // one [NQ rows][128 B] tile of Q^T: per q term (E4M3) or per 64-dim column group (F16)
-    constexpr int QT_BYTES = 2 * Q_SUB, PT_BYTES = NP * 128 * ES;
+    constexpr int Q_SUB = NQ * 128;                    // one [NQ rows][128 B] tile of Q^T (F16: one per 64-dim column group)
+    constexpr int QT_BYTES = Q_SUB * ES, PT_BYTES = NP * 128 * ES;
     constexpr uint32_t FMT_P = FP8 ? 1u : 0u;          // kind::f8f6f4: E4M3 = 0, E5M2 = 1; kind::f16: F16 = 0
     constexpr uint32_t IDESC_QK = instr_desc(0u, 0u, 0u, NQ), IDESC_PV = instr_desc(0u, FMT_P, 1u, NP);
     constexpr int KSTEPS = 4 * ES;                     // 32 bytes of the contraction per MMA: 4 steps per 128-byte group
@@ -251,492 +245,503 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     constexpr uint64_t DESC_K = DESC_HI | ((uint64_t)1u << 16);                       // leading offset unused by K-major operands
     constexpr uint64_t DESC_V = DESC_HI | ((uint64_t)(TILE >> 4) << 16);              // MN-major: the second 64-dim column group one tile further
 
-    const uint32_t split = blockIdx.x, seq = blockIdx.y;
-    const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len);
-    const uint32_t t_begin = split * a.split_tokens;
-    if (t_begin >= kv_len) return;
-    const uint32_t t_end = min(kv_len, t_begin + a.split_tokens);
-    const uint32_t b_begin = t_begin / BS, n_blk = (t_end + BS - 1) / BS - b_begin;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t* table = a.tables + (size_t)seq * a.table_stride + b_begin;
-#ifdef TKV_TC_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[13] = clock64();
-#endif
+    const uint32_t ranges = a.n_splits;                // token ranges per sequence
+    const uint32_t n_parts = 2u * a.n_splits;          // partial slots per (sequence, kv head): one per range and group
 
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem[];
     Control* c = reinterpret_cast<Control*>(smem);
-    unsigned char* q_tile = smem + 3072;                          // Q^T: [NQ rows][128 B] per column group
-    unsigned char* p_tile = q_tile + QT_BYTES;                    // P^T: one buffer per group
-    unsigned char* stages = p_tile + 2 * PT_BYTES;                // per stage: K tile(s), V tile(s)
+    unsigned char* q_tile = smem + 5120;                          // Q^T of the current range
+    unsigned char* p_tile = q_tile + QT_BYTES;                    // P^T: PBUF buffers per group
+    unsigned char* k_ring = p_tile + 2 * PBUF * PT_BYTES;         // n_k K tiles, then n_v V tiles
+    unsigned char* v_ring = k_ring + (size_t)n_k * KV_TILE;
     const volatile uint32_t* fail_word = &c->fail;
-    const uint32_t stage_bytes = 2 * KV_TILE;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < n_stages; s++) {
-            mbar_init(c->full + s, 1);
-            mbar_init(c->empty + s, 1);
+        for (uint32_t s = 0; s < 8; s++) {
+            mbar_init(c->k_full + s, 1);
+            mbar_init(c->k_empty + s, 1);
+            mbar_init(c->v_full + s, 1);
+            mbar_init(c->v_empty + s, 1);
         }
-        for (int g = 0; g < 2; g++) {
+        for (int g = 0; g < 2; g++)
             for (int b = 0; b < 2; b++) {
                 mbar_init(c->g[g].s_full + b, 1);
                 mbar_init(c->g[g].s_free + b, 4);
+                mbar_init(c->g[g].p_full + b, 4);
+                mbar_init(c->g[g].p_free + b, 1);
                 c->g[g].raise[b] = 0;
             }
-            mbar_init(&c->g[g].p_full, 4);
-            mbar_init(&c->g[g].p_free, 1);
-        }
-        mbar_init(&c->drained, 1);
-        c->fail = 0;
+        mbar_init(&c->q_full, 4);
+        mbar_init(&c->q_free, 1);
+        mbar_init(c->drained, 1);
+        mbar_init(c->drained + 1, 1);
+        // tiles are addressed through descriptors that assume 1024-byte alignment: refuse to run rather than compute garbage
+        c->fail = (smem_u32(smem) & 1023u) ? 2u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 128) c->g[tid >> 6].block_max[(tid >> 5) & 1][tid & 31] = ordered(-INFINITY);
-    if (tid < 64) c->g[tid >> 5].m_used[tid & 31] = -INFINITY;
     if (warp == 9) {                                               // tensor memory: 512 columns, this CTA alone on its SM
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&c->tmem_base)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else if (warp == 8) {
+        // this CTA's ranges: the non-empty (sequence, range) pairs are ranked in sequence order and CTA c takes ranks c, c + gridDim.x,
+        // ..., so every CTA gets the same number of ranges (one more or less) however ragged the lengths are
+        uint32_t count = 0, before = 0;
+        for (uint32_t base = 0; base < a.n_seqs; base += 32) {
+            const uint32_t seq = base + lane;
+            const uint32_t kv_len = seq < a.n_seqs ? min(a.kv_lens[seq], a.max_kv_len) : 0u;
+            const uint32_t cnt = (kv_len + a.split_tokens - 1) / a.split_tokens;
+            uint32_t incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= (uint32_t)o) incl += v;
+            }
+            const uint32_t first_rank = before + incl - cnt;
+            const uint32_t mine = first_rank + (blockIdx.x + gridDim.x - first_rank % gridDim.x) % gridDim.x;   // first rank >= first_rank that is this CTA's
+            const uint32_t n_emit = mine < first_rank + cnt ? (first_rank + cnt - 1 - mine) / gridDim.x + 1 : 0u;
+            uint32_t pos = n_emit;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, pos, o);
+                if (lane >= (uint32_t)o) pos += v;
+            }
+            const uint32_t chunk_total = __shfl_sync(0xFFFFFFFFu, pos, 31);
+            pos = count + pos - n_emit;
+            for (uint32_t e = 0; e < n_emit && pos + e < MAX_ITEMS; e++) {
+                const uint32_t split = mine - first_rank + e * gridDim.x, t_begin = split * a.split_tokens;
+                c->item_id[pos + e] = seq * ranges + split;
+                c->item_blocks[pos + e] = (uint16_t)((min(kv_len, t_begin + a.split_tokens) + BS - 1) / BS - t_begin / BS);
+            }
+            count = min(count + chunk_total, (uint32_t)MAX_ITEMS);
+            before += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
+        if (lane == 0) c->n_items = count;
+    } else if (warp < 8) {
+        // zero the P^T buffers once: entries of other kv heads stay zero for good
+        for (uint32_t i = tid; i < (QT_BYTES + 2 * PBUF * PT_BYTES) / 16; i += 256) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
+        fence_async_smem();
     }
-    if (warp < 8) {
-        // zero Q^T and both P^T buffers (entries of other kv heads stay zero for good), then group 0 writes Q^T:
-        // thread (query head qh = t / 4, dims [32 * (t % 4), +32))
-        for (uint32_t i = tid; i < (2 * PT_BYTES + QT_BYTES) / 16; i += 256) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
-        asm volatile("bar.sync 3, 256;" ::: "memory");
-        if (warp < 4) {
-            const uint32_t qh = tid >> 2, part = tid & 3u, kvh = qh / G, g = qh % G;
-            float x[32];
-            const bool live = qh < a.n_q_heads;
-            const float* qrow = a.q + ((size_t)seq * a.n_q_heads + (live ? qh : 0)) * D + part * 32;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = c->tmem_base, n_items = c->n_items;
+
+    if (warp == 8) {
+        // ---- producer: every block of every range of this CTA, in order; lane 0 issues the copies ----
+        uint32_t k = 0, issued = 0, why = 4u;
+        bool ok = c->fail == 0;
+        for (uint32_t n = 0; n < n_items && ok; n++) {
+            const uint32_t id = c->item_id[n], seq = id / ranges, split = id - seq * ranges, n_blk = c->item_blocks[n];
+            const uint32_t* table = a.tables + (size_t)seq * a.table_stride + split * (a.split_tokens / BS);
+            uint32_t ids_next = lane < n_blk ? __ldg(table + lane) : 0u;
+            for (uint32_t k0 = 0; k0 < n_blk && ok; k0 += 32) {
+                const uint32_t ids = ids_next;
+                ids_next = k0 + 32 + lane < n_blk ? __ldg(table + k0 + 32 + lane) : 0u;
+                const uint32_t lim = min(32u, n_blk - k0);
+                for (uint32_t i = 0; i < lim && ok; i++, k++) {
+                    const uint32_t blk = __shfl_sync(0xFFFFFFFFu, ids, i), sk = k % n_k, sv = k % n_v;
+                    if (lane == 0) {
+                        if (blk >= a.total_blocks) {               // a stale or foreign id is never turned into an address
+                            ok = false;
+                            why = 2u;
+                        }
+                        if (ok && k >= n_k) ok = mbar_wait(c->k_empty + sk, ((k / n_k) - 1u) & 1u, fail_word);
+                        if (ok) {
+                            const uint32_t dst = smem_u32(k_ring + (size_t)sk * KV_TILE);
+                            mbar_expect_tx(c->k_full + sk, KV_TILE);
+#pragma unroll
+                            for (int cg = 0; cg < ES; cg++) tma_box(dst + cg * TILE, &map_k, cg * 128, (int32_t)(blk * ROWS), c->k_full + sk);
+                        }
+                        if (ok && k >= n_v) ok = mbar_wait(c->v_empty + sv, ((k / n_v) - 1u) & 1u, fail_word);
+                        if (ok) {
+                            const uint32_t sc_bytes = a.k_scales ? HKV * 4u : 0u;
+                            const uint32_t dst = smem_u32(v_ring + (size_t)sv * KV_TILE);
+                            mbar_expect_tx(c->v_full + sv, KV_TILE + 2u * sc_bytes);
+#pragma unroll
+                            for (int cg = 0; cg < ES; cg++) tma_box(dst + cg * TILE, &map_v, cg * 128, (int32_t)(blk * ROWS), c->v_full + sv);
+                            if (sc_bytes) {
+                                bulk_copy(smem_u32(&c->scales[sv][0]), a.k_scales + (size_t)blk * HKV, sc_bytes, c->v_full + sv);
+                                bulk_copy(smem_u32(&c->scales[sv][8]), a.v_scales + (size_t)blk * HKV, sc_bytes, c->v_full + sv);
+                            }
+                            issued = k + 1;
+                        }
+                    }
+                    ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicCAS(&c->fail, 0u, why);
+            // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
+            for (uint32_t j = issued > n_v ? issued - n_v : 0u; j < issued; j++)
+                for (uint32_t it = 0; it < (1u << 20); it++)
+                    if (mbar_test(c->v_full + j % n_v, (j / n_v) & 1u) && (j + n_k < issued || mbar_test(c->k_full + j % n_k, (j / n_k) & 1u))) break;
+        }
+    } else if (warp == 9) {
+        // ---- QK issuer: S^T of block i of a range goes to group i & 1, into that group's next S^T buffer ----
+        if (lane == 0) {
+            const uint32_t q_lo = smem_u32(q_tile) >> 4, kr_lo = smem_u32(k_ring) >> 4;
+            uint32_t k = 0, gq[2] = {0, 0};
+            bool ok = c->fail == 0;
+            for (uint32_t n = 0; n < n_items && ok; n++) {
+                const uint32_t n_blk = c->item_blocks[n];
+                ok = mbar_wait(&c->q_full, n & 1u, fail_word);                    // this range's Q^T is in place
+                for (uint32_t i = 0; i < n_blk && ok; i++, k++) {
+                    const uint32_t g = i & 1u, sb = gq[g] & 1u, sk = k % n_k;
+                    ok = mbar_wait(c->k_full + sk, (k / n_k) & 1u, fail_word);
+                    if (ok && gq[g] >= 2) ok = mbar_wait(c->g[g].s_free + sb, ((gq[g] >> 1) - 1u) & 1u, fail_word);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d = tmem + g * 256u + 128u + sb * 64u, k_lo = kr_lo + sk * (KV_TILE >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ks++)
+                        mma<FP8>(d, DESC_K | (k_lo + (ks / 4) * (TILE >> 4) + (ks % 4) * 2),
+                                 DESC_K | (q_lo + (ks / 4) * (Q_SUB >> 4) + (ks % 4) * 2), IDESC_QK, ks > 0 ? 1u : 0u);
+                    tc_commit(c->g[g].s_full + sb);
+                    tc_commit(c->k_empty + sk);                                    // the K tile goes back to the producer as soon as its scores exist
+                    gq[g]++;
+                }
+                tc_commit(&c->q_free);                                            // Q^T may be rewritten once these MMAs are done
+            }
+            if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            tc_commit(c->drained);
+            for (uint32_t it = 0; it < (1u << 22); it++)
+                if (mbar_test(c->drained, 0u)) break;
+        }
+        __syncwarp();
+    } else if (warp == 10) {
+        // ---- PV issuer: O^T of the block's group += V^T P^T as soon as the group has written P^T ----
+        if (lane == 0) {
+            const uint32_t vr_lo = smem_u32(v_ring) >> 4, p_lo = smem_u32(p_tile) >> 4;
+            uint32_t k = 0, gp[2] = {0, 0};
+            bool ok = c->fail == 0;
+            for (uint32_t n = 0; n < n_items && ok; n++) {
+                const uint32_t n_blk = c->item_blocks[n];
+                for (uint32_t i = 0; i < n_blk && ok; i++, k++) {
+                    const uint32_t g = i & 1u, pb = gp[g] % PBUF, sv = k % n_v;
+                    ok = mbar_wait(c->g[g].p_full + pb, (gp[g] / PBUF) & 1u, fail_word) && mbar_wait(c->v_full + sv, (k / n_v) & 1u, fail_word);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t v_lo = vr_lo + sv * (KV_TILE >> 4), pg_lo = p_lo + (g * PBUF + pb) * (PT_BYTES >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ks++)         // V^T MN-major: 32 / ES block rows of 128 B per step; P^T K-major: 32 bytes of the row per step
+                        mma<FP8>(tmem + g * 256u, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
+                                 IDESC_PV, (i >= 2 || ks > 0) ? 1u : 0u);            // a group's first block of a range starts its accumulator afresh
+                    tc_commit(c->v_empty + sv);
+                    tc_commit(c->g[g].p_free + pb);
+                    gp[g]++;
+                }
+            }
+            if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            tc_commit(c->drained + 1);
+            for (uint32_t it = 0; it < (1u << 22); it++)
+                if (mbar_test(c->drained + 1, 0u)) break;
+        }
+        __syncwarp();
+    } else {
+        // ---- softmax: group grp = warp / 4 takes blocks grp, grp + 2, ... of every range; thread t of the group owns block
+        // row t = (token t / 8, kv head t % 8) and tensor-memory lane t ----
+        const uint32_t grp = warp >> 2, t = tid & 127u, kvh = t & 7u, tok = t >> 3;
+        Group* gs = &c->g[grp];
+        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
+        const uint32_t tmem_o = tmem + grp * 256u, tmem_s = tmem_o + 128u;
+        uint32_t p_off[G][PT];                                      // where this row's probabilities go in P^T (row = kv head, term, query head; column = this row)
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int term = 0; term < PT; term++)
+                p_off[g][term] = FP8 ? swz(kvh * CP + term * G + g, t >> 4) + (t & 15u)
+                                     : (t >> 6) * (NP * 128) + swz(kvh * CP + g, (t & 63u) >> 3) + (t & 7u) * 2;
+        // Q^T of a range: group 0, thread (query head qh = t / 4, dims [32 * (t % 4), +32)); the values wait in registers
+        // from the start of the previous range
+        float qx[32];
+        auto q_fetch = [&](uint32_t n) {
+            const uint32_t seq = c->item_id[n] / ranges, qh = t >> 2;
+            const float* qrow = a.q + ((size_t)seq * a.n_q_heads + (qh < a.n_q_heads ? qh : 0)) * D + (t & 3u) * 32;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const float4 f = live ? *reinterpret_cast<const float4*>(qrow + 4 * i) : make_float4(0, 0, 0, 0);
-                x[4 * i] = f.x * a.q_scale;
-                x[4 * i + 1] = f.y * a.q_scale;
-                x[4 * i + 2] = f.z * a.q_scale;
-                x[4 * i + 3] = f.w * a.q_scale;
+                const float4 f = qh < a.n_q_heads ? __ldg(reinterpret_cast<const float4*>(qrow) + i) : make_float4(0, 0, 0, 0);
+                qx[4 * i] = f.x;
+                qx[4 * i + 1] = f.y;
+                qx[4 * i + 2] = f.z;
+                qx[4 * i + 3] = f.w;
             }
+        };
+        auto q_write = [&](uint32_t n) {
+            const uint32_t qh = t >> 2, part = t & 3u, qkvh = qh / G, g = qh % G;
             if (FP8) {
                 float amax = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+                for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(qx[i] * a.q_scale));
                 amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
                 amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
                 // power of two that brings the head's largest element into [128, 256): exact to apply and to undo
                 int e = 0;
                 if (amax > 0.0f && amax < INFINITY) e = 7 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
                 e = max(-60, min(60, e));
-                const float up = __uint_as_float((uint32_t)(127 + e) << 23);
-                if (part == 0 && live) c->q_inv[qh] = __uint_as_float((uint32_t)(127 - e) << 23);
-                if (live) {
+                const float up = a.q_scale * __uint_as_float((uint32_t)(127 + e) << 23);
+                if (part == 0) c->q_inv[n & 1u][qh] = __uint_as_float((uint32_t)(127 - e) << 23);
 #pragma unroll
-                    for (int ch = 0; ch < 2; ch++) {                // two 16-byte chunks of the row per term
-                        uint32_t hi[4], lo[4];
+                for (int ch = 0; ch < 2; ch++) {                    // two 16-byte chunks of the row per term
+                    uint32_t hi[4], lo[4];
 #pragma unroll
-                        for (int wd = 0; wd < 4; wd++) {
-                            hi[wd] = lo[wd] = 0;
+                    for (int wd = 0; wd < 4; wd++) {
+                        hi[wd] = lo[wd] = 0;
 #pragma unroll
-                            for (int b = 0; b < 4; b++) {
-                                const float v = x[ch * 16 + wd * 4 + b] * up;
-                                const uint32_t h = e4m3_of(v);
-                                const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
-                                hi[wd] |= h << (8 * b);
-                                lo[wd] |= l << (8 * b);
-                            }
+                        for (int b = 0; b < 4; b++) {
+                            const float v = qx[ch * 16 + wd * 4 + b] * up;
+                            const uint32_t h = e4m3_of(v);
+                            const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
+                            hi[wd] |= h << (8 * b);
+                            lo[wd] |= l << (8 * b);
                         }
-                        const uint32_t chunk = part * 2 + ch;
-                        *reinterpret_cast<uint4*>(q_tile + swz(kvh * CQ + g, chunk)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        *reinterpret_cast<uint4*>(q_tile + Q_SUB + swz(kvh * CQ + g, chunk)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     }
+                    const uint32_t chunk = part * 2 + ch;
+                    *reinterpret_cast<uint4*>(q_tile + swz(qkvh * CQ + g, chunk)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(q_tile + swz(qkvh * CQ + G + g, chunk)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
             } else {
-                if (part == 0 && live) c->q_inv[qh] = 1.0f;
-                if (live) {
+                if (part == 0) c->q_inv[n & 1u][qh] = 1.0f;
 #pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {                // 32 dims * 2 B = four 16-byte chunks; dims [64, 128) live in the second column group
-                        uint32_t wv[4];
+                for (int ch = 0; ch < 4; ch++) {                    // 32 dims * 2 B = four 16-byte chunks; dims [64, 128) live in the second column group
+                    uint32_t wv[4];
 #pragma unroll
-                        for (int wd = 0; wd < 4; wd++) {
-                            __half2 h = __floats2half2_rn(x[ch * 8 + wd * 2], x[ch * 8 + wd * 2 + 1]);
-                            wv[wd] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                        const uint32_t group = part >> 1, chunk = (part & 1u) * 4 + ch;
-                        *reinterpret_cast<uint4*>(q_tile + group * Q_SUB + swz(kvh * CQ + g, chunk)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    for (int wd = 0; wd < 4; wd++) {
+                        __half2 h = __floats2half2_rn(qx[ch * 8 + wd * 2] * a.q_scale, qx[ch * 8 + wd * 2 + 1] * a.q_scale);
+                        wv[wd] = *reinterpret_cast<uint32_t*>(&h);
                     }
+                    const uint32_t cgp = part >> 1, chunk = (part & 1u) * 4 + ch;
+                    *reinterpret_cast<uint4*>(q_tile + cgp * Q_SUB + swz(qkvh * CQ + g, chunk)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                 }
             }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->q_full);
+        };
+        bool ok = c->fail == 0;
+        if (grp == 0 && n_items) {
+            q_fetch(0);
+            q_write(0);
         }
-        fence_async_smem();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = c->tmem_base;
-#ifdef TKV_TC_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[14] = clock64();
-#endif
-
-    if (warp == 8) {
-        // ---- producer: the block table 32 entries at a time; lane 0 issues the copies ----
-        uint32_t issued = 0, why = 4u;
-        bool ok = true;
-        uint32_t ids_next = lane < n_blk ? __ldg(table + lane) : 0u;
-        for (uint32_t k0 = 0; k0 < n_blk && ok; k0 += 32) {
-            const uint32_t ids = ids_next;
-            ids_next = k0 + 32 + lane < n_blk ? __ldg(table + k0 + 32 + lane) : 0u;
-            const uint32_t lim = min(32u, n_blk - k0);
-            for (uint32_t i = 0; i < lim && ok; i++) {
-                const uint32_t id = __shfl_sync(0xFFFFFFFFu, ids, i);
-                const uint32_t k = k0 + i, s = k % n_stages;
-                if (lane == 0) {
-                    if (id >= a.total_blocks) {                   // a stale or foreign id is never turned into an address
-                        ok = false;
-                        why = 2u;
-                    }
-                    if (ok && k >= n_stages) ok = mbar_wait(c->empty + s, ((k / n_stages) - 1u) & 1u, fail_word);
-                    if (ok) {
-                        const uint32_t sc_bytes = a.k_scales ? HKV * 4u : 0u;
-                        const uint32_t dst = smem_u32(stages + (size_t)s * stage_bytes);
-                        mbar_expect_tx(c->full + s, 2u * KV_TILE + 2u * sc_bytes);
+        uint32_t gj = 0, base_k = 0;                                // blocks this group has taken so far; ring index of the range's first block
+        for (uint32_t n = 0; n < n_items; n++) {
+            const uint32_t id = c->item_id[n], seq = id / ranges, split = id - seq * ranges, n_blk = c->item_blocks[n];
+            const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len), b_begin = split * (a.split_tokens / BS);
+            const uint32_t n_mine = n_blk > grp ? (n_blk - grp + 1u) / 2u : 0u;
+            if (grp == 0 && n + 1 < n_items) q_fetch(n + 1);        // the next range's query rows, on their way while this one is worked
+            float m_used[G], l[G], q_inv[G];
 #pragma unroll
-                        for (int grp = 0; grp < ES; grp++) {
-                            tma_box(dst + grp * TILE, &map_k, grp * 128, (int32_t)(id * ROWS), c->full + s);
-                            tma_box(dst + KV_TILE + grp * TILE, &map_v, grp * 128, (int32_t)(id * ROWS), c->full + s);
-                        }
-                        if (sc_bytes) {
-                            bulk_copy(smem_u32(&c->scales[s][0]), a.k_scales + (size_t)id * HKV, sc_bytes, c->full + s);
-                            bulk_copy(smem_u32(&c->scales[s][8]), a.v_scales + (size_t)id * HKV, sc_bytes, c->full + s);
-                        }
-                        issued = k + 1;
-                    }
-                }
-                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
+            for (int g = 0; g < G; g++) {
+                m_used[g] = -INFINITY;
+                l[g] = 0.0f;
             }
-        }
-        if (!ok && lane == 0) {
-            atomicCAS(&c->fail, 0u, why);
-            // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
-            for (uint32_t k = issued > n_stages ? issued - n_stages : 0u; k < issued; k++)
-                for (uint32_t it = 0; it < (1u << 20); it++)
-                    if (mbar_test(c->full + k % n_stages, (k / n_stages) & 1u)) break;
-        }
-    } else if (warp == 9) {
-        // ---- MMA issuer: one thread; QK of block k as soon as its copies have landed and its S^T buffer is free,
-        // PV of block k as soon as its P^T is written.  Block k belongs to group k & 1 (its j-th block, j = k >> 1). ----
-        if (lane == 0) {
-            const uint32_t q_lo = smem_u32(q_tile) >> 4, st_lo = smem_u32(stages) >> 4, p_lo = smem_u32(p_tile) >> 4;
-            uint32_t qk = 0, pv = 0, idle = 0;
-            bool ok = true;
-            while (pv < n_blk && ok) {
-                bool did = false;
-                if (qk < n_blk) {
-                    const uint32_t g = qk & 1u, j = qk >> 1, sb = j & 1u, s = qk % n_stages;
-                    if (mbar_test(c->full + s, (qk / n_stages) & 1u) && (j < 2 || mbar_test(c->g[g].s_free + sb, ((j >> 1) - 1u) & 1u))) {
-                        tc_fence_after();
-                        const uint32_t d = tmem + g * 256u + 128u + sb * 64u, k_lo = st_lo + s * (stage_bytes >> 4);
-                        if (FP8) {
-                            // q = hi + lo: two passes over the K tile into the same accumulator columns
-#pragma unroll
-                            for (int term = 0; term < 2; term++)
-#pragma unroll
-                                for (int ks = 0; ks < 4; ks++)
-                                    mma<FP8>(d, DESC_K | (k_lo + ks * 2), DESC_K | (q_lo + term * (Q_SUB >> 4) + ks * 2), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
-                        } else {
-#pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ks++)
-                                mma<FP8>(d, DESC_K | (k_lo + (ks / 4) * (TILE >> 4) + (ks % 4) * 2), DESC_K | (q_lo + (ks / 4) * (Q_SUB >> 4) + (ks % 4) * 2),
-                                         IDESC_QK, ks > 0 ? 1u : 0u);
-                        }
-                        tc_commit(c->g[g].s_full + sb);
-                        qk++;
-                        did = true;
-                    }
-                }
-                if (pv < qk) {
-                    const uint32_t g = pv & 1u, j = pv >> 1, s = pv % n_stages;
-                    if (mbar_test(&c->g[g].p_full, j & 1u)) {
-                        tc_fence_after();
-                        const uint32_t v_lo = st_lo + s * (stage_bytes >> 4) + (KV_TILE >> 4), pg_lo = p_lo + g * (PT_BYTES >> 4);
-#pragma unroll
-                        for (int ks = 0; ks < KSTEPS; ks++)     // V^T MN-major: 32 / ES block rows of 128 B per step; P^T K-major: 32 bytes of the row per step
-                            mma<FP8>(tmem + g * 256u, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
-                                     IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                        tc_commit(c->empty + s);
-                        tc_commit(&c->g[g].p_free);
-                        pv++;
-                        did = true;
-                    }
-                }
-                if (did) idle = 0;
-                else if (++idle > (1u << 24) || ((idle & 63u) == 63u && *fail_word)) ok = false;
-            }
-            if (!ok) atomicCAS(&c->fail, 0u, 4u);
-            // nothing of this CTA may still be writing tensor memory when it is freed
-            tc_commit(&c->drained);
-            for (uint32_t it = 0; it < (1u << 22); it++)
-                if (mbar_test(&c->drained, 0u)) break;
-        }
-        __syncwarp();
-    } else {
-        // ---- softmax: group grp = warp / 4 takes blocks grp, grp + 2, ...; thread t of the group owns block row
-        // t = (token t / 8, kv head t % 8) and tensor-memory lane t ----
-        const uint32_t grp = warp >> 2, t = tid & 127u, kvh = t & 7u, tok = t >> 3;
-        Group* gs = &c->g[grp];
-        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
-        const uint32_t tmem_o = tmem + grp * 256u, tmem_s = tmem_o + 128u;
-        const uint32_t n_mine = n_blk > grp ? (n_blk - grp + 1u) / 2u : 0u;
-        unsigned char* pt = p_tile + grp * PT_BYTES;
-        float m_used[G], l[G], q_inv[G];
-        uint32_t p_off[G][PT];                                      // where this row's probabilities go in P^T (row = kv head, term, query head; column = this row)
-#pragma unroll
-        for (int g = 0; g < G; g++) {
-            m_used[g] = -INFINITY;
-            l[g] = 0.0f;
-            q_inv[g] = c->q_inv[kvh * G + g];
-#pragma unroll
-            for (int term = 0; term < PT; term++)
-                p_off[g][term] = FP8 ? swz(kvh * CP + term * G + g, t >> 4) + (t & 15u)
-                                     : (t >> 6) * (NP * 128) + swz(kvh * CP + g, (t & 63u) >> 3) + (t & 7u) * 2;
-        }
-        bool ok = true;
-        for (uint32_t j = 0; j < n_mine; j++) {
-            const uint32_t i = 2u * j + grp, s = i % n_stages, b = j & 1u;
-#ifdef TKV_TC_TIMING
-            const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && j == 3;
-#endif
-            TKV_STAMP(0);
-            const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + i) * BS);
-            const bool valid = tok < n_valid;
-            float sc[G];                                            // this row's scores against its own kv head's query heads (log2 domain)
-            float lv = 0.0f, inv_vs = 1.0f;
-            if (ok) {
-                ok = mbar_wait(gs->s_full + b, (j >> 1) & 1u, fail_word) && mbar_wait(c->full + s, (i / n_stages) & 1u, fail_word);
-                if (!ok) atomicCAS(&c->fail, 0u, 4u);
-            }
-            TKV_STAMP(1);
-            if (ok) {
-                tc_fence_after();
-                float part[CQ];
-                uint32_t r[32];
-                tmem_ld32(tmem_s + b * 64u + lane_base, r);
-                tmem_wait_ld();
-                TKV_STAMP(2);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(gs->s_free + b);
-                TKV_STAMP(3);
-                // keep the CQ columns of this row's kv head
-#if TKV_TC_ABLATE >= 2
-#pragma unroll
-                for (int h = 0; h < HKV; h++)
-                    if ((uint32_t)h == kvh) {
-#pragma unroll
-                        for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[h * CQ + q]);
-                    }
-#else
-#pragma unroll
-                for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[q]);
-#endif
-                float ks = 1.0f, vs = 1.0f;
-                if (a.k_scales) {
-                    ks = c->scales[s][kvh];
-                    vs = c->scales[s][8 + kvh];
-                    lv = fast_log2(vs);
-                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));   // scales the row sum only
-                }
-#pragma unroll
-                for (int g = 0; g < G; g++) sc[g] = valid ? part[g] * (ks * q_inv[g]) + lv : -INFINITY;   // the V scale rides in the exponent
-            } else {
-#pragma unroll
-                for (int g = 0; g < G; g++) sc[g] = -INFINITY;
-            }
-            TKV_STAMP(4);
-            // does any query head of this kv head exceed its running maximum by more than 2^RAISE in this block?
-            bool want = false;
-#pragma unroll
-            for (int g = 0; g < G; g++) want = want || sc[g] > m_used[g] + RAISE;
-            if (__any_sync(0xFFFFFFFFu, want)) {                    // rare: post this warp's maxima
-#pragma unroll
-                for (int g = 0; g < G; g++) {
-                    float bm = sc[g];
-                    bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 8));
-                    bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 16));
-                    if (lane < 8 && bm > m_used[g] + RAISE) {
-                        atomicMax(&gs->block_max[b][kvh * G + g], ordered(bm));
-                        gs->raise[b] = 1u;
-                    }
-                }
-            }
-            TKV_STAMP(5);
+            if (t < 32) gs->m_used[t] = -INFINITY;
             asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
-            TKV_STAMP(6);
-            if (gs->raise[b]) {
-                // ---- raise the maxima: rescale O^T in tensor memory and the row sums; a few times per sequence at most ----
-                if (t < 32) {
-                    const float bm = unordered(gs->block_max[b][t]), mo = gs->m_used[t];
-                    const float mn = fmaxf(mo, bm);
-                    gs->factor[t] = (mn == mo) ? 1.0f : (mo == -INFINITY ? 0.0f : fast_exp2(mo - mn));
-                    gs->m_used[t] = mn;
-                    gs->block_max[b][t] = ordered(-INFINITY);
+            for (uint32_t j = 0; j < n_mine; j++, gj++) {
+                const uint32_t i = 2u * j + grp, k = base_k + i, s = k % n_v, b = gj & 1u, pb = gj % PBUF;
+                const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + i) * BS);
+                const bool valid = tok < n_valid;
+                float sc[G];                                        // this row's scores against its own kv head's query heads (log2 domain)
+                float inv_vs = 1.0f;
+                if (ok) {
+                    ok = mbar_wait(gs->s_full + b, (gj >> 1) & 1u, fail_word) && mbar_wait(c->v_full + s, (k / n_v) & 1u, fail_word);
+                    if (!ok) atomicCAS(&c->fail, 0u, 4u);
+                }
+                if (ok) {
+                    tc_fence_after();
+                    if (j == 0) {
+#pragma unroll
+                        for (int g = 0; g < G; g++) q_inv[g] = c->q_inv[n & 1u][kvh * G + g];
+                    }
+                    float part[CQ];
+                    uint32_t r[NQ];
+                    if (NQ == 64) tmem_ld64(tmem_s + b * 64u + lane_base, reinterpret_cast<uint32_t(&)[64]>(r));
+                    else tmem_ld32(tmem_s + b * 64u + lane_base, reinterpret_cast<uint32_t(&)[32]>(r));
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gs->s_free + b);
+                    // keep the CQ columns of this row's kv head
+#pragma unroll
+                    for (int h = 0; h < HKV; h++)
+                        if ((uint32_t)h == kvh) {
+#pragma unroll
+                            for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[h * CQ + q]);
+                        }
+                    float ks = 1.0f, lv = 0.0f;
+                    if (a.k_scales) {
+                        ks = c->scales[s][kvh];
+                        const float vs = c->scales[s][8 + kvh];
+                        lv = fast_log2(vs);
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));   // scales the row sum only
+                    }
+#pragma unroll
+                    for (int g = 0; g < G; g++) {                   // the V scale rides in the exponent
+                        const float raw = FP8 ? part[g] + part[G + g] : part[g];
+                        sc[g] = valid ? raw * (ks * q_inv[g]) + lv : -INFINITY;
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < G; g++) sc[g] = -INFINITY;
+                }
+                // does any query head of this kv head exceed its running maximum by more than 2^RAISE in this block?
+                bool want = false;
+#pragma unroll
+                for (int g = 0; g < G; g++) want = want || sc[g] > m_used[g] + RAISE;
+                if (__any_sync(0xFFFFFFFFu, want)) {                // rare: post this warp's maxima
+#pragma unroll
+                    for (int g = 0; g < G; g++) {
+                        float bm = sc[g];
+                        bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 8));
+                        bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 16));
+                        if (lane < 8 && bm > m_used[g] + RAISE) {
+                            atomicMax(&gs->block_max[b][kvh * G + g], ordered(bm));
+                            gs->raise[b] = 1u;
+                        }
+                    }
                 }
                 asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
-                if (t == 0) gs->raise[b] = 0u;
-                if (j > 0) {
-                    // the PV MMA of the group's previous block must have finished with O^T; none follows until this block's P^T is published
-                    if (ok) ok = mbar_wait(&gs->p_free, (j - 1u) & 1u, fail_word);
-                    if (ok) {
-                        tc_fence_after();
+                if (gs->raise[b]) {
+                    // ---- raise the maxima: rescale O^T in tensor memory and the row sums; a few times per range at most ----
+                    if (t < 32) {
+                        const float bm = unordered(gs->block_max[b][t]), mo = gs->m_used[t];
+                        const float mn = fmaxf(mo, bm);
+                        gs->factor[t] = (mn == mo) ? 1.0f : (mo == -INFINITY ? 0.0f : fast_exp2(mo - mn));
+                        gs->m_used[t] = mn;
+                        gs->block_max[b][t] = ordered(-INFINITY);
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
+                    if (t == 0) gs->raise[b] = 0u;
+                    if (j > 0) {
+                        // the PV MMA of the group's previous block must have finished with O^T; none follows until this block's P^T is published
+                        if (ok) ok = mbar_wait(gs->p_free + (gj - 1u) % PBUF, ((gj - 1u) / PBUF) & 1u, fail_word);
+                        if (ok) {
+                            tc_fence_after();
 #pragma unroll
-                        for (int c0 = 0; c0 < NP; c0 += 32) {
-                            uint32_t r[32];
-                            tmem_ld32(tmem_o + lane_base + c0, r);
-                            tmem_wait_ld();
+                            for (int c0 = 0; c0 < NP; c0 += 32) {
+                                uint32_t r[32];
+                                tmem_ld32(tmem_o + lane_base + c0, r);
+                                tmem_wait_ld();
 #pragma unroll
-                            for (int q = 0; q < 32; q++) {
-                                const int col = c0 + q, head = (col / CP) * G + (col % CP) % G;
-                                r[q] = __float_as_uint(__uint_as_float(r[q]) * gs->factor[head]);
+                                for (int q = 0; q < 32; q++) {
+                                    const int col = c0 + q, head = (col / CP) * G + (col % CP) % G;
+                                    r[q] = __float_as_uint(__uint_as_float(r[q]) * gs->factor[head]);
+                                }
+                                tmem_st32(tmem_o + lane_base + c0, r);
                             }
-                            tmem_st32(tmem_o + lane_base + c0, r);
+                            tmem_wait_st();
+                            tc_fence_before();
                         }
-                        tmem_wait_st();
-                        tc_fence_before();
+                    }
+#pragma unroll
+                    for (int g = 0; g < G; g++) {
+                        l[g] *= gs->factor[kvh * G + g];
+                        m_used[g] = gs->m_used[kvh * G + g];
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");   // factor[] and m_used[] are read before the next raise rewrites them
+                }
+                if (ok && gj >= (uint32_t)PBUF) ok = mbar_wait(gs->p_free + pb, ((gj / PBUF) - 1u) & 1u, fail_word);
+                if (ok) {
+                    // weights 2^(score - maximum + SHIFT), two query heads at a time in half2.  E4M3 pool: an E5M2 byte is the top
+                    // byte of an F16, so the three terms are peeled off by masking the low byte and subtracting (exact in F16: the
+                    // weights are non-negative and every residual fits); the row sum takes the value the three terms add up to.
+                    unsigned char* pt = p_tile + (grp * PBUF + pb) * PT_BYTES;
+                    const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
+#pragma unroll
+                    for (int g = 0; g < G; g += 2) {
+                        const int g1 = g + 1 < G ? g + 1 : g;
+                        const float x0 = fast_exp2(sc[g] - m_used[g] + SHIFT);                     // <= 2^(RAISE + SHIFT); 0 for a row past the sequence end
+                        const float x1 = (g + 1 < G) ? fast_exp2(sc[g1] - m_used[g1] + SHIFT) : 0.0f;
+                        __half2 h = __floats2half2_rn(x0, x1);
+                        if (FP8) {
+                            const uint32_t t1 = *reinterpret_cast<uint32_t*>(&h) & 0xFF00FF00u;
+                            const __half2 r1 = __hsub2(h, *reinterpret_cast<const __half2*>(&t1));
+                            const uint32_t t2 = *reinterpret_cast<const uint32_t*>(&r1) & 0xFF00FF00u;
+                            const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
+                            const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
+                            h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));     // = t1 + t2 + t3
+                            pt[p_off[g][0]] = (unsigned char)(t1 >> 8);
+                            pt[p_off[g][1 < PT ? 1 : 0]] = (unsigned char)(t2 >> 8);
+                            pt[p_off[g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 8);
+                            if (g + 1 < G) {
+                                pt[p_off[g1][0]] = (unsigned char)(t1 >> 24);
+                                pt[p_off[g1][1 < PT ? 1 : 0]] = (unsigned char)(t2 >> 24);
+                                pt[p_off[g1][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 24);
+                            }
+                        } else {
+                            *reinterpret_cast<__half*>(pt + p_off[g][0]) = __low2half(h);
+                            if (g + 1 < G) *reinterpret_cast<__half*>(pt + p_off[g1][0]) = __high2half(h);
+                        }
+                        const float2 q = __half22float2(h);
+                        l[g] += q.x * l_scale;
+                        if (g + 1 < G) l[g1] += q.y * l_scale;
+                    }
+                    if (!valid) {
+                        // a row past the sequence end holds whatever the pool held there: 0 * NaN must not reach O^T
+                        unsigned char* vt = v_ring + (size_t)s * KV_TILE;
+#pragma unroll
+                        for (int cg = 0; cg < ES; cg++)
+#pragma unroll
+                            for (int ch = 0; ch < 8; ch++) *reinterpret_cast<uint4*>(vt + cg * TILE + swz(t, ch)) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_async_smem();
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(gs->p_full + pb);        // also after a failure: the issuer then ends through the fail word
+            }
+            // ---- the next range's Q^T goes in as soon as this range's QK MMAs are done, ahead of this range's epilogue ----
+            if (grp == 0 && n + 1 < n_items) {
+                if (ok) ok = mbar_wait(&c->q_free, n & 1u, fail_word);
+                q_write(n + 1);
+            }
+            // ---- this group's partial of the range: its last PV MMA done, row sums over the group, O^T rows out of tensor memory ----
+            if (ok && n_mine) {
+                ok = mbar_wait(gs->p_free + (gj - 1u) % PBUF, ((gj - 1u) / PBUF) & 1u, fail_word);
+                if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float x = l[g];
+                x += __shfl_xor_sync(0xFFFFFFFFu, x, 8);
+                x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);
+                if (lane < 8) gs->l_sum[warp & 3u][kvh * G + g] = x;
+            }
+            asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
+            if (ok) {
+                const float down = __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
+                const uint32_t part_slot = split * 2u + grp;
+                float* pr0 = a.partial + (((size_t)seq * HKV * n_parts + part_slot) * G) * (D + 2);
+                const size_t head_stride = (size_t)n_parts * G * (D + 2);
+                if (t < HKV * G && t < a.n_q_heads) {               // one thread per query head: its maximum and row sum (-inf and 0 for a group without blocks)
+                    float* pr = pr0 + (size_t)(t / G) * head_stride + (size_t)(t % G) * (D + 2);
+                    pr[0] = n_mine ? gs->m_used[t] : -INFINITY;
+                    pr[1] = n_mine ? gs->l_sum[0][t] + gs->l_sum[1][t] + gs->l_sum[2][t] + gs->l_sum[3][t] : 0.0f;
+                }
+                float acc[HKV * G];                                 // this thread's output dim t, every query head: the terms' columns folded
+#pragma unroll
+                for (int q = 0; q < HKV * G; q++) acc[q] = 0.0f;
+                if (n_mine) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int c0 = 0; c0 < NP; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_o + lane_base + c0, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int q = 0; q < 32; q++) {
+                            const int col = c0 + q;
+                            if (col < NP) acc[(col / CP) * G + (col % CP) % G] += __uint_as_float(r[q]);
+                        }
                     }
                 }
 #pragma unroll
-                for (int g = 0; g < G; g++) {
-                    l[g] *= gs->factor[kvh * G + g];
-                    m_used[g] = gs->m_used[kvh * G + g];
-                }
-                asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");   // factor[] and m_used[] are read before the next raise rewrites them
+                for (int q = 0; q < HKV * G; q++)
+                    if ((uint32_t)q < a.n_q_heads) pr0[(size_t)(q / G) * head_stride + (size_t)(q % G) * (D + 2) + 2 + t] = acc[q] * down;
+                if (n_mine) tc_fence_before();
             }
-            TKV_STAMP(7);
-            if (ok && j >= 1) ok = mbar_wait(&gs->p_free, (j - 1u) & 1u, fail_word);
-            TKV_STAMP(8);
-            if (ok) {
-                // weights 2^(score - maximum + SHIFT), two query heads at a time in half2.  E4M3 pool: an E5M2 byte is the top
-                // byte of an F16, so the three terms are peeled off by masking the low byte and subtracting (exact in F16: the
-                // weights are non-negative and every residual fits); the row sum takes the value the three terms add up to.
-                const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
-#if TKV_TC_ABLATE >= 3
-#pragma unroll
-                for (int g = 0; g < G; g += 2) {
-                    const float x0 = fast_exp2(sc[g] - m_used[g] + SHIFT);                         // <= 2^(RAISE + SHIFT); 0 for a row past the sequence end
-                    const float x1 = (g + 1 < G) ? fast_exp2(sc[g + 1 < G ? g + 1 : g] - m_used[g + 1 < G ? g + 1 : g] + SHIFT) : 0.0f;
-                    __half2 h = __floats2half2_rn(x0, x1);
-                    if (FP8) {
-                        const uint32_t t1 = *reinterpret_cast<uint32_t*>(&h) & 0xFF00FF00u;
-                        const __half2 r1 = __hsub2(h, *reinterpret_cast<const __half2*>(&t1));
-                        const uint32_t t2 = *reinterpret_cast<const uint32_t*>(&r1) & 0xFF00FF00u;
-                        const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
-                        const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
-                        h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));         // = t1 + t2 + t3
-#if TKV_TC_ABLATE >= 9
-                        pt[p_off[g][0]] = (unsigned char)(t1 >> 8);
-                        pt[p_off[g][1]] = (unsigned char)(t2 >> 8);
-                        pt[p_off[g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 8);
-                        if (g + 1 < G) {
-                            pt[p_off[g + 1 < G ? g + 1 : g][0]] = (unsigned char)(t1 >> 24);
-                            pt[p_off[g + 1 < G ? g + 1 : g][1]] = (unsigned char)(t2 >> 24);
-                            pt[p_off[g + 1 < G ? g + 1 : g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 24);
-                        }
-#else
-                        l[g] += __uint_as_float(t1 ^ t2 ^ t3);
-#endif
-                    } else {
-                        *reinterpret_cast<__half*>(pt + p_off[g][0]) = __low2half(h);
-                        if (g + 1 < G) *reinterpret_cast<__half*>(pt + p_off[g + 1 < G ? g + 1 : g][0]) = __high2half(h);
-                    }
-                    const float2 q = __half22float2(h);
-                    l[g] += q.x * l_scale;
-                    if (g + 1 < G) l[g + 1 < G ? g + 1 : g] += q.y * l_scale;
-                }
-#else
-                l[0] += l_scale + sc[0] + sc[1] + sc[2 < G ? 2 : 0] + sc[3 < G ? 3 : 0];
-#endif
-                if (!valid) {
-                    // a row past the sequence end holds whatever the pool held there: 0 * NaN must not reach O^T
-                    unsigned char* vt = stages + (size_t)s * stage_bytes + KV_TILE;
-#pragma unroll
-                    for (int cg = 0; cg < ES; cg++)
-#pragma unroll
-                        for (int ch = 0; ch < 8; ch++) *reinterpret_cast<uint4*>(vt + cg * TILE + swz(t, ch)) = make_uint4(0, 0, 0, 0);
-                }
-                TKV_STAMP(9);
-                fence_async_smem();
-                TKV_STAMP(10);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&gs->p_full);                // also after a failure: the issuer then ends through the fail word
-            TKV_STAMP(11);
-        }
-#ifdef TKV_TC_TIMING
-        if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[12] = clock64();
-#endif
-        // ---- the group's result: wait for its last PV MMA, row sums over the group, O^T rows out of tensor memory ----
-        if (ok && n_mine) {
-            ok = mbar_wait(&gs->p_free, (n_mine - 1u) & 1u, fail_word);
-            if (!ok) atomicCAS(&c->fail, 0u, 4u);
-        }
-#pragma unroll
-        for (int g = 0; g < G; g++) {
-            float x = l[g];
-            x += __shfl_xor_sync(0xFFFFFFFFu, x, 8);
-            x += __shfl_xor_sync(0xFFFFFFFFu, x, 16);
-            if (lane < 8) gs->l_sum[warp & 3u][kvh * G + g] = x;
-        }
-        float acc[HKV * G];                                         // this thread's output dim t, every query head
-#pragma unroll
-        for (int q = 0; q < HKV * G; q++) acc[q] = 0.0f;
-        if (ok && n_mine) {
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < NP; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_o + lane_base + c0, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int q = 0; q < 32; q++) {
-                    const int col = c0 + q;
-                    if (col < NP) acc[(col / CP) * G + (col % CP) % G] += __uint_as_float(r[q]);
-                }
-            }
-            tc_fence_before();
-        }
-        // group 1 hands its numerators over through shared memory (the ring is idle by now); group 0 merges and writes the partial
-        float* other = reinterpret_cast<float*>(stages);            // [query head][dim]
-        float* merge = other + HKV * G * D;                         // per query head: weight of group 0, weight of group 1
-        asm volatile("bar.sync 3, 256;" ::: "memory");              // both groups have seen their last MMA complete: no copy or MMA touches the ring any more
-        if (grp == 1) {
-#pragma unroll
-            for (int q = 0; q < HKV * G; q++) other[q * D + t] = acc[q];
-        } else if (t < HKV * G && t < a.n_q_heads) {                // one thread per query head: the two groups' maxima and row sums
-            const float m0 = c->g[0].m_used[t], m1 = c->g[1].m_used[t], mm = fmaxf(m0, m1);
-            const float f0 = m0 == -INFINITY ? 0.0f : fast_exp2(m0 - mm), f1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - mm);
-            float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                l0 += c->g[0].l_sum[w][t];
-                l1 += c->g[1].l_sum[w][t];
-            }
-            const float down = __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
-            merge[2 * t] = f0 * down;
-            merge[2 * t + 1] = f1 * down;
-            if (ok) {
-                float* pr = a.partial + ((((size_t)seq * HKV + t / G) * a.n_splits + split) * G + t % G) * (D + 2);
-                pr[0] = mm;
-                pr[1] = l0 * f0 + l1 * f1;
-            }
-        }
-        asm volatile("bar.sync 3, 256;" ::: "memory");
-        if (grp == 0 && ok) {
-            float* pr0 = a.partial + (((size_t)seq * HKV * a.n_splits + split) * G) * (D + 2) + 2 + t;
-            const size_t head_stride = (size_t)a.n_splits * G * (D + 2);
-#pragma unroll
-            for (int q = 0; q < HKV * G; q++) {
-                if ((uint32_t)q < a.n_q_heads) {
-                    const float2 f = *reinterpret_cast<const float2*>(merge + 2 * q);
-                    const float v1 = f.y != 0.0f ? other[q * D + t] * f.y : 0.0f;
-                    pr0[(size_t)(q / G) * head_stride + (size_t)(q % G) * (D + 2)] = acc[q] * f.x + v1;
-                }
-            }
+            base_k += n_blk;
         }
     }
     tc_fence_before();
@@ -746,9 +751,6 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
     if (tid == 0 && c->fail && a.status) atomicCAS(a.status, 0u, c->fail);
-#ifdef TKV_TC_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) g_tc_stamps[15] = clock64();
-#endif
 }
 
 // ---- self-check of the operand plumbing ---------------------------------------------------------------
@@ -880,40 +882,46 @@ bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t tot
     return n_kv_heads == HKV && group == 4 && (uint64_t)total_blocks * ROWS < (1ull << 31);
 }
 
-template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t st) {
-    constexpr int ES = FP8 ? 1 : 2, QT = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;
-    constexpr int CQ = (G < 2) ? 2 : G, CP = (G * PT < 2) ? 2 : G * PT;
-    (void)QT;
-    constexpr size_t fixed = 1024 /* alignment slack */ + 3072 + 2 * (size_t)HKV * CQ * 128 + 2 * (size_t)HKV * CP * 128 * ES;
-    constexpr size_t stage = 2 * (size_t)TILE * ES;
-    const uint32_t n_stages = (uint32_t)std::min<size_t>(8, (227 * 1024 - fixed) / stage);
-    if (n_stages < 2) return cudaErrorInvalidConfiguration;
-    const size_t smem = fixed + n_stages * stage;
+template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, cudaStream_t st) {
+    constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = FP8 ? 2 : 1;
+    constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS, CP = (G * PT < 2) ? 2 : G * PT;
+    constexpr size_t fixed = 5120 + (size_t)HKV * CQ * 128 * ES + 2 * (size_t)PBUF * HKV * CP * 128 * ES;
+    constexpr size_t tile = (size_t)TILE * ES;              // K or V of one block
+    const uint32_t tiles = (uint32_t)((227 * 1024 - fixed) / tile);
+    // a K tile is held from its arrival to the end of its QK MMAs, a V tile through the softmax of its block as well: most slots go to V
+    const uint32_t n_k = FP8 ? 4u : 2u, n_v = std::min(8u, tiles - n_k);
+    if (tiles < n_k + 2) return cudaErrorInvalidConfiguration;
+    const size_t smem = fixed + (size_t)(n_k + n_v) * tile;
     auto kernel = decode_attn_tc<FP8, G>;
     static std::mutex mu;
     static bool granted[64] = {};
+    static int sms[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     {
         std::lock_guard<std::mutex> lk(mu);
-        if (dev >= 0 && dev < 64 && !granted[dev]) {
+        if (!granted[dev]) {
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess) return e;
             granted[dev] = true;
         }
     }
-    kernel<<<grid, 320, smem, st>>>(mk, mv, a, n_stages);
+    // one persistent CTA per SM walks its share of the (sequence, range) list; more CTAs only when a share would not fit its list
+    const uint64_t total = (uint64_t)a.n_seqs * a.n_splits;
+    const uint64_t grid = std::max<uint64_t>(std::min<uint64_t>(total, (uint64_t)sms[dev]), (total + (MAX_ITEMS - 32) - 1) / (MAX_ITEMS - 32));
+    kernel<<<(uint32_t)grid, 352, smem, st>>>(mk, mv, a, n_k, n_v);
     return cudaGetLastError();
 }
 
-cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer, const Args& a, uint32_t n_splits, uint32_t n_seqs, cudaStream_t st) {
+cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer, const Args& a, cudaStream_t st) {
     CUtensorMap mk, mv;
     const uint32_t es = fp8 ? 1u : 2u;
     if (!make_map(&mk, k_layer, a.total_blocks, es) || !make_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
-    const dim3 grid(n_splits, n_seqs);
     if (group != 4) return cudaErrorInvalidConfiguration;
-    return fp8 ? launch_one<true, 4>(mk, mv, a, grid, st) : launch_one<false, 4>(mk, mv, a, grid, st);
+    return fp8 ? launch_one<true, 4>(mk, mv, a, st) : launch_one<false, 4>(mk, mv, a, st);
 }
 
 // Fills the two operands with small dyadic values, runs the four combinations, returns the mismatch counts.
@@ -972,11 +980,5 @@ cudaError_t selfcheck(uint64_t out[4]) {
     return e;
 }
 
-#ifdef TKV_TC_TIMING
-cudaError_t read_stamps(unsigned long long out[16]) { return cudaMemcpyFromSymbol(out, g_tc_stamps, 16 * sizeof(unsigned long long)); }
-#endif
 
 }  // namespace tkv_tc
-#ifdef TKV_TC_TIMING
-extern "C" int32_t tkv_debug_tc_stamps(unsigned long long* out) { return tkv_tc::read_stamps(out) == cudaSuccess ? 0 : 3; }
-#endif

@@ -11,8 +11,9 @@ struct Args {
     const float* q;               // [n_seqs][n_q_heads][128]
     const uint32_t* tables;       // [n_seqs][table_stride]
     const uint32_t* kv_lens;
-    float* partial;               // [n_seqs][8][n_splits][group][128 + 2]: running maximum, row sum, 128 numerators
-    uint32_t n_q_heads, table_stride, n_splits, split_tokens, max_kv_len, total_blocks;
+    float* partial;               // [n_seqs][8][2 * n_splits][group][128 + 2]: running maximum, row sum, 128 numerators; two parts per
+                                  // token range (the kernel's two softmax groups take alternate blocks and each writes its own)
+    uint32_t n_seqs, n_q_heads, table_stride, n_splits, split_tokens, max_kv_len, total_blocks;
     float q_scale;                // softmax scale * log2(e)
     uint32_t* status;             // optional device word: first failure wins
 };
@@ -20,7 +21,7 @@ struct Args {
 // 8 kv heads of 128 dims in 16-token blocks (one block = one 128-row operand tile), 4 query heads per kv head
 bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t total_blocks);
 // launches on the current device; layer tensors as raw device addresses
-cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer, const Args& a, uint32_t n_splits, uint32_t n_seqs, cudaStream_t st);
+cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer, const Args& a, cudaStream_t st);
 
 // operand plumbing of the tcgen05 path (tensor-map copy, swizzle, descriptors, tensor-memory reads) on exact small cases:
 // out[0..3] = mismatches of {E4M3 K-major, E4M3 x E5M2 MN-major, F16 K-major, F16 MN-major}
