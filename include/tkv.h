@@ -369,6 +369,8 @@ enum { TKV_ATTN_DEFAULT = 0,
        TKV_ATTN_MMA_SYNC = 2       /* whole-block form on warp-level mma.sync instead of tcgen05 with
                                       tensor-memory accumulators (the default where the shape allows:
                                       8 kv heads, 4 query heads per kv head)                        */ };
+/* Scratch for the partial results: two per token range and query head (running maximum, row sum, head_dim
+ * numerators each), sized for the smallest range the library may choose unless split_tokens fixes one.  */
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens /* 0 = default */);
 int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* args, void* stream);
