@@ -582,6 +582,60 @@ def quick_config(H, name, steps, peak):
     return out
 
 
+def exchange_tables(w, is_prefill: bool, mover: bool, partner: int, dst_dtype: str) -> dict:
+    """The handoff's metadata crosses the process boundary as the library's checksummed session messages
+    (tkv_session_pack / tkv_session_unpack; SessionTransfer's field set, engine/src/session.rs:194-200): the rank whose GPU
+    does not run the kernel announces, for every prompt, the pages it holds in ITS pool -- two page-granular pieces per
+    prompt, sent in reverse order -- and the rank that runs the kernel builds that side of its block tables from the
+    messages alone (its own seeded copy of the far side's table is wiped first).  The K/V bytes do not travel in the
+    messages: the kernel moves them."""
+    import torch
+    import torch.distributed as dist
+    from tempura_b200 import _native as N
+    from tempura_b200 import session as S
+    code = {"f32": N.DTYPE_F32, "f16": N.DTYPE_F16, "e4m3": N.DTYPE_E4M3}
+    mine_dtype = code["f16"] if is_prefill else code[dst_dtype]
+    far_dtype = code[dst_dtype] if is_prefill else code["f16"]
+    n_msgs = 0
+    if not mover:
+        tables = w.src_tables if is_prefill else w.dst_tables
+        msgs = S.pack_batch(w.seq_lens, tables, w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, mine_dtype, pieces=2)[::-1]
+        blob = S.frame(msgs)
+        dist.send(torch.tensor([len(blob), len(msgs)], dtype=torch.int64, device="cuda"), partner)
+        dist.send(torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda(), partner)
+        n_msgs, n_bytes = len(msgs), len(blob)
+    else:
+        far = w.dst_tables if is_prefill else w.src_tables
+        seeded = far.copy()
+        far.fill(0xFFFFFFFF)
+        head = torch.zeros(2, dtype=torch.int64, device="cuda")
+        dist.recv(head, partner)
+        n_bytes, n_msgs = int(head[0]), int(head[1])
+        buf = torch.zeros(n_bytes, dtype=torch.uint8, device="cuda")
+        dist.recv(buf, partner)
+        got = S.unframe(buf.cpu().numpy().tobytes())
+        assert len(got) == n_msgs
+        seen = {}
+        for m in got:
+            h, blocks, _ = S.unpack(m)                       # refuses a damaged or truncated message
+            q = int(h.seed)
+            if (h.n_layers, h.n_kv_heads, h.head_dim, h.block_size, h.kv_dtype) != (w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, far_dtype) \
+                    or h.seq_len != int(w.seq_lens[q]):
+                raise SystemExit(f"session message for prompt {q} does not match this pool's geometry")
+            far[q, h.block_begin:h.block_begin + h.n_blocks] = blocks
+            seen[q] = seen.get(q, 0) + 1
+            assert seen[q] <= h.piece_count
+        bs = w.block_size
+        for q, n in enumerate(w.seq_lens):
+            nb = (int(n) + bs - 1) // bs
+            if not np.array_equal(far[q, :nb], seeded[q, :nb]):
+                raise SystemExit(f"block table of prompt {q} differs from what its owner holds")
+    return {"messages": n_msgs, "bytes": n_bytes, "pieces_per_prompt": 2, "order": "reversed",
+            "direction": "prefill rank -> decode rank" if is_prefill != mover else "decode rank -> prefill rank",
+            "what": "tkv_session_pack messages (header + the sender's block table, checksummed) over torch.distributed; the "
+                    "rank whose GPU runs the kernel builds the far side's block table from them alone"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -674,6 +728,9 @@ def run_ours(args):
         else:
             src_remote = theirs
 
+    wire = None
+    if multi:
+        wire = exchange_tables(w, is_prefill, mover, partner, dst_dtype)
     batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens)
     plan = None
     if mover:
@@ -899,6 +956,8 @@ def run_ours(args):
         }
         if nccl is not None:
             line["nccl_baseline"] = nccl
+        if wire is not None:
+            line["wire"] = wire
         if not multi and not args.no_cpu:
             layers = sample_layers(w)
             v1, sample = time_cpu(w, 1, layers, 3)
