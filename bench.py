@@ -520,7 +520,7 @@ def nccl_baseline(H, w, batch, src, dst, is_prefill, partner, local, scales, ste
 # our arm
 # ----------------------------------------------------------------------------------------
 KERNEL_NAMES = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e4m3_warp", 4: "handoff_f16_e4m3_generic",
-                5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant", 8: "handoff_f32_cast_vec"}
+                5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant", 8: "handoff_f32_cast_vec", 9: "handoff_copy_wide"}
 
 
 def time_handoffs(H, plan, w, steps, stream, done_flag, gen):
@@ -728,9 +728,9 @@ def run_ours(args):
         else:
             src_remote = theirs
 
-    wire = None
+    wire_msgs = None
     if multi:
-        wire = exchange_tables(w, is_prefill, mover, partner, dst_dtype)
+        wire_msgs = exchange_tables(w, is_prefill, mover, partner, dst_dtype)
     batch = H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride, w.prefix_lens)
     plan = None
     if mover:
@@ -956,8 +956,8 @@ def run_ours(args):
         }
         if nccl is not None:
             line["nccl_baseline"] = nccl
-        if wire is not None:
-            line["wire"] = wire
+        if wire_msgs is not None:
+            line["wire_messages"] = wire_msgs
         if not multi and not args.no_cpu:
             layers = sample_layers(w)
             v1, sample = time_cpu(w, 1, layers, 3)

@@ -149,7 +149,8 @@ enum {
                                        tkv_ipc_import on the destination side).                     */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
-       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7, TKV_VARIANT_CAST_VEC = 8 };
+       TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7, TKV_VARIANT_CAST_VEC = 8,
+       TKV_VARIANT_WIDE = 9 /* the register copy with 32-byte accesses (tkv_plan_tune_vector; the default of a pulled plan) */ };
 
 /* ---- library -------------------------------------------------------------- */
 /* Copies the calling thread's last error text (NUL-terminated) into buf. */

@@ -25,7 +25,7 @@ DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
 PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER, PLAN_PEER_BULK_STORES, PLAN_PULL = 1, 2, 4, 8, 16, 32
 ATTN_PER_HEAD_CTAS = 1
 ATTN_MMA_SYNC = 2
-VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC, VARIANT_FP8_STAGED, VARIANT_DEQUANT, VARIANT_CAST_VEC = 1, 2, 3, 4, 5, 6, 7, 8
+VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC, VARIANT_FP8_STAGED, VARIANT_DEQUANT, VARIANT_CAST_VEC, VARIANT_WIDE = 1, 2, 3, 4, 5, 6, 7, 8, 9
 
 
 class TkvPool(C.Structure):

@@ -864,7 +864,7 @@ int32_t tkv_plan_stats(const tkv_plan* p, TkvStats* out) {
     *out = p->stats;
     out->grid = p->grid;
     out->block = p->variant == TKV_VARIANT_BULK ? 32u : 256u;
-    out->kernel_variant = p->variant;
+    out->kernel_variant = (p->variant == TKV_VARIANT_VECTOR && wide_eligible(p)) ? (uint32_t)TKV_VARIANT_WIDE : p->variant;
     return TKV_OK;
 }
 

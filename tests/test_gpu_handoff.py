@@ -78,7 +78,7 @@ def test_config2_shape_f16_copy_32_byte_accesses(H, unroll, hint):
     plan.enqueue()
     torch.cuda.synchronize()
     assert_pool_equals_host(dd, hd, f"32-byte copy unroll {unroll} hint {hint}")
-    assert plan.stats().kernel_variant == 1
+    assert plan.stats().kernel_variant == N.VARIANT_WIDE
 
 
 def test_config2_lengths_exact_multiple_and_single_token(H):
