@@ -523,6 +523,9 @@ KERNEL_NAMES = {1: "handoff_copy_vec", 2: "handoff_copy_bulk", 3: "handoff_f16_e
                 5: "handoff_f32_cast_generic", 6: "handoff_f16_e4m3_staged", 7: "handoff_e4m3_dequant", 8: "handoff_f32_cast_vec", 9: "handoff_copy_wide"}
 
 
+FLUSH_THEN_READ = False
+
+
 def time_handoffs(H, plan, w, steps, stream, done_flag, gen):
     """K handoffs, inputs resident in HBM, device-timed on the launching stream.  A batch whose bytes would fit L2
     (126 MB) is timed launch by launch with a 256 MB write in between, so every timed launch starts with a cold
@@ -531,10 +534,13 @@ def time_handoffs(H, plan, w, steps, stream, done_flag, gen):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if is_small(w):
         flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        clean = torch.zeros(64 << 20, dtype=torch.int32, device="cuda") if FLUSH_THEN_READ else None
         ms = 0.0
         for i in range(steps):
             gen += 1
             flush.fill_(i & 0xFF)
+            if clean is not None:
+                clean.sum()                 # probe: leave L2 full of clean lines, so the timed kernel evicts nothing dirty
             ev0.record(stream)
             plan.enqueue(stream, done_flag, gen)
             ev1.record(stream)
@@ -741,11 +747,15 @@ def run_ours(args):
             plan.tune_grid(args.grid_tune)
         if args.vec_tune:
             plan.tune_vector(*[int(x) for x in args.vec_tune.split(",")])
+        if args.small_tune:
+            plan.tune_small(*[int(x) for x in args.small_tune.split(",")])
     stream = torch.cuda.current_stream()
     # where the kernel publishes completion: the host-visible flag on one GPU; the decode GPU's flag across GPUs (its own
     # memory when it pulls, the mapped peer word when the prefill GPU pushes)
     done_flag = flag.data_ptr() if (not multi or pull) else (remote_flag if is_prefill else 0)
     waits_on_flag = multi and not pull and not is_prefill     # a pushed handoff is awaited by the decode rank
+    if args.no_flag:
+        done_flag = 0                                         # probe: the launch alone, nothing published
 
     def barrier():
         if multi:
@@ -1246,6 +1256,9 @@ def main():
     ap.add_argument("--bulk-tune", default=None, help="stages,ctas_per_sm,stage_bytes for the bulk-copy variant")
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--vec-tune", default=None, help="bytes_per_access,unroll,store_hint for the register copy kernel (e.g. 32,8,0)")
+    ap.add_argument("--flush-then-read", action="store_true", help="probe for small batches: after the L2 flush (a 256 MB write) read 256 MB, so L2 holds clean lines when the timed launch starts")
+    ap.add_argument("--no-flag", action="store_true", help="probe (--sweep, one GPU): enqueue without a completion flag")
+    ap.add_argument("--small-tune", default=None, help="flag_mode,inline_list of tkv_plan_tune_small (e.g. 1,1 = flag from the kernel, list from device memory)")
     ap.add_argument("--push", action="store_true", help="N > 1: the prefill GPU's kernel stores into the decode pool (default for a same-dtype batch: the decode GPU pulls)")
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -1256,6 +1269,8 @@ def main():
     ap.add_argument("--host-bulk", action="store_true", help="host-buffer leg: bulk-copy ring reading the pinned buffer (experiment)")
     ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")
     args = ap.parse_args()
+    global FLUSH_THEN_READ
+    FLUSH_THEN_READ = args.flush_then_read
     if args.warmup < 3:
         args.warmup = 3
     if args.workload == "prefix":

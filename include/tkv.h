@@ -255,7 +255,8 @@ int32_t tkv_handoff_noalloc(const TkvPool* src, const TkvPool* dst, const TkvBat
                             const TkvShard* shard /* NULL = everything */, void* stream);
 
 /* Tuning of the bulk-copy variant (ring depth per CTA, CTAs per SM, bytes per ring
- * stage); ctas_per_sm 0 derives it from the stage size.  The staged FP8 kernel takes the
+ * stage; without this call 32 KiB, or 8 KiB for a batch with fewer than four chunks per SM); ctas_per_sm 0 derives it from
+ * the stage size.  The staged FP8 kernel takes the
  * ring depth and the CTA cap from the same call (its stage is one chunk).  No reference
  * counterpart.
  * Takes effect at the next enqueue.                                             */
@@ -265,6 +266,13 @@ int32_t tkv_plan_tune_bulk(tkv_plan* plan, uint32_t stages, uint32_t ctas_per_sm
  * (4, 8, 16; the 32-byte kernel only), cache policy of the stores (0 default, 1 streaming, 2 no L1
  * allocation; the 32-byte kernel only).  No reference counterpart.  Takes effect at the next enqueue. */
 int32_t tkv_plan_tune_vector(tkv_plan* plan, uint32_t bytes_per_access, uint32_t unroll, uint32_t store_hint);
+/* Two choices that matter to small handoffs.  flag_mode: who writes the completion flag -- 0 the library's choice
+ * (a stream-ordered 32-bit write behind the kernel where the launching device's stream can reach the word: its own
+ * memory or page-locked host memory; the kernel's last CTA for a peer GPU's word and inside a stream capture), 1 always
+ * the kernel's last CTA, 2 the stream write wherever it is possible.  inline_list: 0 the library's choice (a host-built
+ * work list of at most 256 pairs and 64 layers rides in the kernel's parameter block when the batch has few chunks per
+ * SM, and nothing is uploaded for it), 1 never, 2 whenever it fits.  No reference counterpart. */
+int32_t tkv_plan_tune_small(tkv_plan* plan, uint32_t flag_mode, uint32_t inline_list);
 /* Caps the resident CTAs per SM of the register (non-bulk) kernels; 0 = as many as fit. */
 int32_t tkv_plan_tune_grid(tkv_plan* plan, uint32_t ctas_per_sm);
 /* Reads the plan's device-side error word (synchronous): 0, or 1 when a kernel of

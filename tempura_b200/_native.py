@@ -144,6 +144,7 @@ SIGNATURES = {
     "tkv_plan_tune_bulk": (_i32, [_vp, _u32, _u32, _u32]),
     "tkv_plan_tune_vector": (_i32, [_vp, _u32, _u32, _u32]),
     "tkv_plan_tune_grid": (_i32, [_vp, _u32]),
+    "tkv_plan_tune_small": (_i32, [_vp, _u32, _u32]),
     "tkv_plan_error": (_i32, [_vp, _u32p]),
     "tkv_flag_wait_host": (_i32, [_i32, _u64, _u32, _u64]),
     "tkv_flag_wait_enqueue": (_i32, [_vp, _u64, _u32, _u64, _u64]),

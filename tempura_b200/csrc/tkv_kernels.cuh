@@ -42,6 +42,7 @@ struct HandoffArgs {
     uint32_t flag_value;
     uint32_t contiguous;        // rows abut on both sides
     const uint32_t* n_pairs_dev; // set = the work list was built on the device: its length is read here (n_pairs is the capacity)
+    uint32_t local_fences;      // 1 = both pools are this GPU's memory: CTAs count themselves with a GPU-scope release, only the last one fences at system scope
 };
 
 // Block pairs the launch really has: the host's count, or the device-built list's (never above the capacity).
@@ -72,6 +73,31 @@ __device__ __forceinline__ Chunk decode_chunk(const HandoffArgs& a, uint32_t w) 
     return c;
 }
 
+// A short work list carried in the kernel's parameter block: the pairs and the four layer-pointer arrays sit in the
+// constant bank the launch fills, so a small handoff starts its first payload load without a dependent fetch of the
+// list from device memory (and the host uploads nothing).
+constexpr uint32_t INLINE_PAIRS = 256, INLINE_LAYERS = 64;
+struct InlineList {
+    uint4 pairs[INLINE_PAIRS];
+    uint64_t ptr[4][INLINE_LAYERS];   // src K, src V, dst K, dst V
+};
+
+__device__ __forceinline__ Chunk decode_chunk_inline(const HandoffArgs& a, const InlineList& il, uint32_t w) {
+    Chunk c;
+    c.is_v = w & 1u;
+    uint32_t q = w >> 1;
+    c.layer = q % a.n_layers;
+    uint4 t = il.pairs[q / a.n_layers];
+    uint64_t sb = il.ptr[c.is_v][c.layer];
+    uint64_t db = il.ptr[2u + c.is_v][c.layer];
+    c.src = reinterpret_cast<const char*>(sb + (uint64_t)t.x * a.src_block_stride + a.src_head_off);
+    c.dst = reinterpret_cast<char*>(db + (uint64_t)t.y * a.dst_block_stride + a.dst_head_off);
+    c.n_valid = t.z;
+    c.dst_block = t.y;
+    c.src_block = t.x;
+    return c;
+}
+
 // Last CTA to finish publishes the completion flag.  Every CTA fences its
 // payload stores to system scope before counting itself, so a reader that
 // acquires the flag (host, peer GPU) sees all of them.
@@ -79,8 +105,15 @@ __device__ __forceinline__ void signal_done(const HandoffArgs& a) {
     if (a.done_flag == nullptr) return;
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        uint32_t prev = atomicAdd(a.done_counter, 1u);
+        uint32_t prev;
+        if (a.local_fences) {
+            // The payload went to this GPU's own memory: a release at GPU scope orders it before the count, the last
+            // CTA's acquire of the count and its system-scope release below carry it on to the flag's reader.
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(a.done_counter) : "memory");
+        } else {
+            __threadfence_system();
+            prev = atomicAdd(a.done_counter, 1u);
+        }
         if (prev == gridDim.x - 1) {
             *a.done_counter = 0;  // ready for the next enqueue (stream order)
             __threadfence_system();
@@ -251,8 +284,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 }
 
 #ifndef TKV_KERNELS_TEMPLATES_ONLY
-__global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uint32_t stage_bytes, uint32_t n_stages,
-                                                        uint32_t pieces, uint32_t* error_flag) {
+template <bool INLINE>
+__device__ __forceinline__ void bulk_copy_body(const HandoffArgs& a, const InlineList* il, uint32_t stage_bytes, uint32_t n_stages,
+                                               uint32_t pieces, uint32_t* error_flag) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                    // up to 8 barriers
     BulkItem* items = reinterpret_cast<BulkItem*>(smem + 64);              // 64 decoded items
@@ -276,7 +310,7 @@ __global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uin
         if (k < n_mine) {
             uint64_t it = (uint64_t)blockIdx.x + (uint64_t)k * gridDim.x;
             uint32_t piece = (uint32_t)(it % pieces);
-            Chunk c = decode_chunk(a, (uint32_t)(it / pieces));
+            Chunk c = INLINE ? decode_chunk_inline(a, *il, (uint32_t)(it / pieces)) : decode_chunk(a, (uint32_t)(it / pieces));
             uint32_t cb = c.n_valid * a.src_row_bytes;                     // valid bytes of this chunk
             uint32_t off = piece * stage_bytes;
             BulkItem bi;
@@ -351,6 +385,17 @@ __global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uin
     }
     __syncwarp();
     signal_done(a);
+}
+
+__global__ void __launch_bounds__(32) handoff_copy_bulk(const HandoffArgs a, uint32_t stage_bytes, uint32_t n_stages,
+                                                        uint32_t pieces, uint32_t* error_flag) {
+    bulk_copy_body<false>(a, nullptr, stage_bytes, n_stages, pieces, error_flag);
+}
+
+// The same ring with the work list in the parameter block (at most INLINE_PAIRS pairs and INLINE_LAYERS layers).
+__global__ void __launch_bounds__(32) handoff_copy_bulk_inline(const __grid_constant__ HandoffArgs a, const __grid_constant__ InlineList il,
+                                                               uint32_t stage_bytes, uint32_t n_stages, uint32_t pieces, uint32_t* error_flag) {
+    bulk_copy_body<true>(a, &il, stage_bytes, n_stages, pieces, error_flag);
 }
 #endif  // TKV_KERNELS_TEMPLATES_ONLY
 

@@ -165,9 +165,16 @@ struct tkv_plan {
     tkv::HandoffArgs args{};
     TkvStats stats{};
     uint32_t grid = 0;
-    uint32_t bulk_stages = 3, bulk_ctas_per_sm = 0, bulk_stage_bytes = 32768;  // ctas 0 = derive from the stage size
+    uint32_t bulk_stages = 3, bulk_ctas_per_sm = 0, bulk_stage_bytes = 0;  // ctas 0 = derive from the stage size; stage 0 = 32 KiB, 8 KiB for few chunks
     uint32_t fp8_stages = 2;         // staged FP8 kernel: ring depth per CTA
     uint32_t vec_bytes = 0, vec_unroll = 8, vec_hint = 0;   // register copy kernel: bytes per access (0 = the library's choice), loads in flight per thread, store cache policy
+    // Small handoffs: where the completion flag is written from (0 = the library's choice, 1 = by the kernel's last CTA,
+    // 2 = by a stream-ordered 32-bit write behind the kernel) and whether a short work list rides in the kernel's parameter
+    // block (0 = the library's choice, 1 = never, 2 = whenever it fits).
+    uint32_t flag_mode = 0, inline_mode = 0;
+    bool ever_uploaded = false;      // the device block (counter, error word, layer pointers) has been initialised once
+    uint64_t flag_checked = 0;       // the last completion-flag address classified, and whether a stream write may target it
+    bool flag_stream_ok = false;
     uint32_t grid_ctas_per_sm = 0;   // cap for the register kernels (0 = occupancy limit)   // ring depth and residency of the bulk-copy kernel
     std::vector<uint8_t> seen;  // scratch bitmap over destination blocks
     std::vector<char> image;    // host image of the device block, built before any CUDA call
@@ -417,6 +424,7 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
     a.dst_layer_begin = sh.dst_layer_begin;
     a.flag_value = 0;
     a.contiguous = (a.src_row_bytes == a.src_row_stride && a.dst_row_bytes == a.dst_row_stride) ? 1u : 0u;
+    a.local_fences = (s.device == d.device && !p->host_side) ? 1u : 0u;
 
     // widest vector that divides every offset and address involved
     int vec = 16;
@@ -458,6 +466,7 @@ int32_t ensure_uploaded(tkv_plan* p, cudaStream_t st, bool need_host_list = true
         p->dirty = false;
         p->list_clobbered = false;
         p->upload_pending = true;
+        p->ever_uploaded = true;
     } else if (p->upload_pending) {
         CU(cudaStreamWaitEvent(st, p->upload_ev, 0));
     }
@@ -524,13 +533,61 @@ bool bulk_eligible(const tkv_plan* p) {
     return p->mode == MODE_COPY && p->args.contiguous && p->vec == 16 && reach && host_ok && p->args.src_k_scales == nullptr;
 }
 
+// The work list fits the kernel's parameter block: one list for all layers, built on the host, short enough.
+bool inline_eligible(const tkv_plan* p) {
+    const tkv::HandoffArgs& a = p->args;
+    if (p->inline_mode == 1 || a.n_pairs_dev != nullptr || a.work_layer_stride != 0) return false;
+    if (a.n_pairs > tkv::INLINE_PAIRS || a.n_layers > tkv::INLINE_LAYERS) return false;
+    if (p->inline_mode == 2) return true;
+    // the library's choice: only where the list fetch is a visible share of the launch (few chunks per SM)
+    DevInfo di;
+    if (dev_info(p->launch_dev, &di)) return false;
+    return (uint64_t)a.n_pairs * a.n_layers * 2 <= 16ull * di.sm_count;
+}
+
+// A 32-bit write the stream performs behind everything enqueued before it (cuStreamWriteValue32: the driver orders it
+// after the preceding kernel's writes at system scope).  Taken from the driver by name; 0 where the driver lacks it.
+typedef int (*write_value_fn)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
+write_value_fn stream_write_value() {
+    static write_value_fn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &f, cudaEnableDefault, &qr) != cudaSuccess) f = nullptr;
+        cudaGetLastError();
+        return reinterpret_cast<write_value_fn>(f);
+    }();
+    return fn;
+}
+
+// May the completion flag at `flag` be written by a stream operation of the launching device?  Yes for that device's own
+// memory and for page-locked host memory whose device address equals its host address; a peer GPU's word stays with the
+// kernel's last CTA (whose release store is known to reach it).
+bool flag_by_stream(tkv_plan* p, uint64_t flag) {
+    if (p->flag_mode == 1 || !flag || !stream_write_value()) return false;
+    if (p->flag_checked == flag) return p->flag_stream_ok;
+    p->flag_checked = flag;
+    p->flag_stream_ok = false;
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, reinterpret_cast<void*>(flag)) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (at.type == cudaMemoryTypeDevice) p->flag_stream_ok = at.device == p->launch_dev;
+    else if (at.type == cudaMemoryTypeHost) p->flag_stream_ok = reinterpret_cast<uint64_t>(at.devicePointer) == flag;
+    return p->flag_stream_ok;
+}
+
 int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     const tkv::HandoffArgs& a = p->args;
     DevInfo di;
     int32_t rc = dev_info(p->launch_dev, &di);
     if (rc) return rc;
     const uint32_t chunk = a.block_size * a.src_row_bytes;
-    const uint32_t stage = std::min<uint32_t>(p->bulk_stage_bytes, (chunk + 127u) & ~127u);
+    // Few chunks per SM: cut them into 8 KiB pieces so that every SM carries loads from the first cycle and the last
+    // piece of the slowest CTA is short.
+    const uint64_t n_chunks = (uint64_t)a.n_pairs * a.n_layers * 2;
+    const uint32_t stage_cap = p->bulk_stage_bytes ? p->bulk_stage_bytes : (n_chunks < 4ull * di.sm_count ? 8192u : 32768u);
+    const uint32_t stage = std::min<uint32_t>(stage_cap, (chunk + 127u) & ~127u);
     const uint32_t pieces = (chunk + stage - 1) / stage;
     const uint32_t stages = std::max(2u, std::min(8u, p->bulk_stages));
     const size_t smem = 64 + 64 * sizeof(tkv::BulkItem) + (size_t)stages * stage;
@@ -545,7 +602,18 @@ int32_t launch_bulk(tkv_plan* p, cudaStream_t st) {
     p->grid = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)di.sm_count * per_sm, items));
     p->variant = TKV_VARIANT_BULK;
     uint32_t* err = a.done_counter + 1;   // second word of the zeroed slot in the plan's device block
-    tkv::handoff_copy_bulk<<<p->grid, 32, smem, st>>>(a, stage, stages, pieces, err);
+    if (inline_eligible(p)) {
+        rc = grant_smem(tkv::handoff_copy_bulk_inline, p->launch_dev, smem);
+        if (rc) return rc;
+        static thread_local tkv::InlineList il;
+        const size_t L = a.n_layers;
+        const uint64_t* ptrs = reinterpret_cast<const uint64_t*>(p->h_buf);           // [src K | src V | dst K | dst V][L]
+        for (int k = 0; k < 4; k++) memcpy(il.ptr[k], ptrs + k * L, L * sizeof(uint64_t));
+        memcpy(il.pairs, p->h_buf + p->off_work, (size_t)a.n_pairs * sizeof(uint4));
+        tkv::handoff_copy_bulk_inline<<<p->grid, 32, smem, st>>>(a, il, stage, stages, pieces, err);
+    } else {
+        tkv::handoff_copy_bulk<<<p->grid, 32, smem, st>>>(a, stage, stages, pieces, err);
+    }
     CU(cudaGetLastError());
     return TKV_OK;
 }
@@ -883,12 +951,31 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         p->grid = 0;
         return TKV_OK;
     }
-    {
+    a.n_pairs_dev = nullptr;
+    // The flag: by a stream-ordered write behind the kernel where the stream can reach it (no fence, counter and
+    // flag store inside the kernel: they cost a small handoff several microseconds), else by the kernel's last CTA.
+    bool by_stream = flag_by_stream(p, done_flag);
+    if (by_stream) {                       // inside a stream capture the kernel's own store is the form every driver can record
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) by_stream = false;
+    }
+    if (by_stream) a.done_flag = nullptr;
+    // A launch that carries its list in the parameter block reads nothing of the device block once that is initialised.
+    const bool needs_block = !(p->ever_uploaded && p->mode == MODE_COPY && !(p->flags & TKV_PLAN_FORCE_VECTOR) && bulk_eligible(p) && inline_eligible(p));
+    if (needs_block) {
         int32_t rc = ensure_uploaded(p, st);
         if (rc) return rc;
     }
-    a.n_pairs_dev = nullptr;
-    return dispatch(p, chunks, st);
+    int32_t rc = dispatch(p, chunks, st);
+    if (rc) return rc;
+    if (by_stream) {
+        int r = stream_write_value()(st, (unsigned long long)done_flag, flag_value, 0u);
+        if (r != 0) {                      // not supported here after all: the kernel publishes from now on, this one by a copy
+            p->flag_mode = 1;
+            CU(cudaMemcpyAsync(reinterpret_cast<void*>(done_flag), &a.flag_value, 4, cudaMemcpyDefault, st));
+        }
+    }
+    return TKV_OK;
 }
 
 }  // extern "C"
@@ -1023,6 +1110,15 @@ int32_t tkv_plan_tune_vector(tkv_plan* p, uint32_t bytes_per_access, uint32_t un
     p->vec_bytes = bytes_per_access;
     p->vec_unroll = unroll;
     p->vec_hint = store_hint;
+    return TKV_OK;
+}
+
+int32_t tkv_plan_tune_small(tkv_plan* p, uint32_t flag_mode, uint32_t inline_list) {
+    if (!p) return fail(TKV_ERR_INVALID_CONFIG, "NULL plan");
+    if (flag_mode > 2 || inline_list > 2) return fail(TKV_ERR_INVALID_CONFIG, "flag_mode and inline_list must be 0, 1 or 2");
+    p->flag_mode = flag_mode;
+    p->inline_mode = inline_list;
+    p->flag_checked = 0;
     return TKV_OK;
 }
 

@@ -279,6 +279,9 @@ class Plan:
     def tune_vector(self, bytes_per_access: int, unroll: int = 8, store_hint: int = 0) -> None:
         check(lib().tkv_plan_tune_vector(self._h, bytes_per_access, unroll, store_hint))
 
+    def tune_small(self, flag_mode: int = 0, inline_list: int = 0) -> None:
+        check(lib().tkv_plan_tune_small(self._h, flag_mode, inline_list))
+
     def tune_grid(self, ctas_per_sm: int) -> None:
         check(lib().tkv_plan_tune_grid(self._h, ctas_per_sm))
 

@@ -330,6 +330,47 @@ def test_bulk_variant_parity(H, tune):
         assert_pool_equals_host(dd, hd, f"bulk {w.name} {tune}")
 
 
+@pytest.mark.parametrize("flag_mode", [0, 1, 2])
+@pytest.mark.parametrize("inline_list", [0, 1, 2])
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_small_handoff_choices_change_no_byte(H, flag_mode, inline_list, where):
+    """Who publishes the flag (the kernel's last CTA or a stream-ordered write behind the kernel) and where the work list
+    sits (device memory or the kernel's parameter block) are latency choices: same bytes, same flag, plan updates included."""
+    import torch
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda") if where == "device" else torch.zeros(1, dtype=torch.int32).pin_memory()
+    w = W.tinyllama_cpu()
+    hs, hd = host_pools(w)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "f16")
+    oracle.handoff(hs, hd, oracle_batch(w))
+    plan = H.Plan(ds, dd, device_batch(w))
+    plan.tune_small(flag_mode, inline_list)
+    for gen in (1, 2, 3):
+        plan.enqueue(done_flag=flag.data_ptr(), flag_value=gen)
+        H.flag_wait_host(0, flag.data_ptr(), gen, 5_000_000)
+        if gen == 1:
+            assert_pool_equals_host(dd, hd, f"small flag {flag_mode} inline {inline_list}")
+    assert plan.device_error() == 0
+    # a new batch through the same plan: the parameter-block list must follow the update, not the first batch
+    w2 = W.Workload("small-update", w.n_layers, w.n_kv_heads, w.head_dim, w.block_size, w.src_blocks, w.dst_blocks,
+                    np.array([33, 7], dtype=np.uint32), seed=78).build_tables()
+    hs2, hd2 = host_pools(w2)
+    ds2, dd2 = to_device_pool(hs2, "f16"), to_device_pool(hd2, "f16")
+    oracle.handoff(hs2, hd2, oracle_batch(w2))
+    plan2 = H.Plan(ds2, dd2, device_batch(w))             # created for the first batch ...
+    plan2.tune_small(flag_mode, inline_list)
+    plan2.enqueue(done_flag=flag.data_ptr(), flag_value=4)
+    H.flag_wait_host(0, flag.data_ptr(), 4, 5_000_000)
+    for arrs in (dd2.k, dd2.v):                           # ... whose rows are wiped again before the update
+        for l in range(w2.n_layers):
+            arrs[l].view(torch.uint8).fill_(0x5A)
+    plan2.update(device_batch(w2))
+    plan2.enqueue(done_flag=flag.data_ptr(), flag_value=5)
+    H.flag_wait_host(0, flag.data_ptr(), 5, 5_000_000)
+    assert_pool_equals_host(dd2, hd2, "after update")
+    with pytest.raises(N.TkvError):
+        plan.tune_small(3, 0)
+
+
 def test_bulk_variant_refuses_strided_rows(H):
     w = W.Workload("bulk-shard", 2, 8, 128, 16, 64, 64, np.array([40], dtype=np.uint32), seed=42).build_tables()
     hs, hd = host_pools(w, dst_heads=2)
