@@ -7,8 +7,10 @@ A step is one handoff of the whole batch.  The default workload is the benchmark
 (Llama-3.1-70B shape, 80 layers, 32 prompts of 4096 tokens, 42.9 GB of F16 K/V) at every N: N = 1 moves it
 between a prefill pool and a decode pool on the same GPU (HBM-bound); N = 2, 4, 8 is one process per GPU,
 ranks [0, N/2) prefill and ranks [N/2, N) decode, the batch's KV heads split evenly over the pairs
-(tkv_pairing_make) and every pair moving its share with stores into the peer pool over NVLink (strong scaling:
-the batch is fixed).  --workload cfg1..cfg4 select the other configurations (at N > 1 every pair then moves its
+(tkv_pairing_make) and every pair moving its share over NVLink -- pulled by the decode GPU's kernel (loads from the
+mapped prefill pool, local stores) or, with --push, stored into the peer pool by the prefill GPU's kernel -- (strong
+scaling: the batch is fixed).  The block tables of the side that does not run the kernel reach the other rank as
+tkv_session_pack messages.  --workload cfg1..cfg4 select the other configurations (at N > 1 every pair then moves its
 own batch: weak scaling).  Every run ends with a parity step outside the timed region: every moved row of every
 layer on the destination against the source, bit for bit, or the run exits non-zero.  Prints ONE JSON line on rank 0.
 """

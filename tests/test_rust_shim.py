@@ -153,3 +153,16 @@ def test_worker_crate_calls_exist_with_the_right_arity():
     assert "impl<E: PrefillEngine> PrefillWorker for GpuPrefillWorker<E>" in text
     assert "impl<D: DecodeEngine> DecodeWorker for GpuDecodeWorker<D>" in text
     assert "KernelError::DimensionMismatch { expected, got }" in text and "KernelError::InvalidConfig" in text
+
+
+def test_the_integration_guide_quotes_the_crates_verbatim():
+    """Every fenced rust block of the guide is an excerpt of a file under rust/: the guide cannot drift from the crates."""
+    import re
+    guide = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```rust\n(.*?)```", guide, flags=re.S)
+    assert blocks, "the guide quotes at least the status mapping"
+    sources = []
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "rust")):
+        sources += [open(os.path.join(dirpath, f)).read() for f in files if f.endswith(".rs")]
+    for b in blocks:
+        assert any(b in src for src in sources), b[:80]
