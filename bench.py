@@ -55,8 +55,11 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index, also=()):
+        """Samples `gpu_index` (whose clock is reported) and the GPUs in `also` (whose throttle reasons count as well:
+        across GPUs the kernel may run on the partner)."""
         self.gpu = gpu_index
+        self.gpus = [gpu_index] + [g for g in also if g != gpu_index]
         self.rows = []
         self.proc = None
         self.marks = []
@@ -64,12 +67,15 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", ",".join(str(g) for g in self.gpus)], stdout=subprocess.PIPE, text=True)
         except OSError:
             self.proc = None
             return
         self.t = threading.Thread(target=self._read, daemon=True)
         self.t.start()
+        t0 = time.perf_counter()                      # the tool takes a moment to come up: the timed region must not beat it
+        while not self.rows and time.perf_counter() - t0 < 8.0:
+            time.sleep(0.02)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -89,27 +95,39 @@ class ClockSampler:
             self.proc.kill()
         lo = self.marks[0] if self.marks else 0.0
         hi = self.marks[-1] if len(self.marks) > 1 else float("inf")
-        sm, mx, reasons, n = [], [], set(), 0
+        sm, mx, reasons, n, others = [], [], set(), 0, {}
         for t, line in self.rows:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                clk, cmax = float(parts[1]), float(parts[2])
+                idx, clk, cmax = int(parts[0]), float(parts[1]), float(parts[2])
             except ValueError:
                 continue
             inside = lo - 0.05 <= t <= hi + 0.05
             if inside:
-                sm.append(clk)
-                n += 1
+                if idx == self.gpu:
+                    sm.append(clk)
+                    n += 1
+                else:
+                    others.setdefault(idx, []).append(clk)
                 for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
                     if val.lower().startswith("active"):
                         reasons.add(name)
             mx.append(cmax)
         if not sm:   # region shorter than the sampling period: use everything seen
             sm = [float(r[1].split(",")[1]) for r in self.rows if len(r[1].split(",")) >= 9] or [0.0]
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": n}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None,
+               "reasons": sorted(reasons), "samples": n}
+        if others:
+            out["partner_sm_mhz"] = {str(k): statistics.median(v) for k, v in others.items()}
+        return out
+
+
+class NullSampler:
+    def start(self): pass
+    def mark(self): pass
+    def stop(self): return {}
 
 
 # ----------------------------------------------------------------------------------------
@@ -663,7 +681,7 @@ def run_ours(args):
     if world > 1 and world % 2:
         raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
     wname = default_workload(args)
-    w = pick_workload(wname, world, args.pool_blocks, layers=args.layers, single_tokens=args.single_tokens)
+    w = pick_workload(wname, world, args.pool_blocks, heads=args.heads_per_pair, layers=args.layers, single_tokens=args.single_tokens)
     if args.src_f32:                # the reference's own transfer dtype: F32 rows into the F16 cache (one GPU only)
         if world != 1 or w.dst_dtype != "f16":
             raise SystemExit("--src-f32 is a one-GPU probe of the F32 -> F16 cast")
@@ -673,7 +691,7 @@ def run_ours(args):
     role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode); heads split by tkv_pairing_make
     pairs = max(1, world // 2)
     strong = wname == "cfg5"                         # one batch, its KV heads split over the pairs
-    if strong and multi and not args.single_tokens:
+    if strong and multi and not args.single_tokens and not args.heads_per_pair:
         assert w.n_kv_heads == role.n_heads, "the pools hold exactly the pair's share of the KV heads"
     is_prefill, partner = role.is_prefill, role.partner
     dst_dtype = w.dst_dtype
@@ -686,7 +704,8 @@ def run_ours(args):
     if args.peer_bulk:
         flags |= H.N.PLAN_PEER_BULK_STORES
 
-    sampler = ClockSampler(local)
+    # rank 0 samples its own GPU and its partner's (the pulled handoff's kernel runs there); one nvidia-smi for the whole job
+    sampler = ClockSampler(local, also=[partner] if multi else []) if rank == 0 else NullSampler()
     src = dst = None
     remote_base = 0
     # Across GPUs a same-dtype batch is PULLED: the kernel runs on the decode GPU, fetches the prefill pool's blocks with
@@ -1259,6 +1278,7 @@ def main():
     ap.add_argument("--grid-tune", type=int, default=None, help="CTAs per SM cap for the register kernels")
     ap.add_argument("--vec-tune", default=None, help="bytes_per_access,unroll,store_hint for the register copy kernel (e.g. 32,8,0)")
     ap.add_argument("--flush-then-read", action="store_true", help="probe for small batches: after the L2 flush (a 256 MB write) read 256 MB, so L2 holds clean lines when the timed launch starts")
+    ap.add_argument("--heads-per-pair", type=int, default=None, help="probe (cfg5): pools of this many kv heads, e.g. 2 at N = 2 reproduces one pair's share of the N = 8 run")
     ap.add_argument("--no-flag", action="store_true", help="probe (--sweep, one GPU): enqueue without a completion flag")
     ap.add_argument("--small-tune", default=None, help="flag_mode,inline_list of tkv_plan_tune_small (e.g. 1,1 = flag from the kernel, list from device memory)")
     ap.add_argument("--push", action="store_true", help="N > 1: the prefill GPU's kernel stores into the decode pool (default for a same-dtype batch: the decode GPU pulls)")

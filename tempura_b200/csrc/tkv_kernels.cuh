@@ -234,20 +234,51 @@ template <int UNROLL, int HINT>
 __global__ void __launch_bounds__(256) handoff_copy_wide(const HandoffArgs a) {
     const uint32_t total = live_pairs(a) * a.n_layers * 2u;
     const uint32_t vec_per_row = a.src_row_bytes / 32u;
-    for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
-        const Chunk c = decode_chunk(a, w);
-        const uint32_t nvec = c.n_valid * vec_per_row;
-        for (uint32_t base = 0; base < nvec; base += 256u * UNROLL) {
-            Vec32 v[UNROLL];
+    const uint32_t vpc = a.block_size * vec_per_row;              // 32-byte vectors of a whole chunk
+    constexpr uint32_t PER_PASS = 256u * UNROLL;
+    // Measured over NVLink (pulled handoff, one CTA per SM): four 32-byte loads in flight per thread -- one 32 KiB chunk per
+    // pass -- fetch 786 GB/s; sixteen in flight, spread over four chunks, 763.  So a pass covers 32 KiB whatever the chunk size.
+    constexpr int UG = UNROLL < 4 ? UNROLL : 4;
+    constexpr uint32_t GROUP_PASS = 256u * UG;
+    if (vpc >= GROUP_PASS) {
+        for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
+            const Chunk c = decode_chunk(a, w);
+            const uint32_t nvec = c.n_valid * vec_per_row;
+            for (uint32_t base = 0; base < nvec; base += PER_PASS) {
+                Vec32 v[UNROLL];
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const uint32_t i = base + u * 256u + threadIdx.x;
-                if (i < nvec) v[u] = ld_stream32(c.src + (size_t)i * 32u);
+                for (int u = 0; u < UNROLL; u++) {
+                    const uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) v[u] = ld_stream32(c.src + (size_t)i * 32u);
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    const uint32_t i = base + u * 256u + threadIdx.x;
+                    if (i < nvec) st32<HINT>(c.dst + (size_t)i * 32u, v[u]);
+                }
+            }
+        }
+    } else {
+        // Chunks shorter than one pass (few kv heads per pool): a pass spans several chunks, so that a thread's loads in flight do
+        // not shrink with the chunk.
+        const uint32_t group = GROUP_PASS / vpc;                   // whole chunks per pass
+        for (uint64_t w0 = (uint64_t)blockIdx.x * group; w0 < total; w0 += (uint64_t)gridDim.x * group) {
+            Vec32 v[UG];
+#pragma unroll
+            for (int u = 0; u < UG; u++) {
+                const uint32_t q = u * 256u + threadIdx.x, off = q / vpc, i = q - off * vpc;
+                if (off < group && w0 + off < total) {
+                    const Chunk c = decode_chunk(a, (uint32_t)(w0 + off));
+                    if (i < c.n_valid * vec_per_row) v[u] = ld_stream32(c.src + (size_t)i * 32u);
+                }
             }
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const uint32_t i = base + u * 256u + threadIdx.x;
-                if (i < nvec) st32<HINT>(c.dst + (size_t)i * 32u, v[u]);
+            for (int u = 0; u < UG; u++) {
+                const uint32_t q = u * 256u + threadIdx.x, off = q / vpc, i = q - off * vpc;
+                if (off < group && w0 + off < total) {
+                    const Chunk c = decode_chunk(a, (uint32_t)(w0 + off));   // the list and the layer pointers are cache hits by now
+                    if (i < c.n_valid * vec_per_row) st32<HINT>(c.dst + (size_t)i * 32u, v[u]);
+                }
             }
         }
     }

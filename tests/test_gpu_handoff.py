@@ -79,6 +79,17 @@ def test_config2_shape_f16_copy_32_byte_accesses(H, unroll, hint):
     torch.cuda.synchronize()
     assert_pool_equals_host(dd, hd, f"32-byte copy unroll {unroll} hint {hint}")
     assert plan.stats().kernel_variant == N.VARIANT_WIDE
+    # two kv heads per pool (one pair's share of a batch split over four pairs): 8 KiB chunks, several per pass
+    w = W.Workload("two-heads", 3, 2, 128, 16, 256, 256, W.lengths(7, 1, 300, 5, 3), seed=6).build_tables()
+    hs, hd = host_pools(w)
+    ds, dd = to_device_pool(hs, "f16"), to_device_pool(hd, "f16")
+    oracle.handoff(hs, hd, oracle_batch(w), None, "copy")
+    plan = H.Plan(ds, dd, device_batch(w), None, N.PLAN_FORCE_VECTOR)
+    plan.tune_vector(32, unroll, hint)
+    plan.enqueue()
+    torch.cuda.synchronize()
+    assert_pool_equals_host(dd, hd, f"32-byte copy of 8 KiB chunks, unroll {unroll}")
+    assert plan.stats().kernel_variant == N.VARIANT_WIDE
 
 
 def test_config2_lengths_exact_multiple_and_single_token(H):
