@@ -499,10 +499,15 @@ typedef struct TkvPrefixIndexStats {
     uint64_t live_nodes, tombstones, capacity, ticks;
     uint32_t group_tokens;
     uint32_t table_full;          /* 1 once an insert found no free slot (nodes of that call are missing) */
+    uint64_t key_collisions;      /* walks that found their 64-bit key on a node whose first / last token id differ from
+                                     theirs: treated as a miss instead of adopting the other prefix's page             */
 } TkvPrefixIndexStats;
 #define TKV_PREFIX_NO_PAGE 0xFFFFFFFFu
 int32_t tkv_prefix_index_create(int32_t device, uint64_t capacity /* power of two */, uint32_t group_tokens, tkv_prefix_index** out);
 void tkv_prefix_index_destroy(tkv_prefix_index*);
+/* Test hook for the collision guard: cut the node keys to `bits` bits ([4, 64]) so that prefixes collide; only before the
+ * first insert / lookup.  Lookups then match less (a collision is a checked miss) but never return another prefix's page. */
+int32_t tkv_prefix_index_set_key_bits(tkv_prefix_index*, uint32_t bits);
 /* RadixTree::insert for every sequence of the batch */
 int32_t tkv_prefix_index_insert(tkv_prefix_index*, const TkvPrefixBatch*, void* stream);
 /* RadixTree::lookup: out_matched[s] = matched nodes of sequence s (times group_tokens = its prefix

@@ -64,7 +64,7 @@ class TkvPrefixBatch(C.Structure):
 
 class TkvPrefixIndexStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("hits", "tokens_saved", "live_nodes", "tombstones", "capacity", "ticks")] + [
-        ("group_tokens", C.c_uint32), ("table_full", C.c_uint32)]
+        ("group_tokens", C.c_uint32), ("table_full", C.c_uint32), ("key_collisions", C.c_uint64)]
 
 
 class TkvPageBatch(C.Structure):
@@ -194,6 +194,7 @@ SIGNATURES = {
     "tkv_prefix_index_release": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _vp]),
     "tkv_prefix_index_evict_lru": (_i32, [_vp, _u32, _u64, _u32, _u64, _u64, _vp]),
     "tkv_prefix_index_stats": (_i32, [_vp, _vp, C.POINTER(TkvPrefixIndexStats)]),
+    "tkv_prefix_index_set_key_bits": (_i32, [_vp, _u32]),
     "tkv_device_page_allocator_create": (_i32, [_i32, _u32, C.POINTER(_vp)]),
     "tkv_device_page_allocator_destroy": (None, [_vp]),
     "tkv_device_page_allocator_allocate": (_i32, [_vp, C.POINTER(TkvPageBatch), _u64, _vp]),

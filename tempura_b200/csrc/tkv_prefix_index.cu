@@ -8,8 +8,12 @@
 // node per KV block) and a node is named by a 64-bit key chained from the root:
 //     raw_i = raw_{i-1} * C + hash(tokens of element i)  (mod 2^64),   key_i = mix(raw_i),
 // linear so that all keys of a sequence come out of one parallel scan.  Equal keys mean equal
-// prefixes up to a 64-bit hash collision (the index does not store the tokens; two different
-// prefixes collide with probability ~2^-64 per pair; the hash is not hardened against chosen tokens).
+// prefixes up to a 64-bit hash collision (two different prefixes collide with probability ~2^-64 per
+// pair; the hash is not hardened against chosen tokens).  The index does not store whole prefixes, but
+// every node keeps the first and the last token id of its own element: a walk that finds its key on
+// a node whose guard differs treats the node as absent (a checked miss, counted) instead of adopting
+// another prompt's page.  What still gets through is a collision between prefixes whose colliding
+// elements also begin and end with the same token ids.
 //
 // Batch semantics: one call handles many sequences and is ONE tick of the reference's clock.  Its
 // result equals the reference's methods applied to the sequences in index order at that tick:
@@ -50,7 +54,7 @@ struct Meta {                   // 32 bytes per slot
 };
 
 struct Counters {               // device-side statistics and the eviction scratch
-    unsigned long long hits, tokens_saved, live, tombstones;
+    unsigned long long hits, tokens_saved, live, tombstones, collisions;
     uint32_t error;             // 1 = table full during an insert
     uint32_t evict_ctas_done;
 };
@@ -65,6 +69,8 @@ struct View {
     Meta* meta;
     Counters* ctr;
     Candidate* cand;            // one per eviction CTA
+    uint2* guard;               // per slot: first and last token id of the node's element
+    unsigned long long key_mask;   // all ones; fewer bits only to provoke collisions in tests
     uint32_t mask;              // capacity - 1
     uint32_t group;
 };
@@ -101,8 +107,8 @@ __device__ __forceinline__ unsigned long long element_hash(const uint32_t* tok, 
 // of the raw value (real keys are >= 2).
 constexpr unsigned long long CHAIN_MUL = 0xBF58476D1CE4E5B9ull, ROOT_RAW = 0x243F6A8885A308D3ull;
 
-__device__ __forceinline__ unsigned long long key_of_raw(unsigned long long raw) {
-    const unsigned long long k = mix64(raw ^ 0x632BE59BD9B4E019ull);
+__device__ __forceinline__ unsigned long long key_of_raw(unsigned long long raw, unsigned long long key_mask) {
+    const unsigned long long k = mix64(raw ^ 0x632BE59BD9B4E019ull) & key_mask;
     return k < 2 ? k + 2 : k;
 }
 
@@ -194,7 +200,8 @@ __global__ void __launch_bounds__(WALK_THREADS) prefix_walk(View ix, Batch b, un
         for (uint32_t wv = 0; wv < warp; wv++) before = then(before, warp_total[wv]);
         f = then(before, f);
         const unsigned long long raw = carry_raw * f.a + f.b;
-        const unsigned long long key = key_of_raw(raw);
+        const unsigned long long key = key_of_raw(raw, ix.key_mask);
+        const uint2 guard = active ? make_uint2(__ldg(row + (size_t)i * ix.group), __ldg(row + (size_t)i * ix.group + ix.group - 1u)) : make_uint2(0u, 0u);
         __syncthreads();                                   // everyone has read carry_raw
         if (tid == WALK_THREADS - 1) carry_raw = raw;
         // ---- the table ----
@@ -221,7 +228,31 @@ __global__ void __launch_bounds__(WALK_THREADS) prefix_walk(View ix, Batch b, un
             __syncthreads();
             if (tid == WALK_THREADS - 1) parent_carry = slot;
         } else {
-            const uint32_t slot = active ? find_slot(ix, key) : NO_SLOT;
+            uint32_t slot = active ? find_slot(ix, key) : NO_SLOT;
+            if (OP == OP_INSERT_PAGES) {
+                // The node belongs to the sequence whose creation order the claim pass left on it (the lowest-numbered one
+                // that walked the key in this call): that one writes the page and the guard.  Nobody reads a guard here,
+                // so none is read while it is being written.
+                if (slot != NO_SLOT) {
+                    Meta& m = ix.meta[slot];
+                    const unsigned long long order = (tick << (ORDER_SEQ_BITS + ORDER_DEPTH_BITS)) |
+                                                     ((unsigned long long)seq << ORDER_DEPTH_BITS) | min(i, (1u << ORDER_DEPTH_BITS) - 1u);
+                    if (m.order == order) {
+                        const uint32_t n_pages = b.pages ? (b.page_lens ? min(b.page_lens[seq], b.page_stride) : b.page_stride) : 0u;
+                        m.page = i < n_pages ? b.pages[(size_t)seq * b.page_stride + i] : NO_PAGE;
+                        ix.guard[slot] = guard;
+                    }
+                }
+                __syncthreads();
+                continue;
+            }
+            if (slot != NO_SLOT) {
+                const uint2 g = ix.guard[slot];
+                if (g.x != guard.x || g.y != guard.y) {    // the key of another prefix: not this sequence's node
+                    slot = NO_SLOT;
+                    atomicAdd(&ix.ctr->collisions, 1ull);
+                }
+            }
             if (slot == NO_SLOT) atomicMin(&first_miss, tid);
             __syncthreads();
             const uint32_t run = first_miss;               // matched nodes of this pass, from its start
@@ -231,15 +262,8 @@ __global__ void __launch_bounds__(WALK_THREADS) prefix_walk(View ix, Batch b, un
                     atomicAdd(&m.refs, 1);
                     atomicMax(&m.stamp, tick);
                     if (out_pages && i < out_stride) out_pages[(size_t)seq * out_stride + i] = m.page;
-                } else if (OP == OP_RELEASE) {
+                } else {                                                           // OP_RELEASE
                     if (atomicAdd(&m.refs, -1) <= 0) atomicAdd(&m.refs, 1);       // never below zero
-                } else {                                                           // OP_INSERT_PAGES: the creator writes its page
-                    const unsigned long long order = (tick << (ORDER_SEQ_BITS + ORDER_DEPTH_BITS)) |
-                                                     ((unsigned long long)seq << ORDER_DEPTH_BITS) | min(i, (1u << ORDER_DEPTH_BITS) - 1u);
-                    if (m.order == order) {
-                        const uint32_t n_pages = b.pages ? (b.page_lens ? min(b.page_lens[seq], b.page_stride) : b.page_stride) : 0u;
-                        m.page = i < n_pages ? b.pages[(size_t)seq * b.page_stride + i] : NO_PAGE;
-                    }
                 }
             }
             matched += run;
@@ -500,7 +524,9 @@ int32_t tkv_prefix_index_create(int32_t device, uint64_t capacity, uint32_t grou
     if (e == cudaSuccess) e = cudaMalloc(&ix->view.meta, capacity * sizeof(Meta));
     if (e == cudaSuccess) e = cudaMalloc(&ix->view.ctr, sizeof(Counters));
     if (e == cudaSuccess) e = cudaMalloc(&ix->view.cand, (size_t)ix->evict_ctas * sizeof(Candidate));
+    if (e == cudaSuccess) e = cudaMalloc(&ix->view.guard, capacity * sizeof(uint2));
     if (e == cudaSuccess) {
+        ix->view.key_mask = ~0ull;
         ix->view.mask = (uint32_t)(capacity - 1);
         ix->view.group = group_tokens;
         prefix_index_clear<<<std::max(sms, 1) * 2, 256>>>(ix->view);
@@ -522,7 +548,18 @@ void tkv_prefix_index_destroy(tkv_prefix_index* ix) {
     cudaFree(ix->view.meta);
     cudaFree(ix->view.ctr);
     cudaFree(ix->view.cand);
+    cudaFree(ix->view.guard);
     delete ix;
+}
+
+// Test hook for the collision guard: keys are cut to `bits` bits, so that different prefixes share keys often.  Only on an
+// index that holds nothing yet.
+int32_t tkv_prefix_index_set_key_bits(tkv_prefix_index* ix, uint32_t bits) {
+    if (!ix) return fail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (bits < 4 || bits > 64) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: key bits must be in [4, 64]");
+    if (ix->tick) return fail(TKV_ERR_INVALID_CONFIG, "prefix index: key bits can only be set before the first call that walks the index");
+    ix->view.key_mask = bits == 64 ? ~0ull : ((1ull << bits) - 1ull);
+    return TKV_OK;
 }
 
 int32_t tkv_prefix_index_insert(tkv_prefix_index* ix, const TkvPrefixBatch* batch, void* stream) {
@@ -605,6 +642,7 @@ int32_t tkv_prefix_index_stats(tkv_prefix_index* ix, void* stream, TkvPrefixInde
     out->ticks = ix->tick;
     out->group_tokens = ix->group;
     out->table_full = c.error;
+    out->key_collisions = c.collisions;
     return TKV_OK;
 }
 

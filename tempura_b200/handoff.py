@@ -512,6 +512,10 @@ class PrefixIndex:
         n_pages, n_nodes = (int(x) for x in counts.cpu())
         return pages[:n_pages].cpu().tolist(), n_nodes
 
+    def set_key_bits(self, bits: int) -> None:
+        """Test hook: cut the keys to ``bits`` bits so that prefixes collide (the guard must then turn them into misses)."""
+        check(lib().tkv_prefix_index_set_key_bits(self._h, bits))
+
     def stats(self, stream=None) -> N.TkvPrefixIndexStats:
         st = N.TkvPrefixIndexStats()
         check(lib().tkv_prefix_index_stats(self._h, self._stream(stream), C.byref(st)))

@@ -244,3 +244,41 @@ def test_device_page_allocator_matches_the_reference_stack(H):
     big = torch.zeros((1, total + 8), dtype=torch.int32, device="cuda")
     dev_alloc.free(big, torch.tensor([total - before + 1], dtype=torch.int32).cuda())
     assert int(dev_alloc.status.item()) == N.ERR_INVALID_CONFIG and dev_alloc.available() == before
+
+
+@pytest.mark.parametrize("bits", [64, 9])
+def test_a_key_collision_is_a_checked_miss_not_another_prompts_page(H, bits):
+    """The index keeps no whole prefixes, only 64-bit keys plus the first and last token id of each node's element.  With the
+    keys cut to 9 bits (test hook) different prefixes share keys all the time: a lookup may then match less than the
+    reference would, but every page it returns is the page inserted for exactly that prefix."""
+    rng = np.random.default_rng(5)
+    group = 4
+    seqs = [list(map(int, rng.integers(1, 50_000, size=int(rng.integers(2, 12)) * group))) for _ in range(120)]
+    for s in range(0, 120, 5):                                     # some share a stem
+        seqs[s + 1][: 2 * group] = seqs[s][: 2 * group]
+    pages, owner, nxt = [], {}, 0
+    for s in seqs:                                                 # the page of a node = what its first inserter brought
+        row = []
+        for i in range(len(s) // group):
+            row.append(nxt)
+            owner.setdefault(tuple(s[: (i + 1) * group]), nxt)
+            nxt += 1
+        pages.append(row)
+    ix = H.PrefixIndex(0, 8192, group_tokens=group)
+    if bits != 64:
+        ix.set_key_bits(bits)
+    ix.insert(*dev(seqs, pages))
+    got = lookup(ix, seqs)
+    short = 0
+    for s, (matched, pg) in zip(seqs, got):
+        assert matched <= len(s) // group
+        short += matched < len(s) // group
+        for i in range(matched):
+            assert pg[i] == owner[tuple(s[: (i + 1) * group])], (i, pg[i])
+    st = ix.stats()
+    if bits == 64:
+        assert short == 0 and st.key_collisions == 0
+    else:
+        assert short > 0 and st.key_collisions > 0                 # collisions happened, and each was refused
+    with pytest.raises(N.TkvError):
+        ix.set_key_bits(32)                                        # not on an index that has been walked
