@@ -35,7 +35,7 @@ METRIC = "kv_handoff_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch divided by the algorithmic bytes of
 # the same launch, from the ncu captures summarised under profiles/ (None until captured).
-NCU_TRAFFIC_RATIO = {"handoff_copy_bulk": 0.961, "handoff_copy_vec": 0.954, "handoff_f16_e4m3_warp": 0.942,
+NCU_TRAFFIC_RATIO = {"handoff_copy_bulk": 0.979, "handoff_copy_vec": 0.954, "handoff_f16_e4m3_warp": 0.942,
                      "handoff_f16_e4m3_staged": 0.964}
 
 
