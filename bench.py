@@ -1091,6 +1091,84 @@ def run_attention(args):
 
 
 
+def run_prefill_attention(args):
+    """--workload prefill: causal attention of one prompt's tokens over its own paged cache, one layer per launch, on the
+    tcgen05 kernel (tkv_prefill_attn_enqueue): --prefill-tokens T new tokens after --prefill-start cached ones, the
+    Llama-3.1-8B shape (32 query heads on 8 kv heads of 128 dims), E4M3 + scales pool filled by a handoff (or the F16
+    pool with --attn-f16).  FLOPs counted: 4 * head_dim * query heads * sum over query tokens of the positions each
+    attends to (both contractions, causal); the tensor-core work the kernel adds for its operand terms is not counted."""
+    import torch
+    from tempura_b200 import handoff as H
+    from tempura_b200 import workloads as W
+    torch.cuda.set_device(0)
+    t, start = args.prefill_tokens, args.prefill_start
+    total = start + t
+    layers = args.layers or 4
+    fp8 = not args.attn_f16
+    blocks = (total + 15) // 16 + 8
+    w = W.Workload("llama3.1-8b-prefill", layers, 8, 128, 16, blocks, blocks, np.array([total], dtype=np.uint32),
+                   dst_dtype="e4m3" if fp8 else "f16", seed=9).build_tables()
+    src = H.Pool.allocate(0, layers, 8, 128, 16, w.src_blocks, "f16")
+    fill_source(src, w, 78)
+    if fp8:
+        pool = H.Pool.allocate(0, layers, 8, 128, 16, w.dst_blocks, "e4m3", scales=True, fill_byte=0x5A)
+        H.Plan(src, pool, H.Batch(w.seq_lens, w.src_tables, w.dst_tables, w.table_stride)).enqueue()
+        row_np = w.dst_tables[0]
+    else:
+        pool, row_np = src, w.src_tables[0]
+    row = torch.from_numpy(row_np.astype(np.int64)).to(torch.int32).cuda()
+    q = torch.randn((t, 32, 128), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+    outs = [H.prefill_attention(pool, l, q, row, start, status=status) for l in range(layers)]     # plain launches first
+    torch.cuda.synchronize()
+    if int(status.item()):
+        raise SystemExit(f"prefill attention reported status {int(status.item())}")
+    # parity inside the run: a sample of query tokens against the decode kernel's mma.sync path (an independent kernel)
+    pick = sorted({0, t // 3, t - 1})
+    tabs = row.reshape(1, -1).expand(len(pick), -1).contiguous()
+    lens = torch.tensor([start + i + 1 for i in pick], dtype=torch.int32, device="cuda")
+    ref = H.decode_attention(pool, layers - 1, q[pick].contiguous(), tabs, lens, max_kv_len=total, flags=2)
+    err = float((outs[-1][pick] - ref).abs().max())
+    scale = float(ref.abs().max())
+    if not err <= 4e-3 * max(scale, 1.0):
+        raise SystemExit(f"prefill attention differs from the decode kernel on sampled tokens: max err {err:.3e}")
+    def step():
+        for l in range(layers):
+            H.prefill_attention(pool, l, q, row, start)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler.mark()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    sampler.mark()
+    clocks = sampler.stop()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    attended = t * start + t * (t + 1) // 2
+    flops = 4.0 * 128 * 32 * attended * layers
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak_tf, kind = (float(json.load(open(path))["bf16_tflops"]), "measured") if os.path.exists(path) else (1590.0, "fallback")
+    achieved = flops / (ms * 1e-3) / 1e12
+    es = 1 if fp8 else 2
+    print(json.dumps({
+        "metric": "paged_prefill_attention_TFLOPs", "value": round(achieved, 1), "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 5), "us_per_layer": round(ms * 1e3 / layers, 2), "higher_is_better": True,
+        "dtype": "e4m3 x e4m3 / e5m2 x e4m3 tcgen05.mma, f32 accumulate in tensor memory" if fp8 else "f16 tcgen05.mma, f32 accumulate in tensor memory",
+        "data": "synthetic",
+        "config": {"workload": w.name + ("-e4m3" if fp8 else "-f16"), "layers": layers, "kv_heads": 8, "q_heads": 32, "head_dim": 128,
+                   "new_tokens": t, "cached_before": start, "l2": "K/V of one layer (%d MB) is re-read by every group of 32 query tokens, mostly from L2" % (total * 8 * 128 * 2 * es >> 20)},
+        "parity": {"sampled_tokens": pick, "max_abs_err_vs_mma_sync_decode_kernel": err, "max_abs_value": scale},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4),
+                     "traffic": None, "peak_source": f"{kind} cuBLAS bf16 burst peak (the kernel's FP8 MMAs run at twice that rate but it issues 2.5 times the counted work: two q terms, three probability terms)" if fp8 else f"{kind} cuBLAS bf16 burst peak"},
+        "gpu_launches": (args.warmup + args.steps) * layers, "clocks": clocks}), flush=True)
+
+
 def bench_prefix_index(args) -> None:
     """--workload prefix: the device-resident prefix index on the shared-prefix benchmark shape (64 prompts x
     8 192 tokens with a common 2 048-token prefix, one node per 16-token block).  A step is one lookup of the
@@ -1262,7 +1340,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefix", "admit"])
+    ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefill", "prefix", "admit"])
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="--workload prefill: new tokens of the prompt")
+    ap.add_argument("--prefill-start", type=int, default=0, help="--workload prefill: tokens already cached before them")
     ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")
     ap.add_argument("--attn-seqs", type=int, default=None, help="--workload attn: this many prompts instead of the configuration's 16")
@@ -1299,6 +1379,8 @@ def main():
         return bench_prefix_index(args)
     if args.workload == "admit":
         return bench_admission(args)
+    if args.workload == "prefill":
+        return run_prefill_attention(args)
     if args.workload == "attn":
         run_attention(args)
     elif args.impl == "reference":

@@ -383,6 +383,26 @@ enum { TKV_ATTN_DEFAULT = 0,
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens /* 0 = default */);
 int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* args, void* stream);
+
+/* The prefill-side twin: causal attention of n_tokens NEW tokens of ONE sequence over its paged cache, their K/V rows
+ * already written at positions start_pos .. start_pos + n_tokens - 1; query token t attends to positions
+ * 0 .. start_pos + t (paged_flash_attention, kernels/src/attention.rs:486-590, with a causal bound per query token; the
+ * reference's kernel for the FP8 pool, cutile_flash_attn_heads_paged_e4m3, kernels/src/cutile_flash_attention.rs:868, reads
+ * unscaled bytes, this one applies the per-(layer, block, kv-head) scales).  Runs on the tcgen05 tensor cores; built for
+ * the benchmark's geometry only: 8 kv heads of 128 dims, 32 query heads, 16-token blocks, F16 or E4M3 pool
+ * (TKV_ERR_DIMENSION_MISMATCH otherwise).  All pointers are device memory of pool->device.                          */
+typedef struct TkvPrefillAttn {
+    uint32_t n_tokens, n_q_heads, layer, start_pos;
+    uint32_t table_len;           /* entries of `table`; at least ceil((start_pos + n_tokens) / 16) */
+    float sm_scale;               /* usually 1 / sqrt(head_dim)                                     */
+    uint32_t flags, reserved;     /* 0                                                              */
+    uint64_t q;                   /* f32 [n_tokens][n_q_heads][128]                                 */
+    uint64_t out;                 /* f32, same shape                                                */
+    uint64_t table;               /* u32 [table_len] block ids of the sequence                      */
+    uint64_t status;              /* 0, or a device u32 (zero it before the launch): TKV_ERR_TIMEOUT if a bounded wait gave
+                                     up, TKV_ERR_INVALID_CONFIG if a table entry named a block outside the pool      */
+} TkvPrefillAttn;
+int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefillAttn* args, void* stream);
 /* Device self-check of the tcgen05 path's operand plumbing (tensor-map copy with the 128-byte swizzle,
  * shared-memory and instruction descriptors, tensor-memory reads) on operands of small dyadic values whose
  * products and sums are exact: mismatches[0..3] count wrong accumulators for E4M3 K-major, E4M3 x E5M2

@@ -9,6 +9,7 @@ const SOURCES: &[&str] = &[
     "tkv_noalloc.cu",
     "tkv_attention.cu",
     "tkv_attention_tc.cu",
+    "tkv_prefill_tc.cu",
     "tkv_prefix_index.cu",
     "tkv_hostobj.cpp",
     "tkv_session.cpp",
@@ -37,6 +38,7 @@ fn main() {
     }
     println!("cargo:rerun-if-changed={}", csrc.join("tkv_kernels.cuh").display());
     println!("cargo:rerun-if-changed={}", csrc.join("tkv_attention_tc.h").display());
+    println!("cargo:rerun-if-changed={}", csrc.join("tkv_tc_common.cuh").display());
     println!("cargo:rerun-if-changed={}", root.join("include").join("tkv.h").display());
     let status = cmd.status().expect("nvcc not found: set NVCC or put it on PATH");
     assert!(status.success(), "nvcc failed to build libtkv.so");

@@ -9,8 +9,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libtkv.so")
-SOURCES = ["tkv_lib.cu", "tkv_noalloc.cu", "tkv_attention.cu", "tkv_attention_tc.cu", "tkv_prefix_index.cu", "tkv_hostobj.cpp", "tkv_session.cpp", "tkv_coordinator.cpp"]
-HEADERS = ["tkv_kernels.cuh", "tkv_attention_tc.h", os.path.join("..", "..", "include", "tkv.h")]
+SOURCES = ["tkv_lib.cu", "tkv_noalloc.cu", "tkv_attention.cu", "tkv_attention_tc.cu", "tkv_prefill_tc.cu", "tkv_prefix_index.cu", "tkv_hostobj.cpp", "tkv_session.cpp", "tkv_coordinator.cpp"]
+HEADERS = ["tkv_kernels.cuh", "tkv_attention_tc.h", "tkv_tc_common.cuh", os.path.join("..", "..", "include", "tkv.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

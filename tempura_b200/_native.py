@@ -57,6 +57,11 @@ class TkvDecodeAttn(C.Structure):
         ("sm_scale", C.c_float), ("split_tokens", C.c_uint32), ("flags", C.c_uint32)] + [(n, C.c_uint64) for n in ("q", "out", "tables", "kv_lens", "scratch", "scratch_bytes", "total_kv_tokens", "status")]
 
 
+class TkvPrefillAttn(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_tokens", "n_q_heads", "layer", "start_pos", "table_len")] + [("sm_scale", C.c_float)] + [
+        (n, C.c_uint32) for n in ("flags", "reserved")] + [(n, C.c_uint64) for n in ("q", "out", "table", "status")]
+
+
 class TkvPrefixBatch(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_seqs", "stride", "page_stride", "reserved")] + [
         (n, C.c_uint64) for n in ("tokens", "lens", "pages", "page_lens")]
@@ -193,6 +198,7 @@ SIGNATURES = {
     "tkv_prefix_index_lookup": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _u64, _u32, _u64, _vp]),
     "tkv_prefix_index_release": (_i32, [_vp, C.POINTER(TkvPrefixBatch), _vp]),
     "tkv_prefix_index_evict_lru": (_i32, [_vp, _u32, _u64, _u32, _u64, _u64, _vp]),
+    "tkv_prefill_attn_enqueue": (_i32, [C.POINTER(TkvPool), C.POINTER(TkvPrefillAttn), _vp]),
     "tkv_prefix_index_stats": (_i32, [_vp, _vp, C.POINTER(TkvPrefixIndexStats)]),
     "tkv_prefix_index_set_key_bits": (_i32, [_vp, _u32]),
     "tkv_device_page_allocator_create": (_i32, [_i32, _u32, C.POINTER(_vp)]),

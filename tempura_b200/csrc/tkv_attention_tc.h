@@ -27,4 +27,18 @@ cudaError_t launch(bool fp8, uint32_t group, uint64_t k_layer, uint64_t v_layer,
 // out[0..3] = mismatches of {E4M3 K-major, E4M3 x E5M2 MN-major, F16 K-major, F16 MN-major}
 cudaError_t selfcheck(uint64_t out[4]);
 
+// ---- prefill side: causal attention of a chunk of new tokens of one sequence (tkv_prefill_tc.cu) ----
+struct PrefillArgs {
+    const float* k_scales;        // [total_blocks][8] of this layer, or null
+    const float* v_scales;
+    const float* q;               // [n_tokens][n_q_heads][128]
+    float* out;                   // same shape
+    const uint32_t* table;        // the sequence's block ids, at least ceil((start_pos + n_tokens) / 16) of them
+    uint32_t n_tokens, start_pos, n_q_heads, total_blocks;
+    float q_scale;                // softmax scale * log2(e)
+    uint32_t* status;             // optional device word: first failure wins
+};
+bool prefill_eligible(uint32_t n_kv_heads, uint32_t n_q_heads, uint32_t head_dim, uint32_t block_size, uint32_t total_blocks);
+cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const PrefillArgs& a, cudaStream_t st);
+
 }  // namespace tkv_tc

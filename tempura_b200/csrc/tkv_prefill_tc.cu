@@ -1,0 +1,555 @@
+// Causal attention of a chunk of new tokens of one sequence over the paged pool, on the fifth-generation tensor
+// cores (tcgen05, sm_100a): the prefill-side twin of the decode kernel, scale-aware for an E4M3 pool.
+//
+// What is computed is paged_flash_attention (kernels/src/attention.rs:486-590) for query tokens at positions
+// start_pos .. start_pos + T - 1, token t attending to positions 0 .. start_pos + t, over the widened pool values
+// (the reference's paged prefill kernel for the FP8 pool, cutile_flash_attn_heads_paged_e4m3,
+// kernels/src/cutile_flash_attention.rs:868, reads unscaled bytes; here every (block, kv head) carries its scale).
+//
+// One CTA owns one kv head and 32 consecutive query tokens: with four query heads per kv head that is 128 rows, row
+// r = (query head r / 32, token r % 32).  It walks the cached tokens 128 at a time (eight pool blocks).  Per tile
+//
+//     S[128 rows][128 tokens] = Q . K_tile^T     (tcgen05.mma, M = N = 128; K_tile = eight [16 tokens][128 B] tensor-map boxes of this kv head)
+//     O[128 rows][128 dims]  += P . V_tile       (P written by the softmax threads, V read MN-major from the same kind of tile)
+//
+// with S double-buffered and O resident in tensor memory.  A softmax thread owns one row and one tensor-memory
+// lane: the running maximum, the row sum and the rescale of O on a raised maximum are all thread-local (the rescale is
+// taken lazily, when a tile exceeds the maximum in use by 2^6).  Operand precision as in the decode kernel: an F16 pool
+// takes F16 q and probabilities; an E4M3 pool takes q as two E4M3 terms under a per-row power-of-two scale and the
+// probabilities as three E5M2 terms (all terms accumulate into the same accumulator here, since they differ in the A
+// operand only).  The block scales: K's multiplies the scores of its 16 columns; V's multiplies the probabilities of
+// its 16 columns, normalised by a power of two that bounds every V scale of the sequence (found by a pass over the
+// scales before the first tile) so that the scaled probabilities stay inside the E5M2 range whatever the scales are.
+//
+// Every wait is bounded; a CTA that gives up reports through `status`, waits for its copies and frees its tensor memory.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <stdint.h>
+
+#include <algorithm>
+#include <cmath>
+#include <mutex>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/tkv.h"
+#include "tkv_attention_tc.h"
+#include "tkv_tc_common.cuh"
+
+namespace tkv_internal {
+int32_t set_error(int32_t code, int32_t cuda_code, const char* text);
+}
+
+namespace tkv_tc {
+
+namespace {
+
+constexpr int PD = 128, PBS = 16, PHKV = 8, PG = 4;
+constexpr int QT = 32;                         // query tokens per CTA: QT * PG = 128 rows
+constexpr int KT = 128;                        // cached tokens per tile = 8 blocks
+constexpr int PTILE = 128 * 128;               // bytes of one [128 rows][128 B] swizzled tile
+constexpr float P_RAISE = 6.0f, P_SHIFT = 9.0f;
+
+struct PControl {
+    uint64_t kv_full[2], kv_empty[2];          // K and V of a tile landed / its PV MMAs are done
+    uint64_t s_full[2], s_free[2];             // S buffers: QK done / all four softmax warps have read it
+    uint64_t p_full, pv_done, q_ready, drained;
+    uint32_t tmem_base, fail, pad[2];
+    float scales[2][16];                       // per stage: 8 K scales, 8 V scales (normalised) of the tile's blocks
+    float vmax_part[4];
+};
+static_assert(sizeof(PControl) <= 1024, "control block");
+
+template <bool FP8>
+__global__ void __launch_bounds__(192, 1)
+prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
+    constexpr int ES = FP8 ? 1 : 2;
+    constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;
+    constexpr int KV_TILE = PTILE * ES;                     // K (or V) of one tile of 128 tokens
+    constexpr int Q_BYTES = FP8 ? QTERMS * PTILE : 2 * PTILE, P_BYTES = FP8 ? PT * PTILE : 2 * PTILE;
+    constexpr int KSTEPS = 4 * ES;
+    constexpr uint32_t IDESC_QK = instr_desc2(0u, 0u, 0u, 0u, 128u);
+    constexpr uint32_t IDESC_PV = instr_desc2(FP8 ? 1u : 0u, 0u, 0u, 1u, 128u);      // A = P (E5M2 / F16, K-major), B = V (MN-major)
+    constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+    constexpr uint64_t DESC_K = DESC_HI | ((uint64_t)1u << 16);
+    constexpr uint64_t DESC_V = DESC_HI | ((uint64_t)(PTILE >> 4) << 16);              // MN-major: the second 64-dim column group one tile further
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t kvh = blockIdx.y;
+    const uint32_t q0 = (gridDim.x - 1u - blockIdx.x) * QT;                           // the longest rows first
+    const uint32_t rows_tokens = min((uint32_t)QT, a.n_tokens - q0);
+    const uint32_t kv_limit = a.start_pos + q0 + rows_tokens;                         // tokens the last row of this CTA attends to
+    const uint32_t n_tiles = (kv_limit + KT - 1) / KT, n_blocks = (kv_limit + PBS - 1) / PBS;
+
+    extern __shared__ __align__(1024) unsigned char smem[];
+    PControl* c = reinterpret_cast<PControl*>(smem);
+    unsigned char* q_tile = smem + 1024;
+    unsigned char* p_tile = q_tile + Q_BYTES;
+    unsigned char* k_ring = p_tile + P_BYTES;               // 2 stages of K, then 2 stages of V
+    unsigned char* v_ring = k_ring + 2 * KV_TILE;
+    const volatile uint32_t* fail_word = &c->fail;
+
+    if (tid == 0) {
+        for (int s = 0; s < 2; s++) {
+            mbar_init(c->kv_full + s, 1);
+            mbar_init(c->kv_empty + s, 1);
+            mbar_init(c->s_full + s, 1);
+            mbar_init(c->s_free + s, 4);
+        }
+        mbar_init(&c->p_full, 4);
+        mbar_init(&c->pv_done, 1);
+        mbar_init(&c->q_ready, 4);
+        mbar_init(&c->drained, 1);
+        c->fail = (smem_u32(smem) & 1023u) ? 2u : 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&c->tmem_base)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // the largest V scale among the blocks this CTA will read, as a power of two (1 for an unscaled pool)
+    float vmax = 0.0f;
+    if (warp < 4 && a.v_scales) {
+        for (uint32_t b = tid; b < n_blocks; b += 128) {
+            const uint32_t blk = a.table[b];
+            if (blk < a.total_blocks) vmax = fmaxf(vmax, a.v_scales[(size_t)blk * PHKV + kvh]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xFFFFFFFFu, vmax, o));
+        if (lane == 0) c->vmax_part[warp] = vmax;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = c->tmem_base;
+    int v_exp = 0;                                                         // V scales are used as vs * 2^-v_exp <= 1
+    if (a.v_scales) {
+        const float m = fmaxf(fmaxf(c->vmax_part[0], c->vmax_part[1]), fmaxf(c->vmax_part[2], c->vmax_part[3]));
+        if (m > 0.0f && m < INFINITY) v_exp = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 126;   // 2^(v_exp - 1) <= m < 2^v_exp
+        v_exp = max(-100, min(100, v_exp));
+    }
+    const float v_down = __uint_as_float((uint32_t)(127 - v_exp) << 23);
+
+    if (warp == 4) {
+        // ---- producer: the tile's blocks, one lane per block: K and V boxes of this kv head, the block's two scales ----
+        bool ok = c->fail == 0;
+        uint32_t why = 4u, issued = 0;
+        for (uint32_t j = 0; j < n_tiles && ok; j++) {
+            const uint32_t st = j & 1u, nb = min(8u, n_blocks - j * 8u);
+            uint32_t blk = 0;
+            if (lane < nb) {
+                blk = a.table[j * 8u + lane];
+                if (blk >= a.total_blocks) {                 // a stale or foreign id is never turned into an address
+                    ok = false;
+                    why = 2u;
+                }
+            }
+            if (__any_sync(0xFFFFFFFFu, why == 2u)) why = 2u;      // whichever lane met the bad id, lane 0 reports it
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (ok && lane == 0 && j >= 2) ok = mbar_wait(c->kv_empty + st, ((j >> 1) - 1u) & 1u, fail_word);
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
+            if (!ok) break;
+            if (lane < 8) {
+                float ks = 1.0f, vs = 1.0f;
+                if (lane < nb && a.k_scales) {
+                    ks = a.k_scales[(size_t)blk * PHKV + kvh];
+                    vs = a.v_scales[(size_t)blk * PHKV + kvh] * v_down;
+                }
+                c->scales[st][lane] = ks;
+                c->scales[st][8 + lane] = vs;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(c->kv_full + st, nb * 2u * (PBS * 128u) * ES);
+            __syncwarp();
+            if (lane < nb) {
+                const uint32_t kd = smem_u32(k_ring + (size_t)st * KV_TILE) + lane * (PBS * 128u);
+                const uint32_t vd = smem_u32(v_ring + (size_t)st * KV_TILE) + lane * (PBS * 128u);
+#pragma unroll
+                for (int cg = 0; cg < ES; cg++) {
+                    tma_head_rows(kd + cg * PTILE, &map_k, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->kv_full + st);
+                    tma_head_rows(vd + cg * PTILE, &map_v, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->kv_full + st);
+                }
+            }
+            issued = j + 1;
+        }
+        if (!ok && lane == 0) {
+            atomicCAS(&c->fail, 0u, why);
+            for (uint32_t j = issued > 2 ? issued - 2 : 0u; j < issued; j++)       // copies still in flight get a bounded chance to land
+                for (uint32_t it = 0; it < (1u << 20); it++)
+                    if (mbar_test(c->kv_full + (j & 1u), (j >> 1) & 1u)) break;
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer: QK of tile j, then PV of tile j - 1, so the softmax of a tile overlaps the next tile's scores ----
+        if (lane == 0) {
+            const uint32_t q_lo = smem_u32(q_tile) >> 4, p_lo = smem_u32(p_tile) >> 4;
+            const uint32_t kr_lo = smem_u32(k_ring) >> 4, vr_lo = smem_u32(v_ring) >> 4;
+            bool ok = c->fail == 0 && mbar_wait(&c->q_ready, 0u, fail_word);
+            auto pv = [&](uint32_t j) {
+                ok = mbar_wait(&c->p_full, j & 1u, fail_word);
+                if (!ok) return;
+                tc_fence_after();
+                const uint32_t v_lo = vr_lo + (j & 1u) * (KV_TILE >> 4);
+#pragma unroll
+                for (int term = 0; term < PT; term++)
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ks++)
+                        mma<FP8>(tmem + 256u,
+                                 DESC_K | (p_lo + (FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2)),
+                                 DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), IDESC_PV, (j > 0 || term > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(&c->pv_done);
+                tc_commit(c->kv_empty + (j & 1u));
+            };
+            for (uint32_t j = 0; j < n_tiles && ok; j++) {
+                const uint32_t st = j & 1u;
+                ok = mbar_wait(c->kv_full + st, (j >> 1) & 1u, fail_word);
+                if (ok && j >= 2) ok = mbar_wait(c->s_free + st, ((j >> 1) - 1u) & 1u, fail_word);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4);
+#pragma unroll
+                for (int term = 0; term < QTERMS; term++)
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ks++) {
+                        const uint32_t a_off = FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                        const uint32_t b_off = (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                        mma<FP8>(tmem + st * 128u, DESC_K | (q_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                    }
+                tc_commit(c->s_full + st);
+                if (j > 0) pv(j - 1);
+            }
+            if (ok && n_tiles) pv(n_tiles - 1);
+            if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            tc_commit(&c->drained);
+            for (uint32_t it = 0; it < (1u << 22); it++)
+                if (mbar_test(&c->drained, 0u)) break;
+        }
+        __syncwarp();
+    } else {
+        // ---- softmax: thread r owns row r = (query head r / 32, token r % 32) and tensor-memory lane r ----
+        const uint32_t r = tid, g = r >> 5, tq = r & 31u;
+        const bool row_live = tq < rows_tokens;
+        const uint32_t q_pos = a.start_pos + q0 + (row_live ? tq : 0u);
+        const uint32_t lane_base = (warp * 32u) << 16;
+        float q_inv = 1.0f;
+        {
+            // Q row: scaled into the log2 domain; E4M3 pool: two E4M3 terms under a power-of-two scale that brings the row's largest
+            // element into [128, 256)
+            const float* qrow = a.q + ((size_t)(q0 + (row_live ? tq : 0u)) * a.n_q_heads + kvh * PG + g) * PD;
+            float up = a.q_scale;
+            if (FP8) {
+                float amax = 0.0f;
+                for (int i = 0; i < PD / 4; i++) {
+                    const float4 f = __ldg(reinterpret_cast<const float4*>(qrow) + i);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+                }
+                amax *= fabsf(a.q_scale);
+                int e = 0;
+                if (amax > 0.0f && amax < INFINITY) e = 7 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
+                e = max(-60, min(60, e));
+                up = a.q_scale * __uint_as_float((uint32_t)(127 + e) << 23);
+                q_inv = __uint_as_float((uint32_t)(127 - e) << 23);
+            }
+            if (!row_live) up = 0.0f;
+#pragma unroll
+            for (int ch = 0; ch < PD / 16; ch++) {                  // 16 dims at a time
+                float x[16];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 f = __ldg(reinterpret_cast<const float4*>(qrow) + ch * 4 + i);
+                    x[4 * i] = f.x * up;
+                    x[4 * i + 1] = f.y * up;
+                    x[4 * i + 2] = f.z * up;
+                    x[4 * i + 3] = f.w * up;
+                }
+                if (FP8) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int wd = 0; wd < 4; wd++) {
+                        hi[wd] = lo[wd] = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            const float v = x[wd * 4 + b];
+                            const uint32_t h = e4m3_of(v);
+                            const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
+                            hi[wd] |= h << (8 * b);
+                            lo[wd] |= l << (8 * b);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(q_tile + swz(r, ch)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(q_tile + PTILE + swz(r, ch)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                } else {
+                    uint32_t wv[8];
+#pragma unroll
+                    for (int wd = 0; wd < 8; wd++) {
+                        __half2 h = __floats2half2_rn(x[2 * wd], x[2 * wd + 1]);
+                        wv[wd] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    // 16 dims = 32 B = two 16-byte chunks; dims [64, 128) live in the second column group
+                    unsigned char* base = q_tile + (ch / 4) * PTILE;
+                    *reinterpret_cast<uint4*>(base + swz(r, (ch % 4) * 2)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    *reinterpret_cast<uint4*>(base + swz(r, (ch % 4) * 2 + 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->q_ready);
+        }
+        bool ok = c->fail == 0;
+        float m_used = -INFINITY, l = 0.0f;
+        for (uint32_t j = 0; j < n_tiles; j++) {
+            const uint32_t st = j & 1u, t0 = j * KT;
+            if (ok) {
+                ok = mbar_wait(c->s_full + st, (j >> 1) & 1u, fail_word);
+                if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            }
+            const uint32_t tmem_s = tmem + st * 128u + lane_base;
+            // ---- pass 1: the row's maximum over the tile's allowed columns ----
+            float m_tile = -INFINITY;
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < KT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + c0, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 32; q++) {
+                        const uint32_t col = c0 + q;
+                        const float s = __uint_as_float(v[q]) * (c->scales[st][col >> 4] * q_inv);
+                        if (t0 + col <= q_pos) m_tile = fmaxf(m_tile, s);
+                    }
+                }
+            }
+            // ---- a raised maximum rescales the row sum and this row of O (after the previous tile's PV MMAs) ----
+            const bool raise = m_tile > m_used + P_RAISE;
+            float factor = 1.0f;
+            if (raise) {
+                factor = m_used == -INFINITY ? 0.0f : fast_exp2(m_used - m_tile);
+                m_used = m_tile;
+                l *= factor;
+            }
+            if (ok && j > 0) {
+                ok = mbar_wait(&c->pv_done, (j - 1u) & 1u, fail_word);          // P may be rewritten, O may be touched
+                if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            }
+            if (j > 0 && __any_sync(0xFFFFFFFFu, raise) && ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < PD; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + 256u + lane_base + c0, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 32; q++) v[q] = __float_as_uint(__uint_as_float(v[q]) * factor);
+                    tmem_st32(tmem + 256u + lane_base + c0, v);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+            }
+            // ---- pass 2: probabilities 2^(s - m + SHIFT) * v scale into P (three E5M2 terms for an E4M3 pool) ----
+            if (ok) {
+#pragma unroll
+                for (int c0 = 0; c0 < KT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + c0, v);
+                    tmem_wait_ld();
+                    if (c0 == KT - 32) {                             // S has been read for the last time
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(c->s_free + st);
+                    }
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {           // 16 columns = one block of the pool = one pair of scales
+                        const uint32_t blk = (c0 >> 4) + half;
+                        const float ks = c->scales[st][blk] * q_inv, vs = c->scales[st][8 + blk];
+                        float inv_vs;
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));
+                        const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)P_SHIFT) << 23);
+                        const float lv = fast_log2(vs) + P_SHIFT - m_used;
+                        uint32_t t1w[4] = {0, 0, 0, 0}, t2w[4] = {0, 0, 0, 0}, t3w[4] = {0, 0, 0, 0}, hw[8];
+#pragma unroll
+                        for (int q = 0; q < 16; q += 2) {
+                            const uint32_t col = c0 + half * 16 + q;
+                            const float s0 = __uint_as_float(v[half * 16 + q]) * ks, s1 = __uint_as_float(v[half * 16 + q + 1]) * ks;
+                            const float x0 = (t0 + col <= q_pos) ? fast_exp2(s0 + lv) : 0.0f;
+                            const float x1 = (t0 + col + 1 <= q_pos) ? fast_exp2(s1 + lv) : 0.0f;
+                            __half2 h = __floats2half2_rn(x0, x1);
+                            if (FP8) {
+                                const uint32_t t1 = *reinterpret_cast<uint32_t*>(&h) & 0xFF00FF00u;
+                                const __half2 r1 = __hsub2(h, *reinterpret_cast<const __half2*>(&t1));
+                                const uint32_t t2 = *reinterpret_cast<const uint32_t*>(&r1) & 0xFF00FF00u;
+                                const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
+                                const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
+                                h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));   // = t1 + t2 + t3
+                                const int wd = q >> 2, sh = (q & 3) * 8;
+                                t1w[wd] |= (((t1 >> 8) & 0xFFu) | ((t1 >> 16) & 0xFF00u)) << sh;
+                                t2w[wd] |= (((t2 >> 8) & 0xFFu) | ((t2 >> 16) & 0xFF00u)) << sh;
+                                t3w[wd] |= (((t3 >> 8) & 0xFFu) | ((t3 >> 16) & 0xFF00u)) << sh;
+                            } else {
+                                hw[q >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            const float2 f = __half22float2(h);
+                            l += (f.x + f.y) * l_scale;
+                        }
+                        if (FP8) {
+                            const uint32_t off = swz(r, blk);       // 16 columns = one 16-byte chunk of the row
+                            *reinterpret_cast<uint4*>(p_tile + off) = make_uint4(t1w[0], t1w[1], t1w[2], t1w[3]);
+                            *reinterpret_cast<uint4*>(p_tile + PTILE + off) = make_uint4(t2w[0], t2w[1], t2w[2], t2w[3]);
+                            *reinterpret_cast<uint4*>(p_tile + 2 * PTILE + off) = make_uint4(t3w[0], t3w[1], t3w[2], t3w[3]);
+                        } else {
+                            unsigned char* base = p_tile + (blk >> 2) * PTILE;    // columns [64, 128) live in the second column group
+                            *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                            *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2 + 1)) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+                        }
+                    }
+                }
+                // rows of the V tile past the last attended token hold whatever the pool (or an earlier tile) left there: 0 * NaN must not reach O
+                if (t0 + KT > kv_limit && t0 + r >= kv_limit) {
+                    unsigned char* vt = v_ring + (size_t)st * KV_TILE;
+#pragma unroll
+                    for (int cg = 0; cg < ES; cg++)
+#pragma unroll
+                        for (int ch = 0; ch < 8; ch++) *reinterpret_cast<uint4*>(vt + cg * PTILE + swz(r, ch)) = make_uint4(0, 0, 0, 0);
+                }
+                fence_async_smem();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->p_full);              // also after a failure: the issuer then ends through the fail word
+        }
+        // ---- epilogue: O row / row sum, undoing the shift and the V-scale normalisation ----
+        if (ok && n_tiles) {
+            ok = mbar_wait(&c->pv_done, (n_tiles - 1u) & 1u, fail_word);
+            if (!ok) atomicCAS(&c->fail, 0u, 4u);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float norm = __uint_as_float((uint32_t)(127 - (int)P_SHIFT + v_exp) << 23) / l;
+            float* orow = a.out + ((size_t)(q0 + tq) * a.n_q_heads + kvh * PG + g) * PD;
+#pragma unroll
+            for (int c0 = 0; c0 < PD; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + 256u + lane_base + c0, v);
+                tmem_wait_ld();
+                if (row_live) {
+#pragma unroll
+                    for (int q = 0; q < 32; q += 4)
+                        *reinterpret_cast<float4*>(orow + c0 + q) = make_float4(__uint_as_float(v[q]) * norm, __uint_as_float(v[q + 1]) * norm,
+                                                                                 __uint_as_float(v[q + 2]) * norm, __uint_as_float(v[q + 3]) * norm);
+                }
+            }
+            tc_fence_before();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+    if (tid == 0 && c->fail && a.status) atomicCAS(a.status, 0u, c->fail);
+}
+
+// A layer tensor as a 3-D byte array [token = blocks * 16][kv head = 8][128 * ES bytes], boxes of [16 tokens][1 kv head][128 B]:
+// one kv head's rows of one block.
+bool make_head_map(CUtensorMap* map, uint64_t base, uint32_t total_blocks, uint32_t es) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {128ull * es, (cuuint64_t)PHKV, (cuuint64_t)total_blocks * PBS};
+    const cuuint64_t strides[2] = {128ull * es, 128ull * es * PHKV};
+    const cuuint32_t box[3] = {128u, 1u, (cuuint32_t)PBS};
+    const cuuint32_t elem[3] = {1u, 1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, reinterpret_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool FP8> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
+    constexpr int ES = FP8 ? 1 : 2;
+    constexpr size_t smem = 1024 + (FP8 ? 2 : 2) * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE + 4 * (size_t)PTILE * ES;
+    auto kernel = prefill_attn_tc<FP8>;
+    static std::mutex mu;
+    static bool granted[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!granted[dev]) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            granted[dev] = true;
+        }
+    }
+    const dim3 grid((a.n_tokens + QT - 1) / QT, PHKV);
+    kernel<<<grid, 192, smem, st>>>(mk, mv, a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool prefill_eligible(uint32_t n_kv_heads, uint32_t n_q_heads, uint32_t head_dim, uint32_t block_size, uint32_t total_blocks) {
+    return n_kv_heads == PHKV && n_q_heads == PHKV * PG && head_dim == PD && block_size == PBS && (uint64_t)total_blocks * PBS < (1ull << 31);
+}
+
+cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const PrefillArgs& a, cudaStream_t st) {
+    CUtensorMap mk, mv;
+    const uint32_t es = fp8 ? 1u : 2u;
+    if (!make_head_map(&mk, k_layer, a.total_blocks, es) || !make_head_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
+    return fp8 ? launch_prefill<true>(mk, mv, a, st) : launch_prefill<false>(mk, mv, a, st);
+}
+
+}  // namespace tkv_tc
+
+namespace {
+int32_t pfail(int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    return tkv_internal::set_error(code, 0, buf);
+}
+}  // namespace
+
+extern "C" int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefillAttn* p, void* stream) {
+    if (!pool || !p) return pfail(TKV_ERR_INVALID_CONFIG, "NULL argument");
+    if (pool->dtype != TKV_DTYPE_F16 && pool->dtype != TKV_DTYPE_E4M3)
+        return pfail(TKV_ERR_INVALID_CONFIG, "prefill attention reads F16 or E4M3 pools (dtype %d)", (int)pool->dtype);
+    if (!tkv_tc::prefill_eligible(pool->n_kv_heads, p->n_q_heads, pool->head_dim, pool->block_size, pool->total_blocks))
+        return pfail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %u, got %u (prefill attention is built for 8 kv heads of 128 dims, 32 query heads, 16-token blocks)",
+                     8u, pool->n_kv_heads);
+    if (p->layer >= pool->n_layers) return pfail(TKV_ERR_INVALID_CONFIG, "layer %u outside the pool (%u layers)", p->layer, pool->n_layers);
+    if ((pool->k_scales == 0) != (pool->v_scales == 0)) return pfail(TKV_ERR_INVALID_CONFIG, "k_scales and v_scales must both be set or both be 0");
+    if (pool->k_scales && pool->dtype != TKV_DTYPE_E4M3) return pfail(TKV_ERR_INVALID_CONFIG, "only an E4M3 pool carries scales");
+    if (p->n_tokens == 0) return TKV_OK;
+    if (!p->q || !p->out || !p->table || !pool->k_layer_ptrs || !pool->v_layer_ptrs) return pfail(TKV_ERR_INVALID_CONFIG, "NULL buffer");
+    const uint64_t kv_len = (uint64_t)p->start_pos + p->n_tokens;
+    if (kv_len > (uint64_t)p->table_len * 16u)
+        return pfail(TKV_ERR_DIMENSION_MISMATCH, "dimension mismatch: expected %llu, got %llu (table entries for start_pos + n_tokens)",
+                     (unsigned long long)((kv_len + 15) / 16), (unsigned long long)p->table_len);
+    const uint64_t kp = pool->k_layer_ptrs[p->layer], vp = pool->v_layer_ptrs[p->layer];
+    if ((kp | vp | p->q | p->out) % 16) return pfail(TKV_ERR_INVALID_CONFIG, "layer tensors, q and out must be 16-byte aligned");
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return pfail(TKV_ERR_CUDA, "cudaGetDevice failed");
+    if (dev != pool->device && cudaSetDevice(pool->device) != cudaSuccess) return pfail(TKV_ERR_CUDA, "cannot select device %d", pool->device);
+    tkv_tc::PrefillArgs a{};
+    const size_t layer_scales = (size_t)pool->total_blocks * pool->n_kv_heads;
+    a.k_scales = pool->k_scales ? reinterpret_cast<const float*>(pool->k_scales) + (size_t)p->layer * layer_scales : nullptr;
+    a.v_scales = pool->v_scales ? reinterpret_cast<const float*>(pool->v_scales) + (size_t)p->layer * layer_scales : nullptr;
+    a.q = reinterpret_cast<const float*>(p->q);
+    a.out = reinterpret_cast<float*>(p->out);
+    a.table = reinterpret_cast<const uint32_t*>(p->table);
+    a.n_tokens = p->n_tokens;
+    a.start_pos = p->start_pos;
+    a.n_q_heads = p->n_q_heads;
+    a.total_blocks = pool->total_blocks;
+    a.q_scale = p->sm_scale * 1.4426950408889634f;
+    a.status = reinterpret_cast<uint32_t*>(p->status);
+    const cudaError_t e = tkv_tc::launch_prefill(pool->dtype == TKV_DTYPE_E4M3, kp, vp, a, static_cast<cudaStream_t>(stream));
+    if (dev != pool->device) cudaSetDevice(dev);
+    if (e != cudaSuccess) return tkv_internal::set_error(TKV_ERR_CUDA, (int32_t)e, cudaGetErrorString(e));
+    return TKV_OK;
+}

@@ -580,6 +580,26 @@ def refcount_apply_device_tables(dst: Pool, dst_tables: torch.Tensor, prefix_blo
     check(lib().tkv_refcount_apply_device_tables(C.byref(s), C.byref(b), delta, C.c_void_p(st.cuda_stream)))
 
 
+def prefill_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.Tensor, start_pos: int,
+                      sm_scale: Optional[float] = None, stream: Optional[torch.cuda.Stream] = None,
+                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of ``T`` new tokens of ONE sequence over its paged cache on the tcgen05 tensor cores (the
+    prefill-side twin of ``decode_attention``): the tokens' K/V rows are already in the pool at positions
+    ``start_pos .. start_pos + T - 1`` and query token ``t`` attends to positions ``0 .. start_pos + t``.  ``q`` is f32
+    ``[T, 32, 128]``, ``table_row`` the sequence's int32 block table; 8 kv heads, 16-token blocks, F16 or E4M3 pool
+    (per-block scales applied).  Raises ``TkvError`` for any other geometry (``causal_chunk_attention`` covers those)."""
+    assert q.dtype == torch.float32 and q.is_contiguous() and q.dim() == 3
+    table_row = table_row.to(torch.int32).contiguous()
+    out = torch.empty_like(q)
+    st = stream or torch.cuda.current_stream(q.device)
+    args = N.TkvPrefillAttn(q.shape[0], q.shape[1], layer, start_pos, table_row.numel(),
+                            float(sm_scale if sm_scale is not None else 1.0 / np.sqrt(q.shape[2])), 0, 0,
+                            q.data_ptr(), out.data_ptr(), table_row.data_ptr(), status.data_ptr() if status is not None else 0)
+    ps = pool.c_struct()
+    check(lib().tkv_prefill_attn_enqueue(C.byref(ps), C.byref(args), C.c_void_p(st.cuda_stream)))
+    return out
+
+
 def causal_chunk_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.Tensor, start_pos: int,
                            sm_scale: Optional[float] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Causal attention of ``T`` consecutive new tokens of ONE sequence over the paged pool (their K/V rows already

@@ -246,3 +246,54 @@ def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faul
     # the context still works
     again = H.decode_attention(ds, 0, q, tables, good, max_kv_len=200, flags=flags).cpu().numpy()
     np.testing.assert_array_equal(again, want)
+
+
+@pytest.mark.parametrize("dtype", ["e4m3", "f16"])
+@pytest.mark.parametrize("start,t", [(0, 40), (45, 70), (250, 33), (0, 300)])
+def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, start, t):
+    """The prefill-side twin: T new tokens of one sequence, token t attends to positions 0 .. start + t.  Ragged against
+    every boundary (start not on a block, T not a multiple of the 32 tokens a CTA takes, the last tile of 128 cached tokens
+    partly filled, rows of one CTA ending in different tiles).  Checked against the oracle run once per query token."""
+    import torch
+    total = start + t
+    lens = np.array([total], dtype=np.uint32)
+    kw = dict(dst_dtype="e4m3", outlier_channels=(5,), outlier_gain=20.0) if dtype == "e4m3" else {}
+    w = W.Workload("prefill-chunk", 1, 8, 128, 16, 64, 64, lens, seed=71, **kw).build_tables()
+    if dtype == "e4m3":
+        hs, hd, dd = quantized_pool(H, w)
+    else:
+        hs, _ = host_pools(w)
+        hd, dd = hs, to_device_pool(hs, "f16")
+        w.dst_tables = w.src_tables
+    q = torch.randn((t, 32, 128), generator=torch.Generator().manual_seed(17)).cuda()
+    row = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()[0]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = H.prefill_attention(dd, 0, q, row, start, status=status).cpu().numpy()
+    assert int(status.item()) == 0
+    tables = np.repeat(w.dst_tables.reshape(1, -1), t, axis=0)
+    kv = np.arange(start + 1, start + t + 1, dtype=np.uint32)
+    want = oracle.paged_decode_attention(hd, 0, q.cpu().numpy(), tables, kv, 1.0 / np.sqrt(128.0))
+    close(got, want, v_max_per_dim(hs, 0))
+
+
+def test_prefill_attention_refuses_other_geometries_and_foreign_blocks(H):
+    import torch
+    w = W.Workload("prefill-guard", 1, 8, 128, 16, 64, 64, np.array([100], dtype=np.uint32), seed=3).build_tables()
+    hs, _ = host_pools(w)
+    ds = to_device_pool(hs, "f16")
+    q = torch.randn((20, 32, 128), generator=torch.Generator().manual_seed(3)).cuda()
+    row = torch.from_numpy(w.src_tables.astype(np.int64)).to(torch.int32).cuda()[0]
+    with pytest.raises(N.TkvError) as e:                              # 16 query heads: not the geometry the kernel is built for
+        H.prefill_attention(ds, 0, q[:, :16].contiguous(), row, 80)
+    assert e.value.code == N.ERR_DIMENSION_MISMATCH
+    with pytest.raises(N.TkvError) as e:                              # the table does not reach start + T
+        H.prefill_attention(ds, 0, q, row[:5], 80)
+    assert e.value.code == N.ERR_DIMENSION_MISMATCH
+    bad = row.clone()
+    bad[2] = 1 << 20                                                  # a block id outside the pool is reported, never read
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    H.prefill_attention(ds, 0, q, bad, 80, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == N.ERR_INVALID_CONFIG
+    good = H.prefill_attention(ds, 0, q, row, 80, status=None)       # the context is still usable
+    assert bool(torch.isfinite(good).all())
