@@ -52,25 +52,84 @@ constexpr int QT = 32;                         // query tokens per CTA: QT * PG 
 constexpr int KT = 128;                        // cached tokens per tile = 8 blocks
 constexpr int PTILE = 128 * 128;               // bytes of one [128 rows][128 B] swizzled tile
 constexpr float P_RAISE = 6.0f, P_SHIFT = 9.0f;
+constexpr int NSPLIT = 4;                      // softmax threads per row, 32 of the tile's 128 columns each
+constexpr int SM_WARPS = 4 * NSPLIT, PTHREADS = (SM_WARPS + 2) * 32;   // + producer warp + issuer warp
 
 struct PControl {
-    uint64_t kv_full[2], kv_empty[2];          // K and V of a tile landed / its PV MMAs are done
+    uint64_t kv_full[4], kv_empty[4];          // K and V of a tile landed / its PV MMAs are done
     uint64_t s_full[2], s_free[2];             // S buffers: QK done / all four softmax warps have read it
-    uint64_t p_full, pv_done, q_ready, drained;
+    uint64_t p_full[2], pv_done[2];            // per P buffer: written by all softmax warps / its PV MMAs are done
+    uint64_t q_ready, drained;
     uint32_t tmem_base, fail, pad[2];
-    float scales[2][16];                       // per stage: 8 K scales, 8 V scales (normalised) of the tile's blocks
-    float vmax_part[4];
+    float scales[4][16];                       // per stage: 8 K scales, 8 V scales (normalised) of the tile's blocks
+    float vmax_part[SM_WARPS];
+    float q_inv[128];                          // per row: what undoes the power-of-two scale of its q
+    float pmax[2][NSPLIT][128];                // per tile parity: each split's maximum over its columns of a row
+    float lpart[NSPLIT][128];                  // row sums of the splits, folded in the epilogue
 };
-static_assert(sizeof(PControl) <= 1024, "control block");
+static_assert(sizeof(PControl) <= 8192, "control block");
+
+// Sixteen scores of one row (one block of the pool: one K scale, one V scale) -> sixteen probabilities in P.
+//   x = 2^(raw * ks + lv)   with lv = log2(v scale) + SHIFT - maximum in use, 0 for a column past the row's causal bound;
+// F16 pool: x as F16.  E4M3 pool: x as three E5M2 terms, peeled off an F16 two columns at a time (an E5M2 byte is the top byte of
+// an F16, so a term is the F16 with its low byte cleared, and the residual is exact).  Returns the sum of the sixteen x.
+template <bool FP8, bool MASKED>
+__device__ __forceinline__ float probabilities16(const uint32_t* raw, float ks, float lv, uint32_t first_pos, uint32_t q_pos, unsigned char* p_tile,
+                                                 uint32_t r, uint32_t blk) {
+    float sum = 0.0f;
+    __half2 dropped = __floats2half2_rn(0.0f, 0.0f);            // what the three terms leave out: the row sum must be the sum of what the MMA sees
+    uint32_t w1[4], w2[4], w3[4], hw[8];
+#pragma unroll
+    for (int q = 0; q < 16; q += 4) {
+        float x[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            x[i] = fast_exp2(__fmaf_rn(__uint_as_float(raw[q + i]), ks, lv));
+            if (MASKED && first_pos + q + i > q_pos) x[i] = 0.0f;
+        }
+        sum += (x[0] + x[1]) + (x[2] + x[3]);
+        const __half2 ha = __floats2half2_rn(x[0], x[1]), hb = __floats2half2_rn(x[2], x[3]);
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&ha), b0 = *reinterpret_cast<const uint32_t*>(&hb);
+        if (FP8) {
+            const uint32_t a1 = a0 & 0xFF00FF00u, b1 = b0 & 0xFF00FF00u;
+            const __half2 ra = __hsub2(ha, *reinterpret_cast<const __half2*>(&a1)), rb = __hsub2(hb, *reinterpret_cast<const __half2*>(&b1));
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&ra) & 0xFF00FF00u, b2 = *reinterpret_cast<const uint32_t*>(&rb) & 0xFF00FF00u;
+            const __half2 sa = __hsub2(ra, *reinterpret_cast<const __half2*>(&a2)), sb = __hsub2(rb, *reinterpret_cast<const __half2*>(&b2));
+            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sa) & 0xFF00FF00u, b3 = *reinterpret_cast<const uint32_t*>(&sb) & 0xFF00FF00u;
+            dropped = __hadd2(dropped, __hadd2(__hsub2(sa, *reinterpret_cast<const __half2*>(&a3)), __hsub2(sb, *reinterpret_cast<const __half2*>(&b3))));
+            w1[q >> 2] = __byte_perm(a1, b1, 0x7531);           // the four top bytes, in column order
+            w2[q >> 2] = __byte_perm(a2, b2, 0x7531);
+            w3[q >> 2] = __byte_perm(a3, b3, 0x7531);
+        } else {
+            hw[q >> 1] = a0;
+            hw[(q >> 1) + 1] = b0;
+        }
+    }
+    if (FP8) {
+        const uint32_t off = swz(r, blk);                       // 16 columns = one 16-byte chunk of the row
+        *reinterpret_cast<uint4*>(p_tile + off) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        *reinterpret_cast<uint4*>(p_tile + PTILE + off) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        *reinterpret_cast<uint4*>(p_tile + 2 * PTILE + off) = make_uint4(w3[0], w3[1], w3[2], w3[3]);
+        const float2 d = __half22float2(dropped);
+        sum -= d.x + d.y;
+    } else {
+        unsigned char* base = p_tile + (blk >> 2) * PTILE;      // columns [64, 128) live in the second column group
+        *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2 + 1)) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+    }
+    return sum;
+}
 
 template <bool FP8>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(PTHREADS, 1)
 prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;
     constexpr int KV_TILE = PTILE * ES;                     // K (or V) of one tile of 128 tokens
     constexpr int Q_BYTES = FP8 ? QTERMS * PTILE : 2 * PTILE, P_BYTES = FP8 ? PT * PTILE : 2 * PTILE;
     constexpr int KSTEPS = 4 * ES;
+    constexpr int PBUF = 1;                                 // P buffers
+    constexpr int NST = FP8 ? 4 : 2;                        // K/V tiles in flight (an F16 pool's tiles leave room for two)
     constexpr uint32_t IDESC_QK = instr_desc2(0u, 0u, 0u, 0u, 128u);
     constexpr uint32_t IDESC_PV = instr_desc2(FP8 ? 1u : 0u, 0u, 0u, 1u, 128u);      // A = P (E5M2 / F16, K-major), B = V (MN-major)
     constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -86,34 +145,38 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
 
     extern __shared__ __align__(1024) unsigned char smem[];
     PControl* c = reinterpret_cast<PControl*>(smem);
-    unsigned char* q_tile = smem + 1024;
+    unsigned char* q_tile = smem + 8192;
     unsigned char* p_tile = q_tile + Q_BYTES;
-    unsigned char* k_ring = p_tile + P_BYTES;               // 2 stages of K, then 2 stages of V
-    unsigned char* v_ring = k_ring + 2 * KV_TILE;
+    unsigned char* k_ring = p_tile + PBUF * P_BYTES;        // NST stages of K, then NST stages of V
+    unsigned char* v_ring = k_ring + NST * KV_TILE;
     const volatile uint32_t* fail_word = &c->fail;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < 4; s++) {
             mbar_init(c->kv_full + s, 1);
             mbar_init(c->kv_empty + s, 1);
-            mbar_init(c->s_full + s, 1);
-            mbar_init(c->s_free + s, 4);
         }
-        mbar_init(&c->p_full, 4);
-        mbar_init(&c->pv_done, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(c->s_full + s, 1);
+            mbar_init(c->s_free + s, SM_WARPS);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(c->p_full + b, SM_WARPS);
+            mbar_init(c->pv_done + b, 1);
+        }
         mbar_init(&c->q_ready, 4);
         mbar_init(&c->drained, 1);
         c->fail = (smem_u32(smem) & 1023u) ? 2u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == SM_WARPS + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&c->tmem_base)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // the largest V scale among the blocks this CTA will read, as a power of two (1 for an unscaled pool)
     float vmax = 0.0f;
-    if (warp < 4 && a.v_scales) {
-        for (uint32_t b = tid; b < n_blocks; b += 128) {
+    if (warp < SM_WARPS && a.v_scales) {
+        for (uint32_t b = tid; b < n_blocks; b += SM_WARPS * 32) {
             const uint32_t blk = a.table[b];
             if (blk < a.total_blocks) vmax = fmaxf(vmax, a.v_scales[(size_t)blk * PHKV + kvh]);
         }
@@ -127,18 +190,20 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     const uint32_t tmem = c->tmem_base;
     int v_exp = 0;                                                         // V scales are used as vs * 2^-v_exp <= 1
     if (a.v_scales) {
-        const float m = fmaxf(fmaxf(c->vmax_part[0], c->vmax_part[1]), fmaxf(c->vmax_part[2], c->vmax_part[3]));
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < SM_WARPS; i++) m = fmaxf(m, c->vmax_part[i]);
         if (m > 0.0f && m < INFINITY) v_exp = (int)((__float_as_uint(m) >> 23) & 0xFFu) - 126;   // 2^(v_exp - 1) <= m < 2^v_exp
         v_exp = max(-100, min(100, v_exp));
     }
     const float v_down = __uint_as_float((uint32_t)(127 - v_exp) << 23);
 
-    if (warp == 4) {
+    if (warp == SM_WARPS) {
         // ---- producer: the tile's blocks, one lane per block: K and V boxes of this kv head, the block's two scales ----
         bool ok = c->fail == 0;
         uint32_t why = 4u, issued = 0;
         for (uint32_t j = 0; j < n_tiles && ok; j++) {
-            const uint32_t st = j & 1u, nb = min(8u, n_blocks - j * 8u);
+            const uint32_t st = j % NST, nb = min(8u, n_blocks - j * 8u);
             uint32_t blk = 0;
             if (lane < nb) {
                 blk = a.table[j * 8u + lane];
@@ -149,7 +214,7 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             }
             if (__any_sync(0xFFFFFFFFu, why == 2u)) why = 2u;      // whichever lane met the bad id, lane 0 reports it
             ok = __all_sync(0xFFFFFFFFu, ok);
-            if (ok && lane == 0 && j >= 2) ok = mbar_wait(c->kv_empty + st, ((j >> 1) - 1u) & 1u, fail_word);
+            if (ok && lane == 0 && j >= (uint32_t)NST) ok = mbar_wait(c->kv_empty + st, ((j / NST) - 1u) & 1u, fail_word);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
             if (!ok) break;
             if (lane < 8) {
@@ -177,50 +242,61 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
         if (!ok && lane == 0) {
             atomicCAS(&c->fail, 0u, why);
-            for (uint32_t j = issued > 2 ? issued - 2 : 0u; j < issued; j++)       // copies still in flight get a bounded chance to land
+            for (uint32_t j = issued > (uint32_t)NST ? issued - NST : 0u; j < issued; j++)   // copies still in flight get a bounded chance to land
                 for (uint32_t it = 0; it < (1u << 20); it++)
-                    if (mbar_test(c->kv_full + (j & 1u), (j >> 1) & 1u)) break;
+                    if (mbar_test(c->kv_full + j % NST, (j / NST) & 1u)) break;
         }
-    } else if (warp == 5) {
+    } else if (warp == SM_WARPS + 1) {
         // ---- MMA issuer: QK of tile j, then PV of tile j - 1, so the softmax of a tile overlaps the next tile's scores ----
         if (lane == 0) {
             const uint32_t q_lo = smem_u32(q_tile) >> 4, p_lo = smem_u32(p_tile) >> 4;
             const uint32_t kr_lo = smem_u32(k_ring) >> 4, vr_lo = smem_u32(v_ring) >> 4;
             bool ok = c->fail == 0 && mbar_wait(&c->q_ready, 0u, fail_word);
-            auto pv = [&](uint32_t j) {
-                ok = mbar_wait(&c->p_full, j & 1u, fail_word);
-                if (!ok) return;
-                tc_fence_after();
-                const uint32_t v_lo = vr_lo + (j & 1u) * (KV_TILE >> 4);
+            // Whichever is ready goes next: the scores of the next tile (its K has landed and its S buffer has been read) or the PV product
+            // of the oldest tile whose probabilities are written.  Neither waits behind the other, so a tile's copies are asked for as soon
+            // as the stage's previous PV is done and land while the softmax of the tiles in between runs.
+            uint32_t jq = 0, jp = 0, idle = 0;
+            while (ok && jp < n_tiles) {
+                bool did = false;
+                if (jq < n_tiles) {
+                    const uint32_t st = jq % NST, sb = jq & 1u;
+                    if (mbar_test(c->kv_full + st, (jq / NST) & 1u) && (jq < 2 || mbar_test(c->s_free + sb, ((jq >> 1) - 1u) & 1u))) {
+                        tc_fence_after();
+                        const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4);
 #pragma unroll
-                for (int term = 0; term < PT; term++)
+                        for (int term = 0; term < QTERMS; term++)
 #pragma unroll
-                    for (int ks = 0; ks < KSTEPS; ks++)
-                        mma<FP8>(tmem + 256u,
-                                 DESC_K | (p_lo + (FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2)),
-                                 DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), IDESC_PV, (j > 0 || term > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(&c->pv_done);
-                tc_commit(c->kv_empty + (j & 1u));
-            };
-            for (uint32_t j = 0; j < n_tiles && ok; j++) {
-                const uint32_t st = j & 1u;
-                ok = mbar_wait(c->kv_full + st, (j >> 1) & 1u, fail_word);
-                if (ok && j >= 2) ok = mbar_wait(c->s_free + st, ((j >> 1) - 1u) & 1u, fail_word);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4);
-#pragma unroll
-                for (int term = 0; term < QTERMS; term++)
-#pragma unroll
-                    for (int ks = 0; ks < KSTEPS; ks++) {
-                        const uint32_t a_off = FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
-                        const uint32_t b_off = (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
-                        mma<FP8>(tmem + st * 128u, DESC_K | (q_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                            for (int ks = 0; ks < KSTEPS; ks++) {
+                                const uint32_t a_off = FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                                const uint32_t b_off = (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                                mma<FP8>(tmem + sb * 128u, DESC_K | (q_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                            }
+                        tc_commit(c->s_full + sb);
+                        jq++;
+                        did = true;
                     }
-                tc_commit(c->s_full + st);
-                if (j > 0) pv(j - 1);
+                }
+                if (jp < jq) {
+                    const uint32_t pb = jp % PBUF;
+                    if (mbar_test(c->p_full + pb, (jp / PBUF) & 1u)) {
+                        tc_fence_after();
+                        const uint32_t v_lo = vr_lo + (jp % NST) * (KV_TILE >> 4), pj_lo = p_lo + pb * (P_BYTES >> 4);
+#pragma unroll
+                        for (int term = 0; term < PT; term++)
+#pragma unroll
+                            for (int ks = 0; ks < KSTEPS; ks++)
+                                mma<FP8>(tmem + 256u,
+                                         DESC_K | (pj_lo + (FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2)),
+                                         DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), IDESC_PV, (jp > 0 || term > 0 || ks > 0) ? 1u : 0u);
+                        tc_commit(c->pv_done + pb);
+                        tc_commit(c->kv_empty + jp % NST);
+                        jp++;
+                        did = true;
+                    }
+                }
+                if (did) idle = 0;
+                else if (++idle > (1u << 24) || ((idle & 63u) == 0 && *fail_word)) ok = false;       // bounded: a stuck barrier ends the CTA, not the GPU
             }
-            if (ok && n_tiles) pv(n_tiles - 1);
             if (!ok) atomicCAS(&c->fail, 0u, 4u);
             tc_commit(&c->drained);
             for (uint32_t it = 0; it < (1u << 22); it++)
@@ -228,13 +304,14 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---- softmax: thread r owns row r = (query head r / 32, token r % 32) and tensor-memory lane r ----
-        const uint32_t r = tid, g = r >> 5, tq = r & 31u;
+        // ---- softmax: NSPLIT threads per row; thread (split, r) owns columns [32 * split, +32) of row r = (query head r / 32, token
+        // r % 32) in every S tile and the same columns of the row in O; the row's maximum is exchanged through shared memory ----
+        const uint32_t split = warp >> 2, r = (warp & 3u) * 32u + lane, g = r >> 5, tq = r & 31u;
         const bool row_live = tq < rows_tokens;
         const uint32_t q_pos = a.start_pos + q0 + (row_live ? tq : 0u);
-        const uint32_t lane_base = (warp * 32u) << 16;
-        float q_inv = 1.0f;
-        {
+        const uint32_t lane_base = ((warp & 3u) * 32u) << 16, col0 = split * 32u;
+        if (split == 0) {
+            float q_inv = 1.0f;
             // Q row: scaled into the log2 domain; E4M3 pool: two E4M3 terms under a power-of-two scale that brings the row's largest
             // element into [128, 256)
             const float* qrow = a.q + ((size_t)(q0 + (row_live ? tq : 0u)) * a.n_q_heads + kvh * PG + g) * PD;
@@ -253,7 +330,7 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 q_inv = __uint_as_float((uint32_t)(127 - e) << 23);
             }
             if (!row_live) up = 0.0f;
-#pragma unroll
+#pragma unroll 1
             for (int ch = 0; ch < PD / 16; ch++) {                  // 16 dims at a time
                 float x[16];
 #pragma unroll
@@ -295,35 +372,53 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             }
             fence_async_smem();
             __syncwarp();
+            c->q_inv[r] = q_inv;
             if (lane == 0) mbar_arrive(&c->q_ready);
         }
+        asm volatile("bar.sync 1, %0;" ::"n"(SM_WARPS * 32) : "memory");          // q_inv is in place
+        const float q_inv = c->q_inv[r];
         bool ok = c->fail == 0;
         float m_used = -INFINITY, l = 0.0f;
         for (uint32_t j = 0; j < n_tiles; j++) {
-            const uint32_t st = j & 1u, t0 = j * KT;
+            const uint32_t sb = j & 1u, st = j % NST, t0 = j * KT;
             if (ok) {
-                ok = mbar_wait(c->s_full + st, (j >> 1) & 1u, fail_word);
+                ok = mbar_wait(c->s_full + sb, (j >> 1) & 1u, fail_word);
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
             }
-            const uint32_t tmem_s = tmem + st * 128u + lane_base;
-            // ---- pass 1: the row's maximum over the tile's allowed columns ----
-            float m_tile = -INFINITY;
+            // ---- this thread's 32 scores of the tile, read once; its maximum over the allowed columns (two blocks, each with its K scale) ----
+            uint32_t v[32];
+            float m_part = -INFINITY;
+            const float ks0 = c->scales[st][split * 2u] * q_inv, ks1 = c->scales[st][split * 2u + 1u] * q_inv;
+            const bool masked = t0 + KT > a.start_pos + q0 + 1u;       // some row of this CTA stops inside the tile (or before it)
             if (ok) {
                 tc_fence_after();
+                tmem_ld32(tmem + sb * 128u + lane_base + col0, v);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(c->s_free + sb);
+                float mx0 = -INFINITY, mx1 = -INFINITY;                   // the scales are positive: the maximum commutes with them
+                if (masked) {
 #pragma unroll
-                for (int c0 = 0; c0 < KT; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_s + c0, v);
-                    tmem_wait_ld();
+                    for (int q = 0; q < 16; q++) {
+                        if (t0 + col0 + q <= q_pos) mx0 = fmaxf(mx0, __uint_as_float(v[q]));
+                        if (t0 + col0 + 16 + q <= q_pos) mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
+                    }
+                } else {
 #pragma unroll
-                    for (int q = 0; q < 32; q++) {
-                        const uint32_t col = c0 + q;
-                        const float s = __uint_as_float(v[q]) * (c->scales[st][col >> 4] * q_inv);
-                        if (t0 + col <= q_pos) m_tile = fmaxf(m_tile, s);
+                    for (int q = 0; q < 16; q++) {
+                        mx0 = fmaxf(mx0, __uint_as_float(v[q]));
+                        mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
                     }
                 }
+                m_part = fmaxf(mx0 * ks0, mx1 * ks1);
             }
-            // ---- a raised maximum rescales the row sum and this row of O (after the previous tile's PV MMAs) ----
+            c->pmax[sb][split][r] = m_part;
+            asm volatile("bar.sync %0, %1;" ::"r"(2u + (warp & 3u)), "n"(NSPLIT * 32) : "memory");   // only the warps that share these 32 rows
+            float m_tile = c->pmax[sb][0][r];
+#pragma unroll
+            for (int i = 1; i < NSPLIT; i++) m_tile = fmaxf(m_tile, c->pmax[sb][i][r]);
+            // ---- a raised maximum rescales the row sum and this thread's columns of the row of O (after the previous tile's PV MMAs) ----
             const bool raise = m_tile > m_used + P_RAISE;
             float factor = 1.0f;
             if (raise) {
@@ -331,83 +426,46 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 m_used = m_tile;
                 l *= factor;
             }
-            if (ok && j > 0) {
-                ok = mbar_wait(&c->pv_done, (j - 1u) & 1u, fail_word);          // P may be rewritten, O may be touched
+            const uint32_t pb = j % PBUF;
+            unsigned char* pj = p_tile + pb * P_BYTES;
+            if (ok && j >= (uint32_t)PBUF) {
+                ok = mbar_wait(c->pv_done + pb, ((j / PBUF) - 1u) & 1u, fail_word);   // this P buffer's previous PV MMAs are done
+                if (!ok) atomicCAS(&c->fail, 0u, 4u);
+            }
+            if (j > 0 && __any_sync(0xFFFFFFFFu, raise) && ok) {
+                ok = mbar_wait(c->pv_done + (j - 1u) % PBUF, ((j - 1u) / PBUF) & 1u, fail_word);   // O is at rest: the previous tile's PV MMAs are done
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
             }
             if (j > 0 && __any_sync(0xFFFFFFFFu, raise) && ok) {
                 tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < PD; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem + 256u + lane_base + c0, v);
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < 32; c0 += 16) {           // sixteen columns at a time: the scores wait in registers meanwhile
+                    uint32_t o[16];
+                    tmem_ld16(tmem + 256u + lane_base + col0 + c0, o);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int q = 0; q < 32; q++) v[q] = __float_as_uint(__uint_as_float(v[q]) * factor);
-                    tmem_st32(tmem + 256u + lane_base + c0, v);
+                    for (int q = 0; q < 16; q++) o[q] = __float_as_uint(__uint_as_float(o[q]) * factor);
+                    tmem_st16(tmem + 256u + lane_base + col0 + c0, o);
                 }
                 tmem_wait_st();
                 tc_fence_before();
             }
-            // ---- pass 2: probabilities 2^(s - m + SHIFT) * v scale into P (three E5M2 terms for an E4M3 pool) ----
+            // ---- probabilities 2^(s - m + SHIFT) * v scale into P (three E5M2 terms for an E4M3 pool) ----
             if (ok) {
 #pragma unroll
-                for (int c0 = 0; c0 < KT; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_s + c0, v);
-                    tmem_wait_ld();
-                    if (c0 == KT - 32) {                             // S has been read for the last time
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(c->s_free + st);
-                    }
-#pragma unroll
-                    for (int half = 0; half < 2; half++) {           // 16 columns = one block of the pool = one pair of scales
-                        const uint32_t blk = (c0 >> 4) + half;
-                        const float ks = c->scales[st][blk] * q_inv, vs = c->scales[st][8 + blk];
-                        float inv_vs;
-                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));
-                        const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)P_SHIFT) << 23);
-                        const float lv = fast_log2(vs) + P_SHIFT - m_used;
-                        uint32_t t1w[4] = {0, 0, 0, 0}, t2w[4] = {0, 0, 0, 0}, t3w[4] = {0, 0, 0, 0}, hw[8];
-#pragma unroll
-                        for (int q = 0; q < 16; q += 2) {
-                            const uint32_t col = c0 + half * 16 + q;
-                            const float s0 = __uint_as_float(v[half * 16 + q]) * ks, s1 = __uint_as_float(v[half * 16 + q + 1]) * ks;
-                            const float x0 = (t0 + col <= q_pos) ? fast_exp2(s0 + lv) : 0.0f;
-                            const float x1 = (t0 + col + 1 <= q_pos) ? fast_exp2(s1 + lv) : 0.0f;
-                            __half2 h = __floats2half2_rn(x0, x1);
-                            if (FP8) {
-                                const uint32_t t1 = *reinterpret_cast<uint32_t*>(&h) & 0xFF00FF00u;
-                                const __half2 r1 = __hsub2(h, *reinterpret_cast<const __half2*>(&t1));
-                                const uint32_t t2 = *reinterpret_cast<const uint32_t*>(&r1) & 0xFF00FF00u;
-                                const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
-                                const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
-                                h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));   // = t1 + t2 + t3
-                                const int wd = q >> 2, sh = (q & 3) * 8;
-                                t1w[wd] |= (((t1 >> 8) & 0xFFu) | ((t1 >> 16) & 0xFF00u)) << sh;
-                                t2w[wd] |= (((t2 >> 8) & 0xFFu) | ((t2 >> 16) & 0xFF00u)) << sh;
-                                t3w[wd] |= (((t3 >> 8) & 0xFFu) | ((t3 >> 16) & 0xFF00u)) << sh;
-                            } else {
-                                hw[q >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                            }
-                            const float2 f = __half22float2(h);
-                            l += (f.x + f.y) * l_scale;
-                        }
-                        if (FP8) {
-                            const uint32_t off = swz(r, blk);       // 16 columns = one 16-byte chunk of the row
-                            *reinterpret_cast<uint4*>(p_tile + off) = make_uint4(t1w[0], t1w[1], t1w[2], t1w[3]);
-                            *reinterpret_cast<uint4*>(p_tile + PTILE + off) = make_uint4(t2w[0], t2w[1], t2w[2], t2w[3]);
-                            *reinterpret_cast<uint4*>(p_tile + 2 * PTILE + off) = make_uint4(t3w[0], t3w[1], t3w[2], t3w[3]);
-                        } else {
-                            unsigned char* base = p_tile + (blk >> 2) * PTILE;    // columns [64, 128) live in the second column group
-                            *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                            *reinterpret_cast<uint4*>(base + swz(r, (blk & 3u) * 2 + 1)) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
-                        }
-                    }
+                for (int half = 0; half < 2; half++) {               // 16 columns = one block of the pool = one pair of scales
+                    const uint32_t blk = split * 2u + half;
+                    const float vs = c->scales[st][8 + blk];
+                    float inv_vs;
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));
+                    const float lv = fast_log2(vs) + P_SHIFT - m_used;
+                    const float ks = half ? ks1 : ks0;
+                    const float sum = masked ? probabilities16<FP8, true>(v + half * 16, ks, lv, t0 + col0 + half * 16, q_pos, pj, r, blk)
+                                             : probabilities16<FP8, false>(v + half * 16, ks, lv, 0u, 0u, pj, r, blk);
+                    l += sum * (inv_vs * __uint_as_float((uint32_t)(127 - (int)P_SHIFT) << 23));
                 }
                 // rows of the V tile past the last attended token hold whatever the pool (or an earlier tile) left there: 0 * NaN must not reach O
-                if (t0 + KT > kv_limit && t0 + r >= kv_limit) {
+                if (split == 0 && t0 + KT > kv_limit && t0 + r >= kv_limit) {
                     unsigned char* vt = v_ring + (size_t)st * KV_TILE;
 #pragma unroll
                     for (int cg = 0; cg < ES; cg++)
@@ -417,35 +475,37 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 fence_async_smem();
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&c->p_full);              // also after a failure: the issuer then ends through the fail word
+            if (lane == 0) mbar_arrive(c->p_full + pb);          // also after a failure: the issuer then ends through the fail word
         }
-        // ---- epilogue: O row / row sum, undoing the shift and the V-scale normalisation ----
+        // ---- epilogue: this thread's 32 dims of the O row / the row sum of all splits, undoing the shift and the V-scale normalisation ----
+        c->lpart[split][r] = l;
+        asm volatile("bar.sync 1, %0;" ::"n"(SM_WARPS * 32) : "memory");
+        float l_row = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NSPLIT; i++) l_row += c->lpart[i][r];
         if (ok && n_tiles) {
-            ok = mbar_wait(&c->pv_done, (n_tiles - 1u) & 1u, fail_word);
+            ok = mbar_wait(c->pv_done + (n_tiles - 1u) % PBUF, ((n_tiles - 1u) / PBUF) & 1u, fail_word);
             if (!ok) atomicCAS(&c->fail, 0u, 4u);
         }
         if (ok) {
             tc_fence_after();
-            const float norm = __uint_as_float((uint32_t)(127 - (int)P_SHIFT + v_exp) << 23) / l;
-            float* orow = a.out + ((size_t)(q0 + tq) * a.n_q_heads + kvh * PG + g) * PD;
+            const float norm = __uint_as_float((uint32_t)(127 - (int)P_SHIFT + v_exp) << 23) / l_row;
+            float* orow = a.out + ((size_t)(q0 + tq) * a.n_q_heads + kvh * PG + g) * PD + col0;
+            uint32_t o[32];
+            tmem_ld32(tmem + 256u + lane_base + col0, o);
+            tmem_wait_ld();
+            if (row_live) {
 #pragma unroll
-            for (int c0 = 0; c0 < PD; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem + 256u + lane_base + c0, v);
-                tmem_wait_ld();
-                if (row_live) {
-#pragma unroll
-                    for (int q = 0; q < 32; q += 4)
-                        *reinterpret_cast<float4*>(orow + c0 + q) = make_float4(__uint_as_float(v[q]) * norm, __uint_as_float(v[q + 1]) * norm,
-                                                                                 __uint_as_float(v[q + 2]) * norm, __uint_as_float(v[q + 3]) * norm);
-                }
+                for (int q = 0; q < 32; q += 4)
+                    *reinterpret_cast<float4*>(orow + q) = make_float4(__uint_as_float(o[q]) * norm, __uint_as_float(o[q + 1]) * norm,
+                                                                        __uint_as_float(o[q + 2]) * norm, __uint_as_float(o[q + 3]) * norm);
             }
             tc_fence_before();
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == SM_WARPS + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
@@ -467,7 +527,7 @@ bool make_head_map(CUtensorMap* map, uint64_t base, uint32_t total_blocks, uint3
 
 template <bool FP8> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
     constexpr int ES = FP8 ? 1 : 2;
-    constexpr size_t smem = 1024 + (FP8 ? 2 : 2) * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE + 4 * (size_t)PTILE * ES;
+    constexpr size_t smem = 8192 + 2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE + 2 * (FP8 ? 4 : 2) * (size_t)PTILE * ES;
     auto kernel = prefill_attn_tc<FP8>;
     static std::mutex mu;
     static bool granted[64] = {};
@@ -484,7 +544,7 @@ template <bool FP8> cudaError_t launch_prefill(const CUtensorMap& mk, const CUte
         }
     }
     const dim3 grid((a.n_tokens + QT - 1) / QT, PHKV);
-    kernel<<<grid, 192, smem, st>>>(mk, mv, a);
+    kernel<<<grid, PTHREADS, smem, st>>>(mk, mv, a);
     return cudaGetLastError();
 }
 
