@@ -395,13 +395,15 @@ typedef struct TkvPrefillAttn {
     uint32_t n_tokens, n_q_heads, layer, start_pos;
     uint32_t table_len;           /* entries of `table`; at least ceil((start_pos + n_tokens) / 16) */
     float sm_scale;               /* usually 1 / sqrt(head_dim)                                     */
-    uint32_t flags, reserved;     /* 0                                                              */
+    uint32_t flags, reserved;     /* TKV_PREFILL_*; 0                                               */
     uint64_t q;                   /* f32 [n_tokens][n_q_heads][128]                                 */
     uint64_t out;                 /* f32, same shape                                                */
     uint64_t table;               /* u32 [table_len] block ids of the sequence                      */
     uint64_t status;              /* 0, or a device u32 (zero it before the launch): TKV_ERR_TIMEOUT if a bounded wait gave
                                      up, TKV_ERR_INVALID_CONFIG if a table entry named a block outside the pool      */
 } TkvPrefillAttn;
+enum { TKV_PREFILL_DEFAULT = 0,
+       TKV_PREFILL_SINGLE_TILE = 1 /* one query tile (32 tokens) per CTA even where two fit (the E4M3 pool's default is two taking turns) */ };
 int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefillAttn* args, void* stream);
 /* Device self-check of the tcgen05 path's operand plumbing (tensor-map copy with the 128-byte swizzle,
  * shared-memory and instruction descriptors, tensor-memory reads) on operands of small dyadic values whose

@@ -6,15 +6,17 @@
 // (the reference's paged prefill kernel for the FP8 pool, cutile_flash_attn_heads_paged_e4m3,
 // kernels/src/cutile_flash_attention.rs:868, reads unscaled bytes; here every (block, kv head) carries its scale).
 //
-// One CTA owns one kv head and 32 consecutive query tokens: with four query heads per kv head that is 128 rows, row
-// r = (query head r / 32, token r % 32).  It walks the cached tokens 128 at a time (eight pool blocks).  Per tile
+// A query tile is one kv head and 32 consecutive query tokens: with four query heads per kv head that is 128 rows, row
+// r = (query head r / 32, token r % 32).  A CTA owns one query tile, or two that take turns (E4M3 pool: the MMAs of one tile run
+// under the softmax of the other, and each K/V tile is fetched once for both).  It walks the cached tokens 128 at a time (eight
+// pool blocks).  Per query tile and cached tile
 //
 //     S[128 rows][128 tokens] = Q . K_tile^T     (tcgen05.mma, M = N = 128; K_tile = eight [16 tokens][128 B] tensor-map boxes of this kv head)
 //     O[128 rows][128 dims]  += P . V_tile       (P written by the softmax threads, V read MN-major from the same kind of tile)
 //
-// with S double-buffered and O resident in tensor memory.  A softmax thread owns one row and one tensor-memory
-// lane: the running maximum, the row sum and the rescale of O on a raised maximum are all thread-local (the rescale is
-// taken lazily, when a tile exceeds the maximum in use by 2^6).  Operand precision as in the decode kernel: an F16 pool
+// with S and O in tensor memory.  Four softmax threads share a row (32 of the tile's 128 columns each, the same tensor-memory
+// lane): the row's maximum is exchanged through shared memory, the rescale of O on a raised maximum is taken lazily (when a tile
+// exceeds the maximum in use by 2^6) and each thread rescales its own 32 columns.  Operand precision as in the decode kernel: an F16 pool
 // takes F16 q and probabilities; an E4M3 pool takes q as two E4M3 terms under a per-row power-of-two scale and the
 // probabilities as three E5M2 terms (all terms accumulate into the same accumulator here, since they differ in the A
 // operand only).  The block scales: K's multiplies the scores of its 16 columns; V's multiplies the probabilities of
@@ -56,18 +58,19 @@ constexpr int NSPLIT = 4;                      // softmax threads per row, 32 of
 constexpr int SM_WARPS = 4 * NSPLIT, PTHREADS = (SM_WARPS + 2) * 32;   // + producer warp + issuer warp
 
 struct PControl {
-    uint64_t kv_full[4], kv_empty[4];          // K and V of a tile landed / its PV MMAs are done
-    uint64_t s_full[2], s_free[2];             // S buffers: QK done / all four softmax warps have read it
-    uint64_t p_full[2], pv_done[2];            // per P buffer: written by all softmax warps / its PV MMAs are done
+    uint64_t kv_full[4], kv_empty[4];          // K and V of a tile landed / the PV MMAs of every query tile that reads it are done
+    uint64_t s_full[2], s_free[2];             // S buffers: QK done / all softmax warps have read it
+    uint64_t p_full[2], pv_done[2];            // P buffers: written by all softmax warps / its PV MMAs are done
     uint64_t q_ready, drained;
     uint32_t tmem_base, fail, pad[2];
     float scales[4][16];                       // per stage: 8 K scales, 8 V scales (normalised) of the tile's blocks
     float vmax_part[SM_WARPS];
-    float q_inv[128];                          // per row: what undoes the power-of-two scale of its q
-    float pmax[2][NSPLIT][128];                // per tile parity: each split's maximum over its columns of a row
-    float lpart[NSPLIT][128];                  // row sums of the splits, folded in the epilogue
+    // Exchange area, one use at a time: q_inv[query tile][row] before the first tile; then per step the splits' row maxima
+    // [split][row]; then the splits' row sums [split][row] in the epilogue.
+    float exch[NSPLIT * 128];
 };
-static_assert(sizeof(PControl) <= 8192, "control block");
+static_assert(sizeof(PControl) <= 3072, "control block");
+constexpr int CTRL = 3072;
 
 // Sixteen scores of one row (one block of the pool: one K scale, one V scale) -> sixteen probabilities in P.
 //   x = 2^(raw * ks + lv)   with lv = log2(v scale) + SHIFT - maximum in use, 0 for a column past the row's causal bound;
@@ -120,16 +123,18 @@ __device__ __forceinline__ float probabilities16(const uint32_t* raw, float ks, 
     return sum;
 }
 
-template <bool FP8>
+// NQT query tiles of 32 tokens per CTA.  With two, the softmax warps take the tiles in turns and the MMAs of one tile run under the
+// softmax of the other; each K/V tile is fetched once for both.  (Two tiles of E4M3 operand terms fill shared memory to the byte;
+// an F16 pool's tiles leave room for one.)
+template <bool FP8, int NQT>
 __global__ void __launch_bounds__(PTHREADS, 1)
 prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
     constexpr int ES = FP8 ? 1 : 2;
     constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;
     constexpr int KV_TILE = PTILE * ES;                     // K (or V) of one tile of 128 tokens
-    constexpr int Q_BYTES = FP8 ? QTERMS * PTILE : 2 * PTILE, P_BYTES = FP8 ? PT * PTILE : 2 * PTILE;
+    constexpr int Q_BYTES = 2 * PTILE, P_BYTES = FP8 ? PT * PTILE : 2 * PTILE;     // per query tile
     constexpr int KSTEPS = 4 * ES;
-    constexpr int PBUF = 1;                                 // P buffers
-    constexpr int NST = FP8 ? 4 : 2;                        // K/V tiles in flight (an F16 pool's tiles leave room for two)
+    constexpr int NST = 2;                                  // K/V tiles in flight
     constexpr uint32_t IDESC_QK = instr_desc2(0u, 0u, 0u, 0u, 128u);
     constexpr uint32_t IDESC_PV = instr_desc2(FP8 ? 1u : 0u, 0u, 0u, 1u, 128u);      // A = P (E5M2 / F16, K-major), B = V (MN-major)
     constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -138,16 +143,27 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t kvh = blockIdx.y;
-    const uint32_t q0 = (gridDim.x - 1u - blockIdx.x) * QT;                           // the longest rows first
-    const uint32_t rows_tokens = min((uint32_t)QT, a.n_tokens - q0);
-    const uint32_t kv_limit = a.start_pos + q0 + rows_tokens;                         // tokens the last row of this CTA attends to
-    const uint32_t n_tiles = (kv_limit + KT - 1) / KT, n_blocks = (kv_limit + PBS - 1) / PBS;
+    const uint32_t q0 = (gridDim.x - 1u - blockIdx.x) * (QT * NQT);                   // the longest rows first
+    uint32_t rows_tokens[NQT], n_tiles_x[NQT], n_tiles = 0, kv_limit = 0;
+#pragma unroll
+    for (int x = 0; x < NQT; x++) {
+        const uint32_t first = q0 + x * QT;
+        rows_tokens[x] = first < a.n_tokens ? min((uint32_t)QT, a.n_tokens - first) : 0u;
+        const uint32_t lim = rows_tokens[x] ? a.start_pos + first + rows_tokens[x] : 0u;   // tokens the tile's last row attends to
+        n_tiles_x[x] = (lim + KT - 1) / KT;
+        n_tiles = max(n_tiles, n_tiles_x[x]);
+        kv_limit = max(kv_limit, lim);
+    }
+    const uint32_t n_blocks = (kv_limit + PBS - 1) / PBS;
+    // S of query tile x for cached tile j: one buffer per query tile when there are two, two alternating buffers when there is one
+    auto s_index = [&](uint32_t x, uint32_t j) { return NQT == 2 ? x : (j & 1u); };
+    auto s_phase = [&](uint32_t j) { return NQT == 2 ? j : (j >> 1); };
 
     extern __shared__ __align__(1024) unsigned char smem[];
     PControl* c = reinterpret_cast<PControl*>(smem);
-    unsigned char* q_tile = smem + 8192;
-    unsigned char* p_tile = q_tile + Q_BYTES;
-    unsigned char* k_ring = p_tile + PBUF * P_BYTES;        // NST stages of K, then NST stages of V
+    unsigned char* q_tile = smem + CTRL;                    // NQT tiles
+    unsigned char* p_tile = q_tile + NQT * Q_BYTES;         // NQT buffers
+    unsigned char* k_ring = p_tile + NQT * P_BYTES;         // NST stages of K, then NST stages of V
     unsigned char* v_ring = k_ring + NST * KV_TILE;
     const volatile uint32_t* fail_word = &c->fail;
 
@@ -158,13 +174,11 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(c->s_full + s, 1);
-            mbar_init(c->s_free + s, SM_WARPS);
+            mbar_init(c->s_free + s, SM_WARPS / NQT);
+            mbar_init(c->p_full + s, SM_WARPS / NQT);
+            mbar_init(c->pv_done + s, 1);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(c->p_full + b, SM_WARPS);
-            mbar_init(c->pv_done + b, 1);
-        }
-        mbar_init(&c->q_ready, 4);
+        mbar_init(&c->q_ready, 4 * NQT);
         mbar_init(&c->drained, 1);
         c->fail = (smem_u32(smem) & 1023u) ? 2u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -247,55 +261,77 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                     if (mbar_test(c->kv_full + j % NST, (j / NST) & 1u)) break;
         }
     } else if (warp == SM_WARPS + 1) {
-        // ---- MMA issuer: QK of tile j, then PV of tile j - 1, so the softmax of a tile overlaps the next tile's scores ----
+        // ---- MMA issuer.  Whichever is ready goes next, per query tile: the scores of its next cached tile (K has landed, its S buffer has
+        // been read) or the PV product of its oldest tile whose probabilities are written.  Nothing waits behind anything else, so a stage's
+        // copies are asked for as soon as its last PV is done and land while the softmax of other tiles runs. ----
         if (lane == 0) {
             const uint32_t q_lo = smem_u32(q_tile) >> 4, p_lo = smem_u32(p_tile) >> 4;
             const uint32_t kr_lo = smem_u32(k_ring) >> 4, vr_lo = smem_u32(v_ring) >> 4;
             bool ok = c->fail == 0 && mbar_wait(&c->q_ready, 0u, fail_word);
-            // Whichever is ready goes next: the scores of the next tile (its K has landed and its S buffer has been read) or the PV product
-            // of the oldest tile whose probabilities are written.  Neither waits behind the other, so a tile's copies are asked for as soon
-            // as the stage's previous PV is done and land while the softmax of the tiles in between runs.
-            uint32_t jq = 0, jp = 0, idle = 0;
-            while (ok && jp < n_tiles) {
+            uint32_t jq[NQT], jp[NQT], pv_left[NST], idle = 0, todo = 0;
+#pragma unroll
+            for (int x = 0; x < NQT; x++) {
+                jq[x] = jp[x] = 0;
+                todo += n_tiles_x[x];
+            }
+#pragma unroll
+            for (int s = 0; s < NST; s++) pv_left[s] = 0;
+            while (ok && todo) {
                 bool did = false;
-                if (jq < n_tiles) {
-                    const uint32_t st = jq % NST, sb = jq & 1u;
-                    if (mbar_test(c->kv_full + st, (jq / NST) & 1u) && (jq < 2 || mbar_test(c->s_free + sb, ((jq >> 1) - 1u) & 1u))) {
-                        tc_fence_after();
-                        const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4);
 #pragma unroll
-                        for (int term = 0; term < QTERMS; term++)
+                for (int x = 0; x < NQT; x++) {
+                    if (jq[x] < n_tiles_x[x]) {
+                        const uint32_t j = jq[x], st = j % NST, sb = s_index(x, j);
+                        const bool s_ok = NQT == 2 ? (j < 1 || mbar_test(c->s_free + sb, (j - 1u) & 1u)) : (j < 2 || mbar_test(c->s_free + sb, ((j >> 1) - 1u) & 1u));
+                        if (s_ok && mbar_test(c->kv_full + st, (j / NST) & 1u)) {
+                            tc_fence_after();
+                            const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4), qx_lo = q_lo + x * (Q_BYTES >> 4);
 #pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ks++) {
-                                const uint32_t a_off = FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
-                                const uint32_t b_off = (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
-                                mma<FP8>(tmem + sb * 128u, DESC_K | (q_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                            for (int term = 0; term < QTERMS; term++)
+#pragma unroll
+                                for (int ks = 0; ks < KSTEPS; ks++) {
+                                    const uint32_t a_off = FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                                    const uint32_t b_off = (ks / 4) * (PTILE >> 4) + (ks % 4) * 2;
+                                    mma<FP8>(tmem + sb * 128u, DESC_K | (qx_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
+                                }
+                            tc_commit(c->s_full + sb);
+                            jq[x]++;
+                            did = true;
+                        }
+                    }
+                    if (jp[x] < jq[x]) {
+                        const uint32_t j = jp[x], st = j % NST;
+                        if (mbar_test(c->p_full + x, j & 1u)) {
+                            tc_fence_after();
+                            const uint32_t v_lo = vr_lo + st * (KV_TILE >> 4), pj_lo = p_lo + x * (P_BYTES >> 4);
+#pragma unroll
+                            for (int term = 0; term < PT; term++)
+#pragma unroll
+                                for (int ks = 0; ks < KSTEPS; ks++)
+                                    mma<FP8>(tmem + 256u + x * 128u,
+                                             DESC_K | (pj_lo + (FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2)),
+                                             DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), IDESC_PV, (j > 0 || term > 0 || ks > 0) ? 1u : 0u);
+                            tc_commit(c->pv_done + x);
+                            // the stage goes back to the producer behind the PV of the last query tile that reads this cached tile
+                            uint32_t readers = 0;
+#pragma unroll
+                            for (int y = 0; y < NQT; y++) readers += j < n_tiles_x[y] ? 1u : 0u;
+                            if (++pv_left[st] == readers) {
+                                tc_commit(c->kv_empty + st);
+                                pv_left[st] = 0;
                             }
-                        tc_commit(c->s_full + sb);
-                        jq++;
-                        did = true;
+                            jp[x]++;
+                            todo--;
+                            did = true;
+                        }
                     }
                 }
-                if (jp < jq) {
-                    const uint32_t pb = jp % PBUF;
-                    if (mbar_test(c->p_full + pb, (jp / PBUF) & 1u)) {
-                        tc_fence_after();
-                        const uint32_t v_lo = vr_lo + (jp % NST) * (KV_TILE >> 4), pj_lo = p_lo + pb * (P_BYTES >> 4);
-#pragma unroll
-                        for (int term = 0; term < PT; term++)
-#pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ks++)
-                                mma<FP8>(tmem + 256u,
-                                         DESC_K | (pj_lo + (FP8 ? term * (PTILE >> 4) + ks * 2 : (ks / 4) * (PTILE >> 4) + (ks % 4) * 2)),
-                                         DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), IDESC_PV, (jp > 0 || term > 0 || ks > 0) ? 1u : 0u);
-                        tc_commit(c->pv_done + pb);
-                        tc_commit(c->kv_empty + jp % NST);
-                        jp++;
-                        did = true;
-                    }
+                if (did) {
+                    idle = 0;
+                } else {
+                    if (++idle > (1u << 22) || ((idle & 63u) == 0 && *fail_word)) ok = false;       // bounded: a stuck barrier ends the CTA, not the GPU
+                    __nanosleep(40);                              // leave the issue slots to the softmax warps on this scheduler
                 }
-                if (did) idle = 0;
-                else if (++idle > (1u << 24) || ((idle & 63u) == 0 && *fail_word)) ok = false;       // bounded: a stuck barrier ends the CTA, not the GPU
             }
             if (!ok) atomicCAS(&c->fail, 0u, 4u);
             tc_commit(&c->drained);
@@ -304,19 +340,26 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---- softmax: NSPLIT threads per row; thread (split, r) owns columns [32 * split, +32) of row r = (query head r / 32, token
-        // r % 32) in every S tile and the same columns of the row in O; the row's maximum is exchanged through shared memory ----
-        const uint32_t split = warp >> 2, r = (warp & 3u) * 32u + lane, g = r >> 5, tq = r & 31u;
-        const bool row_live = tq < rows_tokens;
-        const uint32_t q_pos = a.start_pos + q0 + (row_live ? tq : 0u);
-        const uint32_t lane_base = ((warp & 3u) * 32u) << 16, col0 = split * 32u;
+        // ---- softmax.  One query tile: all sixteen warps work on it, four threads per row (32 columns each).  Two query tiles: eight
+        // warps each, two threads per row (64 columns each), and the two groups run out of step, so one group's waits (for S, for the
+        // tensor-memory load, for its partner's maximum) are filled by the other group's arithmetic.  Thread (split, r) owns columns
+        // [CPT * split, +CPT) of row r = (query head r / 32, token r % 32) of every S tile and the same columns of the row in O. ----
+        constexpr int NSP = NQT == 2 ? 2 : 4, CPT = 128 / NSP, GW = NSP * 4;            // splits per row, columns per thread, warps per group
+        const uint32_t x = NQT == 2 ? warp / GW : 0u, gw = warp % GW;                   // this thread's query tile; warp within the group
+        const uint32_t split = gw >> 2, r = (gw & 3u) * 32u + lane, g = r >> 5, tq = r & 31u;
+        const uint32_t lane_base = ((gw & 3u) * 32u) << 16, col0 = split * CPT;
+        const uint32_t bar_rows = 2u + (gw & 3u) + 4u * x, bar_group = 10u + x;        // named barriers: the warps sharing 32 rows; the whole group
+        float* exch = c->exch + x * (NSP * 128);
+        const uint32_t my_rows = rows_tokens[x], my_tiles = n_tiles_x[x];
+        const bool row_live = tq < my_rows;
+        const uint32_t q_pos = a.start_pos + q0 + x * QT + (row_live ? tq : 0u);
         if (split == 0) {
-            float q_inv = 1.0f;
             // Q row: scaled into the log2 domain; E4M3 pool: two E4M3 terms under a power-of-two scale that brings the row's largest
             // element into [128, 256)
-            const float* qrow = a.q + ((size_t)(q0 + (row_live ? tq : 0u)) * a.n_q_heads + kvh * PG + g) * PD;
-            float up = a.q_scale;
-            if (FP8) {
+            const float* qrow = a.q + ((size_t)(q0 + x * QT + (row_live ? tq : 0u)) * a.n_q_heads + kvh * PG + g) * PD;
+            unsigned char* qt = q_tile + x * Q_BYTES;
+            float up = a.q_scale, qi = 1.0f;
+            if (FP8 && row_live) {
                 float amax = 0.0f;
                 for (int i = 0; i < PD / 4; i++) {
                     const float4 f = __ldg(reinterpret_cast<const float4*>(qrow) + i);
@@ -327,19 +370,19 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 if (amax > 0.0f && amax < INFINITY) e = 7 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
                 e = max(-60, min(60, e));
                 up = a.q_scale * __uint_as_float((uint32_t)(127 + e) << 23);
-                q_inv = __uint_as_float((uint32_t)(127 - e) << 23);
+                qi = __uint_as_float((uint32_t)(127 - e) << 23);
             }
             if (!row_live) up = 0.0f;
 #pragma unroll 1
             for (int ch = 0; ch < PD / 16; ch++) {                  // 16 dims at a time
-                float x[16];
+                float xv[16];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const float4 f = __ldg(reinterpret_cast<const float4*>(qrow) + ch * 4 + i);
-                    x[4 * i] = f.x * up;
-                    x[4 * i + 1] = f.y * up;
-                    x[4 * i + 2] = f.z * up;
-                    x[4 * i + 3] = f.w * up;
+                    const float4 f = row_live ? __ldg(reinterpret_cast<const float4*>(qrow) + ch * 4 + i) : make_float4(0, 0, 0, 0);
+                    xv[4 * i] = f.x * up;
+                    xv[4 * i + 1] = f.y * up;
+                    xv[4 * i + 2] = f.z * up;
+                    xv[4 * i + 3] = f.w * up;
                 }
                 if (FP8) {
                     uint32_t hi[4], lo[4];
@@ -348,76 +391,82 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                         hi[wd] = lo[wd] = 0;
 #pragma unroll
                         for (int b = 0; b < 4; b++) {
-                            const float v = x[wd * 4 + b];
+                            const float v = xv[wd * 4 + b];
                             const uint32_t h = e4m3_of(v);
                             const uint32_t l = e4m3_of(v - e4m3_to_f32(h));
                             hi[wd] |= h << (8 * b);
                             lo[wd] |= l << (8 * b);
                         }
                     }
-                    *reinterpret_cast<uint4*>(q_tile + swz(r, ch)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(q_tile + PTILE + swz(r, ch)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(qt + swz(r, ch)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(qt + PTILE + swz(r, ch)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 } else {
                     uint32_t wv[8];
 #pragma unroll
                     for (int wd = 0; wd < 8; wd++) {
-                        __half2 h = __floats2half2_rn(x[2 * wd], x[2 * wd + 1]);
+                        __half2 h = __floats2half2_rn(xv[2 * wd], xv[2 * wd + 1]);
                         wv[wd] = *reinterpret_cast<uint32_t*>(&h);
                     }
                     // 16 dims = 32 B = two 16-byte chunks; dims [64, 128) live in the second column group
-                    unsigned char* base = q_tile + (ch / 4) * PTILE;
+                    unsigned char* base = qt + (ch / 4) * PTILE;
                     *reinterpret_cast<uint4*>(base + swz(r, (ch % 4) * 2)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                     *reinterpret_cast<uint4*>(base + swz(r, (ch % 4) * 2 + 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
                 }
             }
+            exch[r] = qi;
             fence_async_smem();
             __syncwarp();
-            c->q_inv[r] = q_inv;
             if (lane == 0) mbar_arrive(&c->q_ready);
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(SM_WARPS * 32) : "memory");          // q_inv is in place
-        const float q_inv = c->q_inv[r];
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_group), "n"(GW * 32) : "memory");        // q_inv is in place
+        const float q_inv = exch[r];
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_group), "n"(GW * 32) : "memory");        // the exchange area now holds row maxima
         bool ok = c->fail == 0;
         float m_used = -INFINITY, l = 0.0f;
-        for (uint32_t j = 0; j < n_tiles; j++) {
-            const uint32_t sb = j & 1u, st = j % NST, t0 = j * KT;
+        unsigned char* pj = p_tile + x * P_BYTES;
+        const uint32_t tmem_o = tmem + 256u + x * 128u + lane_base + col0;
+        for (uint32_t j = 0; j < my_tiles; j++) {
+            const uint32_t sb = s_index(x, j), st = j % NST, t0 = j * KT;
             if (ok) {
-                ok = mbar_wait(c->s_full + sb, (j >> 1) & 1u, fail_word);
+                ok = mbar_wait(c->s_full + sb, s_phase(j) & 1u, fail_word);
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
             }
-            // ---- this thread's 32 scores of the tile, read once; its maximum over the allowed columns (two blocks, each with its K scale) ----
-            uint32_t v[32];
+            const uint32_t tmem_s = tmem + sb * 128u + lane_base + col0;
+            const bool masked = t0 + KT > a.start_pos + q0 + x * QT + 1u;          // some row of this query tile stops inside the cached tile (or before it)
+            // ---- pass 1: this thread's maximum over its allowed columns (16 columns = one block of the pool = one K scale) ----
             float m_part = -INFINITY;
-            const float ks0 = c->scales[st][split * 2u] * q_inv, ks1 = c->scales[st][split * 2u + 1u] * q_inv;
-            const bool masked = t0 + KT > a.start_pos + q0 + 1u;       // some row of this CTA stops inside the tile (or before it)
             if (ok) {
                 tc_fence_after();
-                tmem_ld32(tmem + sb * 128u + lane_base + col0, v);
-                tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(c->s_free + sb);
-                float mx0 = -INFINITY, mx1 = -INFINITY;                   // the scales are positive: the maximum commutes with them
-                if (masked) {
 #pragma unroll
-                    for (int q = 0; q < 16; q++) {
-                        if (t0 + col0 + q <= q_pos) mx0 = fmaxf(mx0, __uint_as_float(v[q]));
-                        if (t0 + col0 + 16 + q <= q_pos) mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
-                    }
-                } else {
+                for (int c0 = 0; c0 < CPT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + c0, v);
+                    tmem_wait_ld();
+                    float mx0 = -INFINITY, mx1 = -INFINITY;                   // the scales are positive: the maximum commutes with them
+                    if (masked) {
 #pragma unroll
-                    for (int q = 0; q < 16; q++) {
-                        mx0 = fmaxf(mx0, __uint_as_float(v[q]));
-                        mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
+                        for (int q = 0; q < 16; q++) {
+                            if (t0 + col0 + c0 + q <= q_pos) mx0 = fmaxf(mx0, __uint_as_float(v[q]));
+                            if (t0 + col0 + c0 + 16 + q <= q_pos) mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 16; q++) {
+                            mx0 = fmaxf(mx0, __uint_as_float(v[q]));
+                            mx1 = fmaxf(mx1, __uint_as_float(v[16 + q]));
+                        }
                     }
+                    const uint32_t blk = (col0 + c0) >> 4;
+                    m_part = fmaxf(m_part, fmaxf(mx0 * (c->scales[st][blk] * q_inv), mx1 * (c->scales[st][blk + 1u] * q_inv)));
                 }
-                m_part = fmaxf(mx0 * ks0, mx1 * ks1);
             }
-            c->pmax[sb][split][r] = m_part;
-            asm volatile("bar.sync %0, %1;" ::"r"(2u + (warp & 3u)), "n"(NSPLIT * 32) : "memory");   // only the warps that share these 32 rows
-            float m_tile = c->pmax[sb][0][r];
+            // the splits of a row exchange their maxima: wait until the previous tile's values have been read, write, wait, read
+            asm volatile("bar.sync %0, %1;" ::"r"(bar_rows), "n"(NSP * 32) : "memory");
+            exch[split * 128 + r] = m_part;
+            asm volatile("bar.sync %0, %1;" ::"r"(bar_rows), "n"(NSP * 32) : "memory");
+            float m_tile = exch[r];
 #pragma unroll
-            for (int i = 1; i < NSPLIT; i++) m_tile = fmaxf(m_tile, c->pmax[sb][i][r]);
+            for (int i = 1; i < NSP; i++) m_tile = fmaxf(m_tile, exch[i * 128 + r]);
             // ---- a raised maximum rescales the row sum and this thread's columns of the row of O (after the previous tile's PV MMAs) ----
             const bool raise = m_tile > m_used + P_RAISE;
             float factor = 1.0f;
@@ -426,45 +475,51 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 m_used = m_tile;
                 l *= factor;
             }
-            const uint32_t pb = j % PBUF;
-            unsigned char* pj = p_tile + pb * P_BYTES;
-            if (ok && j >= (uint32_t)PBUF) {
-                ok = mbar_wait(c->pv_done + pb, ((j / PBUF) - 1u) & 1u, fail_word);   // this P buffer's previous PV MMAs are done
-                if (!ok) atomicCAS(&c->fail, 0u, 4u);
-            }
-            if (j > 0 && __any_sync(0xFFFFFFFFu, raise) && ok) {
-                ok = mbar_wait(c->pv_done + (j - 1u) % PBUF, ((j - 1u) / PBUF) & 1u, fail_word);   // O is at rest: the previous tile's PV MMAs are done
+            if (ok && j > 0) {
+                ok = mbar_wait(c->pv_done + x, (j - 1u) & 1u, fail_word);            // P may be rewritten, O may be touched
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
             }
             if (j > 0 && __any_sync(0xFFFFFFFFu, raise) && ok) {
                 tc_fence_after();
 #pragma unroll 1
-                for (uint32_t c0 = 0; c0 < 32; c0 += 16) {           // sixteen columns at a time: the scores wait in registers meanwhile
+                for (uint32_t c0 = 0; c0 < (uint32_t)CPT; c0 += 16) {
                     uint32_t o[16];
-                    tmem_ld16(tmem + 256u + lane_base + col0 + c0, o);
+                    tmem_ld16(tmem_o + c0, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int q = 0; q < 16; q++) o[q] = __float_as_uint(__uint_as_float(o[q]) * factor);
-                    tmem_st16(tmem + 256u + lane_base + col0 + c0, o);
+                    tmem_st16(tmem_o + c0, o);
                 }
                 tmem_wait_st();
                 tc_fence_before();
             }
-            // ---- probabilities 2^(s - m + SHIFT) * v scale into P (three E5M2 terms for an E4M3 pool) ----
+            // ---- pass 2: probabilities 2^(s - m + SHIFT) * v scale into P (three E5M2 terms for an E4M3 pool), S read again ----
             if (ok) {
+                tc_fence_after();
 #pragma unroll
-                for (int half = 0; half < 2; half++) {               // 16 columns = one block of the pool = one pair of scales
-                    const uint32_t blk = split * 2u + half;
-                    const float vs = c->scales[st][8 + blk];
-                    float inv_vs;
-                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));
-                    const float lv = fast_log2(vs) + P_SHIFT - m_used;
-                    const float ks = half ? ks1 : ks0;
-                    const float sum = masked ? probabilities16<FP8, true>(v + half * 16, ks, lv, t0 + col0 + half * 16, q_pos, pj, r, blk)
-                                             : probabilities16<FP8, false>(v + half * 16, ks, lv, 0u, 0u, pj, r, blk);
-                    l += sum * (inv_vs * __uint_as_float((uint32_t)(127 - (int)P_SHIFT) << 23));
+                for (int c0 = 0; c0 < CPT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + c0, v);
+                    tmem_wait_ld();
+                    if (c0 == CPT - 32) {                            // S has been read for the last time
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(c->s_free + sb);
+                    }
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {           // 16 columns = one block of the pool = one pair of scales
+                        const uint32_t blk = ((col0 + c0) >> 4) + half;
+                        const float ks = c->scales[st][blk] * q_inv, vs = c->scales[st][8 + blk];
+                        float inv_vs;
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_vs) : "f"(vs));
+                        const float lv = fast_log2(vs) + P_SHIFT - m_used;
+                        const float sum = masked ? probabilities16<FP8, true>(v + half * 16, ks, lv, t0 + blk * 16u, q_pos, pj, r, blk)
+                                                 : probabilities16<FP8, false>(v + half * 16, ks, lv, 0u, 0u, pj, r, blk);
+                        l += sum * (inv_vs * __uint_as_float((uint32_t)(127 - (int)P_SHIFT) << 23));
+                    }
                 }
-                // rows of the V tile past the last attended token hold whatever the pool (or an earlier tile) left there: 0 * NaN must not reach O
+                // rows of the V tile past the last attended token hold whatever the pool (or an earlier tile) left there: 0 * NaN must not
+                // reach O.  Each group clears them before its own PV (the same zeros, whoever comes first).
                 if (split == 0 && t0 + KT > kv_limit && t0 + r >= kv_limit) {
                     unsigned char* vt = v_ring + (size_t)st * KV_TILE;
 #pragma unroll
@@ -475,30 +530,34 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 fence_async_smem();
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(c->p_full + pb);          // also after a failure: the issuer then ends through the fail word
+            if (lane == 0) mbar_arrive(c->p_full + x);            // also after a failure: the issuer then ends through the fail word
         }
-        // ---- epilogue: this thread's 32 dims of the O row / the row sum of all splits, undoing the shift and the V-scale normalisation ----
-        c->lpart[split][r] = l;
-        asm volatile("bar.sync 1, %0;" ::"n"(SM_WARPS * 32) : "memory");
+        // ---- epilogue: this thread's columns of the O row / the row sum of all splits, undoing the shift and the V-scale normalisation ----
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_group), "n"(GW * 32) : "memory");        // the last maxima have been read
+        exch[split * 128 + r] = l;
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_group), "n"(GW * 32) : "memory");
         float l_row = 0.0f;
 #pragma unroll
-        for (int i = 0; i < NSPLIT; i++) l_row += c->lpart[i][r];
-        if (ok && n_tiles) {
-            ok = mbar_wait(c->pv_done + (n_tiles - 1u) % PBUF, ((n_tiles - 1u) / PBUF) & 1u, fail_word);
+        for (int i = 0; i < NSP; i++) l_row += exch[i * 128 + r];
+        if (ok && my_tiles) {
+            ok = mbar_wait(c->pv_done + x, (my_tiles - 1u) & 1u, fail_word);
             if (!ok) atomicCAS(&c->fail, 0u, 4u);
         }
-        if (ok) {
+        if (ok && my_tiles) {
             tc_fence_after();
             const float norm = __uint_as_float((uint32_t)(127 - (int)P_SHIFT + v_exp) << 23) / l_row;
-            float* orow = a.out + ((size_t)(q0 + tq) * a.n_q_heads + kvh * PG + g) * PD + col0;
-            uint32_t o[32];
-            tmem_ld32(tmem + 256u + lane_base + col0, o);
-            tmem_wait_ld();
-            if (row_live) {
+            float* orow = a.out + ((size_t)(q0 + x * QT + tq) * a.n_q_heads + kvh * PG + g) * PD + col0;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < (uint32_t)CPT; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + c0, o);
+                tmem_wait_ld();
+                if (row_live) {
 #pragma unroll
-                for (int q = 0; q < 32; q += 4)
-                    *reinterpret_cast<float4*>(orow + q) = make_float4(__uint_as_float(o[q]) * norm, __uint_as_float(o[q + 1]) * norm,
-                                                                        __uint_as_float(o[q + 2]) * norm, __uint_as_float(o[q + 3]) * norm);
+                    for (int q = 0; q < 32; q += 4)
+                        *reinterpret_cast<float4*>(orow + c0 + q) = make_float4(__uint_as_float(o[q]) * norm, __uint_as_float(o[q + 1]) * norm,
+                                                                                 __uint_as_float(o[q + 2]) * norm, __uint_as_float(o[q + 3]) * norm);
+                }
             }
             tc_fence_before();
         }
@@ -525,10 +584,11 @@ bool make_head_map(CUtensorMap* map, uint64_t base, uint32_t total_blocks, uint3
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool FP8> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
+template <bool FP8, int NQT> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
     constexpr int ES = FP8 ? 1 : 2;
-    constexpr size_t smem = 8192 + 2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE + 2 * (FP8 ? 4 : 2) * (size_t)PTILE * ES;
-    auto kernel = prefill_attn_tc<FP8>;
+    constexpr size_t smem = CTRL + NQT * (2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE) + 2 * 2 * (size_t)PTILE * ES;
+    static_assert(smem <= 227 * 1024, "shared memory of one CTA");
+    auto kernel = prefill_attn_tc<FP8, NQT>;
     static std::mutex mu;
     static bool granted[64] = {};
     int dev = 0;
@@ -543,7 +603,7 @@ template <bool FP8> cudaError_t launch_prefill(const CUtensorMap& mk, const CUte
             granted[dev] = true;
         }
     }
-    const dim3 grid((a.n_tokens + QT - 1) / QT, PHKV);
+    const dim3 grid((a.n_tokens + QT * NQT - 1) / (QT * NQT), PHKV);
     kernel<<<grid, PTHREADS, smem, st>>>(mk, mv, a);
     return cudaGetLastError();
 }
@@ -558,7 +618,9 @@ cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const P
     CUtensorMap mk, mv;
     const uint32_t es = fp8 ? 1u : 2u;
     if (!make_head_map(&mk, k_layer, a.total_blocks, es) || !make_head_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
-    return fp8 ? launch_prefill<true>(mk, mv, a, st) : launch_prefill<false>(mk, mv, a, st);
+    // E4M3 pool: two query tiles per CTA taking turns; an F16 pool's tiles leave shared memory for one (a.single_tile forces one, for comparison)
+    if (fp8) return a.single_tile ? launch_prefill<true, 1>(mk, mv, a, st) : launch_prefill<true, 2>(mk, mv, a, st);
+    return launch_prefill<false, 1>(mk, mv, a, st);
 }
 
 }  // namespace tkv_tc
@@ -608,6 +670,7 @@ extern "C" int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefil
     a.total_blocks = pool->total_blocks;
     a.q_scale = p->sm_scale * 1.4426950408889634f;
     a.status = reinterpret_cast<uint32_t*>(p->status);
+    a.single_tile = (p->flags & TKV_PREFILL_SINGLE_TILE) ? 1u : 0u;
     const cudaError_t e = tkv_tc::launch_prefill(pool->dtype == TKV_DTYPE_E4M3, kp, vp, a, static_cast<cudaStream_t>(stream));
     if (dev != pool->device) cudaSetDevice(dev);
     if (e != cudaSuccess) return tkv_internal::set_error(TKV_ERR_CUDA, (int32_t)e, cudaGetErrorString(e));

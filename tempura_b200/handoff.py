@@ -582,7 +582,7 @@ def refcount_apply_device_tables(dst: Pool, dst_tables: torch.Tensor, prefix_blo
 
 def prefill_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.Tensor, start_pos: int,
                       sm_scale: Optional[float] = None, stream: Optional[torch.cuda.Stream] = None,
-                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      status: Optional[torch.Tensor] = None, flags: int = 0) -> torch.Tensor:
     """Causal attention of ``T`` new tokens of ONE sequence over its paged cache on the tcgen05 tensor cores (the
     prefill-side twin of ``decode_attention``): the tokens' K/V rows are already in the pool at positions
     ``start_pos .. start_pos + T - 1`` and query token ``t`` attends to positions ``0 .. start_pos + t``.  ``q`` is f32
@@ -593,7 +593,7 @@ def prefill_attention(pool: Pool, layer: int, q: torch.Tensor, table_row: torch.
     out = torch.empty_like(q)
     st = stream or torch.cuda.current_stream(q.device)
     args = N.TkvPrefillAttn(q.shape[0], q.shape[1], layer, start_pos, table_row.numel(),
-                            float(sm_scale if sm_scale is not None else 1.0 / np.sqrt(q.shape[2])), 0, 0,
+                            float(sm_scale if sm_scale is not None else 1.0 / np.sqrt(q.shape[2])), flags, 0,
                             q.data_ptr(), out.data_ptr(), table_row.data_ptr(), status.data_ptr() if status is not None else 0)
     ps = pool.c_struct()
     check(lib().tkv_prefill_attn_enqueue(C.byref(ps), C.byref(args), C.c_void_p(st.cuda_stream)))

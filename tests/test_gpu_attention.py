@@ -248,9 +248,9 @@ def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faul
     np.testing.assert_array_equal(again, want)
 
 
-@pytest.mark.parametrize("dtype", ["e4m3", "f16"])
-@pytest.mark.parametrize("start,t", [(0, 40), (45, 70), (250, 33), (0, 300)])
-def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, start, t):
+@pytest.mark.parametrize("dtype,flags", [("e4m3", 0), ("e4m3", N.PREFILL_SINGLE_TILE), ("f16", 0)])
+@pytest.mark.parametrize("start,t", [(0, 40), (45, 70), (250, 33), (0, 300), (100, 64), (3, 129)])
+def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, flags, start, t):
     """The prefill-side twin: T new tokens of one sequence, token t attends to positions 0 .. start + t.  Ragged against
     every boundary (start not on a block, T not a multiple of the 32 tokens a CTA takes, the last tile of 128 cached tokens
     partly filled, rows of one CTA ending in different tiles).  Checked against the oracle run once per query token."""
@@ -268,7 +268,7 @@ def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, start, t):
     q = torch.randn((t, 32, 128), generator=torch.Generator().manual_seed(17)).cuda()
     row = torch.from_numpy(w.dst_tables.astype(np.int64)).to(torch.int32).cuda()[0]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    got = H.prefill_attention(dd, 0, q, row, start, status=status).cpu().numpy()
+    got = H.prefill_attention(dd, 0, q, row, start, status=status, flags=flags).cpu().numpy()
     assert int(status.item()) == 0
     tables = np.repeat(w.dst_tables.reshape(1, -1), t, axis=0)
     kv = np.arange(start + 1, start + t + 1, dtype=np.uint32)
