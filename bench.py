@@ -1121,7 +1121,7 @@ def run_prefill_attention(args):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     sampler = ClockSampler(0)
     sampler.start()
-    pf_flags = 1 if args.prefill_single_tile else 0
+    pf_flags = 1 if args.prefill_single_tile else (2 if args.prefill_two_tiles else 0)
     outs = [H.prefill_attention(pool, l, q, row, start, status=status, flags=pf_flags) for l in range(layers)]     # plain launches first
     torch.cuda.synchronize()
     if int(status.item()):
@@ -1344,6 +1344,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "attn", "prefill", "prefix", "admit"])
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="--workload prefill: new tokens of the prompt")
     ap.add_argument("--prefill-single-tile", action="store_true", help="--workload prefill: one query tile per CTA (TKV_PREFILL_SINGLE_TILE)")
+    ap.add_argument("--prefill-two-tiles", action="store_true", help="--workload prefill: two query tiles per CTA (TKV_PREFILL_TWO_TILES)")
     ap.add_argument("--prefill-start", type=int, default=0, help="--workload prefill: tokens already cached before them")
     ap.add_argument("--attn-split", type=int, default=0, help="--workload attn: cached tokens per CTA (0 = library default)")
     ap.add_argument("--attn-no-hint", action="store_true", help="--workload attn: do not tell the library the batch's total cached tokens")

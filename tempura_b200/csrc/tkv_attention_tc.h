@@ -37,7 +37,7 @@ struct PrefillArgs {
     uint32_t n_tokens, start_pos, n_q_heads, total_blocks;
     float q_scale;                // softmax scale * log2(e)
     uint32_t* status;             // optional device word: first failure wins
-    uint32_t single_tile;         // 1 = one query tile per CTA even where two fit
+    uint32_t single_tile;         // 1 = one query tile per CTA, 2 = two, 0 = the library's choice
 };
 bool prefill_eligible(uint32_t n_kv_heads, uint32_t n_q_heads, uint32_t head_dim, uint32_t block_size, uint32_t total_blocks);
 cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const PrefillArgs& a, cudaStream_t st);

@@ -58,12 +58,13 @@ constexpr int NSPLIT = 4;                      // softmax threads per row, 32 of
 constexpr int SM_WARPS = 4 * NSPLIT, PTHREADS = (SM_WARPS + 2) * 32;   // + producer warp + issuer warp
 
 struct PControl {
-    uint64_t kv_full[4], kv_empty[4];          // K and V of a tile landed / the PV MMAs of every query tile that reads it are done
+    uint64_t k_full[2], k_empty[2];            // K of a tile landed / the QK MMAs of every query tile that reads it are done
+    uint64_t v_full[2], v_empty[2];            // V of a tile landed / the PV MMAs of every query tile that reads it are done
     uint64_t s_full[2], s_free[2];             // S buffers: QK done / all softmax warps have read it
     uint64_t p_full[2], pv_done[2];            // P buffers: written by all softmax warps / its PV MMAs are done
     uint64_t q_ready, drained;
     uint32_t tmem_base, fail, pad[2];
-    float scales[4][16];                       // per stage: 8 K scales, 8 V scales (normalised) of the tile's blocks
+    float scales[4][16];                       // per cached tile (mod 4): 8 K scales, 8 V scales (normalised) of the tile's blocks
     float vmax_part[SM_WARPS];
     // Exchange area, one use at a time: q_inv[query tile][row] before the first tile; then per step the splits' row maxima
     // [split][row]; then the splits' row sums [split][row] in the epilogue.
@@ -134,7 +135,9 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     constexpr int KV_TILE = PTILE * ES;                     // K (or V) of one tile of 128 tokens
     constexpr int Q_BYTES = 2 * PTILE, P_BYTES = FP8 ? PT * PTILE : 2 * PTILE;     // per query tile
     constexpr int KSTEPS = 4 * ES;
-    constexpr int NST = 2;                                  // K/V tiles in flight
+    // K and V tiles in flight (separate rings: a K tile is free again after its QK MMAs, a V tile after its PV MMAs).  Two query tiles of
+    // F16 operands leave room for one of each.
+    constexpr int NSK = (!FP8 && NQT == 2) ? 1 : 2, NSV = NSK;
     constexpr uint32_t IDESC_QK = instr_desc2(0u, 0u, 0u, 0u, 128u);
     constexpr uint32_t IDESC_PV = instr_desc2(FP8 ? 1u : 0u, 0u, 0u, 1u, 128u);      // A = P (E5M2 / F16, K-major), B = V (MN-major)
     constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -163,16 +166,16 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     PControl* c = reinterpret_cast<PControl*>(smem);
     unsigned char* q_tile = smem + CTRL;                    // NQT tiles
     unsigned char* p_tile = q_tile + NQT * Q_BYTES;         // NQT buffers
-    unsigned char* k_ring = p_tile + NQT * P_BYTES;         // NST stages of K, then NST stages of V
-    unsigned char* v_ring = k_ring + NST * KV_TILE;
+    unsigned char* k_ring = p_tile + NQT * P_BYTES;         // NSK stages of K, then NSV stages of V
+    unsigned char* v_ring = k_ring + NSK * KV_TILE;
     const volatile uint32_t* fail_word = &c->fail;
 
     if (tid == 0) {
-        for (int s = 0; s < 4; s++) {
-            mbar_init(c->kv_full + s, 1);
-            mbar_init(c->kv_empty + s, 1);
-        }
         for (int s = 0; s < 2; s++) {
+            mbar_init(c->k_full + s, 1);
+            mbar_init(c->k_empty + s, 1);
+            mbar_init(c->v_full + s, 1);
+            mbar_init(c->v_empty + s, 1);
             mbar_init(c->s_full + s, 1);
             mbar_init(c->s_free + s, SM_WARPS / NQT);
             mbar_init(c->p_full + s, SM_WARPS / NQT);
@@ -215,9 +218,9 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     if (warp == SM_WARPS) {
         // ---- producer: the tile's blocks, one lane per block: K and V boxes of this kv head, the block's two scales ----
         bool ok = c->fail == 0;
-        uint32_t why = 4u, issued = 0;
+        uint32_t why = 4u, issued = 0, issued_k = 0;
         for (uint32_t j = 0; j < n_tiles && ok; j++) {
-            const uint32_t st = j % NST, nb = min(8u, n_blocks - j * 8u);
+            const uint32_t sk = j % NSK, sv = j % NSV, nb = min(8u, n_blocks - j * 8u);
             uint32_t blk = 0;
             if (lane < nb) {
                 blk = a.table[j * 8u + lane];
@@ -228,37 +231,48 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             }
             if (__any_sync(0xFFFFFFFFu, why == 2u)) why = 2u;      // whichever lane met the bad id, lane 0 reports it
             ok = __all_sync(0xFFFFFFFFu, ok);
-            if (ok && lane == 0 && j >= (uint32_t)NST) ok = mbar_wait(c->kv_empty + st, ((j / NST) - 1u) & 1u, fail_word);
+            // K first: its stage frees as soon as the QK MMAs of the tile that held it are done
+            if (ok && lane == 0 && j >= (uint32_t)NSK) ok = mbar_wait(c->k_empty + sk, ((j / NSK) - 1u) & 1u, fail_word);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
             if (!ok) break;
-            if (lane < 8) {
+            if (lane < 8) {                                  // the scales of tile j are read until its softmax ends: four slots outlast any stage
                 float ks = 1.0f, vs = 1.0f;
                 if (lane < nb && a.k_scales) {
                     ks = a.k_scales[(size_t)blk * PHKV + kvh];
                     vs = a.v_scales[(size_t)blk * PHKV + kvh] * v_down;
                 }
-                c->scales[st][lane] = ks;
-                c->scales[st][8 + lane] = vs;
+                c->scales[j & 3u][lane] = ks;
+                c->scales[j & 3u][8 + lane] = vs;
             }
             __syncwarp();
-            if (lane == 0) mbar_expect_tx(c->kv_full + st, nb * 2u * (PBS * 128u) * ES);
+            if (lane == 0) mbar_expect_tx(c->k_full + sk, nb * (PBS * 128u) * ES);
             __syncwarp();
             if (lane < nb) {
-                const uint32_t kd = smem_u32(k_ring + (size_t)st * KV_TILE) + lane * (PBS * 128u);
-                const uint32_t vd = smem_u32(v_ring + (size_t)st * KV_TILE) + lane * (PBS * 128u);
+                const uint32_t kd = smem_u32(k_ring + (size_t)sk * KV_TILE) + lane * (PBS * 128u);
 #pragma unroll
-                for (int cg = 0; cg < ES; cg++) {
-                    tma_head_rows(kd + cg * PTILE, &map_k, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->kv_full + st);
-                    tma_head_rows(vd + cg * PTILE, &map_v, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->kv_full + st);
-                }
+                for (int cg = 0; cg < ES; cg++) tma_head_rows(kd + cg * PTILE, &map_k, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->k_full + sk);
+            }
+            issued_k = j + 1;
+            if (lane == 0 && j >= (uint32_t)NSV) ok = mbar_wait(c->v_empty + sv, ((j / NSV) - 1u) & 1u, fail_word);
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(c->v_full + sv, nb * (PBS * 128u) * ES);
+            __syncwarp();
+            if (lane < nb) {
+                const uint32_t vd = smem_u32(v_ring + (size_t)sv * KV_TILE) + lane * (PBS * 128u);
+#pragma unroll
+                for (int cg = 0; cg < ES; cg++) tma_head_rows(vd + cg * PTILE, &map_v, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->v_full + sv);
             }
             issued = j + 1;
         }
         if (!ok && lane == 0) {
             atomicCAS(&c->fail, 0u, why);
-            for (uint32_t j = issued > (uint32_t)NST ? issued - NST : 0u; j < issued; j++)   // copies still in flight get a bounded chance to land
+            for (uint32_t j = issued_k > (uint32_t)NSK ? issued_k - NSK : 0u; j < issued_k; j++)   // copies still in flight get a bounded chance to land
                 for (uint32_t it = 0; it < (1u << 20); it++)
-                    if (mbar_test(c->kv_full + j % NST, (j / NST) & 1u)) break;
+                    if (mbar_test(c->k_full + j % NSK, (j / NSK) & 1u)) break;
+            for (uint32_t j = issued > (uint32_t)NSV ? issued - NSV : 0u; j < issued; j++)
+                for (uint32_t it = 0; it < (1u << 20); it++)
+                    if (mbar_test(c->v_full + j % NSV, (j / NSV) & 1u)) break;
         }
     } else if (warp == SM_WARPS + 1) {
         // ---- MMA issuer.  Whichever is ready goes next, per query tile: the scores of its next cached tile (K has landed, its S buffer has
@@ -268,22 +282,20 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             const uint32_t q_lo = smem_u32(q_tile) >> 4, p_lo = smem_u32(p_tile) >> 4;
             const uint32_t kr_lo = smem_u32(k_ring) >> 4, vr_lo = smem_u32(v_ring) >> 4;
             bool ok = c->fail == 0 && mbar_wait(&c->q_ready, 0u, fail_word);
-            uint32_t jq[NQT], jp[NQT], pv_left[NST], idle = 0, todo = 0;
+            uint32_t jq[NQT], jp[NQT], qk_left[2] = {0, 0}, pv_left[2] = {0, 0}, idle = 0, todo = 0;
 #pragma unroll
             for (int x = 0; x < NQT; x++) {
                 jq[x] = jp[x] = 0;
                 todo += n_tiles_x[x];
             }
-#pragma unroll
-            for (int s = 0; s < NST; s++) pv_left[s] = 0;
             while (ok && todo) {
                 bool did = false;
 #pragma unroll
                 for (int x = 0; x < NQT; x++) {
                     if (jq[x] < n_tiles_x[x]) {
-                        const uint32_t j = jq[x], st = j % NST, sb = s_index(x, j);
+                        const uint32_t j = jq[x], st = j % NSK, sb = s_index(x, j);
                         const bool s_ok = NQT == 2 ? (j < 1 || mbar_test(c->s_free + sb, (j - 1u) & 1u)) : (j < 2 || mbar_test(c->s_free + sb, ((j >> 1) - 1u) & 1u));
-                        if (s_ok && mbar_test(c->kv_full + st, (j / NST) & 1u)) {
+                        if (s_ok && mbar_test(c->k_full + st, (j / NSK) & 1u)) {
                             tc_fence_after();
                             const uint32_t k_lo = kr_lo + st * (KV_TILE >> 4), qx_lo = q_lo + x * (Q_BYTES >> 4);
 #pragma unroll
@@ -295,13 +307,21 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                                     mma<FP8>(tmem + sb * 128u, DESC_K | (qx_lo + a_off), DESC_K | (k_lo + b_off), IDESC_QK, (term > 0 || ks > 0) ? 1u : 0u);
                                 }
                             tc_commit(c->s_full + sb);
+                            // the K stage goes back to the producer behind the QK of the last query tile that reads this cached tile
+                            uint32_t k_readers = 0;
+#pragma unroll
+                            for (int y = 0; y < NQT; y++) k_readers += j < n_tiles_x[y] ? 1u : 0u;
+                            if (++qk_left[st] == k_readers) {
+                                tc_commit(c->k_empty + st);
+                                qk_left[st] = 0;
+                            }
                             jq[x]++;
                             did = true;
                         }
                     }
                     if (jp[x] < jq[x]) {
-                        const uint32_t j = jp[x], st = j % NST;
-                        if (mbar_test(c->p_full + x, j & 1u)) {
+                        const uint32_t j = jp[x], st = j % NSV;
+                        if (mbar_test(c->p_full + x, j & 1u) && mbar_test(c->v_full + st, (j / NSV) & 1u)) {
                             tc_fence_after();
                             const uint32_t v_lo = vr_lo + st * (KV_TILE >> 4), pj_lo = p_lo + x * (P_BYTES >> 4);
 #pragma unroll
@@ -317,7 +337,7 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
 #pragma unroll
                             for (int y = 0; y < NQT; y++) readers += j < n_tiles_x[y] ? 1u : 0u;
                             if (++pv_left[st] == readers) {
-                                tc_commit(c->kv_empty + st);
+                                tc_commit(c->v_empty + st);
                                 pv_left[st] = 0;
                             }
                             jp[x]++;
@@ -426,7 +446,7 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         unsigned char* pj = p_tile + x * P_BYTES;
         const uint32_t tmem_o = tmem + 256u + x * 128u + lane_base + col0;
         for (uint32_t j = 0; j < my_tiles; j++) {
-            const uint32_t sb = s_index(x, j), st = j % NST, t0 = j * KT;
+            const uint32_t sb = s_index(x, j), st = j & 3u, sv = j % NSV, t0 = j * KT;
             if (ok) {
                 ok = mbar_wait(c->s_full + sb, s_phase(j) & 1u, fail_word);
                 if (!ok) atomicCAS(&c->fail, 0u, 4u);
@@ -520,8 +540,12 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
                 }
                 // rows of the V tile past the last attended token hold whatever the pool (or an earlier tile) left there: 0 * NaN must not
                 // reach O.  Each group clears them before its own PV (the same zeros, whoever comes first).
-                if (split == 0 && t0 + KT > kv_limit && t0 + r >= kv_limit) {
-                    unsigned char* vt = v_ring + (size_t)st * KV_TILE;
+                if (split == 0 && t0 + KT > kv_limit) {               // uniform over the warp; the copies of V must have landed first
+                    ok = mbar_wait(c->v_full + sv, (j / NSV) & 1u, fail_word);
+                    if (!ok) atomicCAS(&c->fail, 0u, 4u);
+                }
+                if (ok && split == 0 && t0 + KT > kv_limit && t0 + r >= kv_limit) {
+                    unsigned char* vt = v_ring + (size_t)sv * KV_TILE;
 #pragma unroll
                     for (int cg = 0; cg < ES; cg++)
 #pragma unroll
@@ -586,7 +610,8 @@ bool make_head_map(CUtensorMap* map, uint64_t base, uint32_t total_blocks, uint3
 
 template <bool FP8, int NQT> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
     constexpr int ES = FP8 ? 1 : 2;
-    constexpr size_t smem = CTRL + NQT * (2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE) + 2 * 2 * (size_t)PTILE * ES;
+    constexpr size_t stages = (!FP8 && NQT == 2) ? 1 : 2;
+    constexpr size_t smem = CTRL + NQT * (2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE) + 2 * stages * (size_t)PTILE * ES;
     static_assert(smem <= 227 * 1024, "shared memory of one CTA");
     auto kernel = prefill_attn_tc<FP8, NQT>;
     static std::mutex mu;
@@ -618,9 +643,12 @@ cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const P
     CUtensorMap mk, mv;
     const uint32_t es = fp8 ? 1u : 2u;
     if (!make_head_map(&mk, k_layer, a.total_blocks, es) || !make_head_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
-    // E4M3 pool: two query tiles per CTA taking turns; an F16 pool's tiles leave shared memory for one (a.single_tile forces one, for comparison)
-    if (fp8) return a.single_tile ? launch_prefill<true, 1>(mk, mv, a, st) : launch_prefill<true, 2>(mk, mv, a, st);
-    return launch_prefill<false, 1>(mk, mv, a, st);
+    // Two query tiles per CTA, their softmax groups out of step, unless a.single_tile asks for one.  Measured on B200 (useful TFLOP/s,
+    // one tile / two tiles): E4M3 pool 270 / 290 at 2 048 tokens, 395 / 461 at 4 096, 471 / 661 at 8 192; F16 pool (whose two-tile form
+    // has one K and one V tile in flight instead of two) 339 / 305, 487 / 458, 578 / 617: two tiles from 6 144 tokens on.
+    const bool two = a.single_tile == 2u || (a.single_tile == 0u && (fp8 || a.n_tokens >= 6144u));
+    if (fp8) return two ? launch_prefill<true, 2>(mk, mv, a, st) : launch_prefill<true, 1>(mk, mv, a, st);
+    return two ? launch_prefill<false, 2>(mk, mv, a, st) : launch_prefill<false, 1>(mk, mv, a, st);
 }
 
 }  // namespace tkv_tc
@@ -670,7 +698,7 @@ extern "C" int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefil
     a.total_blocks = pool->total_blocks;
     a.q_scale = p->sm_scale * 1.4426950408889634f;
     a.status = reinterpret_cast<uint32_t*>(p->status);
-    a.single_tile = (p->flags & TKV_PREFILL_SINGLE_TILE) ? 1u : 0u;
+    a.single_tile = (p->flags & TKV_PREFILL_SINGLE_TILE) ? 1u : (p->flags & TKV_PREFILL_TWO_TILES) ? 2u : 0u;
     const cudaError_t e = tkv_tc::launch_prefill(pool->dtype == TKV_DTYPE_E4M3, kp, vp, a, static_cast<cudaStream_t>(stream));
     if (dev != pool->device) cudaSetDevice(dev);
     if (e != cudaSuccess) return tkv_internal::set_error(TKV_ERR_CUDA, (int32_t)e, cudaGetErrorString(e));

@@ -248,7 +248,7 @@ def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faul
     np.testing.assert_array_equal(again, want)
 
 
-@pytest.mark.parametrize("dtype,flags", [("e4m3", 0), ("e4m3", N.PREFILL_SINGLE_TILE), ("f16", 0)])
+@pytest.mark.parametrize("dtype,flags", [("e4m3", 0), ("e4m3", N.PREFILL_SINGLE_TILE), ("f16", 0), ("f16", N.PREFILL_TWO_TILES)])
 @pytest.mark.parametrize("start,t", [(0, 40), (45, 70), (250, 33), (0, 300), (100, 64), (3, 129)])
 def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, flags, start, t):
     """The prefill-side twin: T new tokens of one sequence, token t attends to positions 0 .. start + t.  Ragged against
@@ -274,6 +274,26 @@ def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, flags, start
     kv = np.arange(start + 1, start + t + 1, dtype=np.uint32)
     want = oracle.paged_decode_attention(hd, 0, q.cpu().numpy(), tables, kv, 1.0 / np.sqrt(128.0))
     close(got, want, v_max_per_dim(hs, 0))
+
+
+def test_prefill_attention_f16_long_prompt_takes_the_two_tile_form(H):
+    """An F16 pool switches to two query tiles per CTA from 6 144 new tokens on (one K and one V tile in flight): sampled query
+    tokens of a 6 400-token prompt against the oracle."""
+    import torch
+    t = 6400
+    w = W.Workload("prefill-long", 1, 8, 128, 16, 512, 512, np.array([t], dtype=np.uint32), seed=73).build_tables()
+    hs, _ = host_pools(w)
+    dd = to_device_pool(hs, "f16")
+    q = torch.randn((t, 32, 128), generator=torch.Generator().manual_seed(19)).cuda()
+    row = torch.from_numpy(w.src_tables.astype(np.int64)).to(torch.int32).cuda()[0]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = H.prefill_attention(dd, 0, q, row, 0, status=status)
+    assert int(status.item()) == 0
+    pick = [0, 31, 32, 63, 64, 2047, 4100, 6143, 6399]
+    tables = np.repeat(w.src_tables.reshape(1, -1), len(pick), axis=0)
+    kv = np.array([p + 1 for p in pick], dtype=np.uint32)
+    want = oracle.paged_decode_attention(hs, 0, q[pick].cpu().numpy(), tables, kv, 1.0 / np.sqrt(128.0))
+    close(got[pick].cpu().numpy(), want, v_max_per_dim(hs, 0))
 
 
 def test_prefill_attention_refuses_other_geometries_and_foreign_blocks(H):
