@@ -51,7 +51,7 @@ struct AttnArgs {
     uint64_t block_stride;        // bytes
     uint32_t row_stride;          // bytes between token rows
     uint32_t n_q_heads, n_kv_heads, group, table_stride, n_splits, split_tokens;   // n_splits counts partial slots
-    uint32_t parts_per_split;     // partial slots one token range writes (2 in the whole-block form)
+    uint32_t parts_per_split;     // partial slots one token range writes (one per softmax group in the tcgen05 form)
     float q_scale;                // softmax scale * log2(e), folded into q
     uint32_t max_kv_len;          // the host's bound: sized the grid, the table rows and the scratch; device lengths are clamped to it
     uint32_t total_blocks;        // blocks in the pool: a table entry at or above it is never dereferenced
@@ -848,10 +848,10 @@ extern "C" {
 
 uint64_t tkv_decode_attn_scratch_bytes(uint32_t n_seqs, uint32_t n_q_heads, uint32_t head_dim, uint32_t max_kv_len,
                                        uint32_t split_tokens) {
-    // sized for the smallest token range the library may choose (64) unless the caller fixes one; two partial results per
-    // range (the tcgen05 kernel's two softmax groups each write their own)
+    // sized for the smallest token range the library may choose (64) unless the caller fixes one; one partial result per range and
+    // softmax group of the tcgen05 kernel
     if (split_tokens == 0) split_tokens = 64;
-    return 2ull * n_seqs * n_q_heads * splits_for(max_kv_len, split_tokens) * (head_dim + 2) * sizeof(float);
+    return (uint64_t)tkv_tc::PARTS_PER_RANGE * n_seqs * n_q_heads * splits_for(max_kv_len, split_tokens) * (head_dim + 2) * sizeof(float);
 }
 
 int32_t tkv_selfcheck_tensor_cores(uint64_t mismatches[4]) {
@@ -975,8 +975,8 @@ int32_t tkv_decode_attn_enqueue(const TkvPool* pool, const TkvDecodeAttn* d, voi
             t.q_scale = a.q_scale;
             t.status = a.status;
             e = tkv_tc::launch(pool->dtype == TKV_DTYPE_E4M3, a.group, kp, vp, t, st);
-            a.n_splits = 2u * n_splits;              // partial slots per (sequence, kv head): two per token range
-            a.parts_per_split = 2;
+            a.n_splits = tkv_tc::PARTS_PER_RANGE * n_splits;   // partial slots per (sequence, kv head): one per token range and softmax group
+            a.parts_per_split = tkv_tc::PARTS_PER_RANGE;
             if (e == cudaSuccess) {
                 decode_attn_combine<<<dim3(d->n_q_heads, d->n_seqs), D, 0, st>>>(a);
                 e = cudaGetLastError();

@@ -58,6 +58,9 @@ constexpr float SHIFT = 9.0f;                              // probabilities ente
 // range; each has its own S^T buffers, P^T buffers, O^T accumulator, running maxima and row sums, and writes its own
 // partial result (the split-merge kernel folds them together with the other ranges').
 constexpr int MAX_ITEMS = 128;        // token ranges one CTA walks
+constexpr int NG = (int)PARTS_PER_RANGE;   // softmax groups, taking the blocks of a range in turn
+constexpr int SBUF = NG == 2 ? 2 : 1; // S^T buffers per group (tensor memory: NG * (O^T + SBUF * S^T) <= 512 columns)
+constexpr int ATHREADS = (4 * NG + 3) * 32;
 struct Group {
     uint64_t s_full[2], s_free[2];    // S^T buffers: QK done / every warp of the group has read it
     uint64_t p_full[2], p_free[2];    // P^T buffers: written / the PV MMA has read it
@@ -73,20 +76,22 @@ struct Control {
     uint32_t tmem_base, fail, n_items, pad;
     float q_inv[2][32];               // per range parity: what undoes the power-of-two scale of each query head
     float scales[8][16];              // per V slot: 8 K scales, 8 V scales
-    Group g[2];
+    Group g[NG];
     uint32_t item_id[MAX_ITEMS];      // sequence * ranges per sequence + range
     uint16_t item_blocks[MAX_ITEMS];
 };
-static_assert(sizeof(Control) <= 5120, "control block");
+static_assert(sizeof(Control) <= 6144, "control block");
+constexpr int ACTRL = 6144;
 
 // A persistent CTA per SM walks token ranges (sequence, range) c, c + gridDim.x, ...: barriers, tensor memory and the ring
 // are set up once, and the producer runs ahead across range boundaries, so the ring never drains between ranges.
 template <bool FP8, int G>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(ATHREADS, 1)
 decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a, const uint32_t n_k, const uint32_t n_v) {
     constexpr int ES = FP8 ? 1 : 2;                    // bytes per pool element = 128-byte column groups per row
     constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;   // terms a query element / a probability is split into
-    constexpr int PBUF = FP8 ? 2 : 1;                  // P^T buffers per group
+    constexpr int PBUF = (FP8 && NG == 2) ? 2 : 1;     // P^T buffers per group
+    constexpr uint32_t GCOLS = NG == 2 ? 256u : 160u, S_OFF = NG == 2 ? 128u : 96u;   // a group's tensor-memory columns: O^T at 0, S^T behind it
     constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS;   // columns per kv head in S^T and in O^T (N must be a multiple of 16)
     constexpr int CP = (G * PT < 2) ? 2 : G * PT;
     constexpr int NQ = HKV * CQ, NP = HKV * CP;
@@ -105,13 +110,13 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t ranges = a.n_splits;                // token ranges per sequence
-    const uint32_t n_parts = 2u * a.n_splits;          // partial slots per (sequence, kv head): one per range and group
+    const uint32_t n_parts = (uint32_t)NG * a.n_splits;  // partial slots per (sequence, kv head): one per range and group
 
     extern __shared__ __align__(1024) unsigned char smem[];
     Control* c = reinterpret_cast<Control*>(smem);
-    unsigned char* q_tile = smem + 5120;                          // Q^T of the current range
+    unsigned char* q_tile = smem + ACTRL;                          // Q^T of the current range
     unsigned char* p_tile = q_tile + QT_BYTES;                    // P^T: PBUF buffers per group
-    unsigned char* k_ring = p_tile + 2 * PBUF * PT_BYTES;         // n_k K tiles, then n_v V tiles
+    unsigned char* k_ring = p_tile + NG * PBUF * PT_BYTES;         // n_k K tiles, then n_v V tiles
     unsigned char* v_ring = k_ring + (size_t)n_k * KV_TILE;
     const volatile uint32_t* fail_word = &c->fail;
 
@@ -122,7 +127,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             mbar_init(c->v_full + s, 1);
             mbar_init(c->v_empty + s, 1);
         }
-        for (int g = 0; g < 2; g++)
+        for (int g = 0; g < NG; g++)
             for (int b = 0; b < 2; b++) {
                 mbar_init(c->g[g].s_full + b, 1);
                 mbar_init(c->g[g].s_free + b, 4);
@@ -138,11 +143,11 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         c->fail = (smem_u32(smem) & 1023u) ? 2u : 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < 128) c->g[tid >> 6].block_max[(tid >> 5) & 1][tid & 31] = ordered(-INFINITY);
-    if (warp == 9) {                                               // tensor memory: 512 columns, this CTA alone on its SM
+    if (tid < 64 * NG) c->g[tid >> 6].block_max[(tid >> 5) & 1][tid & 31] = ordered(-INFINITY);
+    if (warp == 4 * NG + 1) {                                      // tensor memory: 512 columns, this CTA alone on its SM
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&c->tmem_base)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    } else if (warp == 8) {
+    } else if (warp == 4 * NG) {
         // this CTA's ranges: the non-empty (sequence, range) pairs are ranked in sequence order and CTA c takes ranks c, c + gridDim.x,
         // ..., so every CTA gets the same number of ranges (one more or less) however ragged the lengths are
         uint32_t count = 0, before = 0;
@@ -176,9 +181,9 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             before += __shfl_sync(0xFFFFFFFFu, incl, 31);
         }
         if (lane == 0) c->n_items = count;
-    } else if (warp < 8) {
+    } else if (warp < 4 * NG) {
         // zero the P^T buffers once: entries of other kv heads stay zero for good
-        for (uint32_t i = tid; i < (QT_BYTES + 2 * PBUF * PT_BYTES) / 16; i += 256) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
+        for (uint32_t i = tid; i < (QT_BYTES + NG * PBUF * PT_BYTES) / 16; i += 128 * NG) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
         fence_async_smem();
     }
     tc_fence_before();
@@ -186,7 +191,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = c->tmem_base, n_items = c->n_items;
 
-    if (warp == 8) {
+    if (warp == 4 * NG) {
         // ---- producer: every block of every range of this CTA, in order; lane 0 issues the copies ----
         uint32_t k = 0, issued = 0, why = 4u;
         bool ok = c->fail == 0;
@@ -237,22 +242,22 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 for (uint32_t it = 0; it < (1u << 20); it++)
                     if (mbar_test(c->v_full + j % n_v, (j / n_v) & 1u) && (j + n_k < issued || mbar_test(c->k_full + j % n_k, (j / n_k) & 1u))) break;
         }
-    } else if (warp == 9) {
+    } else if (warp == 4 * NG + 1) {
         // ---- QK issuer: S^T of block i of a range goes to group i & 1, into that group's next S^T buffer ----
         if (lane == 0) {
             const uint32_t q_lo = smem_u32(q_tile) >> 4, kr_lo = smem_u32(k_ring) >> 4;
-            uint32_t k = 0, gq[2] = {0, 0};
+            uint32_t k = 0, gq[NG] = {};
             bool ok = c->fail == 0;
             for (uint32_t n = 0; n < n_items && ok; n++) {
                 const uint32_t n_blk = c->item_blocks[n];
                 ok = mbar_wait(&c->q_full, n & 1u, fail_word);                    // this range's Q^T is in place
                 for (uint32_t i = 0; i < n_blk && ok; i++, k++) {
-                    const uint32_t g = i & 1u, sb = gq[g] & 1u, sk = k % n_k;
+                    const uint32_t g = i % NG, sb = gq[g] % SBUF, sk = k % n_k;
                     ok = mbar_wait(c->k_full + sk, (k / n_k) & 1u, fail_word);
-                    if (ok && gq[g] >= 2) ok = mbar_wait(c->g[g].s_free + sb, ((gq[g] >> 1) - 1u) & 1u, fail_word);
+                    if (ok && gq[g] >= (uint32_t)SBUF) ok = mbar_wait(c->g[g].s_free + sb, ((gq[g] / SBUF) - 1u) & 1u, fail_word);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem + g * 256u + 128u + sb * 64u, k_lo = kr_lo + sk * (KV_TILE >> 4);
+                    const uint32_t d = tmem + g * GCOLS + S_OFF + sb * 64u, k_lo = kr_lo + sk * (KV_TILE >> 4);
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ks++)
                         mma<FP8>(d, DESC_K | (k_lo + (ks / 4) * (TILE >> 4) + (ks % 4) * 2),
@@ -269,24 +274,24 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (mbar_test(c->drained, 0u)) break;
         }
         __syncwarp();
-    } else if (warp == 10) {
+    } else if (warp == 4 * NG + 2) {
         // ---- PV issuer: O^T of the block's group += V^T P^T as soon as the group has written P^T ----
         if (lane == 0) {
             const uint32_t vr_lo = smem_u32(v_ring) >> 4, p_lo = smem_u32(p_tile) >> 4;
-            uint32_t k = 0, gp[2] = {0, 0};
+            uint32_t k = 0, gp[NG] = {};
             bool ok = c->fail == 0;
             for (uint32_t n = 0; n < n_items && ok; n++) {
                 const uint32_t n_blk = c->item_blocks[n];
                 for (uint32_t i = 0; i < n_blk && ok; i++, k++) {
-                    const uint32_t g = i & 1u, pb = gp[g] % PBUF, sv = k % n_v;
+                    const uint32_t g = i % NG, pb = gp[g] % PBUF, sv = k % n_v;
                     ok = mbar_wait(c->g[g].p_full + pb, (gp[g] / PBUF) & 1u, fail_word) && mbar_wait(c->v_full + sv, (k / n_v) & 1u, fail_word);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t v_lo = vr_lo + sv * (KV_TILE >> 4), pg_lo = p_lo + (g * PBUF + pb) * (PT_BYTES >> 4);
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ks++)         // V^T MN-major: 32 / ES block rows of 128 B per step; P^T K-major: 32 bytes of the row per step
-                        mma<FP8>(tmem + g * 256u, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
-                                 IDESC_PV, (i >= 2 || ks > 0) ? 1u : 0u);            // a group's first block of a range starts its accumulator afresh
+                        mma<FP8>(tmem + g * GCOLS, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
+                                 IDESC_PV, (i >= (uint32_t)NG || ks > 0) ? 1u : 0u);            // a group's first block of a range starts its accumulator afresh
                     tc_commit(c->v_empty + sv);
                     tc_commit(c->g[g].p_free + pb);
                     gp[g]++;
@@ -304,7 +309,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         const uint32_t grp = warp >> 2, t = tid & 127u, kvh = t & 7u, tok = t >> 3;
         Group* gs = &c->g[grp];
         const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
-        const uint32_t tmem_o = tmem + grp * 256u, tmem_s = tmem_o + 128u;
+        const uint32_t tmem_o = tmem + grp * GCOLS, tmem_s = tmem_o + S_OFF;
         uint32_t p_off[G][PT];                                      // where this row's probabilities go in P^T (row = kv head, term, query head; column = this row)
 #pragma unroll
         for (int g = 0; g < G; g++)
@@ -387,7 +392,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         for (uint32_t n = 0; n < n_items; n++) {
             const uint32_t id = c->item_id[n], seq = id / ranges, split = id - seq * ranges, n_blk = c->item_blocks[n];
             const uint32_t kv_len = min(a.kv_lens[seq], a.max_kv_len), b_begin = split * (a.split_tokens / BS);
-            const uint32_t n_mine = n_blk > grp ? (n_blk - grp + 1u) / 2u : 0u;
+            const uint32_t n_mine = n_blk > grp ? (n_blk - grp + (uint32_t)NG - 1u) / (uint32_t)NG : 0u;
             if (grp == 0 && n + 1 < n_items) q_fetch(n + 1);        // the next range's query rows, on their way while this one is worked
             float m_used[G], l[G], q_inv[G];
 #pragma unroll
@@ -398,13 +403,13 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (t < 32) gs->m_used[t] = -INFINITY;
             asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
             for (uint32_t j = 0; j < n_mine; j++, gj++) {
-                const uint32_t i = 2u * j + grp, k = base_k + i, s = k % n_v, b = gj & 1u, pb = gj % PBUF;
+                const uint32_t i = (uint32_t)NG * j + grp, k = base_k + i, s = k % n_v, b = gj & 1u, sbuf = gj % SBUF, pb = gj % PBUF;
                 const uint32_t n_valid = min((uint32_t)BS, kv_len - (b_begin + i) * BS);
                 const bool valid = tok < n_valid;
                 float sc[G];                                        // this row's scores against its own kv head's query heads (log2 domain)
                 float inv_vs = 1.0f;
                 if (ok) {
-                    ok = mbar_wait(gs->s_full + b, (gj >> 1) & 1u, fail_word) && mbar_wait(c->v_full + s, (k / n_v) & 1u, fail_word);
+                    ok = mbar_wait(gs->s_full + sbuf, (gj / SBUF) & 1u, fail_word) && mbar_wait(c->v_full + s, (k / n_v) & 1u, fail_word);
                     if (!ok) atomicCAS(&c->fail, 0u, 4u);
                 }
                 if (ok) {
@@ -414,20 +419,21 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         for (int g = 0; g < G; g++) q_inv[g] = c->q_inv[n & 1u][kvh * G + g];
                     }
                     float part[CQ];
+                    // the whole row of S^T in one load (two 32-column loads with their waits cost the E4M3 path 4 us per layer at 16 prompts);
+                    // a thread keeps the CQ columns of its own kv head
                     uint32_t r[NQ];
-                    if (NQ == 64) tmem_ld64(tmem_s + b * 64u + lane_base, reinterpret_cast<uint32_t(&)[64]>(r));
-                    else tmem_ld32(tmem_s + b * 64u + lane_base, reinterpret_cast<uint32_t(&)[32]>(r));
+                    if (NQ == 64) tmem_ld64(tmem_s + sbuf * 64u + lane_base, reinterpret_cast<uint32_t(&)[64]>(r));
+                    else tmem_ld32(tmem_s + sbuf * 64u + lane_base, reinterpret_cast<uint32_t(&)[32]>(r));
                     tmem_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(gs->s_free + b);
-                    // keep the CQ columns of this row's kv head
 #pragma unroll
                     for (int h = 0; h < HKV; h++)
                         if ((uint32_t)h == kvh) {
 #pragma unroll
                             for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[h * CQ + q]);
                         }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gs->s_free + sbuf);
                     float ks = 1.0f, lv = 0.0f;
                     if (a.k_scales) {
                         ks = c->scales[s][kvh];
@@ -569,7 +575,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             asm volatile("bar.sync %0, 128;" ::"r"(1u + grp) : "memory");
             if (ok) {
                 const float down = __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
-                const uint32_t part_slot = split * 2u + grp;
+                const uint32_t part_slot = split * (uint32_t)NG + grp;
                 float* pr0 = a.partial + (((size_t)seq * HKV * n_parts + part_slot) * G) * (D + 2);
                 const size_t head_stride = (size_t)n_parts * G * (D + 2);
                 if (t < HKV * G && t < a.n_q_heads) {               // one thread per query head: its maximum and row sum (-inf and 0 for a group without blocks)
@@ -604,7 +610,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 4 * NG + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
@@ -726,9 +732,9 @@ bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t tot
 }
 
 template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, cudaStream_t st) {
-    constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = FP8 ? 2 : 1;
+    constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = (FP8 && NG == 2) ? 2 : 1;
     constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS, CP = (G * PT < 2) ? 2 : G * PT;
-    constexpr size_t fixed = 5120 + (size_t)HKV * CQ * 128 * ES + 2 * (size_t)PBUF * HKV * CP * 128 * ES;
+    constexpr size_t fixed = ACTRL + (size_t)HKV * CQ * 128 * ES + NG * (size_t)PBUF * HKV * CP * 128 * ES;
     constexpr size_t tile = (size_t)TILE * ES;              // K or V of one block
     const uint32_t tiles = (uint32_t)((227 * 1024 - fixed) / tile);
     // a K tile is held from its arrival to the end of its QK MMAs, a V tile through the softmax of its block as well: most slots go to V
@@ -755,7 +761,7 @@ template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, 
     // one persistent CTA per SM walks its share of the (sequence, range) list; more CTAs only when a share would not fit its list
     const uint64_t total = (uint64_t)a.n_seqs * a.n_splits;
     const uint64_t grid = std::max<uint64_t>(std::min<uint64_t>(total, (uint64_t)sms[dev]), (total + (MAX_ITEMS - 32) - 1) / (MAX_ITEMS - 32));
-    kernel<<<(uint32_t)grid, 352, smem, st>>>(mk, mv, a, n_k, n_v);
+    kernel<<<(uint32_t)grid, ATHREADS, smem, st>>>(mk, mv, a, n_k, n_v);
     return cudaGetLastError();
 }
 

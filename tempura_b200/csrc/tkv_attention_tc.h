@@ -5,14 +5,17 @@
 
 namespace tkv_tc {
 
+// partial results one token range writes: one per softmax group of the kernel
+constexpr uint32_t PARTS_PER_RANGE = 2;
+
 struct Args {
     const float* k_scales;        // [total_blocks][8] of this layer, or null
     const float* v_scales;
     const float* q;               // [n_seqs][n_q_heads][128]
     const uint32_t* tables;       // [n_seqs][table_stride]
     const uint32_t* kv_lens;
-    float* partial;               // [n_seqs][8][2 * n_splits][group][128 + 2]: running maximum, row sum, 128 numerators; two parts per
-                                  // token range (the kernel's two softmax groups take alternate blocks and each writes its own)
+    float* partial;               // [n_seqs][8][PARTS_PER_RANGE * n_splits][group][128 + 2]: running maximum, row sum, 128 numerators;
+                                  // the kernel's softmax groups take the blocks of a range in turn and each writes its own part
     uint32_t n_seqs, n_q_heads, table_stride, n_splits, split_tokens, max_kv_len, total_blocks;
     float q_scale;                // softmax scale * log2(e)
     uint32_t* status;             // optional device word: first failure wins

@@ -137,7 +137,7 @@ def test_decode_attention_arguments_validate_without_a_gpu():
     assert N.lib().tkv_decode_attn_enqueue(C.byref(pool.c_struct()), C.byref(args), None) == N.ERR_INVALID_CONFIG       # layer 5 of 1
     f32 = fake_pool(layers=1, heads=8, dim=128, bs=16, dtype="f32")
     assert N.lib().tkv_decode_attn_enqueue(C.byref(f32.c_struct()), C.byref(args), None) == N.ERR_INVALID_CONFIG
-    assert N.lib().tkv_decode_attn_scratch_bytes(16, 32, 128, 4096, 1024) == 2 * 16 * 32 * 4 * 130 * 4    # two partial results per token range
+    assert N.lib().tkv_decode_attn_scratch_bytes(16, 32, 128, 4096, 1024) == 2 * 16 * 32 * 4 * 130 * 4    # one partial result per token range and softmax group
 
 
 def test_unmapped_peer_destination_is_refused_on_the_host():
