@@ -82,7 +82,7 @@ def test_peer_pull_kernel_on_the_decode_gpu_loads_over_nvlink(H, tune):
         assert_pool_equals_host(dst, hd, "peer pull")
     with torch.cuda.device(0):
         assert_pool_equals_host(src, hs, "peer pull (source untouched)")
-    assert plan.stats().peer == 1 and plan.stats().kernel_variant == 1
+    assert plan.stats().peer == 1 and plan.stats().kernel_variant == (N.VARIANT_VECTOR if tune and tune[0] == 16 else N.VARIANT_WIDE)
     # a pull cannot use the bulk-copy pipelines (they would load a peer's memory with the bulk engine) nor cast
     with pytest.raises(N.TkvError):
         H.Plan(src, dst, device_batch(w), None, N.PLAN_PULL | N.PLAN_FORCE_BULK)
