@@ -83,11 +83,26 @@ struct Control {
 static_assert(sizeof(Control) <= 6144, "control block");
 constexpr int ACTRL = 6144;
 
+// Shared-memory shape of the kernel, known at compile time (so that ring positions are divisions by constants, not by kernel arguments):
+// what is fixed, and how many K and V tiles the rest holds.  A K tile is held from its arrival to the end of its QK MMAs, a V tile
+// through the softmax of its block as well: most slots go to V.
+template <bool FP8, int G> struct Shape {
+    static constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = (FP8 && NG == 2) ? 2 : 1;
+    static constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS, CP = (G * PT < 2) ? 2 : G * PT;
+    static constexpr size_t fixed = ACTRL + (size_t)HKV * CQ * 128 * ES + NG * (size_t)PBUF * HKV * CP * 128 * ES;
+    static constexpr size_t tile = (size_t)TILE * ES;              // K or V of one block
+    static constexpr uint32_t tiles = (uint32_t)((227 * 1024 - fixed) / tile);
+    static constexpr uint32_t n_k = FP8 ? 4u : 2u, n_v = tiles - n_k < 8u ? tiles - n_k : 8u;
+    static_assert(tiles >= n_k + 2, "room for the rings");
+    static constexpr size_t smem = fixed + (size_t)(n_k + n_v) * tile;
+};
+
 // A persistent CTA per SM walks token ranges (sequence, range) c, c + gridDim.x, ...: barriers, tensor memory and the ring
 // are set up once, and the producer runs ahead across range boundaries, so the ring never drains between ranges.
 template <bool FP8, int G>
 __global__ void __launch_bounds__(ATHREADS, 1)
-decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a, const uint32_t n_k, const uint32_t n_v) {
+decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a) {
+    constexpr uint32_t n_k = Shape<FP8, G>::n_k, n_v = Shape<FP8, G>::n_v;      // K and V tiles in the rings
     constexpr int ES = FP8 ? 1 : 2;                    // bytes per pool element = 128-byte column groups per row
     constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;   // terms a query element / a probability is split into
     constexpr int PBUF = (FP8 && NG == 2) ? 2 : 1;     // P^T buffers per group
@@ -732,15 +747,7 @@ bool eligible(uint32_t n_kv_heads, uint32_t group, bool has_scales, uint32_t tot
 }
 
 template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, cudaStream_t st) {
-    constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = (FP8 && NG == 2) ? 2 : 1;
-    constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS, CP = (G * PT < 2) ? 2 : G * PT;
-    constexpr size_t fixed = ACTRL + (size_t)HKV * CQ * 128 * ES + NG * (size_t)PBUF * HKV * CP * 128 * ES;
-    constexpr size_t tile = (size_t)TILE * ES;              // K or V of one block
-    const uint32_t tiles = (uint32_t)((227 * 1024 - fixed) / tile);
-    // a K tile is held from its arrival to the end of its QK MMAs, a V tile through the softmax of its block as well: most slots go to V
-    const uint32_t n_k = FP8 ? 4u : 2u, n_v = std::min(8u, tiles - n_k);
-    if (tiles < n_k + 2) return cudaErrorInvalidConfiguration;
-    const size_t smem = fixed + (size_t)(n_k + n_v) * tile;
+    constexpr size_t smem = Shape<FP8, G>::smem;
     auto kernel = decode_attn_tc<FP8, G>;
     static std::mutex mu;
     static bool granted[64] = {};
@@ -761,7 +768,7 @@ template <bool FP8, int G> static cudaError_t launch_one(const CUtensorMap& mk, 
     // one persistent CTA per SM walks its share of the (sequence, range) list; more CTAs only when a share would not fit its list
     const uint64_t total = (uint64_t)a.n_seqs * a.n_splits;
     const uint64_t grid = std::max<uint64_t>(std::min<uint64_t>(total, (uint64_t)sms[dev]), (total + (MAX_ITEMS - 32) - 1) / (MAX_ITEMS - 32));
-    kernel<<<(uint32_t)grid, ATHREADS, smem, st>>>(mk, mv, a, n_k, n_v);
+    kernel<<<(uint32_t)grid, ATHREADS, smem, st>>>(mk, mv, a);
     return cudaGetLastError();
 }
 
