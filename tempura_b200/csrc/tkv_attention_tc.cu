@@ -440,12 +440,18 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     if (NQ == 64) tmem_ld64(tmem_s + sbuf * 64u + lane_base, reinterpret_cast<uint32_t(&)[64]>(r));
                     else tmem_ld32(tmem_s + sbuf * 64u + lane_base, reinterpret_cast<uint32_t(&)[32]>(r));
                     tmem_wait_ld();
+                    // the CQ columns of this row's kv head, picked by halving on the bits of the head number (56 selects instead of 64 moves
+                    // under eight predicates)
+                    {
+                        static_assert(HKV == 8, "three halvings");
+                        uint32_t h4[4 * CQ], h2[2 * CQ];
 #pragma unroll
-                    for (int h = 0; h < HKV; h++)
-                        if ((uint32_t)h == kvh) {
+                        for (int q = 0; q < 4 * CQ; q++) h4[q] = (kvh & 4u) ? r[4 * CQ + q] : r[q];
 #pragma unroll
-                            for (int q = 0; q < CQ; q++) part[q] = __uint_as_float(r[h * CQ + q]);
-                        }
+                        for (int q = 0; q < 2 * CQ; q++) h2[q] = (kvh & 2u) ? h4[2 * CQ + q] : h4[q];
+#pragma unroll
+                        for (int q = 0; q < CQ; q++) part[q] = __uint_as_float((kvh & 1u) ? h2[CQ + q] : h2[q]);
+                    }
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(gs->s_free + sbuf);
