@@ -87,9 +87,12 @@ constexpr int ACTRL = 6144;
 // what is fixed, and how many K and V tiles the rest holds.  A K tile is held from its arrival to the end of its QK MMAs, a V tile
 // through the softmax of its block as well: most slots go to V.
 template <bool FP8, int G> struct Shape {
-    static constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = (FP8 && NG == 2) ? 2 : 1;
+    static constexpr int ES = FP8 ? 1 : 2, QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1, PBUF = 1;
     static constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS, CP = (G * PT < 2) ? 2 : G * PT;
-    static constexpr size_t fixed = ACTRL + (size_t)HKV * CQ * 128 * ES + NG * (size_t)PBUF * HKV * CP * 128 * ES;
+    // P^T of an E4M3 pool is kept MN-major, [128 block rows][128 B]: a thread's twelve bytes (three terms x four query heads) are three
+    // words of its own row; an F16 pool's P^T stays K-major, [NP rows][128 B] per 64 block rows
+    static constexpr size_t p_bytes = FP8 ? (size_t)ROWS * 128 : (size_t)HKV * CP * 128 * ES;
+    static constexpr size_t fixed = ACTRL + (size_t)HKV * CQ * 128 * ES + NG * (size_t)PBUF * p_bytes;
     static constexpr size_t tile = (size_t)TILE * ES;              // K or V of one block
     static constexpr uint32_t tiles = (uint32_t)((227 * 1024 - fixed) / tile);
     static constexpr uint32_t n_k = FP8 ? 4u : 2u, n_v = tiles - n_k < 8u ? tiles - n_k : 8u;
@@ -105,7 +108,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     constexpr uint32_t n_k = Shape<FP8, G>::n_k, n_v = Shape<FP8, G>::n_v;      // K and V tiles in the rings
     constexpr int ES = FP8 ? 1 : 2;                    // bytes per pool element = 128-byte column groups per row
     constexpr int QTERMS = FP8 ? 2 : 1, PT = FP8 ? 3 : 1;   // terms a query element / a probability is split into
-    constexpr int PBUF = (FP8 && NG == 2) ? 2 : 1;     // P^T buffers per group
+    constexpr int PBUF = 1;     // P^T buffers per group
     constexpr uint32_t GCOLS = NG == 2 ? 256u : 160u, S_OFF = NG == 2 ? 128u : 96u;   // a group's tensor-memory columns: O^T at 0, S^T behind it
     constexpr int CQ = (G * QTERMS < 2) ? 2 : G * QTERMS;   // columns per kv head in S^T and in O^T (N must be a multiple of 16)
     constexpr int CP = (G * PT < 2) ? 2 : G * PT;
@@ -114,9 +117,9 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     static_assert(NQ == 64 || NQ == 32, "S^T is read as one 64- or 32-column load");
     constexpr int KV_TILE = TILE * ES;                 // K (or V) of one block in shared memory
     constexpr int Q_SUB = NQ * 128;                    // one [NQ rows][128 B] tile of Q^T (F16: one per 64-dim column group)
-    constexpr int QT_BYTES = Q_SUB * ES, PT_BYTES = NP * 128 * ES;
+    constexpr int QT_BYTES = Q_SUB * ES, PT_BYTES = (int)Shape<FP8, G>::p_bytes;
     constexpr uint32_t FMT_P = FP8 ? 1u : 0u;          // kind::f8f6f4: E4M3 = 0, E5M2 = 1; kind::f16: F16 = 0
-    constexpr uint32_t IDESC_QK = instr_desc(0u, 0u, 0u, NQ), IDESC_PV = instr_desc(0u, FMT_P, 1u, NP);
+    constexpr uint32_t IDESC_QK = instr_desc(0u, 0u, 0u, NQ), IDESC_PV = FP8 ? instr_desc2(0u, FMT_P, 1u, 1u, NP) : instr_desc(0u, FMT_P, 1u, NP);
     constexpr int KSTEPS = 4 * ES;                     // 32 bytes of the contraction per MMA: 4 steps per 128-byte group
     // operand descriptors: everything but the start address is constant (stride between 8-row groups 1024 B, version 1, 128-byte swizzle)
     constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -305,7 +308,8 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     const uint32_t v_lo = vr_lo + sv * (KV_TILE >> 4), pg_lo = p_lo + (g * PBUF + pb) * (PT_BYTES >> 4);
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ks++)         // V^T MN-major: 32 / ES block rows of 128 B per step; P^T K-major: 32 bytes of the row per step
-                        mma<FP8>(tmem + g * GCOLS, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)), DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2),
+                        mma<FP8>(tmem + g * GCOLS, DESC_V | (v_lo + ks * ((32 / ES) * 128 >> 4)),
+                                 FP8 ? (DESC_V | (pg_lo + ks * (32 * 128 >> 4))) : (DESC_K | (pg_lo + (ks / 4) * (NP * 128 >> 4) + (ks % 4) * 2)),
                                  IDESC_PV, (i >= (uint32_t)NG || ks > 0) ? 1u : 0u);            // a group's first block of a range starts its accumulator afresh
                     tc_commit(c->v_empty + sv);
                     tc_commit(c->g[g].p_free + pb);
@@ -325,13 +329,18 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         Group* gs = &c->g[grp];
         const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
         const uint32_t tmem_o = tmem + grp * GCOLS, tmem_s = tmem_o + S_OFF;
-        uint32_t p_off[G][PT];                                      // where this row's probabilities go in P^T (row = kv head, term, query head; column = this row)
+        uint32_t p_off[G][PT];                                      // F16 pool: where this row's probabilities go in P^T (row = kv head, query head; column = this row)
+        uint32_t p_word[PT];                                        // E4M3 pool: the word of each term in this row of the MN-major P^T (columns kv head, term, query head)
+#pragma unroll
+        for (int term = 0; term < PT; term++) {
+            const uint32_t off = kvh * CP + term * G;               // a multiple of 4: a word never straddles a 16-byte chunk
+            p_word[term] = (t >> 3) * 1024u + (t & 7u) * 128u + (((off >> 4) ^ (t & 7u)) << 4) + (off & 15u);
+        }
 #pragma unroll
         for (int g = 0; g < G; g++)
 #pragma unroll
             for (int term = 0; term < PT; term++)
-                p_off[g][term] = FP8 ? swz(kvh * CP + term * G + g, t >> 4) + (t & 15u)
-                                     : (t >> 6) * (NP * 128) + swz(kvh * CP + g, (t & 63u) >> 3) + (t & 7u) * 2;
+                p_off[g][term] = (t >> 6) * (NP * 128) + swz(kvh * CP + g, (t & 63u) >> 3) + (t & 7u) * 2;
         // Q^T of a range: group 0, thread (query head qh = t / 4, dims [32 * (t % 4), +32)); the values wait in registers
         // from the start of the previous range
         float qx[32];
@@ -534,6 +543,7 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     // weights are non-negative and every residual fits); the row sum takes the value the three terms add up to.
                     unsigned char* pt = p_tile + (grp * PBUF + pb) * PT_BYTES;
                     const float l_scale = inv_vs * __uint_as_float((uint32_t)(127 - (int)SHIFT) << 23);
+                    uint32_t terms[PT][(G + 1) / 2];                  // E4M3 pool: per term, the half2 pairs with their low bytes cleared
 #pragma unroll
                     for (int g = 0; g < G; g += 2) {
                         const int g1 = g + 1 < G ? g + 1 : g;
@@ -547,14 +557,9 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             const __half2 r2 = __hsub2(r1, *reinterpret_cast<const __half2*>(&t2));
                             const uint32_t t3 = *reinterpret_cast<const uint32_t*>(&r2) & 0xFF00FF00u;
                             h = __hsub2(h, __hsub2(r2, *reinterpret_cast<const __half2*>(&t3)));     // = t1 + t2 + t3
-                            pt[p_off[g][0]] = (unsigned char)(t1 >> 8);
-                            pt[p_off[g][1 < PT ? 1 : 0]] = (unsigned char)(t2 >> 8);
-                            pt[p_off[g][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 8);
-                            if (g + 1 < G) {
-                                pt[p_off[g1][0]] = (unsigned char)(t1 >> 24);
-                                pt[p_off[g1][1 < PT ? 1 : 0]] = (unsigned char)(t2 >> 24);
-                                pt[p_off[g1][2 < PT ? 2 : 0]] = (unsigned char)(t3 >> 24);
-                            }
+                            terms[0][g >> 1] = t1;
+                            terms[1 < PT ? 1 : 0][g >> 1] = t2;
+                            terms[2 < PT ? 2 : 0][g >> 1] = t3;
                         } else {
                             *reinterpret_cast<__half*>(pt + p_off[g][0]) = __low2half(h);
                             if (g + 1 < G) *reinterpret_cast<__half*>(pt + p_off[g1][0]) = __high2half(h);
@@ -562,6 +567,12 @@ decode_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         const float2 q = __half22float2(h);
                         l[g] += q.x * l_scale;
                         if (g + 1 < G) l[g1] += q.y * l_scale;
+                    }
+                    if (FP8) {
+                        static_assert(!FP8 || G == 4, "a term's four query heads are one word");
+#pragma unroll
+                        for (int term = 0; term < PT; term++)      // the top bytes of the two pairs, in query-head order
+                            *reinterpret_cast<uint32_t*>(pt + p_word[term]) = __byte_perm(terms[term][0], terms[term][(G + 1) / 2 - 1], 0x7531);
                     }
                     if (!valid) {
                         // a row past the sequence end holds whatever the pool held there: 0 * NaN must not reach O^T
