@@ -902,9 +902,11 @@ def run_ours(args):
             n = min(tile.numel(), hv.numel() - o)
             hv[o:o + n].copy_(tile[:n])
         plan_h = H.Plan.from_transfer(xfer, dst, batch, H.Shard(0, 0, w.n_kv_heads, 0, 0, host_layers),
-                                      H.N.PLAN_FORCE_BULK if args.host_bulk else 0)
+                                      H.N.PLAN_FORCE_BULK if args.host_bulk else (0 if args.host_direct else H.N.PLAN_STAGE_HOST))
         if args.host_bulk and args.bulk_tune:
             plan_h.tune_bulk(*[int(x) for x in args.bulk_tune.split(",")])
+        if args.host_vec_tune:
+            plan_h.tune_vector(*[int(x) for x in args.host_vec_tune.split(",")])
     # this leg's kernel runs on the prefill GPU (its host holds the buffer) and publishes to the decode rank's flag
     host_done = flag.data_ptr() if not multi else (remote_flag if is_prefill else 0)
     barrier()
@@ -975,8 +977,8 @@ def run_ours(args):
                     "h2d_bytes_per_step": int(host_h2d), "d2h_bytes_per_step": 4, "steps": host_steps,
                     "layers": host_layers, "h2d_GBps_per_prefill_rank": [round(float(r.item()), 2) for r in h2d_rates[:pairs]],
                     "what": "K/V of the batch in page-locked HOST memory (contiguous transfer layout) + host block tables -> "
-                            "tkv_plan_update -> tkv_handoff_enqueue of a from_transfer plan (the kernel reads the host buffer "
-                            "over PCIe and stores into the decode pool) -> flag read back"},
+                            "tkv_plan_update -> tkv_handoff_enqueue of a from_transfer plan (TKV_PLAN_STAGE_HOST: the copy engine brings "
+                            "the buffer in one layer at a time while the previous layer's kernel stores into the decode pool) -> flag read back"},
             "e2e_resident": {"value": round(payload_all * e2e_steps / res_s / 1e9, 2), "unit": UNIT,
                              "h2d_bytes_per_step": int(st.worklist_bytes), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                              "what": "same call sequence with the K/V already in the prefill GPU's paged pool (where prefill "
@@ -1372,6 +1374,8 @@ def main():
                     help="N = 1 default run: skip the other four configurations (extra keys of the line)")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the pack -> NCCL send/recv -> scatter comparison")
     ap.add_argument("--host-bulk", action="store_true", help="host-buffer leg: bulk-copy ring reading the pinned buffer (experiment)")
+    ap.add_argument("--host-direct", action="store_true", help="host-buffer leg: the kernel reads the pinned buffer itself instead of the copy engine staging it layer by layer")
+    ap.add_argument("--host-vec-tune", default=None, help="host-buffer leg: bytes_per_access,unroll,store_hint of the register kernel that reads the pinned buffer (probe)")
     ap.add_argument("--host-steps", type=int, default=5, help="steps of the host-buffer end-to-end leg (PCIe-bound)")
     args = ap.parse_args()
     global FLUSH_THEN_READ

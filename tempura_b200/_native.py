@@ -23,7 +23,7 @@ OK, ERR_DIMENSION_MISMATCH, ERR_INVALID_CONFIG, ERR_CUDA, ERR_TIMEOUT, ERR_POOL_
 STATUS_NAMES = {0: "Ok", 1: "DimensionMismatch", 2: "InvalidConfig", 3: "CudaError", 4: "Timeout", 5: "PoolExhausted"}
 DTYPE_F32, DTYPE_F16, DTYPE_E4M3 = 0, 1, 2
 PREFILL_SINGLE_TILE, PREFILL_TWO_TILES = 1, 2
-PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER, PLAN_PEER_BULK_STORES, PLAN_PULL = 1, 2, 4, 8, 16, 32
+PLAN_ALLOW_SHARED_DST, PLAN_FORCE_VECTOR, PLAN_FORCE_BULK, PLAN_INT_QUANTIZER, PLAN_PEER_BULK_STORES, PLAN_PULL, PLAN_STAGE_HOST = 1, 2, 4, 8, 16, 32, 64
 ATTN_PER_HEAD_CTAS = 1
 ATTN_MMA_SYNC = 2
 VARIANT_VECTOR, VARIANT_BULK, VARIANT_FP8_WARP, VARIANT_FP8_GENERIC, VARIANT_CAST_GENERIC, VARIANT_FP8_STAGED, VARIANT_DEQUANT, VARIANT_CAST_VEC, VARIANT_WIDE = 1, 2, 3, 4, 5, 6, 7, 8, 9

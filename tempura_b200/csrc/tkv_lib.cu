@@ -182,7 +182,15 @@ struct tkv_plan {
     // block ids are 0, 1, 2, ... in work-list order (virt 1 = source side, 2 = destination).
     int virt = 0;
     TkvTransfer xfer{};
-    bool host_side = false;     // the transfer buffer is page-locked host memory
+    bool host_side = false;     // the transfer buffer is page-locked host memory (and a kernel touches it directly)
+    // TKV_PLAN_STAGE_HOST: a host transfer buffer is brought in by the copy engine, one layer (K plane + V plane) at a time into two
+    // device buffers, and the handoff kernel of a layer reads its buffer while the next layer's copy runs
+    bool staged = false;
+    char* stage = nullptr;
+    size_t stage_cap = 0, stage_plane = 0;
+    std::vector<uint64_t> stage_host;   // per layer: where its K plane starts in the host buffer
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_begin = nullptr, ev_copied[2] = {nullptr, nullptr}, ev_read[2] = {nullptr, nullptr};
     // device-built work lists (tkv_handoff_enqueue_device_tables): [u32 live pairs][pad][u32 offsets per sequence]
     uint32_t* dev_scratch = nullptr;
     size_t dev_scratch_seqs = 0;
@@ -265,9 +273,33 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
         vp.total_blocks = (uint32_t)pairs;
         vk.resize(L);
         vv.resize(L);
-        for (size_t l = 0; l < L; l++) {
-            vk[l] = p->xfer.data + (2 * l) * plane;
-            vv[l] = p->xfer.data + (2 * l + 1) * plane;
+        if (p->staged) {
+            // layer l is read from device buffer l % 2; the host address of its planes is kept for the copies
+            if (4 * plane > p->stage_cap) {
+                DeviceGuard g(p->launch_dev);
+                if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->launch_dev);
+                if (p->stage) {
+                    CU(cudaDeviceSynchronize());               // a larger batch than the plan was made for: nothing may still read the old buffers
+                    CU(cudaFree(p->stage));
+                    p->stage = nullptr;
+                    p->stage_cap = 0;
+                }
+                const size_t cap = std::max<size_t>(4 * plane, 256);
+                CU(cudaMalloc(&p->stage, cap));
+                p->stage_cap = cap;
+            }
+            p->stage_plane = plane;
+            p->stage_host.resize(L);
+            for (size_t l = 0; l < L; l++) {
+                p->stage_host[l] = p->xfer.data + (2 * l) * plane;
+                vk[l] = reinterpret_cast<uint64_t>(p->stage) + (l & 1) * 2 * plane;
+                vv[l] = vk[l] + plane;
+            }
+        } else {
+            for (size_t l = 0; l < L; l++) {
+                vk[l] = p->xfer.data + (2 * l) * plane;
+                vv[l] = p->xfer.data + (2 * l + 1) * plane;
+            }
         }
         vp.k_layer_ptrs = vk.data();
         vp.v_layer_ptrs = vv.data();
@@ -536,7 +568,7 @@ bool bulk_eligible(const tkv_plan* p) {
 // The work list fits the kernel's parameter block: one list for all layers, built on the host, short enough.
 bool inline_eligible(const tkv_plan* p) {
     const tkv::HandoffArgs& a = p->args;
-    if (p->inline_mode == 1 || a.n_pairs_dev != nullptr || a.work_layer_stride != 0) return false;
+    if (p->inline_mode == 1 || a.n_pairs_dev != nullptr || a.work_layer_stride != 0 || p->staged) return false;
     if (a.n_pairs > tkv::INLINE_PAIRS || a.n_layers > tkv::INLINE_LAYERS) return false;
     if (p->inline_mode == 2) return true;
     // the library's choice: only where the list fetch is a visible share of the launch (few chunks per SM)
@@ -817,6 +849,26 @@ static int32_t create_plan(const TkvPool* src, const TkvPool* dst, const TkvBatc
         p->xfer = *xfer;
         p->host_side = xfer->host_memory != 0;
     }
+    if (flags & TKV_PLAN_STAGE_HOST) {
+        if (virt != 1 || !p->host_side || src->k_scales) {
+            delete p;
+            return fail(TKV_ERR_INVALID_CONFIG, "TKV_PLAN_STAGE_HOST is for plans that read a host transfer buffer without scales");
+        }
+        p->staged = true;
+        p->host_side = false;          // the kernels read device memory
+        p->launch_dev = src->device;
+        DeviceGuard g(p->launch_dev);
+        cudaError_t e = g.ok ? cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking) : cudaErrorInvalidDevice;
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_begin, cudaEventDisableTiming);
+        for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+            e = cudaEventCreateWithFlags(&p->ev_copied[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_read[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) {
+            tkv_plan_destroy(p);
+            return fail(TKV_ERR_CUDA, "staging stream / events: %s", cudaGetErrorString(e));
+        }
+    }
     rc = build_worklist(p, batch);
     if (rc) {
         tkv_plan_destroy(p);
@@ -922,6 +974,16 @@ int32_t tkv_plan_destroy(tkv_plan* p) {
         if (p->h_buf) cudaFreeHost(p->h_buf);
         if (p->d_buf) cudaFree(p->d_buf);
         if (p->dev_scratch) cudaFree(p->dev_scratch);
+        if (p->copy_stream) {
+            cudaStreamSynchronize(p->copy_stream);
+            cudaStreamDestroy(p->copy_stream);
+        }
+        if (p->ev_begin) cudaEventDestroy(p->ev_begin);
+        for (int i = 0; i < 2; i++) {
+            if (p->ev_copied[i]) cudaEventDestroy(p->ev_copied[i]);
+            if (p->ev_read[i]) cudaEventDestroy(p->ev_read[i]);
+        }
+        if (p->stage) cudaFree(p->stage);
     }
     delete p;
     return TKV_OK;
@@ -966,7 +1028,39 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         int32_t rc = ensure_uploaded(p, st);
         if (rc) return rc;
     }
-    int32_t rc = dispatch(p, chunks, st);
+    int32_t rc = TKV_OK;
+    if (p->staged) {
+        // One layer at a time: the copy engine brings the layer's K and V planes into device buffer l % 2 on the plan's own stream,
+        // the layer's kernel follows on the caller's stream, and a buffer is filled again only after the kernel that read it.
+        const uint32_t L = a.n_layers;
+        const tkv::HandoffArgs whole = a;
+        uint32_t* const flag_ptr = a.done_flag;
+        CU(cudaEventRecord(p->ev_begin, st));
+        CU(cudaStreamWaitEvent(p->copy_stream, p->ev_begin, 0));
+        for (uint32_t l = 0; l < L && rc == TKV_OK; l++) {
+            const int buf = l & 1;
+            if (l >= 2) CU(cudaStreamWaitEvent(p->copy_stream, p->ev_read[buf], 0));
+            CU(cudaMemcpyAsync(p->stage + (size_t)buf * 2 * p->stage_plane, reinterpret_cast<const void*>(p->stage_host[l]), 2 * p->stage_plane,
+                               cudaMemcpyHostToDevice, p->copy_stream));
+            CU(cudaEventRecord(p->ev_copied[buf], p->copy_stream));
+            CU(cudaStreamWaitEvent(st, p->ev_copied[buf], 0));
+            a = whole;
+            a.src_k += l;
+            a.src_v += l;
+            a.dst_k += l;
+            a.dst_v += l;
+            a.work += (size_t)l * a.work_layer_stride;
+            a.n_layers = 1;
+            a.src_layer_begin += l;
+            a.dst_layer_begin += l;
+            a.done_flag = l + 1 == L ? flag_ptr : nullptr;       // the last layer's kernel publishes (when the kernel is the one to do it)
+            rc = dispatch(p, (uint64_t)a.n_pairs * 2, st);
+            if (rc == TKV_OK) CU(cudaEventRecord(p->ev_read[buf], st));
+        }
+        a = whole;
+    } else {
+        rc = dispatch(p, chunks, st);
+    }
     if (rc) return rc;
     if (by_stream) {
         int r = stream_write_value()(st, (unsigned long long)done_flag, flag_value, 0u);

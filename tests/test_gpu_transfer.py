@@ -85,7 +85,7 @@ def test_to_transfer_matches_oracle_gather(H, where):
     assert_pool_equals_host(ds, hs, "source untouched")
 
 
-@pytest.mark.parametrize("where", ["device", "host", "host-bulk"])
+@pytest.mark.parametrize("where", ["device", "host", "host-bulk", "host-staged"])
 def test_from_transfer_matches_oracle_scatter(H, where):
     import torch
     w = workload(seed=4)
@@ -110,8 +110,13 @@ def test_from_transfer_matches_oracle_scatter(H, where):
     x.data[: planes.nbytes].copy_(torch.from_numpy(planes.view(np.uint8).reshape(-1)))
     dd = to_device_pool(host_pools(w)[1], "f16")
     # "host-bulk": the bulk-copy ring reading the pinned buffer (measured equal to the register kernel over PCIe)
-    plan = H.Plan.from_transfer(x, dd, device_batch(w), None, N.PLAN_FORCE_BULK if where == "host-bulk" else 0)
-    plan.enqueue()
+    # "host-staged": the copy engine brings one layer at a time into two device buffers of the plan, the kernels read those
+    flags = {"host-bulk": N.PLAN_FORCE_BULK, "host-staged": N.PLAN_STAGE_HOST}.get(where, 0)
+    plan = H.Plan.from_transfer(x, dd, device_batch(w), None, flags)
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    for gen in (1, 2):                                    # twice: the staging buffers and their events are reused
+        plan.enqueue(done_flag=flag.data_ptr(), flag_value=gen)
+        H.flag_wait_host(0, flag.data_ptr(), gen, 10_000_000)
     torch.cuda.synchronize()
     assert plan.stats().kernel_variant == (N.VARIANT_VECTOR if where == "host" else N.VARIANT_BULK) and plan.device_error() == 0
     assert_pool_equals_host(dd, hd, "from_transfer")
@@ -205,3 +210,35 @@ def test_transfer_plan_validation(H):
     plan.enqueue()
     import torch
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dst_dtype", ["f16", "e4m3"])
+def test_staged_host_buffer_follows_plan_updates_and_casts(H, dst_dtype):
+    """TKV_PLAN_STAGE_HOST over several layers (both device buffers are reused), an F16 host buffer into an F16 pool and into
+    an E4M3 + scales pool, then a plan update to a larger batch (the staging buffers grow): every byte and scale equal to
+    the oracle's handoff from a pool that holds the same rows."""
+    import torch
+    for seed, n_seqs in ((11, 3), (12, 7)):               # the second batch is larger than the one the plan was made for
+        w = workload(n_layers=5, n_seqs=n_seqs, seed=seed, dst_dtype=dst_dtype, outlier_channels=(5,), outlier_gain=20.0)
+        hs, hd = host_pools(w)
+        ds = to_device_pool(hs, "f16")
+        total = sum(moved_blocks(w))
+        x = H.Transfer.allocate(5, 8, 128, 16, total, "f16", host=True, fill_byte=FILL)
+        H.Plan.to_transfer(ds, x, device_batch(w)).enqueue()           # the host buffer: this batch's rows in transfer layout
+        torch.cuda.synchronize()
+        dd = to_device_pool(hd, dst_dtype)
+        oracle.handoff(hs, hd, oracle_batch(w), None, "copy" if dst_dtype == "f16" else "f16_e4m3")
+        if seed == 11:
+            plan = H.Plan.from_transfer(x, dd, device_batch(w), None, N.PLAN_STAGE_HOST)
+            first = (x, dd)
+        else:
+            # same plan object cannot change its pools: make a plan for the small batch over these pools, then update it
+            small = workload(n_layers=5, n_seqs=3, seed=11, dst_dtype=dst_dtype, outlier_channels=(5,), outlier_gain=20.0)
+            plan = H.Plan.from_transfer(x, dd, device_batch(small), None, N.PLAN_STAGE_HOST)
+            plan.update(device_batch(w))
+        plan.enqueue()
+        torch.cuda.synchronize()
+        assert plan.device_error() == 0
+        assert_pool_equals_host(dd, hd, f"staged host buffer -> {dst_dtype} pool, {n_seqs} sequences")
+    with pytest.raises(N.TkvError):                       # only for host buffers that a from_transfer plan reads
+        H.Plan(ds, dd, device_batch(w), None, N.PLAN_STAGE_HOST)
