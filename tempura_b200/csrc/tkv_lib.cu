@@ -1035,28 +1035,33 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
         const uint32_t L = a.n_layers;
         const tkv::HandoffArgs whole = a;
         uint32_t* const flag_ptr = a.done_flag;
-        CU(cudaEventRecord(p->ev_begin, st));
-        CU(cudaStreamWaitEvent(p->copy_stream, p->ev_begin, 0));
-        for (uint32_t l = 0; l < L && rc == TKV_OK; l++) {
-            const int buf = l & 1;
-            if (l >= 2) CU(cudaStreamWaitEvent(p->copy_stream, p->ev_read[buf], 0));
-            CU(cudaMemcpyAsync(p->stage + (size_t)buf * 2 * p->stage_plane, reinterpret_cast<const void*>(p->stage_host[l]), 2 * p->stage_plane,
-                               cudaMemcpyHostToDevice, p->copy_stream));
-            CU(cudaEventRecord(p->ev_copied[buf], p->copy_stream));
-            CU(cudaStreamWaitEvent(st, p->ev_copied[buf], 0));
-            a = whole;
-            a.src_k += l;
-            a.src_v += l;
-            a.dst_k += l;
-            a.dst_v += l;
-            a.work += (size_t)l * a.work_layer_stride;
-            a.n_layers = 1;
-            a.src_layer_begin += l;
-            a.dst_layer_begin += l;
-            a.done_flag = l + 1 == L ? flag_ptr : nullptr;       // the last layer's kernel publishes (when the kernel is the one to do it)
-            rc = dispatch(p, (uint64_t)a.n_pairs * 2, st);
-            if (rc == TKV_OK) CU(cudaEventRecord(p->ev_read[buf], st));
-        }
+        auto layers = [&]() -> int32_t {       // a failed call returns from here; the plan's arguments are put back below either way
+            CU(cudaEventRecord(p->ev_begin, st));
+            CU(cudaStreamWaitEvent(p->copy_stream, p->ev_begin, 0));
+            for (uint32_t l = 0; l < L; l++) {
+                const int buf = l & 1;
+                if (l >= 2) CU(cudaStreamWaitEvent(p->copy_stream, p->ev_read[buf], 0));
+                CU(cudaMemcpyAsync(p->stage + (size_t)buf * 2 * p->stage_plane, reinterpret_cast<const void*>(p->stage_host[l]), 2 * p->stage_plane,
+                                   cudaMemcpyHostToDevice, p->copy_stream));
+                CU(cudaEventRecord(p->ev_copied[buf], p->copy_stream));
+                CU(cudaStreamWaitEvent(st, p->ev_copied[buf], 0));
+                a = whole;
+                a.src_k += l;
+                a.src_v += l;
+                a.dst_k += l;
+                a.dst_v += l;
+                a.work += (size_t)l * a.work_layer_stride;
+                a.n_layers = 1;
+                a.src_layer_begin += l;
+                a.dst_layer_begin += l;
+                a.done_flag = l + 1 == L ? flag_ptr : nullptr;   // the last layer's kernel publishes (when the kernel is the one to do it)
+                const int32_t r = dispatch(p, (uint64_t)a.n_pairs * 2, st);
+                if (r != TKV_OK) return r;
+                CU(cudaEventRecord(p->ev_read[buf], st));
+            }
+            return TKV_OK;
+        };
+        rc = layers();
         a = whole;
     } else {
         rc = dispatch(p, chunks, st);

@@ -129,6 +129,20 @@ def test_transfer_buffer_plans_validate_without_a_gpu():
     assert N.lib().tkv_transfer_bytes(2, 4, 16, 4, N.DTYPE_F16, 3) == 2 * 2 * 3 * 4 * 4 * 16 * 2
 
 
+def test_copy_engine_staging_is_only_for_host_buffers_read_into_a_pool():
+    """TKV_PLAN_STAGE_HOST names the one case it serves (a page-locked host transfer buffer, without scales, scattered
+    into a pool); a pool-to-pool plan, a device buffer and a buffer written by the plan are refused before any CUDA call."""
+    pool, b = fake_pool(), batch([8], [[0, 1]], [[2, 3]], 2)
+    msg = expect(N.ERR_INVALID_CONFIG, lambda: H.Plan(fake_pool(), fake_pool(), b, flags=N.PLAN_STAGE_HOST))
+    assert "TKV_PLAN_STAGE_HOST" in msg
+    on_device = N.TkvTransfer(0, N.DTYPE_F16, 0, 0, 0x20000000, 1 << 20, 0)
+    assert N.lib().tkv_plan_create_from_transfer(C.byref(on_device), C.byref(pool.c_struct()), C.byref(b.c_struct()), None,
+                                                 N.PLAN_STAGE_HOST, C.byref(C.c_void_p())) == N.ERR_INVALID_CONFIG
+    on_host = N.TkvTransfer(0, N.DTYPE_F16, 1, 0, 0x20000000, 1 << 20, 0)
+    assert N.lib().tkv_plan_create_to_transfer(C.byref(pool.c_struct()), C.byref(on_host), C.byref(b.c_struct()), None,
+                                               N.PLAN_STAGE_HOST, C.byref(C.c_void_p())) == N.ERR_INVALID_CONFIG
+
+
 def test_decode_attention_arguments_validate_without_a_gpu():
     pool = fake_pool(layers=1, heads=8, dim=128, bs=16)
     args = N.TkvDecodeAttn(1, 12, 1, 0, 16, 0.1, 0, 0, 0x100, 0x200, 0x300, 0x400, 0x500, 1 << 20, 0, 0)
