@@ -415,7 +415,7 @@ def sample_layers(w) -> int:
     return int(max(1, min(w.n_layers, budget // per_layer)))
 
 
-def describe(w, world: int, small: bool, push: bool = False) -> dict:
+def describe(w, world: int, small: bool, push: bool = False, gpu_order: str = "interleaved") -> dict:
     """The `config` object, the same in both arms."""
     pairs = max(1, world // 2)
     strong = w.name.startswith("llama3.1-70b")
@@ -426,7 +426,7 @@ def describe(w, world: int, small: bool, push: bool = False) -> dict:
             "pairs": pairs,
             "placement": ("intra-device: prefill pool -> decode pool on one GPU" if world == 1 else
                           ("one batch, KV heads split over the pairs; " if strong else "every pair its own batch; ") +
-                          "prefill rank i -> decode rank i+N/2, " +
+                          "prefill rank i -> decode rank i+N/2" + (" (GPUs 2i -> 2i+1), " if world > 2 and gpu_order == "interleaved" else ", ") +
                           ("the decode GPU's kernel loads from the prefill pool over NVLink and stores into its own pool" if pulled else
                            "the prefill GPU's kernel stores into the decode pool over NVLink")),
             "l2": ("256 MB written between timed launches (batch fits L2)" if small else "inputs larger than L2 (no flush needed)")}
@@ -467,7 +467,7 @@ def run_reference(args):
     v = c.payload / (ms * 1e-3) / 1e9
     sample = c.what + f"; {steps} timed steps after {max(1, args.warmup)} warm-up"
     full_ms = w_cpu.payload_bytes / (v * 1e9) * 1e3
-    cfg = describe(pick_workload(default_workload(args), world, None), world, is_small(w), getattr(args, "push", False))
+    cfg = describe(pick_workload(default_workload(args), world, None), world, is_small(w), getattr(args, "push", False), args.gpu_order)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": max(1, args.warmup), "ms_per_step": round(ms, 3), "higher_is_better": True,
@@ -674,6 +674,13 @@ def run_ours(args):
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch N > 1 with torch.distributed.run, one rank per GPU")
         args.gpus = world
+    if args.gpu_order == "interleaved" and world > 2:
+        # prefill rank i on GPU 2i, its decode rank on GPU 2i + 1.  Measured at N = 8: host buffers reach prefill GPUs 0, 2, 4, 6 at
+        # 54 GB/s each (216 GB/s together) but GPUs 0, 1, 2, 3 at 28.8 GB/s each (115 GB/s: they share the host's links); NVLink does not care.
+        gpu_of = lambda r: 2 * r if r < world // 2 else 2 * (r - world // 2) + 1
+    else:
+        gpu_of = lambda r: r
+    local = gpu_of(local)
     torch.cuda.set_device(local)
     multi = world > 1
     if multi:
@@ -705,7 +712,7 @@ def run_ours(args):
         flags |= H.N.PLAN_PEER_BULK_STORES
 
     # rank 0 samples its own GPU and its partner's (the pulled handoff's kernel runs there); one nvidia-smi for the whole job
-    sampler = ClockSampler(local, also=[partner] if multi else []) if rank == 0 else NullSampler()
+    sampler = ClockSampler(local, also=[gpu_of(partner)] if multi else []) if rank == 0 else NullSampler()
     src = dst = None
     remote_base = 0
     # Across GPUs a same-dtype batch is PULLED: the kernel runs on the decode GPU, fetches the prefill pool's blocks with
@@ -962,7 +969,7 @@ def run_ours(args):
                         "frac": round(achieved / peak, 4), "traffic": (int(ratio * algo) if ratio else None),
                         "algorithmic_bytes": int(algo), "peak_source": f"{peak_kind} copy peak (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                         "frac_of_nominal_8000": round(achieved / 8000.0, 4)}
-        cfg = describe(w, world, small, args.push)
+        cfg = describe(w, world, small, args.push, args.gpu_order)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(per_launch_ms, 5), "higher_is_better": True,
@@ -987,6 +994,8 @@ def run_ours(args):
             "gpu_launches_whole_run": args.warmup + args.steps + e2e_steps + 1 + host_steps,
             "clocks": clocks,
         }
+        if world > 2:
+            line["e2e"]["prefill_gpus"] = [gpu_of(r) for r in range(pairs)]
         if nccl is not None:
             line["nccl_baseline"] = nccl
         if wire_msgs is not None:
@@ -1366,6 +1375,10 @@ def main():
     ap.add_argument("--heads-per-pair", type=int, default=None, help="probe (cfg5): pools of this many kv heads, e.g. 2 at N = 2 reproduces one pair's share of the N = 8 run")
     ap.add_argument("--no-flag", action="store_true", help="probe (--sweep, one GPU): enqueue without a completion flag")
     ap.add_argument("--small-tune", default=None, help="flag_mode,inline_list of tkv_plan_tune_small (e.g. 1,1 = flag from the kernel, list from device memory)")
+    ap.add_argument("--gpu-order", choices=["paired", "interleaved"], default="interleaved",
+                    help="N > 2: which GPU a rank takes. interleaved (default) = prefill rank i on GPU 2i, its decode rank on GPU 2i+1; "
+                         "paired = rank r on GPU r (prefill GPUs 0 .. N/2-1). NVLink rates are the same either way; host buffers reach "
+                         "GPUs 0-3 of this pool's boxes at 115 GB/s together, so four prefill GPUs side by side halve the host-buffer leg")
     ap.add_argument("--push", action="store_true", help="N > 1: the prefill GPU's kernel stores into the decode pool (default for a same-dtype batch: the decode GPU pulls)")
     ap.add_argument("--peer-bulk", action="store_true", help="N > 1: bulk stores (shared -> peer global) instead of register stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
