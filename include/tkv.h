@@ -149,9 +149,9 @@ enum {
                                        tkv_ipc_import on the destination side).                     */,
     TKV_PLAN_STAGE_HOST = 64        /* from_transfer plans whose buffer is page-locked host memory: instead of the kernel
                                        reading host memory over PCIe (51 GB/s measured), the copy engine brings one layer at a
-                                       time into two device buffers of the plan (55.6 GB/s measured) while the previous layer's
-                                       kernel runs.  The plan owns 4 planes of device memory and a stream; not for buffers
-                                       that carry scales.                                                            */
+                                       time (several where a layer is under 4 MiB) into two device buffers of the plan
+                                       (55.6 GB/s measured) while the previous layer's kernel runs.  The plan owns those
+                                       buffers and a stream; not for buffers that carry scales.                      */
 };
 enum { TKV_VARIANT_VECTOR = 1, TKV_VARIANT_BULK = 2, TKV_VARIANT_FP8_WARP = 3, TKV_VARIANT_FP8_GENERIC = 4,
        TKV_VARIANT_CAST_GENERIC = 5, TKV_VARIANT_FP8_STAGED = 6, TKV_VARIANT_DEQUANT = 7, TKV_VARIANT_CAST_VEC = 8,

@@ -188,6 +188,7 @@ struct tkv_plan {
     bool staged = false;
     char* stage = nullptr;
     size_t stage_cap = 0, stage_plane = 0;
+    uint32_t stage_group = 1;        // layers per staged copy
     std::vector<uint64_t> stage_host;   // per layer: where its K plane starts in the host buffer
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_begin = nullptr, ev_copied[2] = {nullptr, nullptr}, ev_read[2] = {nullptr, nullptr};
@@ -274,8 +275,10 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
         vk.resize(L);
         vv.resize(L);
         if (p->staged) {
-            // layer l is read from device buffer l % 2; the host address of its planes is kept for the copies
-            if (4 * plane > p->stage_cap) {
+            // Layers travel in groups of G (one copy of at least 4 MiB where the layers are small); group g is read from device
+            // buffer g % 2; the host address of each group's planes is kept for the copies.
+            const size_t G = std::min<size_t>(std::max<size_t>(L, 1), std::max<size_t>(1, ((4u << 20) + 2 * plane - 1) / std::max<size_t>(2 * plane, 1)));
+            if (4 * G * plane > p->stage_cap) {
                 DeviceGuard g(p->launch_dev);
                 if (!g.ok) return fail(TKV_ERR_CUDA, "cannot select device %d", p->launch_dev);
                 if (p->stage) {
@@ -284,15 +287,16 @@ int32_t build_worklist(tkv_plan* p, const TkvBatch* b) {
                     p->stage = nullptr;
                     p->stage_cap = 0;
                 }
-                const size_t cap = std::max<size_t>(4 * plane, 256);
+                const size_t cap = std::max<size_t>(4 * G * plane, 256);
                 CU(cudaMalloc(&p->stage, cap));
                 p->stage_cap = cap;
             }
             p->stage_plane = plane;
+            p->stage_group = (uint32_t)G;
             p->stage_host.resize(L);
             for (size_t l = 0; l < L; l++) {
                 p->stage_host[l] = p->xfer.data + (2 * l) * plane;
-                vk[l] = reinterpret_cast<uint64_t>(p->stage) + (l & 1) * 2 * plane;
+                vk[l] = reinterpret_cast<uint64_t>(p->stage) + (((l / G) & 1) * G + l % G) * 2 * plane;
                 vv[l] = vk[l] + plane;
             }
         } else {
@@ -1030,19 +1034,21 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
     }
     int32_t rc = TKV_OK;
     if (p->staged) {
-        // One layer at a time: the copy engine brings the layer's K and V planes into device buffer l % 2 on the plan's own stream,
-        // the layer's kernel follows on the caller's stream, and a buffer is filled again only after the kernel that read it.
+        // One group of layers at a time: the copy engine brings the group's K and V planes into device buffer g % 2 on the plan's own
+        // stream, the group's kernel follows on the caller's stream, and a buffer is filled again only after the kernel that read it.
         const uint32_t L = a.n_layers;
         const tkv::HandoffArgs whole = a;
         uint32_t* const flag_ptr = a.done_flag;
         auto layers = [&]() -> int32_t {       // a failed call returns from here; the plan's arguments are put back below either way
             CU(cudaEventRecord(p->ev_begin, st));
             CU(cudaStreamWaitEvent(p->copy_stream, p->ev_begin, 0));
-            for (uint32_t l = 0; l < L; l++) {
-                const int buf = l & 1;
-                if (l >= 2) CU(cudaStreamWaitEvent(p->copy_stream, p->ev_read[buf], 0));
-                CU(cudaMemcpyAsync(p->stage + (size_t)buf * 2 * p->stage_plane, reinterpret_cast<const void*>(p->stage_host[l]), 2 * p->stage_plane,
-                                   cudaMemcpyHostToDevice, p->copy_stream));
+            const uint32_t G = p->stage_group;
+            for (uint32_t l = 0, g = 0; l < L; l += G, g++) {
+                const int buf = g & 1;
+                const uint32_t n = std::min(G, L - l);
+                if (g >= 2) CU(cudaStreamWaitEvent(p->copy_stream, p->ev_read[buf], 0));
+                CU(cudaMemcpyAsync(p->stage + (size_t)buf * G * 2 * p->stage_plane, reinterpret_cast<const void*>(p->stage_host[l]),
+                                   (size_t)n * 2 * p->stage_plane, cudaMemcpyHostToDevice, p->copy_stream));
                 CU(cudaEventRecord(p->ev_copied[buf], p->copy_stream));
                 CU(cudaStreamWaitEvent(st, p->ev_copied[buf], 0));
                 a = whole;
@@ -1051,11 +1057,11 @@ int32_t tkv_handoff_enqueue(tkv_plan* p, void* stream, uint64_t done_flag, uint3
                 a.dst_k += l;
                 a.dst_v += l;
                 a.work += (size_t)l * a.work_layer_stride;
-                a.n_layers = 1;
+                a.n_layers = n;
                 a.src_layer_begin += l;
                 a.dst_layer_begin += l;
-                a.done_flag = l + 1 == L ? flag_ptr : nullptr;   // the last layer's kernel publishes (when the kernel is the one to do it)
-                const int32_t r = dispatch(p, (uint64_t)a.n_pairs * 2, st);
+                a.done_flag = l + n == L ? flag_ptr : nullptr;   // the last group's kernel publishes (when the kernel is the one to do it)
+                const int32_t r = dispatch(p, (uint64_t)a.n_pairs * 2 * n, st);
                 if (r != TKV_OK) return r;
                 CU(cudaEventRecord(p->ev_read[buf], st));
             }
