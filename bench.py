@@ -674,19 +674,15 @@ def run_ours(args):
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch N > 1 with torch.distributed.run, one rank per GPU")
         args.gpus = world
-    if args.gpu_order == "interleaved" and world > 2:
-        # prefill rank i on GPU 2i, its decode rank on GPU 2i + 1.  Measured at N = 8: host buffers reach prefill GPUs 0, 2, 4, 6 at
-        # 54 GB/s each (216 GB/s together) but GPUs 0, 1, 2, 3 at 28.8 GB/s each (115 GB/s: they share the host's links); NVLink does not care.
-        gpu_of = lambda r: 2 * r if r < world // 2 else 2 * (r - world // 2) + 1
-    else:
-        gpu_of = lambda r: r
+    if world > 1 and world % 2:
+        raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
+    from tempura_b200 import disagg
+    gpu_of = lambda r: disagg.gpu_of_rank(r, world, args.gpu_order)     # N > 2: prefill rank i on GPU 2i, its decode rank on GPU 2i + 1
     local = gpu_of(local)
     torch.cuda.set_device(local)
     multi = world > 1
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if world > 1 and world % 2:
-        raise SystemExit("N > 1 must be even: ranks [0, N/2) prefill, [N/2, N) decode")
     wname = default_workload(args)
     w = pick_workload(wname, world, args.pool_blocks, heads=args.heads_per_pair, layers=args.layers, single_tokens=args.single_tokens)
     if args.src_f32:                # the reference's own transfer dtype: F32 rows into the F16 cache (one GPU only)
@@ -694,7 +690,6 @@ def run_ours(args):
             raise SystemExit("--src-f32 is a one-GPU probe of the F32 -> F16 cast")
         w.src_dtype = "f32"
         w.name += "-f32src"
-    from tempura_b200 import disagg
     role = disagg.role_of(rank, world, 80, 8)        # rank i (prefill) <-> rank i + N/2 (decode); heads split by tkv_pairing_make
     pairs = max(1, world // 2)
     strong = wname == "cfg5"                         # one batch, its KV heads split over the pairs

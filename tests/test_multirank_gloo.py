@@ -41,3 +41,24 @@ def test_roles_cover_every_rank_once():
             assert r.n_heads == 8 // P and r.head_begin == r.pair * (8 // P) and r.n_layers == 80
     with pytest.raises(Exception):
         disagg.role_of(0, 3, 80, 8)
+
+
+def test_ranks_take_every_gpu_once_and_prefill_gpus_are_not_neighbours():
+    """Slots of the pairing are placed on CUDA ordinals so that the GPUs reading host buffers (the prefill ranks) sit on
+    every other ordinal, each next to its own decode rank; two ranks and the paired order keep rank r on GPU r."""
+    from tempura_b200 import disagg
+    for world in (1, 2, 4, 8):
+        gpus = [disagg.gpu_of_rank(r, world) for r in range(world)]
+        assert sorted(gpus) == list(range(world))
+        assert [disagg.gpu_of_rank(r, world, "paired") for r in range(world)] == list(range(world))
+        if world <= 2:
+            assert gpus == list(range(world))
+            continue
+        for r in range(world):
+            role = disagg.role_of(r, world, 80, 8)
+            if role.is_prefill:
+                assert gpus[r] == 2 * role.pair and gpus[role.partner] == gpus[r] + 1
+    with pytest.raises(ValueError):
+        disagg.gpu_of_rank(4, 4)
+    with pytest.raises(ValueError):
+        disagg.gpu_of_rank(0, 4, "striped")
