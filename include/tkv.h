@@ -410,7 +410,7 @@ typedef struct TkvPrefillAttn {
 enum { TKV_PREFILL_DEFAULT = 0,
        TKV_PREFILL_SINGLE_TILE = 1, /* one query tile (32 tokens) per CTA */
        TKV_PREFILL_TWO_TILES = 2    /* two query tiles per CTA, their softmax groups out of step; without either flag the library
-                                       chooses (E4M3 pool: two; F16 pool: two from 6 144 new tokens on) */ };
+                                       chooses (two from 1 536 new tokens on) */ };
 int32_t tkv_prefill_attn_enqueue(const TkvPool* pool, const TkvPrefillAttn* args, void* stream);
 /* Device self-check of the tcgen05 path's operand plumbing (tensor-map copy with the 128-byte swizzle,
  * shared-memory and instruction descriptors, tensor-memory reads) on operands of small dyadic values whose

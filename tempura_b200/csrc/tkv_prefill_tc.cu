@@ -137,7 +137,7 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     constexpr int KSTEPS = 4 * ES;
     // K and V tiles in flight (separate rings: a K tile is free again after its QK MMAs, a V tile after its PV MMAs).  Two query tiles of
     // F16 operands leave room for one of each.
-    constexpr int NSK = (!FP8 && NQT == 2) ? 1 : 2, NSV = NSK;
+    constexpr int NSK = 2, NSV = (!FP8 && NQT == 2) ? 1 : 2;       // an F16 pool's two query tiles leave room for two K tiles and one V tile
     constexpr uint32_t IDESC_QK = instr_desc2(0u, 0u, 0u, 0u, 128u);
     constexpr uint32_t IDESC_PV = instr_desc2(FP8 ? 1u : 0u, 0u, 0u, 1u, 128u);      // A = P (E5M2 / F16, K-major), B = V (MN-major)
     constexpr uint64_t DESC_HI = ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -145,8 +145,10 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     constexpr uint64_t DESC_V = DESC_HI | ((uint64_t)(PTILE >> 4) << 16);              // MN-major: the second 64-dim column group one tile further
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t kvh = blockIdx.y;
-    const uint32_t q0 = (gridDim.x - 1u - blockIdx.x) * (QT * NQT);                   // the longest rows first
+    // CTAs start in index order and a CTA's length grows with its query position (causal): all kv heads of the last query rows
+    // first, then the rows before them, so the SMs end together (with the kv heads outermost a 4 096-token launch ended 17 % later).
+    const uint32_t kvh = blockIdx.x % PHKV;
+    const uint32_t q0 = (gridDim.x / PHKV - 1u - blockIdx.x / PHKV) * (QT * NQT);
     uint32_t rows_tokens[NQT], n_tiles_x[NQT], n_tiles = 0, kv_limit = 0;
 #pragma unroll
     for (int x = 0; x < NQT; x++) {
@@ -219,41 +221,55 @@ prefill_attn_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         // ---- producer: the tile's blocks, one lane per block: K and V boxes of this kv head, the block's two scales ----
         bool ok = c->fail == 0;
         uint32_t why = 4u, issued = 0, issued_k = 0;
-        for (uint32_t j = 0; j < n_tiles && ok; j++) {
-            const uint32_t sk = j % NSK, sv = j % NSV, nb = min(8u, n_blocks - j * 8u);
+        // K runs NSK - NSV tiles ahead of V (a K stage frees after its QK MMAs, long before the V stage of the same tile): the wait for
+        // a V stage never holds back a K tile whose stage is free.
+        auto tile_blocks = [&](uint32_t j, uint32_t& nb) -> uint32_t {     // lane's block of tile j; a stale or foreign id is never turned into an address
+            nb = min(8u, n_blocks - j * 8u);
             uint32_t blk = 0;
             if (lane < nb) {
                 blk = a.table[j * 8u + lane];
-                if (blk >= a.total_blocks) {                 // a stale or foreign id is never turned into an address
+                if (blk >= a.total_blocks) {
                     ok = false;
                     why = 2u;
                 }
             }
             if (__any_sync(0xFFFFFFFFu, why == 2u)) why = 2u;      // whichever lane met the bad id, lane 0 reports it
             ok = __all_sync(0xFFFFFFFFu, ok);
-            // K first: its stage frees as soon as the QK MMAs of the tile that held it are done
-            if (ok && lane == 0 && j >= (uint32_t)NSK) ok = mbar_wait(c->k_empty + sk, ((j / NSK) - 1u) & 1u, fail_word);
-            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
-            if (!ok) break;
-            if (lane < 8) {                                  // the scales of tile j are read until its softmax ends: four slots outlast any stage
-                float ks = 1.0f, vs = 1.0f;
-                if (lane < nb && a.k_scales) {
-                    ks = a.k_scales[(size_t)blk * PHKV + kvh];
-                    vs = a.v_scales[(size_t)blk * PHKV + kvh] * v_down;
+            return blk;
+        };
+        for (uint32_t j = 0; j < n_tiles && ok; j++) {
+            while (ok && issued_k < n_tiles && issued_k <= j + (uint32_t)(NSK - NSV)) {
+                const uint32_t jk = issued_k, sk = jk % NSK;
+                uint32_t nb;
+                const uint32_t blk = tile_blocks(jk, nb);
+                // its stage frees as soon as the QK MMAs of the tile that held it are done
+                if (ok && lane == 0 && jk >= (uint32_t)NSK) ok = mbar_wait(c->k_empty + sk, ((jk / NSK) - 1u) & 1u, fail_word);
+                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
+                if (!ok) break;
+                if (lane < 8) {                              // the scales of a tile are read until its softmax ends: four slots outlast any stage
+                    float ks = 1.0f, vs = 1.0f;
+                    if (lane < nb && a.k_scales) {
+                        ks = a.k_scales[(size_t)blk * PHKV + kvh];
+                        vs = a.v_scales[(size_t)blk * PHKV + kvh] * v_down;
+                    }
+                    c->scales[jk & 3u][lane] = ks;
+                    c->scales[jk & 3u][8 + lane] = vs;
                 }
-                c->scales[j & 3u][lane] = ks;
-                c->scales[j & 3u][8 + lane] = vs;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_expect_tx(c->k_full + sk, nb * (PBS * 128u) * ES);
-            __syncwarp();
-            if (lane < nb) {
-                const uint32_t kd = smem_u32(k_ring + (size_t)sk * KV_TILE) + lane * (PBS * 128u);
+                __syncwarp();
+                if (lane == 0) mbar_expect_tx(c->k_full + sk, nb * (PBS * 128u) * ES);
+                __syncwarp();
+                if (lane < nb) {
+                    const uint32_t kd = smem_u32(k_ring + (size_t)sk * KV_TILE) + lane * (PBS * 128u);
 #pragma unroll
-                for (int cg = 0; cg < ES; cg++) tma_head_rows(kd + cg * PTILE, &map_k, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->k_full + sk);
+                    for (int cg = 0; cg < ES; cg++) tma_head_rows(kd + cg * PTILE, &map_k, cg * 128, (int32_t)kvh, (int32_t)(blk * PBS), c->k_full + sk);
+                }
+                issued_k = jk + 1;
             }
-            issued_k = j + 1;
-            if (lane == 0 && j >= (uint32_t)NSV) ok = mbar_wait(c->v_empty + sv, ((j / NSV) - 1u) & 1u, fail_word);
+            if (!ok) break;
+            const uint32_t sv = j % NSV;
+            uint32_t nb;
+            const uint32_t blk = tile_blocks(j, nb);
+            if (ok && lane == 0 && j >= (uint32_t)NSV) ok = mbar_wait(c->v_empty + sv, ((j / NSV) - 1u) & 1u, fail_word);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0u;
             if (!ok) break;
             if (lane == 0) mbar_expect_tx(c->v_full + sv, nb * (PBS * 128u) * ES);
@@ -610,8 +626,8 @@ bool make_head_map(CUtensorMap* map, uint64_t base, uint32_t total_blocks, uint3
 
 template <bool FP8, int NQT> cudaError_t launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillArgs& a, cudaStream_t st) {
     constexpr int ES = FP8 ? 1 : 2;
-    constexpr size_t stages = (!FP8 && NQT == 2) ? 1 : 2;
-    constexpr size_t smem = CTRL + NQT * (2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE) + 2 * stages * (size_t)PTILE * ES;
+    constexpr size_t stages = (!FP8 && NQT == 2) ? 3 : 4;          // K and V stages together (an F16 pool's two query tiles: two of K, one of V)
+    constexpr size_t smem = CTRL + NQT * (2 * (size_t)PTILE + (FP8 ? 3 : 2) * (size_t)PTILE) + stages * (size_t)PTILE * ES;
     static_assert(smem <= 227 * 1024, "shared memory of one CTA");
     auto kernel = prefill_attn_tc<FP8, NQT>;
     static std::mutex mu;
@@ -628,7 +644,7 @@ template <bool FP8, int NQT> cudaError_t launch_prefill(const CUtensorMap& mk, c
             granted[dev] = true;
         }
     }
-    const dim3 grid((a.n_tokens + QT * NQT - 1) / (QT * NQT), PHKV);
+    const dim3 grid((a.n_tokens + QT * NQT - 1) / (QT * NQT) * PHKV);
     kernel<<<grid, PTHREADS, smem, st>>>(mk, mv, a);
     return cudaGetLastError();
 }
@@ -644,9 +660,10 @@ cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const P
     const uint32_t es = fp8 ? 1u : 2u;
     if (!make_head_map(&mk, k_layer, a.total_blocks, es) || !make_head_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
     // Two query tiles per CTA, their softmax groups out of step, unless a.single_tile asks for one.  Measured on B200 (useful TFLOP/s,
-    // one tile / two tiles): E4M3 pool 270 / 290 at 2 048 tokens, 395 / 461 at 4 096, 471 / 661 at 8 192; F16 pool (whose two-tile form
-    // has one K and one V tile in flight instead of two) 339 / 305, 487 / 458, 578 / 617: two tiles from 6 144 tokens on.
-    const bool two = a.single_tile == 2u || (a.single_tile == 0u && (fp8 || a.n_tokens >= 6144u));
+    // one tile / two tiles): E4M3 pool 69 / 59 at 512 new tokens, 192 / 177 at 1 024, 245 / 288 at 1 536, 295 / 373 at 2 048, 398 / 520 at
+    // 4 096; F16 pool (whose two-tile form has one K and one V tile in flight instead of two) 71 / 66, 249 / 198, 315 / 337, 364 / 428,
+    // 489 / 546, 544 / 607 at 6 144: below 1 536 tokens two tiles leave SMs without a CTA, from there on they win.
+    const bool two = a.single_tile == 2u || (a.single_tile == 0u && a.n_tokens >= 1536u);
     if (fp8) return two ? launch_prefill<true, 2>(mk, mv, a, st) : launch_prefill<true, 1>(mk, mv, a, st);
     return two ? launch_prefill<false, 2>(mk, mv, a, st) : launch_prefill<false, 1>(mk, mv, a, st);
 }
