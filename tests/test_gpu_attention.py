@@ -248,7 +248,8 @@ def test_length_above_the_host_bound_and_foreign_block_id_report_instead_of_faul
     np.testing.assert_array_equal(again, want)
 
 
-@pytest.mark.parametrize("dtype,flags", [("e4m3", 0), ("e4m3", N.PREFILL_SINGLE_TILE), ("f16", 0), ("f16", N.PREFILL_TWO_TILES)])
+# both forms of both pools are forced: chunks this short take one query tile per CTA by default
+@pytest.mark.parametrize("dtype,flags", [("e4m3", N.PREFILL_TWO_TILES), ("e4m3", N.PREFILL_SINGLE_TILE), ("f16", 0), ("f16", N.PREFILL_TWO_TILES)])
 @pytest.mark.parametrize("start,t", [(0, 40), (45, 70), (250, 33), (0, 300), (100, 64), (3, 129)])
 def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, flags, start, t):
     """The prefill-side twin: T new tokens of one sequence, token t attends to positions 0 .. start + t.  Ragged against
@@ -277,8 +278,8 @@ def test_prefill_attention_on_tensor_cores_matches_oracle(H, dtype, flags, start
 
 
 def test_prefill_attention_f16_long_prompt_takes_the_two_tile_form(H):
-    """An F16 pool switches to two query tiles per CTA from 6 144 new tokens on (one K and one V tile in flight): sampled query
-    tokens of a 6 400-token prompt against the oracle."""
+    """A long prompt over an F16 pool: two query tiles per CTA with two K tiles and one V tile in flight, the K ring a tile ahead
+    of V; sampled query tokens of a 6 400-token prompt against the oracle."""
     import torch
     t = 6400
     w = W.Workload("prefill-long", 1, 8, 128, 16, 512, 512, np.array([t], dtype=np.uint32), seed=73).build_tables()
