@@ -661,8 +661,8 @@ cudaError_t launch_prefill(bool fp8, uint64_t k_layer, uint64_t v_layer, const P
     if (!make_head_map(&mk, k_layer, a.total_blocks, es) || !make_head_map(&mv, v_layer, a.total_blocks, es)) return cudaErrorInvalidValue;
     // Two query tiles per CTA, their softmax groups out of step, unless a.single_tile asks for one.  Measured on B200 (useful TFLOP/s,
     // one tile / two tiles): E4M3 pool 69 / 59 at 512 new tokens, 192 / 177 at 1 024, 245 / 288 at 1 536, 295 / 373 at 2 048, 398 / 520 at
-    // 4 096; F16 pool (whose two-tile form has one K and one V tile in flight instead of two) 71 / 66, 249 / 198, 315 / 337, 364 / 428,
-    // 489 / 546, 544 / 607 at 6 144: below 1 536 tokens two tiles leave SMs without a CTA, from there on they win.
+    // 4 096; F16 pool 71 / 66, 249 / 198, 315 / 337, 364 / 468, 489 / 619, 578 / 786 at 8 192: below 1 536 tokens two tiles leave SMs
+    // without a CTA, from there on they win.
     const bool two = a.single_tile == 2u || (a.single_tile == 0u && a.n_tokens >= 1536u);
     if (fp8) return two ? launch_prefill<true, 2>(mk, mv, a, st) : launch_prefill<true, 1>(mk, mv, a, st);
     return two ? launch_prefill<false, 2>(mk, mv, a, st) : launch_prefill<false, 1>(mk, mv, a, st);
